@@ -1,0 +1,27 @@
+"""flashloop_b200: B200-native kernels for FlashLoop's late-loop decode path.
+
+Same module and symbol names as the reference's ``flashloop`` package for the parts
+of the decode hot path it replaces (``packing``, ``kivi_backend``, ``selection``,
+``cache``).  The kernels are hand-written CUDA for sm_100a behind a C ABI
+(``include/flashloop_b200.h``); there is no Triton path, no backend dispatch and no
+CPU fallback.
+"""
+
+from .cache import CrossLoopKVCache, CrossLoopKVLayer
+from .kivi_backend import KiviPacked4Bit, pack_kivi_k_per_channel, pack_kivi_v_per_token
+from .packing import Packed4Bit, pack_k_per_channel, pack_v_per_token
+from .selection import DecodeSelection, select_decode_keys, select_prefill_tokens
+
+__all__ = [
+    "CrossLoopKVCache",
+    "CrossLoopKVLayer",
+    "DecodeSelection",
+    "KiviPacked4Bit",
+    "Packed4Bit",
+    "pack_k_per_channel",
+    "pack_kivi_k_per_channel",
+    "pack_kivi_v_per_token",
+    "pack_v_per_token",
+    "select_decode_keys",
+    "select_prefill_tokens",
+]

@@ -1,0 +1,105 @@
+"""ctypes binding of ``csrc/libflashloop_b200.so`` (the C ABI of include/flashloop_b200.h).
+
+There is no fallback: when the library is missing or a call fails, a RuntimeError is
+raised.  Build the library with ``python -m flashloop_b200.build_kernels``.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import torch
+
+LIBRARY_PATH = Path(__file__).resolve().parent / "csrc" / "libflashloop_b200.so"
+
+FL_STREAMS = 4
+FL_STATE_WORDS = 8
+STATE_QUANT_TOKENS, STATE_TAIL_LEN, STATE_TAIL_START, STATE_ROWS2, STATE_ROWS3 = 0, 1, 2, 3, 4
+DTYPE_CODES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+_vp = C.c_void_p
+_i32, _i64, _f32, _f64, _sz = C.c_int32, C.c_int64, C.c_float, C.c_double, C.c_size_t
+
+
+class FlLayer(C.Structure):
+    """``fl_layer`` of include/flashloop_b200.h."""
+
+    _fields_ = [
+        ("batch", _i32), ("heads", _i32), ("bits", _i32), ("tail_capacity", _i32),
+        ("k_codes", _vp * FL_STREAMS), ("k_min", _vp * FL_STREAMS), ("k_scale", _vp * FL_STREAMS),
+        ("v_codes", _vp * FL_STREAMS), ("v_meta", _vp * FL_STREAMS),
+        ("row_base", _vp * FL_STREAMS), ("group_base", _vp * FL_STREAMS),
+        ("rank", _vp * 2), ("rank_base", _vp),
+        ("tail_k", _vp * FL_STREAMS), ("tail_v", _vp * FL_STREAMS),
+        ("tail_active", _vp * 2), ("seq_state", _vp),
+    ]
+
+
+# name -> (restype, argtypes); every name here is declared in include/flashloop_b200.h
+SIGNATURES = {
+    "fl_last_error": (C.c_char_p, []),
+    "fl_version": (C.c_int, []),
+    "fl_pack_k_rows": (C.c_int, [_vp, _i32, _i64, _i64, _i32, _vp, _vp, _vp, _vp]),
+    "fl_pack_v_rows": (C.c_int, [_vp, _i32, _i64, _i64, _i32, _vp, _vp, _vp, _i64, _vp]),
+    "fl_pack_kivi_k": (C.c_int, [_vp, _i32, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "fl_pack_kivi_v": (C.c_int, [_vp, _i32, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "fl_decode_rows": (C.c_int, [_vp, _vp, _vp, _i32, _i64, _i64, _i64, _i32, _vp, _vp]),
+    "fl_kivi_to_rows_k": (C.c_int, [_vp, _i64, _i64, _vp, _vp]),
+    "fl_kivi_to_rows_v": (C.c_int, [_vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
+    "fl_reader_workspace_bytes": (_sz, [_i64, _i64]),
+    "fl_workspace_init": (C.c_int, [_vp, _sz, _vp]),
+    "fl_workspace_status": (C.c_int, [_vp, _i64, C.POINTER(_i32), _vp]),
+    "fl_dense_source_attention": (C.c_int, [C.POINTER(FlLayer), _i32, _vp, _vp, _vp, _f32, _vp, _vp,
+                                            _i64, _i64, _vp, _sz, _vp]),
+    "fl_sparse_attention_delta": (C.c_int, [C.POINTER(FlLayer), _i32, _vp, _vp, _vp, _vp, _vp, _i64,
+                                            _vp, _vp, _f32, _vp, _vp, _vp, _sz, _vp]),
+    "fl_selected_pv": (C.c_int, [C.POINTER(FlLayer), _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
+    "fl_selected_qk": (C.c_int, [C.POINTER(FlLayer), _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp]),
+    "fl_select_decode_keys": (C.c_int, [_vp, _i64, _i32, _i32, _i32, _vp, _f64, _i32, _vp, _vp, _i64,
+                                        _vp, _vp, _vp, _vp]),
+}
+
+_LIB = None
+
+
+def load() -> C.CDLL:
+    """Load the CUDA library once; raise if it has not been built."""
+
+    global _LIB
+    if _LIB is None:
+        if not LIBRARY_PATH.exists():
+            raise RuntimeError(
+                f"flashloop_b200 requires its CUDA library {LIBRARY_PATH.name}; build it with "
+                "`python -m flashloop_b200.build_kernels` (there is no CPU fallback)")
+        lib = C.CDLL(str(LIBRARY_PATH))
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _LIB = lib
+    return _LIB
+
+
+def check(status: int, what: str = "") -> None:
+    if status != 0:
+        message = load().fl_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"flashloop_b200 {what} failed ({status}): {message}")
+
+
+def ptr(tensor: torch.Tensor | None) -> int | None:
+    """Device address of a tensor (None -> NULL)."""
+
+    if tensor is None:
+        return None
+    return tensor.data_ptr()
+
+
+def current_stream(device: torch.device | None = None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("flashloop_b200 kernels need CUDA tensors (there is no CPU fallback)")

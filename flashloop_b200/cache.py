@@ -1,0 +1,771 @@
+"""Physical anchor-plus-delta Cross-Loop KV cache on the GPU (batched, ragged).
+
+Mirrors the interface of the reference's flashloop/cache.py (``CrossLoopKVLayer``
+:628-1838, ``CrossLoopKVCache`` :1841-1950) for the packed path with additive
+deltas.  Differences that follow from being batched and preallocated:
+
+* one layer object holds every sequence of the batch; per-sequence lengths live in
+  a small device array (``seq_state``) that the kernels read, so sequences of
+  different lengths share every launch;
+* streams are preallocated to a capacity instead of being re-concatenated at every
+  rollover (flashloop/cache.py:179-187 reallocates the whole context);
+* the physical layout is the row layout of flashloop/packing.py, whose append rule
+  (flashloop/cache.py:202-242) keeps every rollover block's metadata group apart;
+  each rollover block of a compact stream starts on a 64-row boundary;
+* the BF16 tail is a 128-slot ring, so a rollover moves no tail rows.
+
+There is no Torch fallback for the readers: without the CUDA library they raise.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Sequence
+
+import torch
+
+from . import _native
+from .packing import Packed4Bit, pack_k_per_channel, pack_v_per_token
+from .selection import PaddedDecodeSelection, select_decode_keys_padded
+
+GROUP = 64
+HEAD_DIM = 128
+TAIL_CAPACITY = 128
+
+_WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def reader_workspace(device: torch.device, batch_heads: int, max_context_tokens: int) -> torch.Tensor:
+    """Zero-initialised scratch shared by every reader call on ``device`` (the kernels
+    leave it zeroed again).  Calls that share it must run on one stream."""
+
+    lib = _native.load()
+    need = int(lib.fl_reader_workspace_bytes(batch_heads, max_context_tokens))
+    key = (device.index if device.index is not None else torch.cuda.current_device(), 0)
+    current = _WORKSPACES.get(key)
+    if current is None or current.numel() < need:
+        current = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = current
+    return current
+
+
+def _round_up(value: int, multiple: int) -> int:
+    return -(-int(value) // multiple) * multiple
+
+
+def _rank_map(tokens: int, positions: torch.Tensor, device: torch.device) -> torch.Tensor:
+    """flashloop/cache.py:281-289."""
+
+    result = torch.full((tokens,), -1, dtype=torch.int32, device=device)
+    if positions.numel():
+        result[positions.long()] = torch.arange(positions.numel(), dtype=torch.int32, device=device)
+    return result
+
+
+def _validate_loop_tensors(keys: Sequence[torch.Tensor], values: Sequence[torch.Tensor]):
+    """flashloop/cache.py:263-278, without the batch-one restriction."""
+
+    if len(keys) != 4 or len(values) != 4:
+        raise ValueError("exactly four loop K/V tensors are required")
+    shape = tuple(int(v) for v in keys[0].shape)
+    if len(shape) != 4:
+        raise ValueError("loop K/V tensors must have shape [batch, heads, tokens, channels]")
+    if any(tuple(t.shape) != shape for t in (*keys, *values)):
+        raise ValueError("all loop K/V tensors must have the same shape")
+    if any(t.dtype != keys[0].dtype for t in (*keys, *values)):
+        raise ValueError("all loop K/V tensors must have the same dtype")
+    if any(t.device != keys[0].device for t in (*keys, *values)):
+        raise ValueError("all loop K/V tensors must share a device")
+    return shape
+
+
+class CrossLoopKVLayer:
+    """One physical layer's packed recurrent cache for a batch of sequences."""
+
+    def __init__(self, *, batch: int, heads: int, token_capacities: Sequence[int],
+                 compact_capacities: Sequence[tuple[int, int]], bits: int = 4,
+                 group_size: int = GROUP, residual_length: int = 64,
+                 device: torch.device | str = "cuda", dtype: torch.dtype = torch.bfloat16) -> None:
+        if group_size != GROUP or residual_length != 64:
+            raise ValueError("the CUDA cache specializes group_size=64 and residual_length=64")
+        if bits not in (4, 2):
+            raise ValueError("bits must be 4 or 2")
+        if dtype != torch.bfloat16:
+            raise ValueError("the CUDA cache stores BF16 tails; loop K/V must be bfloat16")
+        _native.load()
+        self.group_size = group_size
+        self.residual_length = residual_length
+        self.bits = bits
+        self.reader_backend = "kivi_outer"
+        self.absolute_late_overrides = False
+        self.batch, self.heads = int(batch), int(heads)
+        self._device = torch.device(device)
+        self._dtype = dtype
+        self._shape_prefix = (self.batch, self.heads, HEAD_DIM)
+        row_bytes = 16 * bits
+        caps = [[_round_up(c, GROUP) for c in token_capacities],
+                [_round_up(c, GROUP) for c in token_capacities],
+                [_round_up(c[0], GROUP) for c in compact_capacities],
+                [_round_up(c[1], GROUP) for c in compact_capacities]]
+        self._caps = caps
+        dev = self._device
+        self._k_codes, self._k_min, self._k_scale, self._v_codes, self._v_meta = [], [], [], [], []
+        self._row_base, self._group_base, self._row_base_host = [], [], []
+        for s in range(4):
+            bases, off = [], 0
+            for b in range(self.batch):
+                for h in range(self.heads):
+                    bases.append(off + h * caps[s][b])
+                off += self.heads * caps[s][b]
+            total = max(off, GROUP)
+            self._k_codes.append(torch.zeros((total, row_bytes), dtype=torch.uint8, device=dev))
+            self._v_codes.append(torch.zeros((total, row_bytes), dtype=torch.uint8, device=dev))
+            self._k_min.append(torch.zeros((total // GROUP, HEAD_DIM), dtype=torch.float16, device=dev))
+            self._k_scale.append(torch.zeros((total // GROUP, HEAD_DIM), dtype=torch.float16, device=dev))
+            self._v_meta.append(torch.zeros((total, 4), dtype=torch.float16, device=dev))
+            self._row_base_host.append(bases)
+            self._row_base.append(torch.tensor(bases, dtype=torch.int64, device=dev))
+            self._group_base.append(torch.tensor([x // GROUP for x in bases], dtype=torch.int64, device=dev))
+        rank_bases, off = [], 0
+        for b in range(self.batch):
+            rank_bases.append(off)
+            off += caps[0][b]
+        self._rank_base_host = rank_bases
+        self._rank_base = torch.tensor(rank_bases, dtype=torch.int64, device=dev)
+        self._rank = [torch.full((max(off, 1),), -1, dtype=torch.int32, device=dev) for _ in range(2)]
+        bh = self.batch * self.heads
+        self._tail_k = torch.zeros((4, bh, TAIL_CAPACITY, HEAD_DIM), dtype=dtype, device=dev)
+        self._tail_v = torch.zeros_like(self._tail_k)
+        self._tail_active = torch.zeros((2, self.batch, TAIL_CAPACITY), dtype=torch.uint8, device=dev)
+        self._state_host = torch.zeros((self.batch, _native.FL_STATE_WORDS), dtype=torch.int32)
+        self._seq_state = torch.zeros((self.batch, _native.FL_STATE_WORDS), dtype=torch.int32, device=dev)
+        # logical positions held by the compact streams, per sequence (host lists of tensors)
+        self._override_positions = [[torch.empty(0, dtype=torch.int32, device=dev) for _ in range(2)]
+                                    for _ in range(self.batch)]
+        self._native = self._make_native()
+
+    # ------------------------------------------------------------------ native descriptor
+
+    def _make_native(self) -> _native.FlLayer:
+        n = _native.FlLayer()
+        n.batch, n.heads, n.bits, n.tail_capacity = self.batch, self.heads, self.bits, TAIL_CAPACITY
+        for s in range(4):
+            n.k_codes[s] = self._k_codes[s].data_ptr()
+            n.k_min[s] = self._k_min[s].data_ptr()
+            n.k_scale[s] = self._k_scale[s].data_ptr()
+            n.v_codes[s] = self._v_codes[s].data_ptr()
+            n.v_meta[s] = self._v_meta[s].data_ptr()
+            n.row_base[s] = self._row_base[s].data_ptr()
+            n.group_base[s] = self._group_base[s].data_ptr()
+            n.tail_k[s] = self._tail_k[s].data_ptr()
+            n.tail_v[s] = self._tail_v[s].data_ptr()
+        for i in range(2):
+            n.rank[i] = self._rank[i].data_ptr()
+            n.tail_active[i] = self._tail_active[i].data_ptr()
+        n.rank_base = self._rank_base.data_ptr()
+        n.seq_state = self._seq_state.data_ptr()
+        return n
+
+    def _push_state(self) -> None:
+        self._seq_state.copy_(self._state_host, non_blocking=False)
+
+    # ------------------------------------------------------------------ per-sequence views
+
+    def _rows(self, tensor_list, s: int, b: int, per_row: int = 1) -> torch.Tensor:
+        """View [heads, capacity(/per_row), ...] of sequence ``b`` in stream ``s``."""
+
+        cap = self._caps[s][b]
+        start = self._row_base_host[s][b * self.heads] // per_row
+        count = self.heads * cap // per_row
+        t = tensor_list[s]
+        return t[start:start + count].view(self.heads, cap // per_row, *t.shape[1:])
+
+    def _store_stream(self, s: int, b: int, row0: int, key: Packed4Bit, value: Packed4Bit) -> None:
+        """Copy one packed K/V segment of sequence ``b`` into rows ``row0 ..`` of stream ``s``."""
+
+        n = key.original_shape[2]
+        if row0 % GROUP:
+            raise RuntimeError("stream segments must start on a group boundary")
+        if row0 + n > self._caps[s][b]:
+            raise RuntimeError(f"stream {s} of sequence {b} is full ({row0 + n} > {self._caps[s][b]} rows)")
+        groups = key.minimum.shape[2]
+        self._rows(self._k_codes, s, b)[:, row0:row0 + n].copy_(key.payload[0])
+        self._rows(self._k_min, s, b, GROUP)[:, row0 // GROUP:row0 // GROUP + groups].copy_(key.minimum[0])
+        self._rows(self._k_scale, s, b, GROUP)[:, row0 // GROUP:row0 // GROUP + groups].copy_(key.scale[0])
+        self._rows(self._v_codes, s, b)[:, row0:row0 + n].copy_(value.payload[0])
+        meta = self._rows(self._v_meta, s, b)[:, row0:row0 + n]
+        meta[..., 0:2].copy_(value.minimum[0])
+        meta[..., 2:4].copy_(value.scale[0])
+
+    # ------------------------------------------------------------------ construction
+
+    @classmethod
+    def from_prefill(cls, keys: Sequence[torch.Tensor], values: Sequence[torch.Tensor], *,
+                     mask_loop3: torch.Tensor, mask_loop4: torch.Tensor, group_size: int = 64,
+                     residual_length: int = 64, absolute_late_overrides: bool = False,
+                     absolute_override_dtype: str = "int4", reader_backend: str = "kivi_outer",
+                     bits: int = 4, max_new_tokens: int = 0) -> "CrossLoopKVLayer":
+        """flashloop/cache.py:752-817 for a batch of equally long prompts.
+
+        keys/values: four tensors [B, H, T, 128] bfloat16; masks bool [B, T].
+        ``max_new_tokens`` sizes the preallocated room for decode appends."""
+
+        batch, heads, tokens, channels = _validate_loop_tensors(keys, values)
+        if channels != HEAD_DIM:
+            raise ValueError("the CUDA cache specializes head_dim=128")
+        if absolute_late_overrides:
+            raise ValueError("the CUDA cache supports additive cross-loop deltas only")
+        if reader_backend not in {"kivi_outer", "triton_row"}:
+            raise ValueError("unknown KV reader backend")
+        if mask_loop3.shape != (batch, tokens) or mask_loop4.shape != (batch, tokens):
+            raise ValueError("prefill masks must have shape [batch, tokens]")
+        sequences = [([k[b:b + 1] for k in keys], [v[b:b + 1] for v in values],
+                      mask_loop3[b], mask_loop4[b]) for b in range(batch)]
+        return cls.from_prefill_ragged(sequences, group_size=group_size, residual_length=residual_length,
+                                       bits=bits, max_new_tokens=max_new_tokens)
+
+    @classmethod
+    def from_prefill_ragged(cls, sequences, *, group_size: int = 64, residual_length: int = 64,
+                            bits: int = 4, max_new_tokens: int = 0) -> "CrossLoopKVLayer":
+        """Build a layer from per-sequence prompts of different lengths.
+
+        sequences: list of (keys[4], values[4], mask3 [T_b], mask4 [T_b]) with K/V
+        tensors [1, H, T_b, 128]."""
+
+        if not sequences:
+            raise ValueError("at least one sequence is required")
+        heads = int(sequences[0][0][0].shape[1])
+        device = sequences[0][0][0].device
+        dtype = sequences[0][0][0].dtype
+        token_caps, compact_caps, prepared = [], [], []
+        extra = _round_up(max_new_tokens, GROUP) + 2 * GROUP
+        for keys, values, mask3, mask4 in sequences:
+            shape = _validate_loop_tensors(keys, values)
+            if shape[0] != 1 or shape[1] != heads or shape[3] != HEAD_DIM:
+                raise ValueError("ragged sequences must be [1, heads, tokens, 128] with equal heads")
+            tokens = shape[2]
+            mask3 = mask3.reshape(-1).to(device=device, dtype=torch.bool)
+            mask4 = mask4.reshape(-1).to(device=device, dtype=torch.bool)
+            if mask3.numel() != tokens or mask4.numel() != tokens:
+                raise ValueError("prefill masks must cover every prompt token")
+            if not bool(torch.all(~mask4 | mask3).item()):
+                raise ValueError("Loop-4 overrides must be nested in Loop-3 overrides")
+            packed = max(0, ((tokens - residual_length) // group_size) * group_size)
+            n3 = int(mask3[:packed].sum().item())
+            n4 = int(mask4[:packed].sum().item())
+            token_caps.append(packed + extra)
+            compact_caps.append((_round_up(n3, GROUP) + extra, _round_up(n4, GROUP) + extra))
+            prepared.append((keys, values, mask3, mask4, packed))
+        layer = cls(batch=len(sequences), heads=heads, token_capacities=token_caps,
+                    compact_capacities=compact_caps, bits=bits, group_size=group_size,
+                    residual_length=residual_length, device=device, dtype=dtype)
+        for b, (keys, values, mask3, mask4, packed) in enumerate(prepared):
+            layer._encode_sequence(b, keys, values, mask3, mask4, packed)
+        layer._push_state()
+        return layer
+
+    @classmethod
+    def from_streams(cls, key_streams, value_streams, rank_maps) -> "CrossLoopKVLayer":
+        """Adopt already packed row-layout streams (``Packed4Bit``, ``None`` for an empty
+        compact stream) with the reference's rank maps (int32 [Tq], -1 = absent).  Streams
+        of the wrong axis are ignored, so a K-only or V-only set can be adopted for
+        ``qk`` / ``pv``.  The tail starts empty; see :meth:`set_tail`."""
+
+        anchor = key_streams[0]
+        batch, heads, quant, channels = anchor.original_shape
+        if channels != HEAD_DIM:
+            raise ValueError("the CUDA cache specializes head_dim=128")
+        counts = [0 if s is None else int(s.original_shape[2]) for s in key_streams]
+        layer = cls(batch=batch, heads=heads, token_capacities=[quant + GROUP] * batch,
+                    compact_capacities=[(counts[2] + GROUP, counts[3] + GROUP)] * batch, bits=anchor.bits,
+                    device=anchor.payload.device)
+        for b in range(batch):
+            for s in range(4):
+                ks, vs = key_streams[s], value_streams[s]
+                if ks is None:
+                    continue
+                n, rb = counts[s], 16 * anchor.bits
+                if ks.axis == "per_channel":
+                    g = ks.minimum.shape[2]
+                    layer._rows(layer._k_codes, s, b)[:, :n].copy_(ks.payload[b])
+                    layer._rows(layer._k_min, s, b, GROUP)[:, :g].copy_(ks.minimum[b])
+                    layer._rows(layer._k_scale, s, b, GROUP)[:, :g].copy_(ks.scale[b])
+                if vs is not None and vs.axis == "per_token":
+                    layer._rows(layer._v_codes, s, b)[:, :n].copy_(vs.payload[b])
+                    meta = layer._rows(layer._v_meta, s, b)[:, :n]
+                    meta[..., 0:2].copy_(vs.minimum[b])
+                    meta[..., 2:4].copy_(vs.scale[b])
+            base = layer._rank_base_host[b]
+            for i in range(2):
+                rank = rank_maps[i].to(device=layer._device, dtype=torch.int32)
+                if rank.numel() not in (0, quant):
+                    raise ValueError("rank maps must cover the packed prefix")
+                if rank.numel():
+                    layer._rank[i][base:base + quant] = rank
+                    layer._override_positions[b][i] = torch.nonzero(rank >= 0, as_tuple=False).flatten().to(torch.int32)
+            st = layer._state_host[b]
+            st[_native.STATE_QUANT_TOKENS] = quant
+            st[_native.STATE_ROWS2] = _round_up(counts[2], GROUP)
+            st[_native.STATE_ROWS3] = _round_up(counts[3], GROUP)
+        layer._push_state()
+        return layer
+
+    def set_tail(self, loop: int, tail_key: torch.Tensor, tail_value: torch.Tensor) -> None:
+        """Install the BF16 tail of ``loop`` ([B, H, tail, 128], tail <= 128) for every
+        sequence, in token order from ring slot 0."""
+
+        tail = int(tail_key.shape[2])
+        if tail > TAIL_CAPACITY or tuple(tail_key.shape) != (self.batch, self.heads, tail, HEAD_DIM) \
+                or tail_value.shape != tail_key.shape:
+            raise ValueError("tail K/V shape differs from this cache layer")
+        bh = self.batch * self.heads
+        if tail:
+            self._tail_k[loop, :, :tail].copy_(tail_key.reshape(bh, tail, HEAD_DIM))
+            self._tail_v[loop, :, :tail].copy_(tail_value.reshape(bh, tail, HEAD_DIM))
+        if bool((self._state_host[:, _native.STATE_TAIL_LEN] != tail).any()) or \
+                bool((self._state_host[:, _native.STATE_TAIL_START] != 0).any()):
+            self._state_host[:, _native.STATE_TAIL_LEN] = tail
+            self._state_host[:, _native.STATE_TAIL_START] = 0
+            self._push_state()
+
+    def _encode_block(self, keys, values, mask3, mask4):
+        """The residual chain of flashloop/cache.py:1008-1074 on one token block
+        ([1, H, n, 128] per loop): returns the four packed K/V streams and the active
+        positions of streams 2 and 3.  Every subtraction/addition is a bfloat16 tensor
+        operation, as in the reference; the codecs are the CUDA kernels."""
+
+        bits = self.bits
+        streams_k: list[Packed4Bit | None] = [None] * 4
+        streams_v: list[Packed4Bit | None] = [None] * 4
+        streams_k[0] = pack_k_per_channel(keys[0], bits=bits)
+        streams_v[0] = pack_v_per_token(values[0], bits=bits)
+        recon_k = streams_k[0].decode()
+        recon_v = streams_v[0].decode()
+        streams_k[1] = pack_k_per_channel(keys[1] - recon_k, bits=bits)
+        streams_v[1] = pack_v_per_token(values[1] - recon_v, bits=bits)
+        recon_k = recon_k + streams_k[1].decode()
+        recon_v = recon_v + streams_v[1].decode()
+        positions = []
+        for s, mask in ((2, mask3), (3, mask4)):
+            pos = torch.nonzero(mask, as_tuple=False).flatten()
+            positions.append(pos.to(torch.int32))
+            if pos.numel() == 0:
+                continue
+            dk = keys[s].index_select(2, pos) - recon_k.index_select(2, pos)
+            dv = values[s].index_select(2, pos) - recon_v.index_select(2, pos)
+            streams_k[s] = pack_k_per_channel(dk, bits=bits)
+            streams_v[s] = pack_v_per_token(dv, bits=bits)
+            if s == 2:
+                recon_k = recon_k.clone()
+                recon_v = recon_v.clone()
+                recon_k.index_add_(2, pos, streams_k[s].decode())
+                recon_v.index_add_(2, pos, streams_v[s].decode())
+        return streams_k, streams_v, positions
+
+    def _encode_sequence(self, b: int, keys, values, mask3, mask4, packed: int) -> None:
+        tokens = int(keys[0].shape[2])
+        st = self._state_host[b]
+        st[_native.STATE_QUANT_TOKENS] = packed
+        rows = [0, 0]
+        if packed:
+            sk, sv, positions = self._encode_block([k[:, :, :packed] for k in keys],
+                                                   [v[:, :, :packed] for v in values],
+                                                   mask3[:packed], mask4[:packed])
+            for s in range(4):
+                if sk[s] is not None:
+                    self._store_stream(s, b, 0, sk[s], sv[s])
+            base = self._rank_base_host[b]
+            for i in range(2):
+                self._override_positions[b][i] = positions[i]
+                self._rank[i][base:base + packed] = _rank_map(packed, positions[i], self._device)
+                rows[i] = _round_up(int(positions[i].numel()), GROUP)
+        st[_native.STATE_ROWS2], st[_native.STATE_ROWS3] = rows
+        tail = tokens - packed
+        if tail > TAIL_CAPACITY:
+            raise RuntimeError("tail longer than the ring")
+        st[_native.STATE_TAIL_LEN] = tail
+        st[_native.STATE_TAIL_START] = 0
+        sl = slice(b * self.heads, (b + 1) * self.heads)
+        for r in range(4):
+            self._tail_k[r, sl, :tail].copy_(keys[r][0, :, packed:])
+            self._tail_v[r, sl, :tail].copy_(values[r][0, :, packed:])
+        self._tail_active[0, b, :tail].copy_(mask3[packed:].to(torch.uint8))
+        self._tail_active[1, b, :tail].copy_(mask4[packed:].to(torch.uint8))
+
+    # ------------------------------------------------------------------ bookkeeping
+
+    def quantized_tokens_of(self, b: int) -> int:
+        return int(self._state_host[b, _native.STATE_QUANT_TOKENS])
+
+    def tail_tokens_of(self, b: int) -> int:
+        return int(self._state_host[b, _native.STATE_TAIL_LEN])
+
+    @property
+    def quantized_tokens(self) -> int:
+        return self.quantized_tokens_of(0)
+
+    @property
+    def tail_tokens(self) -> int:
+        return self.tail_tokens_of(0)
+
+    @property
+    def token_count(self) -> int:
+        return self.quantized_tokens + self.tail_tokens
+
+    def token_counts(self) -> list[int]:
+        return [self.quantized_tokens_of(b) + self.tail_tokens_of(b) for b in range(self.batch)]
+
+    @property
+    def max_context_tokens(self) -> int:
+        return max(self.token_counts())
+
+    @property
+    def storage_bytes(self) -> int:
+        """Bytes in use (flashloop/cache.py:1084-1101), not the preallocated capacity."""
+
+        row_bytes = 16 * self.bits
+        total = 0
+        for b in range(self.batch):
+            q = self.quantized_tokens_of(b)
+            n = [q, q, int(self._override_positions[b][0].numel()), int(self._override_positions[b][1].numel())]
+            for s in range(4):
+                groups = -(-n[s] // GROUP)
+                total += self.heads * (2 * n[s] * row_bytes + 2 * groups * HEAD_DIM * 2 + n[s] * 8)
+            total += 8 * self.heads * self.tail_tokens_of(b) * HEAD_DIM * 2
+            total += 2 * q * 4 + (n[2] + n[3]) * 4 + 2 * self.tail_tokens_of(b)
+        return total
+
+    @property
+    def dense_bf16_bytes(self) -> int:
+        return sum(4 * 2 * self.heads * t * HEAD_DIM * 2 for t in self.token_counts())
+
+    @property
+    def storage_ratio(self) -> float:
+        dense = self.dense_bf16_bytes
+        return self.storage_bytes / dense if dense else 0.0
+
+    # ------------------------------------------------------------------ export (tests, audits)
+
+    def export_sequence(self, b: int) -> dict:
+        """The sequence's streams in the reference's logical order: for each stream the
+        payload rows, K metadata groups and V metadata of the rows in use (compact
+        streams without their padding), the rank maps and the tails in token order."""
+
+        q = self.quantized_tokens_of(b)
+        out: dict = {"quantized_tokens": q, "tail_tokens": self.tail_tokens_of(b)}
+        base = self._rank_base_host[b]
+        for s in range(4):
+            if s < 2:
+                rows = torch.arange(q, device=self._device)
+            else:
+                rank = self._rank[s - 2][base:base + q]
+                rows = rank[rank >= 0].long()
+                out[f"rank{s + 1}"] = torch.where(
+                    rank >= 0, torch.cumsum((rank >= 0).to(torch.int32), 0, dtype=torch.int32) - 1,
+                    torch.full_like(rank, -1))
+                out[f"pos{s + 1}"] = torch.nonzero(rank >= 0, as_tuple=False).flatten().to(torch.int32)
+            groups = torch.unique_consecutive(rows // GROUP) if rows.numel() else rows
+            out[f"k{s}.payload"] = self._rows(self._k_codes, s, b).index_select(1, rows)
+            out[f"k{s}.minimum"] = self._rows(self._k_min, s, b, GROUP).index_select(1, groups)
+            out[f"k{s}.scale"] = self._rows(self._k_scale, s, b, GROUP).index_select(1, groups)
+            out[f"k{s}.row_groups"] = (torch.searchsorted(groups, rows // GROUP).to(torch.int32)
+                                       if rows.numel() else rows.to(torch.int32))
+            out[f"v{s}.payload"] = self._rows(self._v_codes, s, b).index_select(1, rows)
+            meta = self._rows(self._v_meta, s, b).index_select(1, rows)
+            out[f"v{s}.minimum"] = meta[..., 0:2]
+            out[f"v{s}.scale"] = meta[..., 2:4]
+        tail = self.tail_tokens_of(b)
+        start = int(self._state_host[b, _native.STATE_TAIL_START])
+        slots = (start + torch.arange(tail, device=self._device)) % TAIL_CAPACITY
+        sl = slice(b * self.heads, (b + 1) * self.heads)
+        for r in range(4):
+            out[f"tail_k{r}"] = self._tail_k[r, sl].index_select(1, slots)
+            out[f"tail_v{r}"] = self._tail_v[r, sl].index_select(1, slots)
+        out["tail_active3"] = self._tail_active[0, b].index_select(0, slots).bool()
+        out["tail_active4"] = self._tail_active[1, b].index_select(0, slots).bool()
+        return out
+
+    # ------------------------------------------------------------------ readers
+
+    def _check_vectors(self, *vectors: torch.Tensor) -> None:
+        expected = (self.batch, self.heads, 1, HEAD_DIM)
+        for v in vectors:
+            if tuple(v.shape) != expected:
+                raise ValueError("attention vectors differ from this cache layer")
+            if v.dtype != torch.bfloat16:
+                raise ValueError("fused attention specializes BF16 vectors")
+        _native.require_cuda(*vectors)
+
+    def _workspace(self) -> torch.Tensor:
+        return reader_workspace(self._device, self.batch * self.heads,
+                                max(self._caps[0]) + TAIL_CAPACITY)
+
+    def reader_status(self) -> int:
+        """Synchronise and return the readers' status word: 0, or 1 when a reader gave up
+        waiting for one of its own asynchronous copies (its output is then undefined)."""
+
+        ws = self._workspace()
+        flag = C.c_int32(0)
+        _native.check(_native.load().fl_workspace_status(
+            _native.ptr(ws), self.batch * self.heads, C.byref(flag), _native.current_stream(self._device)),
+            "fl_workspace_status")
+        return int(flag.value)
+
+    def dense_source_attention(self, loop: int, *, query: torch.Tensor, current_key: torch.Tensor,
+                               current_value: torch.Tensor, scaling: float, return_logits: bool,
+                               out: torch.Tensor | None = None, logits_out: torch.Tensor | None = None):
+        """Attention of one query per head over every cached token of ``loop`` plus the
+        current token (flashloop/cache.py:1644-1756).  Returns (output float32
+        [B, H, 1, 128], scaled logits float32 [B, H, 1, N + 1] or None); for a ragged
+        batch N is the longest context and shorter rows are padded with -inf."""
+
+        loop = int(loop)
+        if loop not in range(4):
+            raise ValueError("loop must be in [0, 3]")
+        self._check_vectors(query, current_key, current_value)
+        q, k, v = query.contiguous(), current_key.contiguous(), current_value.contiguous()
+        max_ctx = self.max_context_tokens
+        if out is None:
+            out = torch.empty((self.batch, self.heads, 1, HEAD_DIM), dtype=torch.float32, device=self._device)
+        logits = None
+        stride = 0
+        if return_logits:
+            stride = _round_up(max_ctx + 1, 4)
+            if logits_out is not None:
+                logits = logits_out
+                stride = int(logits.shape[-1])
+            elif len(set(self.token_counts())) == 1:
+                logits = torch.empty((self.batch, self.heads, 1, stride), dtype=torch.float32, device=self._device)
+            else:
+                logits = torch.full((self.batch, self.heads, 1, stride), float("-inf"),
+                                    dtype=torch.float32, device=self._device)
+        ws = self._workspace()
+        lib = _native.load()
+        _native.check(lib.fl_dense_source_attention(
+            C.byref(self._native), loop, _native.ptr(q), _native.ptr(k), _native.ptr(v), float(scaling),
+            _native.ptr(out), _native.ptr(logits), stride, max_ctx, _native.ptr(ws), ws.numel(),
+            _native.current_stream(self._device)), "fl_dense_source_attention")
+        if logits is not None and logits_out is None:
+            logits = logits[..., :max_ctx + 1]
+        return out, logits
+
+    def select_decode_keys(self, logits: torch.Tensor, *, fraction: float) -> PaddedDecodeSelection:
+        """The loop-2 selection of flashloop/engine.py:438-481 from the scaled logits
+        returned by :meth:`dense_source_attention`."""
+
+        return select_decode_keys_padded(logits, fraction=fraction, values_are_logits=True,
+                                         seq_state=self._seq_state, max_keys=self.max_context_tokens + 1)
+
+    def cached_mass_sparse_attention_delta(self, loop: int, *, query: torch.Tensor,
+                                           current_key: torch.Tensor, current_value: torch.Tensor,
+                                           indices: torch.Tensor, valid: torch.Tensor,
+                                           source_selected_output: torch.Tensor, global_mass: torch.Tensor,
+                                           scaling: float, current_position: int | None = None,
+                                           out: torch.Tensor | None = None) -> torch.Tensor:
+        """The cached-mass late-loop attention correction
+        (flashloop/cache.py:1517-1642): ``global_mass * (subset-softmax target -
+        source_selected_output)`` over the valid selected indices.  The current token
+        is index quant + tail of each sequence; ``current_position`` is accepted for
+        interface compatibility and checked against it for a batch of one."""
+
+        loop = int(loop)
+        if loop not in (2, 3):
+            raise ValueError("cached-mass sparse attention is only valid for Loop 3/4")
+        self._check_vectors(query, current_key, current_value)
+        if tuple(source_selected_output.shape) != (self.batch, self.heads, 1, HEAD_DIM):
+            raise ValueError("attention vectors differ from this cache layer")
+        if indices.ndim == 4 and indices.shape[-2] == 1:
+            indices = indices.squeeze(-2)
+        if indices.ndim != 3 or tuple(indices.shape[:2]) != (self.batch, self.heads):
+            raise ValueError("indices must have shape [batch, heads, selected]")
+        if tuple(valid.shape) != tuple(indices.shape):
+            raise ValueError("valid mask must match selected indices")
+        if tuple(global_mass.shape) != (self.batch, self.heads, 1, 1):
+            raise ValueError("global mass must have shape [batch, heads, 1, 1]")
+        if current_position is not None and self.batch == 1 and int(current_position) != self.token_count:
+            raise ValueError("current_position differs from the cache's token count")
+        idx = indices.to(device=self._device, dtype=torch.int32).contiguous()
+        val = valid.to(device=self._device).contiguous()
+        val = val.view(torch.uint8) if val.dtype == torch.bool else val.to(torch.uint8)
+        src = source_selected_output.float().contiguous()
+        mass = global_mass.float().contiguous()
+        if out is None:
+            out = torch.empty((self.batch, self.heads, 1, HEAD_DIM), dtype=torch.float32, device=self._device)
+        ws = self._workspace()
+        lib = _native.load()
+        _native.check(lib.fl_sparse_attention_delta(
+            C.byref(self._native), loop, _native.ptr(query.contiguous()),
+            _native.ptr(current_key.contiguous()), _native.ptr(current_value.contiguous()),
+            _native.ptr(idx), _native.ptr(val), int(idx.shape[-1]), _native.ptr(src), _native.ptr(mass),
+            float(scaling), _native.ptr(out), None, _native.ptr(ws), ws.numel(),
+            _native.current_stream(self._device)), "fl_sparse_attention_delta")
+        return out
+
+    def _normalize_indices(self, indices: torch.Tensor) -> torch.Tensor:
+        if indices.ndim == 1:
+            indices = indices[None, None, :].expand(self.batch, self.heads, -1)
+        elif indices.ndim == 4 and indices.shape[-2] == 1:
+            indices = indices.squeeze(-2)
+        if indices.ndim != 3 or tuple(indices.shape[:2]) != (self.batch, self.heads):
+            raise ValueError("indices must have shape [selected] or [batch, heads, selected]")
+        return indices.to(device=self._device, dtype=torch.int32).contiguous()
+
+    def qk(self, loop: int, query: torch.Tensor, indices: torch.Tensor, *,
+           validate_indices: bool = True, current_key: torch.Tensor | None = None) -> torch.Tensor:
+        """Unscaled logits of selected logical rows (flashloop/cache.py:1202-1356)."""
+
+        loop = int(loop)
+        if loop not in range(4):
+            raise ValueError("loop must be in [0, 3]")
+        self._check_vectors(query)
+        idx = self._normalize_indices(indices)
+        if validate_indices and idx.numel() and (int(idx.min()) < 0 or int(idx.max()) >= self.max_context_tokens):
+            raise IndexError("cache index is outside the logical sequence")
+        out = torch.empty((self.batch, self.heads, 1, idx.shape[-1]), dtype=torch.float32, device=self._device)
+        lib = _native.load()
+        _native.check(lib.fl_selected_qk(
+            C.byref(self._native), loop, _native.ptr(query.contiguous()), _native.ptr(idx), None,
+            int(idx.shape[-1]), _native.ptr(current_key.contiguous()) if current_key is not None else None,
+            _native.ptr(out), _native.current_stream(self._device)), "fl_selected_qk")
+        return out
+
+    def pv(self, loop: int, weights: torch.Tensor, indices: torch.Tensor, *,
+           validate_indices: bool = True, current_value: torch.Tensor | None = None,
+           valid: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Probability-weighted V of selected logical rows (flashloop/cache.py:1358-1515).
+        With ``current_value`` the row of index quant + tail is the current token's value,
+        which folds FlashLoopEngine._selected_value_aggregate (engine.py:346-371) into
+        the same launch."""
+
+        loop = int(loop)
+        if loop not in range(4):
+            raise ValueError("loop must be in [0, 3]")
+        idx = self._normalize_indices(indices)
+        if tuple(weights.shape) != (self.batch, self.heads, 1, idx.shape[-1]):
+            raise ValueError("weights must match [batch, heads, 1, selected]")
+        if validate_indices and idx.numel() and (int(idx.min()) < 0 or int(idx.max()) > self.max_context_tokens):
+            raise IndexError("cache index is outside the logical sequence")
+        w = weights.float().contiguous()
+        val = None
+        if valid is not None:
+            val = valid.contiguous()
+            val = val.view(torch.uint8) if val.dtype == torch.bool else val.to(torch.uint8)
+        if out is None:
+            out = torch.empty((self.batch, self.heads, 1, HEAD_DIM), dtype=torch.float32, device=self._device)
+        ws = self._workspace()
+        lib = _native.load()
+        _native.check(lib.fl_selected_pv(
+            C.byref(self._native), loop, _native.ptr(w), _native.ptr(idx), _native.ptr(val),
+            int(idx.shape[-1]), _native.ptr(current_value.contiguous()) if current_value is not None else None,
+            _native.ptr(out), _native.ptr(ws), ws.numel(), _native.current_stream(self._device)),
+            "fl_selected_pv")
+        return out
+
+    # ------------------------------------------------------------------ append / rollover
+
+    def append_decode_token(self, keys: Sequence[torch.Tensor], values: Sequence[torch.Tensor]) -> None:
+        """Append the four loops' K/V of one decoded token per sequence to the BF16 tail
+        and roll the oldest 64 tail tokens into the packed streams when the tail reaches
+        128 (flashloop/cache.py:1758-1838)."""
+
+        shape = _validate_loop_tensors(keys, values)
+        if shape != (self.batch, self.heads, 1, HEAD_DIM):
+            raise ValueError("decode K/V shape does not match the cache")
+        bh = self.batch * self.heads
+        slots = torch.empty(self.batch, dtype=torch.long)
+        for b in range(self.batch):
+            st = self._state_host[b]
+            slots[b] = (int(st[_native.STATE_TAIL_START]) + int(st[_native.STATE_TAIL_LEN])) % TAIL_CAPACITY
+        slot_bh = slots.repeat_interleave(self.heads).to(self._device)
+        rows = torch.arange(bh, device=self._device)
+        for r in range(4):
+            self._tail_k[r, rows, slot_bh] = keys[r].reshape(bh, HEAD_DIM)
+            self._tail_v[r, rows, slot_bh] = values[r].reshape(bh, HEAD_DIM)
+        seq = torch.arange(self.batch, device=self._device)
+        self._tail_active[:, seq, slots.to(self._device)] = 1
+        for b in range(self.batch):
+            self._state_host[b, _native.STATE_TAIL_LEN] += 1
+            while int(self._state_host[b, _native.STATE_TAIL_LEN]) >= self.residual_length + self.group_size:
+                self._roll_one_group(b)
+        self._push_state()
+
+    def _roll_one_group(self, b: int) -> None:
+        st = self._state_host[b]
+        start = int(st[_native.STATE_TAIL_START])
+        quant = int(st[_native.STATE_QUANT_TOKENS])
+        slots = (start + torch.arange(GROUP, device=self._device)) % TAIL_CAPACITY
+        sl = slice(b * self.heads, (b + 1) * self.heads)
+        keys = [self._tail_k[r, sl].index_select(1, slots).unsqueeze(0) for r in range(4)]
+        values = [self._tail_v[r, sl].index_select(1, slots).unsqueeze(0) for r in range(4)]
+        mask3 = self._tail_active[0, b].index_select(0, slots).bool()
+        mask4 = self._tail_active[1, b].index_select(0, slots).bool()
+        sk, sv, positions = self._encode_block(keys, values, mask3, mask4)
+        row0 = [quant, quant, int(st[_native.STATE_ROWS2]), int(st[_native.STATE_ROWS3])]
+        if quant + GROUP > self._caps[0][b]:
+            raise RuntimeError("the preallocated cache is full; raise max_new_tokens")
+        for s in range(4):
+            if sk[s] is not None:
+                self._store_stream(s, b, row0[s], sk[s], sv[s])
+        base = self._rank_base_host[b]
+        for i in range(2):
+            rank = _rank_map(GROUP, positions[i], self._device)
+            rank = torch.where(rank >= 0, rank + row0[2 + i], rank)
+            self._rank[i][base + quant:base + quant + GROUP] = rank
+            self._override_positions[b][i] = torch.cat(
+                [self._override_positions[b][i], positions[i] + quant]).to(torch.int32)
+        self._tail_active[:, b, slots] = 0
+        st[_native.STATE_QUANT_TOKENS] = quant + GROUP
+        st[_native.STATE_ROWS2] = row0[2] + GROUP
+        st[_native.STATE_ROWS3] = row0[3] + GROUP
+        st[_native.STATE_TAIL_LEN] -= GROUP
+        st[_native.STATE_TAIL_START] = (start + GROUP) % TAIL_CAPACITY
+
+
+class CrossLoopKVCache:
+    """Layer-indexed owner for physical Cross-Loop KV storage (flashloop/cache.py:1841-1950)."""
+
+    def __init__(self, *, num_layers: int) -> None:
+        num_layers = int(num_layers)
+        if num_layers <= 0:
+            raise ValueError("num_layers must be positive")
+        self.layers: list[CrossLoopKVLayer | None] = [None] * num_layers
+
+    def set_layer(self, layer_index: int, layer: CrossLoopKVLayer) -> None:
+        layer_index = int(layer_index)
+        if layer_index not in range(len(self.layers)):
+            raise IndexError("layer index is outside the cache")
+        if self.layers[layer_index] is not None:
+            raise RuntimeError("physical cache layer is already installed")
+        self.layers[layer_index] = layer
+
+    def _require_layer(self, layer_index: int) -> CrossLoopKVLayer:
+        layer_index = int(layer_index)
+        if layer_index not in range(len(self.layers)):
+            raise IndexError("layer index is outside the cache")
+        layer = self.layers[layer_index]
+        if layer is None:
+            raise RuntimeError("physical cache layer has not been installed")
+        return layer
+
+    def physical_layout_audit(self) -> dict:
+        installed = [layer for layer in self.layers if layer is not None]
+        return {"installed_layers": len(installed), "reader_backends": ["kivi_outer"] if installed else [],
+                "kivi_packed_streams": 0, "row_packed_streams": 8 * len(installed),
+                "bf16_cross_loop_layers": 0}
+
+    def qk(self, layer_index, loop, query, indices, *, validate_indices=True):
+        return self._require_layer(layer_index).qk(loop, query, indices, validate_indices=validate_indices)
+
+    def pv(self, layer_index, loop, weights, indices, *, validate_indices=True, **kwargs):
+        return self._require_layer(layer_index).pv(loop, weights, indices,
+                                                   validate_indices=validate_indices, **kwargs)
+
+    def cached_mass_sparse_attention_delta(self, layer_index, loop, **kwargs):
+        return self._require_layer(layer_index).cached_mass_sparse_attention_delta(loop, **kwargs)
+
+    def dense_source_attention(self, layer_index, loop, **kwargs):
+        return self._require_layer(layer_index).dense_source_attention(loop, **kwargs)
+
+    @property
+    def storage_bytes(self) -> int:
+        return sum(layer.storage_bytes for layer in self.layers if layer is not None)

@@ -1,0 +1,362 @@
+// Quantise + pack kernels (row layout and KIVI word layout), decode and layout conversion.
+//
+// Arithmetic follows the reference's CPU quantiser exactly (flashloop/packing.py:35-46 ==
+// flashloop/kivi_backend.py:272-283): float32 min/max, span/levels by IEEE division,
+// (x - min)/scale by IEEE subtraction and division, round-half-to-even, clamp; float16
+// metadata is the RNE rounding of the float32 values the codes were computed with.
+#include "fl_common.cuh"
+
+namespace fl {
+namespace {
+
+// ------------------------------------------------------------------------------- K: per channel
+// One CTA of 128 threads per (64-token group, bh); thread c owns channel c.
+template <typename T, int BITS, bool KIVI>
+__global__ void __launch_bounds__(128)
+pack_k_kernel(const T* __restrict__ values, int64_t tokens, void* __restrict__ out_codes,
+              __half* __restrict__ minimum, __half* __restrict__ scale) {
+  constexpr float kLevels = float((1 << BITS) - 1);
+  constexpr int kRowBytes = 16 * BITS;
+  const int c = threadIdx.x;
+  const int64_t g = blockIdx.x;
+  const int64_t bh = blockIdx.y;
+  const int64_t t0 = g * kGroup;
+  const int cnt = (tokens - t0) < kGroup ? static_cast<int>(tokens - t0) : kGroup;
+  const int64_t groups = (tokens + kGroup - 1) / kGroup;
+  const T* src = values + (bh * tokens + t0) * kHeadDim + c;
+
+  float mn = INFINITY, mx = -INFINITY;
+  for (int i = 0; i < cnt; ++i) {
+    const float x = load_as_float(src + static_cast<int64_t>(i) * kHeadDim);
+    mn = fminf(mn, x);
+    mx = fmaxf(mx, x);
+  }
+  const float sc = quant_scale(mn, mx, kLevels);
+  minimum[(bh * groups + g) * kHeadDim + c] = __float2half_rn(mn);
+  scale[(bh * groups + g) * kHeadDim + c] = __float2half_rn(sc);
+
+  if constexpr (KIVI) {
+    static_assert(BITS == 4, "the KIVI word layout is 4-bit");
+    int32_t* payload = static_cast<int32_t*>(out_codes);
+    const int64_t word_rows = (tokens + 7) / 8;
+    for (int w = 0; w * 8 < cnt; ++w) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int i = w * 8 + j;
+        if (i < cnt) {
+          const float x = load_as_float(src + static_cast<int64_t>(i) * kHeadDim);
+          word |= quant_code(x, mn, sc, kLevels) << (4 * j);
+        }
+      }
+      payload[(bh * word_rows + t0 / 8 + w) * kHeadDim + c] = static_cast<int32_t>(word);
+    }
+  } else {
+    __shared__ uint8_t tile[kGroup][kHeadDim + 4];
+    for (int i = 0; i < cnt; ++i) {
+      const float x = load_as_float(src + static_cast<int64_t>(i) * kHeadDim);
+      tile[i][c] = static_cast<uint8_t>(quant_code(x, mn, sc, kLevels));
+    }
+    __syncthreads();
+    constexpr int kRowWords = kRowBytes / 4;
+    constexpr int kPerWord = 32 / BITS;
+    uint32_t* dst =
+        reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(out_codes) + (bh * tokens + t0) * kRowBytes);
+    for (int idx = c; idx < cnt * kRowWords; idx += 128) {
+      const int row = idx / kRowWords;
+      const int wr = idx % kRowWords;
+      uint32_t word = 0;
+#pragma unroll
+      for (int k = 0; k < kPerWord; ++k) word |= uint32_t(tile[row][wr * kPerWord + k]) << (BITS * k);
+      dst[idx] = word;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------- V: per token
+// One warp per token; lane l owns channels 4l .. 4l+3; the two 64-channel groups are the two
+// 16-lane halves of the warp.
+template <typename T, int BITS, bool KIVI>
+__global__ void __launch_bounds__(128)
+pack_v_kernel(const T* __restrict__ values, int64_t tokens, int64_t total_tokens,
+              void* __restrict__ out_codes, __half* __restrict__ minimum,
+              __half* __restrict__ scale, int64_t meta_stride) {
+  constexpr float kLevels = float((1 << BITS) - 1);
+  constexpr int kRowBytes = 16 * BITS;
+  const int lane = threadIdx.x & 31;
+  const int64_t wg = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  if (wg >= total_tokens) return;
+  const int64_t bh = wg / tokens;
+  const int64_t t = wg % tokens;
+  const T* src = values + wg * kHeadDim + 4 * lane;
+  float x[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) x[k] = load_as_float(src + k);
+  float mn = fminf(fminf(x[0], x[1]), fminf(x[2], x[3]));
+  float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  const float sc = quant_scale(mn, mx, kLevels);
+  uint32_t packed = 0;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) packed |= quant_code(x[k], mn, sc, kLevels) << (BITS * k);
+  const int g = lane >> 4;
+  if constexpr (KIVI) {
+    static_assert(BITS == 4, "the KIVI word layout is 4-bit");
+    const uint32_t other = __shfl_down_sync(0xffffffffu, packed, 1);
+    if ((lane & 1) == 0) {
+      static_cast<int32_t*>(out_codes)[(bh * 16 + (lane >> 1)) * tokens + t] =
+          static_cast<int32_t>(packed | (other << 16));
+    }
+    if ((lane & 15) == 0) {
+      minimum[(bh * 2 + g) * tokens + t] = __float2half_rn(mn);
+      scale[(bh * 2 + g) * tokens + t] = __float2half_rn(sc);
+    }
+  } else {
+    uint8_t* row = static_cast<uint8_t*>(out_codes) + wg * kRowBytes;
+    if constexpr (BITS == 4) {
+      reinterpret_cast<uint16_t*>(row)[lane] = static_cast<uint16_t>(packed);
+    } else {
+      row[lane] = static_cast<uint8_t>(packed);
+    }
+    if ((lane & 15) == 0) {
+      minimum[wg * meta_stride + g] = __float2half_rn(mn);
+      scale[wg * meta_stride + g] = __float2half_rn(sc);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------- decode
+template <int BITS>
+__global__ void decode_rows_kernel(const uint32_t* __restrict__ codes,
+                                   const __half* __restrict__ minimum,
+                                   const __half* __restrict__ scale, int per_channel,
+                                   int64_t meta_stride, int64_t tokens, int64_t total_words,
+                                   __nv_bfloat16* __restrict__ out) {
+  constexpr int kRowWords = 16 * BITS / 4;
+  constexpr int kPerWord = 32 / BITS;
+  const int64_t groups = (tokens + kGroup - 1) / kGroup;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total_words;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = idx / kRowWords;
+    const int wr = static_cast<int>(idx % kRowWords);
+    const int64_t bh = row / tokens;
+    const int64_t t = row % tokens;
+    const uint32_t word = codes[idx];
+#pragma unroll
+    for (int k = 0; k < kPerWord; ++k) {
+      const int c = wr * kPerWord + k;
+      const uint32_t code = (word >> (BITS * k)) & ((1u << BITS) - 1u);
+      const int64_t m = per_channel ? (bh * groups + t / kGroup) * kHeadDim + c
+                                    : row * meta_stride + c / kGroup;
+      out[row * kHeadDim + c] = __float2bfloat16_rn(dequant_f32(code, scale[m], minimum[m]));
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------- KIVI -> rows
+__global__ void kivi_to_rows_k_kernel(const uint32_t* __restrict__ payload, int64_t tokens,
+                                      int64_t total_words, uint32_t* __restrict__ codes) {
+  const int64_t word_rows = (tokens + 7) / 8;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total_words;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = idx / 16;
+    const int wr = static_cast<int>(idx % 16);
+    const int64_t bh = row / tokens;
+    const int64_t t = row % tokens;
+    const uint32_t* src = payload + (bh * word_rows + t / 8) * kHeadDim + wr * 8;
+    const int shift = 4 * static_cast<int>(t % 8);
+    uint32_t word = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) word |= ((src[k] >> shift) & 0xFu) << (4 * k);
+    codes[idx] = word;
+  }
+}
+
+__global__ void kivi_to_rows_v_kernel(const uint32_t* __restrict__ payload,
+                                      const __half* __restrict__ minimum,
+                                      const __half* __restrict__ scale, int64_t tokens,
+                                      int64_t total_words, uint32_t* __restrict__ codes,
+                                      __half* __restrict__ out_min, __half* __restrict__ out_scale,
+                                      int64_t meta_stride) {
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total_words;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = idx / 16;
+    const int wr = static_cast<int>(idx % 16);
+    const int64_t bh = row / tokens;
+    const int64_t t = row % tokens;
+    codes[idx] = payload[(bh * 16 + wr) * tokens + t];
+    if (wr < 2) {
+      out_min[row * meta_stride + wr] = minimum[(bh * 2 + wr) * tokens + t];
+      out_scale[row * meta_stride + wr] = scale[(bh * 2 + wr) * tokens + t];
+    }
+  }
+}
+
+template <int BITS, bool KIVI>
+int launch_pack_k(const void* values, int32_t dtype, int64_t bh, int64_t tokens, void* codes,
+                  void* minimum, void* scale, cudaStream_t stream) {
+  const dim3 grid(static_cast<unsigned>((tokens + kGroup - 1) / kGroup), static_cast<unsigned>(bh));
+  __half* mn = static_cast<__half*>(minimum);
+  __half* sc = static_cast<__half*>(scale);
+  switch (dtype) {
+    case FL_DTYPE_BF16:
+      pack_k_kernel<__nv_bfloat16, BITS, KIVI><<<grid, 128, 0, stream>>>(
+          static_cast<const __nv_bfloat16*>(values), tokens, codes, mn, sc);
+      break;
+    case FL_DTYPE_F16:
+      pack_k_kernel<__half, BITS, KIVI><<<grid, 128, 0, stream>>>(
+          static_cast<const __half*>(values), tokens, codes, mn, sc);
+      break;
+    case FL_DTYPE_F32:
+      pack_k_kernel<float, BITS, KIVI><<<grid, 128, 0, stream>>>(
+          static_cast<const float*>(values), tokens, codes, mn, sc);
+      break;
+    default:
+      set_error("pack K: unknown dtype %d", dtype);
+      return FL_ERR_ARGUMENT;
+  }
+  FL_CHECK_LAUNCH("pack K");
+  return FL_OK;
+}
+
+template <int BITS, bool KIVI>
+int launch_pack_v(const void* values, int32_t dtype, int64_t bh, int64_t tokens, void* codes,
+                  void* minimum, void* scale, int64_t meta_stride, cudaStream_t stream) {
+  const int64_t total = bh * tokens;
+  const unsigned grid = static_cast<unsigned>((total + 3) / 4);
+  __half* mn = static_cast<__half*>(minimum);
+  __half* sc = static_cast<__half*>(scale);
+  switch (dtype) {
+    case FL_DTYPE_BF16:
+      pack_v_kernel<__nv_bfloat16, BITS, KIVI><<<grid, 128, 0, stream>>>(
+          static_cast<const __nv_bfloat16*>(values), tokens, total, codes, mn, sc, meta_stride);
+      break;
+    case FL_DTYPE_F16:
+      pack_v_kernel<__half, BITS, KIVI><<<grid, 128, 0, stream>>>(
+          static_cast<const __half*>(values), tokens, total, codes, mn, sc, meta_stride);
+      break;
+    case FL_DTYPE_F32:
+      pack_v_kernel<float, BITS, KIVI><<<grid, 128, 0, stream>>>(
+          static_cast<const float*>(values), tokens, total, codes, mn, sc, meta_stride);
+      break;
+    default:
+      set_error("pack V: unknown dtype %d", dtype);
+      return FL_ERR_ARGUMENT;
+  }
+  FL_CHECK_LAUNCH("pack V");
+  return FL_OK;
+}
+
+int check_pack_args(const char* who, const void* values, int64_t bh, int64_t tokens,
+                    const void* codes, const void* minimum, const void* scale) {
+  FL_REQUIRE(values && codes && minimum && scale, "%s: null pointer", who);
+  FL_REQUIRE(bh > 0 && tokens > 0, "%s: batch_heads and tokens must be positive", who);
+  FL_REQUIRE(bh <= 65535 * 1024LL && (tokens + kGroup - 1) / kGroup < (1LL << 31),
+             "%s: problem too large for one launch", who);
+  return FL_OK;
+}
+
+unsigned flat_grid(int64_t items) {
+  const int64_t blocks = (items + 255) / 256;
+  return static_cast<unsigned>(blocks < 148LL * 32 ? blocks : 148LL * 32);
+}
+
+}  // namespace
+}  // namespace fl
+
+using namespace fl;
+
+extern "C" int fl_pack_k_rows(const void* values, int32_t dtype, int64_t batch_heads,
+                              int64_t tokens, int32_t bits, void* codes, void* minimum,
+                              void* scale, fl_cuda_stream stream) {
+  if (int rc = check_pack_args("fl_pack_k_rows", values, batch_heads, tokens, codes, minimum, scale)) return rc;
+  FL_REQUIRE(batch_heads <= 65535, "fl_pack_k_rows: batch_heads above 65535");
+  FL_REQUIRE(aligned16(codes), "fl_pack_k_rows: codes must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bits == 4) return launch_pack_k<4, false>(values, dtype, batch_heads, tokens, codes, minimum, scale, s);
+  if (bits == 2) return launch_pack_k<2, false>(values, dtype, batch_heads, tokens, codes, minimum, scale, s);
+  set_error("fl_pack_k_rows: bits must be 4 or 2, got %d", bits);
+  return FL_ERR_ARGUMENT;
+}
+
+extern "C" int fl_pack_v_rows(const void* values, int32_t dtype, int64_t batch_heads,
+                              int64_t tokens, int32_t bits, void* codes, void* minimum,
+                              void* scale, int64_t meta_stride, fl_cuda_stream stream) {
+  if (int rc = check_pack_args("fl_pack_v_rows", values, batch_heads, tokens, codes, minimum, scale)) return rc;
+  FL_REQUIRE(meta_stride >= 2, "fl_pack_v_rows: meta_stride must be >= 2");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bits == 4) return launch_pack_v<4, false>(values, dtype, batch_heads, tokens, codes, minimum, scale, meta_stride, s);
+  if (bits == 2) return launch_pack_v<2, false>(values, dtype, batch_heads, tokens, codes, minimum, scale, meta_stride, s);
+  set_error("fl_pack_v_rows: bits must be 4 or 2, got %d", bits);
+  return FL_ERR_ARGUMENT;
+}
+
+extern "C" int fl_pack_kivi_k(const void* values, int32_t dtype, int64_t batch_heads,
+                              int64_t tokens, void* payload, void* minimum, void* scale,
+                              fl_cuda_stream stream) {
+  if (int rc = check_pack_args("fl_pack_kivi_k", values, batch_heads, tokens, payload, minimum, scale)) return rc;
+  FL_REQUIRE(batch_heads <= 65535, "fl_pack_kivi_k: batch_heads above 65535");
+  return launch_pack_k<4, true>(values, dtype, batch_heads, tokens, payload, minimum, scale,
+                                static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int fl_pack_kivi_v(const void* values, int32_t dtype, int64_t batch_heads,
+                              int64_t tokens, void* payload, void* minimum, void* scale,
+                              fl_cuda_stream stream) {
+  if (int rc = check_pack_args("fl_pack_kivi_v", values, batch_heads, tokens, payload, minimum, scale)) return rc;
+  return launch_pack_v<4, true>(values, dtype, batch_heads, tokens, payload, minimum, scale, 0,
+                                static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int fl_decode_rows(const void* codes, const void* minimum, const void* scale,
+                              int32_t per_channel, int64_t meta_stride, int64_t batch_heads,
+                              int64_t tokens, int32_t bits, void* out, fl_cuda_stream stream) {
+  if (int rc = check_pack_args("fl_decode_rows", codes, batch_heads, tokens, out, minimum, scale)) return rc;
+  FL_REQUIRE(bits == 4 || bits == 2, "fl_decode_rows: bits must be 4 or 2");
+  FL_REQUIRE(per_channel || meta_stride >= 2, "fl_decode_rows: meta_stride must be >= 2 for V");
+  const int64_t words = batch_heads * tokens * (16 * bits / 4);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bits == 4) {
+    decode_rows_kernel<4><<<flat_grid(words), 256, 0, s>>>(
+        static_cast<const uint32_t*>(codes), static_cast<const __half*>(minimum),
+        static_cast<const __half*>(scale), per_channel, meta_stride, tokens, words,
+        static_cast<__nv_bfloat16*>(out));
+  } else {
+    decode_rows_kernel<2><<<flat_grid(words), 256, 0, s>>>(
+        static_cast<const uint32_t*>(codes), static_cast<const __half*>(minimum),
+        static_cast<const __half*>(scale), per_channel, meta_stride, tokens, words,
+        static_cast<__nv_bfloat16*>(out));
+  }
+  FL_CHECK_LAUNCH("fl_decode_rows");
+  return FL_OK;
+}
+
+extern "C" int fl_kivi_to_rows_k(const void* payload, int64_t batch_heads, int64_t tokens,
+                                 void* codes, fl_cuda_stream stream) {
+  FL_REQUIRE(payload && codes && batch_heads > 0 && tokens > 0, "fl_kivi_to_rows_k: bad argument");
+  const int64_t words = batch_heads * tokens * 16;
+  kivi_to_rows_k_kernel<<<flat_grid(words), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(payload), tokens, words, static_cast<uint32_t*>(codes));
+  FL_CHECK_LAUNCH("fl_kivi_to_rows_k");
+  return FL_OK;
+}
+
+extern "C" int fl_kivi_to_rows_v(const void* payload, const void* minimum, const void* scale,
+                                 int64_t batch_heads, int64_t tokens, void* codes,
+                                 void* out_minimum, void* out_scale, int64_t meta_stride,
+                                 fl_cuda_stream stream) {
+  FL_REQUIRE(payload && minimum && scale && codes && out_minimum && out_scale && batch_heads > 0 &&
+                 tokens > 0 && meta_stride >= 2,
+             "fl_kivi_to_rows_v: bad argument");
+  const int64_t words = batch_heads * tokens * 16;
+  kivi_to_rows_v_kernel<<<flat_grid(words), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(payload), static_cast<const __half*>(minimum),
+      static_cast<const __half*>(scale), tokens, words, static_cast<uint32_t*>(codes),
+      static_cast<__half*>(out_minimum), static_cast<__half*>(out_scale), meta_stride);
+  FL_CHECK_LAUNCH("fl_kivi_to_rows_v");
+  return FL_OK;
+}

@@ -1,0 +1,1338 @@
+// Decode-attention readers over the packed anchor + delta streams (row layout).
+//
+//   dense_reader_kernel     one launch: QK^T over streams 0..loop + BF16 tail + current token,
+//                           online softmax, PV, split over token chunks, partials merged by the
+//                           last-arriving CTA of each (b,h) (an atomic ticket, no waiting).
+//   selected_reader_kernel  the same over a gathered list of selected logical indices:
+//                           cached-mass sparse delta, weighted PV, or plain QK.
+//
+// Work decomposition: a warp handles eight tokens per step, one per lane quad; lane `sub` of a
+// quad owns channels 32*sub .. 32*sub+31 of the token's K row and V row, i.e. one 16-byte
+// (4-bit) or 8-byte (2-bit) piece of each packed row.  A 64-byte row is one coalesced 128-bit
+// load per lane of the quad, eight rows per warp-wide load instruction.
+//
+// Dequantisation never leaves registers.  Codes are turned into exact float16 integers with
+// the 0x6400 magic-number trick and centred (code - 2^(bits-1)); the per-channel K scale is
+// folded into the query once per 64-token group (w_c = q_c * s_c, bias = sum_c q_c * (m_c +
+// centre * s_c)), the per-token V scale into the probability (W = p * s).  Products accumulate
+// in float16 pairs over at most eight terms (K) or one group (V) and are then widened to
+// float32.
+#include <climits>
+#include <cstdlib>
+
+#include "fl_common.cuh"
+
+namespace fl {
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kWarps = kThreads / kWarp;
+constexpr int kPartialStride = 132;  // acc[128], running max (log2 domain), denominator, pad
+constexpr int kMaxSplits = 64;
+
+struct ReaderParams {
+  LayerView L;
+  int loop;
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* kcur;
+  const __nv_bfloat16* vcur;
+  float scaling;
+  float scaling_log2;
+  float* out;
+  float* logits;
+  int64_t logits_stride;
+  float* partial;
+  int* tickets;
+  int* status;
+  int* queue;  // [0]: next work item, [1]: CTAs that have left
+  int grid_chunks;
+  int chunk_tokens;
+  int max_chunks;
+  // selected readers
+  const int32_t* indices;
+  const uint8_t* valid;
+  int capacity;
+  int slots_per_cta;
+  const float* weights;
+  const float* source_out;
+  const float* mass;
+  float* cur_logits;
+};
+
+// ------------------------------------------------------------------------------ code handling
+
+template <int BITS>
+struct Codes;
+template <>
+struct Codes<4> {
+  uint32_t w[4];
+};
+template <>
+struct Codes<2> {
+  uint32_t w[2];
+};
+
+template <int BITS>
+__device__ __forceinline__ Codes<BITS> load_codes(const uint8_t* row, int sub) {
+  Codes<BITS> c;
+  if constexpr (BITS == 4) {
+    const uint4 v = ldg128(row + sub * 16);
+    c.w[0] = v.x; c.w[1] = v.y; c.w[2] = v.z; c.w[3] = v.w;
+  } else {
+    const uint2 v = ldg64(row + sub * 8);
+    c.w[0] = v.x; c.w[1] = v.y;
+  }
+  return c;
+}
+
+template <int BITS>
+__device__ __forceinline__ Codes<BITS> load_codes_shared(const uint8_t* piece) {
+  Codes<BITS> c;
+  if constexpr (BITS == 4) {
+    const uint4 v = *reinterpret_cast<const uint4*>(piece);
+    c.w[0] = v.x; c.w[1] = v.y; c.w[2] = v.z; c.w[3] = v.w;
+  } else {
+    const uint2 v = *reinterpret_cast<const uint2*>(piece);
+    c.w[0] = v.x; c.w[1] = v.y;
+  }
+  return c;
+}
+
+template <int BITS>
+constexpr int kCentre = 1 << (BITS - 1);
+
+// Channel (0..31 within the lane) held by half `hi` of pair `p` after unpack_centred.
+template <int BITS>
+__host__ __device__ constexpr int pair_channel(int p, int hi) {
+  return BITS == 4 ? (p / 4) * 8 + (p % 4) + 4 * hi : (p / 8) * 16 + (p % 8) + 8 * hi;
+}
+// Inverse: accumulator slot 2*p + hi of the lane's channel cc.
+template <int BITS>
+__host__ __device__ constexpr int channel_slot(int cc) {
+  return BITS == 4 ? 2 * ((cc / 8) * 4 + (cc % 8) % 4) + (cc % 8) / 4
+                   : 2 * ((cc / 16) * 8 + (cc % 16) % 8) + (cc % 16) / 8;
+}
+
+// The lane's 32 codes as 16 half2 of exact integers (code - centre), in pair order.
+template <int BITS>
+__device__ __forceinline__ void unpack_centred(const Codes<BITS>& c, __half2 (&h)[16]) {
+  const uint32_t kMagic = 0x64006400u;
+  if constexpr (BITS == 4) {
+    const __half2 kOff = __floats2half2_rn(1032.f, 1032.f);
+    const __half2 k16th = __floats2half2_rn(0.0625f, 0.0625f);
+    const __half2 kOff16 = __floats2half2_rn(-72.f, -72.f);
+#pragma unroll
+    for (int wd = 0; wd < 4; ++wd) {
+      const uint32_t w = c.w[wd];
+      const uint32_t w8 = w >> 8;
+      h[4 * wd + 0] = __hsub2(as_half2(and_or(w, 0x000F000Fu, kMagic)), kOff);
+      h[4 * wd + 1] = __hfma2(as_half2(and_or(w, 0x00F000F0u, kMagic)), k16th, kOff16);
+      h[4 * wd + 2] = __hsub2(as_half2(and_or(w8, 0x000F000Fu, kMagic)), kOff);
+      h[4 * wd + 3] = __hfma2(as_half2(and_or(w8, 0x00F000F0u, kMagic)), k16th, kOff16);
+    }
+  } else {
+    const __half2 kOff = __floats2half2_rn(1026.f, 1026.f);
+    const __half2 k4th = __floats2half2_rn(0.25f, 0.25f);
+    const __half2 kOff4 = __floats2half2_rn(-258.f, -258.f);
+    const __half2 k16th = __floats2half2_rn(0.0625f, 0.0625f);
+    const __half2 kOff16 = __floats2half2_rn(-66.f, -66.f);
+    const __half2 k64th = __floats2half2_rn(0.015625f, 0.015625f);
+    const __half2 kOff64 = __floats2half2_rn(-18.f, -18.f);
+#pragma unroll
+    for (int wd = 0; wd < 2; ++wd) {
+      const uint32_t w = c.w[wd];
+      const uint32_t w8 = w >> 8;
+      h[8 * wd + 0] = __hsub2(as_half2(and_or(w, 0x00030003u, kMagic)), kOff);
+      h[8 * wd + 1] = __hfma2(as_half2(and_or(w, 0x000C000Cu, kMagic)), k4th, kOff4);
+      h[8 * wd + 2] = __hfma2(as_half2(and_or(w, 0x00300030u, kMagic)), k16th, kOff16);
+      h[8 * wd + 3] = __hfma2(as_half2(and_or(w, 0x00C000C0u, kMagic)), k64th, kOff64);
+      h[8 * wd + 4] = __hsub2(as_half2(and_or(w8, 0x00030003u, kMagic)), kOff);
+      h[8 * wd + 5] = __hfma2(as_half2(and_or(w8, 0x000C000Cu, kMagic)), k4th, kOff4);
+      h[8 * wd + 6] = __hfma2(as_half2(and_or(w8, 0x00300030u, kMagic)), k16th, kOff16);
+      h[8 * wd + 7] = __hfma2(as_half2(and_or(w8, 0x00C000C0u, kMagic)), k64th, kOff64);
+    }
+  }
+}
+
+// The lane's 32 codes as 16 half2 of exact integers in natural channel order (2k, 2k+1).
+template <int BITS>
+__device__ __forceinline__ void unpack_natural(const Codes<BITS>& c, __half2 (&h)[16]) {
+  if constexpr (BITS == 4) {
+    const __half2 kMul = __floats2half2_rn(1.f, 0.0625f);
+    const __half2 kAdd = __floats2half2_rn(-1024.f, -64.f);
+#pragma unroll
+    for (int wd = 0; wd < 4; ++wd) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        // bytes [b_j, 0x64, b_j, 0x64]; keep the low nibble in the low half, the high nibble
+        // in the high half: {1024 + n_even, 1024 + 16 * n_odd}.
+        const uint32_t v = __byte_perm(c.w[wd], 0x64646464u, 0x4040u | (j << 8) | j) & 0xFFF0FF0Fu;
+        h[4 * wd + j] = __hfma2(as_half2(v), kMul, kAdd);
+      }
+    }
+  } else {
+    const __half2 kMulA = __floats2half2_rn(1.f, 0.25f);
+    const __half2 kAddA = __floats2half2_rn(-1024.f, -256.f);
+    const __half2 kMulB = __floats2half2_rn(0.0625f, 0.015625f);
+    const __half2 kAddB = __floats2half2_rn(-64.f, -16.f);
+#pragma unroll
+    for (int wd = 0; wd < 2; ++wd) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t rep = __byte_perm(c.w[wd], 0x64646464u, 0x4040u | (j << 8) | j);
+        h[8 * wd + 2 * j + 0] = __hfma2(as_half2(rep & 0xFF0CFF03u), kMulA, kAddA);
+        h[8 * wd + 2 * j + 1] = __hfma2(as_half2(rep & 0xFFC0FF30u), kMulB, kAddB);
+      }
+    }
+  }
+}
+
+// K, fast path: sum over the lane's 32 channels of w_c * (code_c - centre).
+template <int BITS>
+__device__ __forceinline__ float k_dot_fast(const Codes<BITS>& c, const __half2 (&mult)[16]) {
+  __half2 h[16];
+  unpack_centred<BITS>(c, h);
+  __half2 a0 = __hmul2(h[0], mult[0]);
+  __half2 a1 = __hmul2(h[1], mult[1]);
+#pragma unroll
+  for (int p = 2; p < 16; p += 2) {
+    a0 = __hfma2(h[p], mult[p], a0);
+    a1 = __hfma2(h[p + 1], mult[p + 1], a1);
+  }
+  const float2 f0 = __half22float2(a0);
+  const float2 f1 = __half22float2(a1);
+  return (f0.x + f0.y) + (f1.x + f1.y);
+}
+
+// K, gather path: dequantise the lane's 32 channels against metadata read from memory
+// (natural channel order) and dot them with the query.
+template <int BITS>
+__device__ __forceinline__ float k_dot_meta(const Codes<BITS>& c, const __half* __restrict__ scale,
+                                            const __half* __restrict__ minimum,
+                                            const __half2 (&q2)[16]) {
+  __half2 h[16];
+  unpack_natural<BITS>(c, h);
+  __half2 a0 = __floats2half2_rn(0.f, 0.f), a1 = a0;
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const uint4 s4 = ldg128(scale + 8 * v);
+    const uint4 m4 = ldg128(minimum + 8 * v);
+    const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w};
+    const uint32_t mw[4] = {m4.x, m4.y, m4.z, m4.w};
+#pragma unroll
+    for (int k = 0; k < 4; k += 2) {
+      const __half2 k0 = __hfma2(h[4 * v + k], as_half2(sw[k]), as_half2(mw[k]));
+      const __half2 k1 = __hfma2(h[4 * v + k + 1], as_half2(sw[k + 1]), as_half2(mw[k + 1]));
+      a0 = __hfma2(k0, q2[4 * v + k], a0);
+      a1 = __hfma2(k1, q2[4 * v + k + 1], a1);
+    }
+  }
+  const float2 f0 = __half22float2(a0);
+  const float2 f1 = __half22float2(a1);
+  return (f0.x + f0.y) + (f1.x + f1.y);
+}
+
+template <int BITS>
+__device__ __forceinline__ void v_accumulate(const Codes<BITS>& c, __half2 w, __half2 (&hacc)[16]) {
+  __half2 h[16];
+  unpack_centred<BITS>(c, h);
+#pragma unroll
+  for (int p = 0; p < 16; ++p) hacc[p] = __hfma2(h[p], w, hacc[p]);
+}
+
+__device__ __forceinline__ void flush_pairs(__half2 (&hacc)[16], float (&acc)[32]) {
+#pragma unroll
+  for (int p = 0; p < 16; ++p) {
+    const float2 f = __half22float2(hacc[p]);
+    acc[2 * p] += f.x;
+    acc[2 * p + 1] += f.y;
+    hacc[p] = __floats2half2_rn(0.f, 0.f);
+  }
+}
+
+__device__ __forceinline__ float quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  return v;
+}
+__device__ __forceinline__ float across_quads_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+  return v;
+}
+__device__ __forceinline__ float across_quads_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  v += __shfl_xor_sync(0xffffffffu, v, 8);
+  v += __shfl_xor_sync(0xffffffffu, v, 16);
+  return v;
+}
+
+// The lane's 32 bf16 channels of a BF16 row (tail or current token): dot with q / weighted add.
+__device__ __forceinline__ void load_bf16_row(const __nv_bfloat16* row, int sub, uint32_t (&w)[16]) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const uint4 x = ldg128(row + sub * 32 + v * 8);
+    w[4 * v + 0] = x.x; w[4 * v + 1] = x.y; w[4 * v + 2] = x.z; w[4 * v + 3] = x.w;
+  }
+}
+
+struct OnlineState {
+  float m;        // running maximum of the scaled logits, log2 domain
+  float l;        // sum of probabilities of this lane's tokens (equal in the 4 lanes of a quad)
+  float vbias;    // sum of p * (v_min + centre * v_scale) of the lane's channel group
+  float acc[32];  // sum of p * v_scale * (code - centre), pair order
+};
+
+__device__ __forceinline__ void state_init(OnlineState& s) {
+  s.m = -INFINITY;
+  s.l = 0.f;
+  s.vbias = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) s.acc[i] = 0.f;
+}
+
+// Raise the running maximum to at least `mx` (warp-uniform) and rescale the sums.
+__device__ __forceinline__ void state_raise(OnlineState& s, float mx) {
+  if (mx > s.m) {
+    const float r = exp2f(s.m - mx);  // exp2f(-inf) == 0 on the first raise
+    s.l *= r;
+    s.vbias *= r;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) s.acc[i] *= r;
+    s.m = mx;
+  }
+}
+
+// Reduce the warp's state over its eight quads and park it in shared memory as
+// acc[128] (natural channel order), m, l.
+template <int BITS>
+__device__ __forceinline__ void state_store(OnlineState& s, int lane, float* dst) {
+  const int sub = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) s.acc[i] = across_quads_sum(s.acc[i]);
+  const float vb = across_quads_sum(s.vbias);
+  const float l = across_quads_sum(s.l);
+  if (lane < 4) {
+#pragma unroll
+    for (int cc = 0; cc < 32; ++cc) dst[sub * 32 + cc] = s.acc[channel_slot<BITS>(cc)] + vb;
+    if (lane == 0) {
+      dst[128] = s.m;
+      dst[129] = l;
+    }
+  }
+}
+
+// CTA-level merge of the warps' states, publication of the partial and, in the last CTA of
+// this (b,h), the merge over all partials.  Returns true in the CTA that holds the final
+// result: `total` (this thread's channel, un-normalised) and `denom`.
+template <int NWARPS>
+__device__ __forceinline__ bool merge_and_publish(const ReaderParams& p, float (*s_merge)[kPartialStride],
+                                                  int* s_last, int64_t bh, int slot, int nslots,
+                                                  float& total, float& denom) {
+  const int c = threadIdx.x & (kHeadDim - 1);
+  const bool worker = threadIdx.x < kHeadDim;
+  __syncthreads();
+  float mmax = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < NWARPS; ++w) mmax = fmaxf(mmax, s_merge[w][128]);
+  float a = 0.f, l = 0.f;
+#pragma unroll
+  for (int w = 0; w < NWARPS; ++w) {
+    const float mw = s_merge[w][128];
+    const float r = (mw == -INFINITY) ? 0.f : exp2f(mw - mmax);
+    a += s_merge[w][c] * r;
+    l += s_merge[w][129] * r;
+  }
+  if (nslots == 1) {
+    total = a;
+    denom = l;
+    return true;
+  }
+  float* mine = p.partial + (bh * p.max_chunks + slot) * kPartialStride;
+  if (worker) mine[c] = a;
+  if (threadIdx.x == 0) {
+    mine[128] = mmax;
+    mine[129] = l;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int t = atomicAdd(p.tickets + bh, 1);
+    *s_last = (t == nslots - 1);
+    if (t == nslots - 1) p.tickets[bh] = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!*s_last) return false;
+  __threadfence();
+  const float* base = p.partial + bh * p.max_chunks * kPartialStride;
+  float gm = -INFINITY;
+  for (int j = 0; j < nslots; ++j) gm = fmaxf(gm, __ldcg(base + j * kPartialStride + 128));
+  a = 0.f;
+  l = 0.f;
+  for (int j = 0; j < nslots; ++j) {
+    const float mj = __ldcg(base + j * kPartialStride + 128);
+    const float r = (mj == -INFINITY) ? 0.f : exp2f(mj - gm);
+    a += __ldcg(base + j * kPartialStride + c) * r;
+    l += __ldcg(base + j * kPartialStride + 129) * r;
+  }
+  total = a;
+  denom = l;
+  return true;
+}
+
+// One BF16 row (tail or current token) for every quad of the warp: logits, online softmax, PV.
+template <int BITS>
+__device__ __forceinline__ float bf16_row_dot(const __nv_bfloat16* row, int sub, const float* s_qf) {
+  uint32_t w[16];
+  load_bf16_row(row, sub, w);
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    dot = fmaf(bf16_lo(w[i]), s_qf[sub * 32 + 2 * i], dot);
+    dot = fmaf(bf16_hi(w[i]), s_qf[sub * 32 + 2 * i + 1], dot);
+  }
+  return dot;
+}
+template <int BITS>
+__device__ __forceinline__ void bf16_row_accumulate(const __nv_bfloat16* row, int sub, float pr,
+                                                    float (&acc)[32]) {
+  uint32_t w[16];
+  load_bf16_row(row, sub, w);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    acc[channel_slot<BITS>(2 * i)] = fmaf(pr, bf16_lo(w[i]), acc[channel_slot<BITS>(2 * i)]);
+    acc[channel_slot<BITS>(2 * i + 1)] = fmaf(pr, bf16_hi(w[i]), acc[channel_slot<BITS>(2 * i + 1)]);
+  }
+}
+
+__device__ __forceinline__ void load_query(const ReaderParams& p, int64_t bh, float* s_qf, __half* s_qh) {
+  const int c = threadIdx.x;
+  const float q = __bfloat162float(p.q[bh * kHeadDim + c]);
+  s_qf[c] = q;
+  s_qh[c] = __float2half_rn(q);
+}
+
+// ------------------------------------------------------------------------------ dense reader
+//
+// Eight warps per CTA; each warp owns whole 64-token blocks of the chunk and runs its own
+// two-stage shared-memory ring.  A "unit" is one (block, stream, K|V) piece: the 64 packed rows
+// (4 KiB at 4 bits) plus their metadata (K: the scale/min rows of the one or two 64-row groups
+// the rows live in; V: the rows' 8-byte scale/min words).  Lane 0 of the warp arms the stage's
+// mbarrier with the byte count and issues the TMA bulk copies (cp.async.bulk, global ->
+// shared); the warp then waits on the barrier's phase, computes from shared memory, and
+// re-issues the unit two places ahead into the stage it has just drained.  No CTA-wide
+// synchronisation happens until the final merge, and waits are bounded: a wait that runs out
+// raises the status word in the workspace and the kernel runs to its end.
+
+constexpr int kDenseWarps = 8;
+constexpr int kDenseThreads = kDenseWarps * kWarp;
+constexpr int kStages = 2;
+constexpr int kWaitLimit = 1 << 12;
+constexpr uint32_t kSuspendNs = 100000;
+
+template <int BITS>
+struct Stage {
+  static constexpr int kRowBytes = 16 * BITS;
+  static constexpr int kCodes = kGroup * kRowBytes;
+  static constexpr int kMeta = 1024;  // K: scale/min of two groups; V: up to 66 rows of 8 bytes
+  static constexpr int kBytes = kCodes + kMeta;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* ptr) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(ptr));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+// Bounded wait for the phase with the given parity; false when the limit ran out.  Each try
+// lets the hardware suspend the thread for up to kSuspendNs, so a waiting warp issues almost
+// nothing; kWaitLimit tries bound the total wait to a fraction of a second.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int i = 0; i < kWaitLimit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(kSuspendNs)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+// Rows [r0, r0 + m) of stream s (relative to the (b,h) row base) that hold the tokens of the
+// 64-token block starting at t0.  The rows of one block are consecutive.
+struct Span {
+  int r0;
+  int m;
+};
+__device__ __forceinline__ Span block_span(const LayerView& L, int s, int b, int t0, int lane) {
+  if (s < 2) return Span{t0, kGroup};
+  const int32_t* rank = L.rank[s - 2] + L.rank_base[b] + t0;
+  const int ra = rank[lane], rb = rank[lane + 32];
+  const uint32_t ma = __ballot_sync(0xffffffffu, ra >= 0);
+  const uint32_t mb = __ballot_sync(0xffffffffu, rb >= 0);
+  const int first_a = __shfl_sync(0xffffffffu, ra, ma ? __ffs(ma) - 1 : 0);
+  const int first_b = __shfl_sync(0xffffffffu, rb, mb ? __ffs(mb) - 1 : 0);
+  Span sp;
+  sp.m = __popc(ma) + __popc(mb);
+  sp.r0 = ma ? first_a : (mb ? first_b : 0);
+  return sp;
+}
+
+// A work item: one chunk of one (b,h) head (chunk < nchunks - 1) or its BF16 tail plus the
+// current token (chunk == nchunks - 1).
+struct ItemDesc {
+  int id;  // -1: the queue is empty
+  int bh, b, chunk, nchunks, quant, tail_len, tail_start, blk_begin, blk_end;
+};
+
+// Take the next valid item from the global queue (one thread per CTA calls this).
+__device__ __forceinline__ void draw_item(const ReaderParams& p, ItemDesc* d) {
+  const LayerView& L = p.L;
+  const int batch_heads = L.batch * L.heads;
+  const int total = batch_heads * p.grid_chunks;
+  for (;;) {
+    const int id = atomicAdd(p.queue, 1);
+    if (id >= total) {
+      d->id = -1;
+      return;
+    }
+    const int chunk = id / batch_heads;  // chunk-major: the long heads' extra chunks come last
+    const int bh = id - chunk * batch_heads;
+    const int b = bh / L.heads;
+    const int32_t* st = L.seq_state + b * FL_STATE_WORDS;
+    const int quant = st[FL_STATE_QUANT_TOKENS];
+    const int nq_chunks = (quant + p.chunk_tokens - 1) / p.chunk_tokens;
+    if (chunk > nq_chunks) continue;
+    d->bh = bh;
+    d->b = b;
+    d->chunk = chunk;
+    d->nchunks = nq_chunks + 1;
+    d->quant = quant;
+    d->tail_len = st[FL_STATE_TAIL_LEN];
+    d->tail_start = st[FL_STATE_TAIL_START];
+    d->blk_begin = chunk * (p.chunk_tokens / kGroup);
+    d->blk_end = chunk == nq_chunks ? d->blk_begin
+                                    : min(d->blk_begin + p.chunk_tokens / kGroup, quant / kGroup);
+    d->id = id;
+    return;
+  }
+}
+
+// Blocks of an item that belong to `warp` (blocks warp, warp + 8, ... of the chunk).
+__device__ __forceinline__ int blocks_of_warp(int blk_begin, int blk_end, int warp) {
+  const int n = blk_end - blk_begin - warp;
+  return n > 0 ? (n + kDenseWarps - 1) / kDenseWarps : 0;
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(kDenseThreads, 2)
+dense_reader_kernel(const __grid_constant__ ReaderParams p) {
+  using St = Stage<BITS>;
+  constexpr int kRowBytes = St::kRowBytes;
+  constexpr int kLaneBytes = kRowBytes / 4;
+  extern __shared__ __align__(128) uint8_t s_ring[];  // [warp][stage][St::kBytes]
+  __shared__ __align__(16) float s_qf[2][kHeadDim];
+  __shared__ __align__(16) __half s_wtab[kDenseWarps][2][kHeadDim];
+  __shared__ __align__(16) float s_merge[2][kDenseWarps][kPartialStride];
+  __shared__ __align__(8) uint64_t s_bar[kDenseWarps][kStages];
+  __shared__ ItemDesc s_item[3];
+  __shared__ int s_last[2];
+
+  const LayerView& L = p.L;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int quad = lane >> 2;
+  const int sub = lane & 3;
+  const int streams = p.loop + 1;
+  const int units_per_block = 2 * streams;
+  uint8_t* ring = s_ring + static_cast<size_t>(warp) * kStages * St::kBytes;
+
+  if (lane == 0) {
+#pragma unroll
+    for (int k = 0; k < kStages; ++k) mbar_init(smem_u32(&s_bar[warp][k]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (tid == 0) {
+    draw_item(p, &s_item[0]);
+    draw_item(p, &s_item[1]);
+  }
+  __syncthreads();
+  if (s_item[0].id >= 0 && tid < kHeadDim) {
+    s_qf[0][tid] = __bfloat162float(p.q[static_cast<int64_t>(s_item[0].bh) * kHeadDim + tid]);
+  }
+  __syncthreads();
+
+  // Per-warp pipeline counters: units issued / consumed since the kernel started.  Unit g lives
+  // in stage g % kStages and completes that stage's phase (g / kStages) & 1.
+  uint32_t issued = 0, consumed = 0;
+  // Issue cursor: item sequence number, block index within my blocks of that item, unit in block.
+  int iss_item = 0, iss_blk = 0, iss_j = 0;
+  bool timed_out = false;
+
+  for (int k = 0;; ++k) {
+    const ItemDesc cur = s_item[k % 3];
+    if (cur.id < 0) break;
+    // Look ahead: thread 0 draws item k+2; the upper half of the CTA fetches the query of item
+    // k+1.  Both become visible to the other warps at this item's merge barrier.
+    if (tid == 0) draw_item(p, &s_item[(k + 2) % 3]);
+    if (tid >= kHeadDim) {
+      const int next_id = s_item[(k + 1) % 3].id;
+      if (next_id >= 0) {
+        s_qf[(k + 1) & 1][tid - kHeadDim] = __bfloat162float(
+            p.q[static_cast<int64_t>(s_item[(k + 1) % 3].bh) * kHeadDim + tid - kHeadDim]);
+      }
+    }
+    const int64_t bh = cur.bh;
+    const int b = cur.b;
+    const float* qf = s_qf[k & 1];
+    float* logits_row = p.logits ? p.logits + bh * p.logits_stride : nullptr;
+
+    OnlineState S;
+    state_init(S);
+
+    if (cur.chunk < cur.nchunks - 1) {
+      const int my_blocks = blocks_of_warp(cur.blk_begin, cur.blk_end, warp);
+      float lg[8];
+      __half2 hacc[16];
+      __half2 hbias = __floats2half2_rn(0.f, 0.f);  // sum of p * (v_min + centre * v_scale) of one block
+      for (int cb = 0; cb < my_blocks; ++cb) {
+        const int blk = cur.blk_begin + warp + cb * kDenseWarps;
+        const int t0 = blk * kGroup;
+        for (int j = 0; j < units_per_block; ++j) {
+          // ---- keep the ring full: issue units of this item, then of the next one
+          while (issued - consumed < static_cast<uint32_t>(kStages)) {
+            if (iss_item > k + 1) break;
+            const ItemDesc* it = &s_item[iss_item % 3];
+            if (it->id < 0) break;
+            const int it_blocks =
+                it->chunk < it->nchunks - 1 ? blocks_of_warp(it->blk_begin, it->blk_end, warp) : 0;
+            if (iss_blk >= it_blocks) {
+              ++iss_item;
+              iss_blk = 0;
+              iss_j = 0;
+              continue;
+            }
+            const int64_t ibh = it->bh;
+            const int iblk = it->blk_begin + warp + iss_blk * kDenseWarps;
+            const bool iv = iss_j >= streams;
+            const int is = iv ? iss_j - streams : iss_j;
+            const Span sp = block_span(L, is, it->b, iblk * kGroup, lane);
+            if (lane == 0) {
+              const uint32_t stage_index = issued % kStages;
+              const uint32_t bar = smem_u32(&s_bar[warp][stage_index]);
+              const uint32_t dst = smem_u32(ring + stage_index * St::kBytes);
+              if (sp.m == 0) {
+                mbar_arrive(bar);
+              } else {
+                const int64_t row = L.row_base[is][ibh] + sp.r0;
+                const uint32_t code_bytes = static_cast<uint32_t>(sp.m) * kRowBytes;
+                if (!iv) {
+                  const int g0 = sp.r0 >> 6, g1 = (sp.r0 + sp.m - 1) >> 6;
+                  const int64_t grp = L.group_base[is][ibh] + g0;
+                  const uint32_t ng = g1 - g0 + 1;
+                  mbar_arrive_expect_tx(bar, code_bytes + ng * 512u);
+                  bulk_copy_g2s(dst, L.k_codes[is] + row * kRowBytes, code_bytes, bar);
+                  for (uint32_t gi = 0; gi < ng; ++gi) {
+                    bulk_copy_g2s(dst + St::kCodes + gi * 512u, L.k_scale[is] + (grp + gi) * kHeadDim, 256u, bar);
+                    bulk_copy_g2s(dst + St::kCodes + gi * 512u + 256u, L.k_min[is] + (grp + gi) * kHeadDim, 256u,
+                                  bar);
+                  }
+                } else {
+                  const int64_t even = row & ~int64_t(1);
+                  const uint32_t meta_rows = static_cast<uint32_t>(((row + sp.m + 1) & ~int64_t(1)) - even);
+                  mbar_arrive_expect_tx(bar, code_bytes + meta_rows * 8u);
+                  bulk_copy_g2s(dst, L.v_codes[is] + row * kRowBytes, code_bytes, bar);
+                  bulk_copy_g2s(dst + St::kCodes, L.v_meta[is] + even * 4, meta_rows * 8u, bar);
+                }
+              }
+            }
+            ++issued;
+            if (++iss_j == units_per_block) {
+              iss_j = 0;
+              ++iss_blk;
+            }
+          }
+
+          // ---- consume unit (blk, j)
+          const bool is_v = j >= streams;
+          const int s = is_v ? j - streams : j;
+          const uint32_t stage_index = consumed % kStages;
+          const uint8_t* stage = ring + stage_index * St::kBytes;
+          if (!mbar_wait(smem_u32(&s_bar[warp][stage_index]), (consumed / kStages) & 1u)) timed_out = true;
+          const Span sp = block_span(L, s, b, t0, lane);
+          const int32_t* rank = s >= 2 ? L.rank[s - 2] + L.rank_base[b] + t0 : nullptr;
+        const int g0 = sp.r0 >> 6;
+        const int ng = sp.m > 0 ? ((sp.r0 + sp.m - 1) >> 6) - g0 + 1 : 0;
+        // A block whose 64 tokens are all present in one metadata group (always true for streams
+        // 0 and 1) takes the branch-free path: row i of the stage is token i.
+        const bool full = sp.m == kGroup && ng == 1;
+        if (!is_v) {
+          if (s == 0) {
+  #pragma unroll
+            for (int it = 0; it < 8; ++it) lg[it] = 0.f;
+          }
+          // w_c = q_c * scale_c and bias = sum_c q_c * (min_c + centre * scale_c) per group
+          float kbias0 = 0.f, kbias1 = 0.f;
+          for (int gi = 0; gi < ng; ++gi) {
+            const uint2 sc = *reinterpret_cast<const uint2*>(stage + St::kCodes + gi * 512 + lane * 8);
+            const uint2 mn = *reinterpret_cast<const uint2*>(stage + St::kCodes + gi * 512 + 256 + lane * 8);
+            const float2 sc01 = __half22float2(as_half2(sc.x)), sc23 = __half22float2(as_half2(sc.y));
+            const float2 mn01 = __half22float2(as_half2(mn.x)), mn23 = __half22float2(as_half2(mn.y));
+            const float4 q4 = *reinterpret_cast<const float4*>(&qf[4 * lane]);
+            const float kc = float(kCentre<BITS>);
+            float bias = q4.x * fmaf(kc, sc01.x, mn01.x);
+            bias = fmaf(q4.y, fmaf(kc, sc01.y, mn01.y), bias);
+            bias = fmaf(q4.z, fmaf(kc, sc23.x, mn23.x), bias);
+            bias = fmaf(q4.w, fmaf(kc, sc23.y, mn23.y), bias);
+            __half* tab = &s_wtab[warp][gi][(4 * lane) & ~31];
+            const int cc = (4 * lane) & 31;
+            tab[channel_slot<BITS>(cc + 0)] = __float2half_rn(q4.x * sc01.x);
+            tab[channel_slot<BITS>(cc + 1)] = __float2half_rn(q4.y * sc01.y);
+            tab[channel_slot<BITS>(cc + 2)] = __float2half_rn(q4.z * sc23.x);
+            tab[channel_slot<BITS>(cc + 3)] = __float2half_rn(q4.w * sc23.y);
+            bias = 0.25f * warp_sum(bias);
+            if (gi == 0) kbias0 = bias; else kbias1 = bias;
+          }
+          __syncwarp();
+          if (full) {
+            __half2 mult[16];
+            const uint4* src = reinterpret_cast<const uint4*>(&s_wtab[warp][0][sub * 32]);
+  #pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const uint4 x = src[v];
+              mult[4 * v + 0] = as_half2(x.x); mult[4 * v + 1] = as_half2(x.y);
+              mult[4 * v + 2] = as_half2(x.z); mult[4 * v + 3] = as_half2(x.w);
+            }
+            const uint8_t* piece = stage + quad * kRowBytes + sub * kLaneBytes;
+            Codes<BITS> c[8];
+  #pragma unroll
+            for (int it = 0; it < 8; ++it) c[it] = load_codes_shared<BITS>(piece + it * 8 * kRowBytes);
+  #pragma unroll
+            for (int it = 0; it < 8; ++it) lg[it] += k_dot_fast<BITS>(c[it], mult) + kbias0;
+          } else if (sp.m > 0) {
+  #pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int r = rank[it * 8 + quad];
+              if (r >= 0) {
+                const int gi = (r >> 6) - g0;
+                __half2 mult[16];
+                const uint4* src = reinterpret_cast<const uint4*>(&s_wtab[warp][gi][sub * 32]);
+  #pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                  const uint4 x = src[v];
+                  mult[4 * v + 0] = as_half2(x.x); mult[4 * v + 1] = as_half2(x.y);
+                  mult[4 * v + 2] = as_half2(x.z); mult[4 * v + 3] = as_half2(x.w);
+                }
+                const Codes<BITS> c =
+                    load_codes_shared<BITS>(stage + (r - sp.r0) * kRowBytes + sub * kLaneBytes);
+                lg[it] += k_dot_fast<BITS>(c, mult) + (gi == 0 ? kbias0 : kbias1);
+              }
+            }
+          }
+          if (s == p.loop) {
+            // all streams summed: logits -> probabilities of my eight tokens
+            float mx = -INFINITY;
+  #pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const float raw = quad_sum(lg[it]);
+              if (logits_row && sub == 0) logits_row[t0 + it * 8 + quad] = raw * p.scaling;
+              lg[it] = raw * p.scaling_log2;
+              mx = fmaxf(mx, lg[it]);
+            }
+            state_raise(S, across_quads_max(mx));
+  #pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              lg[it] = exp2f(lg[it] - S.m);
+              S.l += lg[it];
+            }
+  #pragma unroll
+            for (int i = 0; i < 16; ++i) hacc[i] = __floats2half2_rn(0.f, 0.f);
+          }
+        } else {
+          const int64_t row = L.row_base[s][bh] + sp.r0;
+          const uint8_t* meta = stage + St::kCodes + static_cast<int>(row & 1) * 8;
+          // my channel group's minimum / scale, duplicated into both halves
+          const uint32_t pick = (sub < 2) ? 0x1010u : 0x3232u;
+          const __half2 centre2 = __floats2half2_rn(float(kCentre<BITS>), float(kCentre<BITS>));
+          if (full) {
+            const uint8_t* piece = stage + quad * kRowBytes + sub * kLaneBytes;
+  #pragma unroll
+            for (int half_block = 0; half_block < 2; ++half_block) {
+              Codes<BITS> c[4];
+              uint2 mt[4];
+  #pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const int it = half_block * 4 + k;
+                c[k] = load_codes_shared<BITS>(piece + it * 8 * kRowBytes);
+                mt[k] = *reinterpret_cast<const uint2*>(meta + (it * 8 + quad) * 8);
+              }
+  #pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const __half2 vm2 = as_half2(__byte_perm(mt[k].x, 0u, pick));
+                const __half2 vs2 = as_half2(__byte_perm(mt[k].y, 0u, pick));
+                const __half2 p2 = __float2half2_rn(lg[half_block * 4 + k]);
+                hbias = __hfma2(p2, __hfma2(centre2, vs2, vm2), hbias);
+                v_accumulate<BITS>(c[k], __hmul2(p2, vs2), hacc);
+              }
+            }
+          } else if (sp.m > 0) {
+  #pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int r = rank[it * 8 + quad];
+              if (r >= 0) {
+                const int ri = r - sp.r0;
+                const Codes<BITS> c = load_codes_shared<BITS>(stage + ri * kRowBytes + sub * kLaneBytes);
+                const uint2 mt = *reinterpret_cast<const uint2*>(meta + ri * 8);
+                const __half2 vm2 = as_half2(__byte_perm(mt.x, 0u, pick));
+                const __half2 vs2 = as_half2(__byte_perm(mt.y, 0u, pick));
+                const __half2 p2 = __float2half2_rn(lg[it]);
+                hbias = __hfma2(p2, __hfma2(centre2, vs2, vm2), hbias);
+                v_accumulate<BITS>(c, __hmul2(p2, vs2), hacc);
+              }
+            }
+          }
+          if (s == p.loop) {
+            flush_pairs(hacc, S.acc);
+            S.vbias += __low2float(hbias);
+            hbias = __floats2half2_rn(0.f, 0.f);
+          }
+        }
+          __syncwarp();
+          ++consumed;
+        }
+      }
+    }
+    // Every unit of this item has been issued: park the issue cursor on the next item, so that
+    // it never looks at the descriptor slot thread 0 is about to overwrite.
+    if (iss_item <= k) {
+      iss_item = k + 1;
+      iss_blk = 0;
+      iss_j = 0;
+    }
+    if (cur.chunk == cur.nchunks - 1 && warp < 4) {
+      // ---- the BF16 tail and the current token: entries 0..tail_len (the last is the current)
+      const int entries = cur.tail_len + 1;
+      const __nv_bfloat16* tk = L.tail_k[p.loop] + bh * L.tail_capacity * kHeadDim;
+      const __nv_bfloat16* tv = L.tail_v[p.loop] + bh * L.tail_capacity * kHeadDim;
+      for (int e0 = warp * 8; e0 < entries; e0 += 4 * 8) {
+        const int e = e0 + quad;
+        const bool ok = e < entries;
+        const int slot = (cur.tail_start + e) % L.tail_capacity;
+        const __nv_bfloat16* krow = (e == cur.tail_len) ? p.kcur + bh * kHeadDim : tk + slot * kHeadDim;
+        const __nv_bfloat16* vrow = (e == cur.tail_len) ? p.vcur + bh * kHeadDim : tv + slot * kHeadDim;
+        float dot = 0.f;
+        if (ok) dot = bf16_row_dot<BITS>(krow, sub, qf);
+        dot = quad_sum(dot);
+        if (ok && logits_row && sub == 0) logits_row[cur.quant + e] = dot * p.scaling;
+        const float x = ok ? dot * p.scaling_log2 : -INFINITY;
+        state_raise(S, across_quads_max(x));
+        const float pr = ok ? exp2f(x - S.m) : 0.f;
+        S.l += pr;
+        if (ok) bf16_row_accumulate<BITS>(vrow, sub, pr, S.acc);
+      }
+    }
+
+    // ---- merge the eight warps' states, publish the item's partial, finish the head if last
+    const int buf = k & 1;
+    state_store<BITS>(S, lane, s_merge[buf][warp]);
+    __syncthreads();
+    if (warp < 4) {
+      const int c = tid;
+      float mmax = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kDenseWarps; ++w) mmax = fmaxf(mmax, s_merge[buf][w][128]);
+      float a = 0.f, l = 0.f;
+#pragma unroll
+      for (int w = 0; w < kDenseWarps; ++w) {
+        const float mw = s_merge[buf][w][128];
+        const float r = (mw == -INFINITY) ? 0.f : exp2f(mw - mmax);
+        a += s_merge[buf][w][c] * r;
+        l += s_merge[buf][w][129] * r;
+      }
+      if (cur.nchunks == 1) {
+        p.out[bh * kHeadDim + c] = a / l;
+      } else {
+        float* mine = p.partial + (bh * p.max_chunks + cur.chunk) * kPartialStride;
+        mine[c] = a;
+        if (c == 0) {
+          mine[128] = mmax;
+          mine[129] = l;
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (c == 0) {
+          const int t = atomicAdd(p.tickets + bh, 1);
+          s_last[buf] = (t == cur.nchunks - 1);
+          if (t == cur.nchunks - 1) p.tickets[bh] = 0;  // ready for the next launch
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (s_last[buf]) {
+          __threadfence();
+          const float* base = p.partial + bh * p.max_chunks * kPartialStride;
+          float gm = -INFINITY;
+          for (int jj = 0; jj < cur.nchunks; ++jj) gm = fmaxf(gm, __ldcg(base + jj * kPartialStride + 128));
+          a = 0.f;
+          l = 0.f;
+          for (int jj = 0; jj < cur.nchunks; ++jj) {
+            const float mj = __ldcg(base + jj * kPartialStride + 128);
+            const float r = (mj == -INFINITY) ? 0.f : exp2f(mj - gm);
+            a += __ldcg(base + jj * kPartialStride + c) * r;
+            l += __ldcg(base + jj * kPartialStride + 129) * r;
+          }
+          p.out[bh * kHeadDim + c] = a / l;
+        }
+      }
+    }
+  }
+
+  if (timed_out && lane == 0) atomicExch(p.status, 1);
+  if (tid == 0) {
+    // the last CTA to leave rewinds the queue for the next launch
+    const int d = atomicAdd(p.queue + 1, 1);
+    if (d == static_cast<int>(gridDim.x) - 1) {
+      p.queue[0] = 0;
+      p.queue[1] = 0;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ selected readers
+
+enum { kModeDelta = 0, kModePV = 1, kModeQK = 2 };
+
+template <int BITS, int MODE>
+__global__ void __launch_bounds__(kThreads)
+selected_reader_kernel(const __grid_constant__ ReaderParams p) {
+  constexpr int kRowBytes = 16 * BITS;
+  __shared__ __align__(16) float s_qf[kHeadDim];
+  __shared__ __align__(16) __half s_qh[kHeadDim];
+  __shared__ __align__(16) float s_merge[kWarps][kPartialStride];
+  __shared__ int s_last;
+
+  const LayerView& L = p.L;
+  const int64_t bh = blockIdx.y;
+  const int b = static_cast<int>(bh / L.heads);
+  const int32_t* st = L.seq_state + b * FL_STATE_WORDS;
+  const int quant = st[FL_STATE_QUANT_TOKENS];
+  const int tail_len = st[FL_STATE_TAIL_LEN];
+  const int tail_start = st[FL_STATE_TAIL_START];
+  const int cur_pos = quant + tail_len;
+  const int nsplits = (p.capacity + p.slots_per_cta - 1) / p.slots_per_cta;
+  const int split = blockIdx.x;
+  const int slot_begin = split * p.slots_per_cta;
+  const int slot_end = min(p.capacity, slot_begin + p.slots_per_cta);
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int quad = lane >> 2;
+  const int sub = lane & 3;
+  __half2 q2[16];
+  if constexpr (MODE != kModePV) {
+    load_query(p, bh, s_qf, s_qh);
+    __syncthreads();
+    const uint4* src = reinterpret_cast<const uint4*>(&s_qh[sub * 32]);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const uint4 x = src[v];
+      q2[4 * v + 0] = as_half2(x.x); q2[4 * v + 1] = as_half2(x.y);
+      q2[4 * v + 2] = as_half2(x.z); q2[4 * v + 3] = as_half2(x.w);
+    }
+  }
+
+  OnlineState S;
+  state_init(S);
+  if constexpr (MODE == kModePV) S.m = 0.f;
+  const int32_t* idx_row = p.indices + bh * p.capacity;
+  const uint8_t* valid_row = p.valid ? p.valid + bh * p.capacity : nullptr;
+  const __nv_bfloat16* tk = L.tail_k[p.loop] + bh * L.tail_capacity * kHeadDim;
+  const __nv_bfloat16* tv = L.tail_v[p.loop] + bh * L.tail_capacity * kHeadDim;
+
+  for (int j0 = slot_begin + warp * 8; j0 < slot_end; j0 += kWarps * 8) {
+    const int j = j0 + quad;
+    const bool in_range = j < slot_end;
+    int idx = -1;
+    if (in_range && (!valid_row || valid_row[j])) idx = idx_row[j];
+    // kind: 0 nothing, 1 packed prefix, 2 tail, 3 current token
+    int kind = 0;
+    const __nv_bfloat16* krow = nullptr;
+    const __nv_bfloat16* vrow = nullptr;
+    if (idx >= 0) {
+      if (idx == cur_pos) {
+        if constexpr (MODE == kModePV) {
+          kind = p.vcur ? 3 : 0;
+        } else {
+          kind = p.kcur ? 3 : 0;
+        }
+        krow = p.kcur ? p.kcur + bh * kHeadDim : nullptr;
+        vrow = p.vcur ? p.vcur + bh * kHeadDim : nullptr;
+      } else if (idx >= quant) {
+        if (idx - quant < tail_len) {
+          kind = 2;
+          const int slot = (tail_start + idx - quant) % L.tail_capacity;
+          krow = tk + slot * kHeadDim;
+          vrow = tv + slot * kHeadDim;
+        }
+      } else {
+        kind = 1;
+      }
+    }
+    int rows[4];
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      rows[s] = -1;
+      if (kind == 1 && s <= p.loop) {
+        rows[s] = s < 2 ? idx : L.rank[s - 2][L.rank_base[b] + idx];
+      }
+    }
+
+    float pr = 0.f;
+    if constexpr (MODE != kModePV) {
+      float dot = 0.f;
+      if (kind == 1) {
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          if (rows[s] >= 0) {
+            const int64_t row = L.row_base[s][bh] + rows[s];
+            const int64_t g = L.group_base[s][bh] + (rows[s] >> 6);
+            const Codes<BITS> c = load_codes<BITS>(L.k_codes[s] + row * kRowBytes, sub);
+            dot += k_dot_meta<BITS>(c, L.k_scale[s] + g * kHeadDim + sub * 32,
+                                    L.k_min[s] + g * kHeadDim + sub * 32, q2);
+          }
+        }
+      } else if (kind >= 2) {
+        dot = bf16_row_dot<BITS>(krow, sub, s_qf);
+      }
+      dot = quad_sum(dot);
+      if constexpr (MODE == kModeQK) {
+        if (in_range && sub == 0) p.logits[bh * p.capacity + j] = kind ? dot : 0.f;
+        continue;
+      }
+      if (kind == 3 && p.cur_logits && sub == 0) p.cur_logits[bh] = dot * p.scaling;
+      const float x = kind ? dot * p.scaling_log2 : -INFINITY;
+      const float mx = across_quads_max(x);
+      if (mx > -INFINITY) state_raise(S, mx);
+      pr = kind ? exp2f(x - S.m) : 0.f;
+      S.l += pr;
+    } else {
+      pr = kind ? p.weights[bh * p.capacity + j] : 0.f;
+    }
+
+    if (kind == 1) {
+      __half2 hacc[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) hacc[i] = __floats2half2_rn(0.f, 0.f);
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        if (rows[s] >= 0) {
+          const int64_t row = L.row_base[s][bh] + rows[s];
+          const Codes<BITS> c = load_codes<BITS>(L.v_codes[s] + row * kRowBytes, sub);
+          const uint2 mt = ldg64(L.v_meta[s] + row * 4);
+          const __half2 mins = as_half2(mt.x), scales = as_half2(mt.y);
+          const float vs = (sub < 2) ? __low2float(scales) : __high2float(scales);
+          const float vm = (sub < 2) ? __low2float(mins) : __high2float(mins);
+          S.vbias = fmaf(pr, fmaf(float(kCentre<BITS>), vs, vm), S.vbias);
+          const __half wh = __float2half_rn(pr * vs);
+          v_accumulate<BITS>(c, __halves2half2(wh, wh), hacc);
+        }
+      }
+      flush_pairs(hacc, S.acc);
+    } else if (kind >= 2) {
+      bf16_row_accumulate<BITS>(vrow, sub, pr, S.acc);
+    }
+  }
+  if constexpr (MODE == kModeQK) return;
+
+  state_store<BITS>(S, lane, s_merge[warp]);
+  float total, denom;
+  if (merge_and_publish<kWarps>(p, s_merge, &s_last, bh, split, nsplits, total, denom)) {
+    const int c = threadIdx.x;
+    if constexpr (MODE == kModeDelta) {
+      const float target = denom > 0.f ? total / denom : 0.f;
+      p.out[bh * kHeadDim + c] = p.mass[bh] * (target - p.source_out[bh * kHeadDim + c]);
+    } else {
+      p.out[bh * kHeadDim + c] = total;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ host side
+
+int choose_chunk_tokens(int64_t batch_heads, int64_t max_context_tokens) {
+  // Work items of the persistent dense reader: one 64-token block per warp (512 tokens) unless
+  // that gives every CTA more than ~32 items, then two or four blocks per warp.
+  const int64_t ctas = 148 * 2;
+  int chunk = kGroup * kDenseWarps;
+  while (chunk < 2048 && batch_heads * ((max_context_tokens + chunk - 1) / chunk) > 32 * ctas) chunk *= 2;
+  if (const char* env = getenv("FL_CHUNK")) chunk = atoi(env);
+  return chunk;
+}
+
+int choose_slots_per_cta(int64_t batch_heads, int64_t capacity) {
+  const int64_t budget = 148 * 6;
+  int64_t slots = 32;
+  while ((batch_heads * ((capacity + slots - 1) / slots) > budget || (capacity + slots - 1) / slots > kMaxSplits) &&
+         slots < capacity)
+    slots += 32;
+  return static_cast<int>(slots);
+}
+
+// tickets[batch_heads], one status word and the two words of the work queue, padded to 256 bytes
+size_t tickets_bytes(int64_t batch_heads) { return (((batch_heads + 3) * sizeof(int) + 255) / 256) * 256; }
+
+int max_partials(int64_t batch_heads, int64_t max_context_tokens) {
+  const int chunk = choose_chunk_tokens(batch_heads, max_context_tokens);
+  const int64_t dense = (max_context_tokens + chunk - 1) / chunk + 1;
+  return static_cast<int>(dense > kMaxSplits ? dense : kMaxSplits);
+}
+
+}  // namespace
+
+int validate_layer(const fl_layer* layer, int loop, const char* who) {
+  FL_REQUIRE(layer != nullptr, "%s: null layer", who);
+  FL_REQUIRE(layer->batch > 0 && layer->heads > 0, "%s: batch and heads must be positive", who);
+  FL_REQUIRE(static_cast<int64_t>(layer->batch) * layer->heads <= 65535, "%s: batch*heads above 65535", who);
+  FL_REQUIRE(layer->bits == 4 || layer->bits == 2, "%s: bits must be 4 or 2, got %d", who, layer->bits);
+  FL_REQUIRE(loop >= 0 && loop < 4, "%s: loop must be in [0, 3], got %d", who, loop);
+  FL_REQUIRE(layer->tail_capacity >= 1, "%s: tail_capacity must be positive", who);
+  FL_REQUIRE(layer->seq_state != nullptr, "%s: seq_state is null", who);
+  for (int s = 0; s <= loop; ++s) {
+    FL_REQUIRE(layer->k_codes[s] && layer->k_min[s] && layer->k_scale[s] && layer->v_codes[s] &&
+                   layer->v_meta[s] && layer->row_base[s] && layer->group_base[s],
+               "%s: stream %d has a null pointer", who, s);
+    FL_REQUIRE(aligned16(layer->k_codes[s]) && aligned16(layer->v_codes[s]) && aligned16(layer->k_min[s]) &&
+                   aligned16(layer->k_scale[s]) && aligned16(layer->v_meta[s]),
+               "%s: stream %d is not 16-byte aligned", who, s);
+  }
+  if (loop >= 2) {
+    FL_REQUIRE(layer->rank[0] && layer->rank_base, "%s: loop %d needs the loop-3 rank map", who, loop);
+    if (loop >= 3) FL_REQUIRE(layer->rank[1] != nullptr, "%s: loop 3 needs the loop-4 rank map", who);
+  }
+  FL_REQUIRE(layer->tail_k[loop] && layer->tail_v[loop], "%s: tail of loop %d is null", who, loop);
+  FL_REQUIRE(aligned16(layer->tail_k[loop]) && aligned16(layer->tail_v[loop]),
+             "%s: tails must be 16-byte aligned", who);
+  return FL_OK;
+}
+
+}  // namespace fl
+
+using namespace fl;
+
+extern "C" size_t fl_reader_workspace_bytes(int64_t batch_heads, int64_t max_context_tokens) {
+  if (batch_heads <= 0 || max_context_tokens < 0) return 0;
+  return tickets_bytes(batch_heads) +
+         static_cast<size_t>(batch_heads) * max_partials(batch_heads, max_context_tokens) * kPartialStride *
+             sizeof(float);
+}
+
+extern "C" int fl_workspace_status(const void* workspace, int64_t batch_heads, int32_t* status,
+                                   fl_cuda_stream stream) {
+  FL_REQUIRE(workspace != nullptr && status != nullptr && batch_heads > 0, "fl_workspace_status: bad argument");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t err = cudaMemcpyAsync(status, static_cast<const int*>(workspace) + batch_heads, sizeof(int32_t),
+                                    cudaMemcpyDeviceToHost, s);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+  if (err != cudaSuccess) {
+    set_error("fl_workspace_status: %s", cudaGetErrorString(err));
+    return FL_ERR_CUDA;
+  }
+  return FL_OK;
+}
+
+extern "C" int fl_workspace_init(void* workspace, size_t bytes, fl_cuda_stream stream) {
+  FL_REQUIRE(workspace != nullptr && bytes > 0, "fl_workspace_init: empty workspace");
+  const cudaError_t err = cudaMemsetAsync(workspace, 0, bytes, static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) {
+    set_error("fl_workspace_init: %s", cudaGetErrorString(err));
+    return FL_ERR_CUDA;
+  }
+  return FL_OK;
+}
+
+namespace {
+
+int fill_common(ReaderParams& p, const fl_layer* layer, int loop, void* workspace, size_t workspace_bytes,
+                int64_t max_context_tokens, const char* who) {
+  const int64_t bh = static_cast<int64_t>(layer->batch) * layer->heads;
+  const size_t need = fl_reader_workspace_bytes(bh, max_context_tokens);
+  if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) {
+    set_error("%s: workspace of %zu bytes (16-byte aligned) required, got %zu", who, need, workspace_bytes);
+    return FL_ERR_WORKSPACE;
+  }
+  p.L = make_view(*layer);
+  p.loop = loop;
+  p.tickets = static_cast<int*>(workspace);
+  p.status = p.tickets + bh;
+  p.queue = p.tickets + bh + 1;
+  p.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + tickets_bytes(bh));
+  p.max_chunks = max_partials(bh, max_context_tokens);
+  return FL_OK;
+}
+
+}  // namespace
+
+extern "C" int fl_dense_source_attention(const fl_layer* layer, int32_t loop, const void* query,
+                                         const void* current_key, const void* current_value,
+                                         float scaling, float* output, float* logits,
+                                         int64_t logits_stride, int64_t max_context_tokens,
+                                         void* workspace, size_t workspace_bytes,
+                                         fl_cuda_stream stream) {
+  if (int rc = validate_layer(layer, loop, "fl_dense_source_attention")) return rc;
+  FL_REQUIRE(query && current_key && current_value && output, "fl_dense_source_attention: null vector");
+  FL_REQUIRE(aligned16(query) && aligned16(current_key) && aligned16(current_value),
+             "fl_dense_source_attention: vectors must be 16-byte aligned");
+  FL_REQUIRE(max_context_tokens >= 0, "fl_dense_source_attention: negative max_context_tokens");
+  FL_REQUIRE(!logits || logits_stride > max_context_tokens,
+             "fl_dense_source_attention: logits_stride must exceed max_context_tokens");
+  ReaderParams p{};
+  if (int rc = fill_common(p, layer, loop, workspace, workspace_bytes, max_context_tokens,
+                           "fl_dense_source_attention"))
+    return rc;
+  const int64_t bh = static_cast<int64_t>(layer->batch) * layer->heads;
+  p.q = static_cast<const __nv_bfloat16*>(query);
+  p.kcur = static_cast<const __nv_bfloat16*>(current_key);
+  p.vcur = static_cast<const __nv_bfloat16*>(current_value);
+  p.scaling = scaling;
+  p.scaling_log2 = scaling * 1.4426950408889634f;
+  p.out = output;
+  p.logits = logits;
+  p.logits_stride = logits_stride;
+  p.chunk_tokens = choose_chunk_tokens(bh, max_context_tokens);
+  p.grid_chunks = static_cast<int>((max_context_tokens + p.chunk_tokens - 1) / p.chunk_tokens) + 1;
+  // persistent CTAs, two per SM, fed from the work queue in the workspace
+  static const int sm_count = [] {
+    int dev = 0, n = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n > 0 ? n : 148;
+  }();
+  const int64_t items = bh * p.grid_chunks;
+  const unsigned grid = static_cast<unsigned>(items < 2 * sm_count ? items : 2 * sm_count);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (layer->bits == 4) {
+    constexpr int kSmem = kDenseWarps * kStages * Stage<4>::kBytes;
+    static const cudaError_t attr = cudaFuncSetAttribute(
+        dense_reader_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    (void)attr;
+    dense_reader_kernel<4><<<grid, kDenseThreads, kSmem, s>>>(p);
+  } else {
+    constexpr int kSmem = kDenseWarps * kStages * Stage<2>::kBytes;
+    static const cudaError_t attr = cudaFuncSetAttribute(
+        dense_reader_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    (void)attr;
+    dense_reader_kernel<2><<<grid, kDenseThreads, kSmem, s>>>(p);
+  }
+  FL_CHECK_LAUNCH("fl_dense_source_attention");
+  return FL_OK;
+}
+
+namespace {
+
+template <int MODE>
+int launch_selected(const fl_layer* layer, ReaderParams& p, cudaStream_t s, const char* who) {
+  const int64_t bh = static_cast<int64_t>(layer->batch) * layer->heads;
+  p.slots_per_cta = choose_slots_per_cta(bh, p.capacity);
+  const int splits = (p.capacity + p.slots_per_cta - 1) / p.slots_per_cta;
+  const dim3 grid(splits, static_cast<unsigned>(bh));
+  if (layer->bits == 4) {
+    selected_reader_kernel<4, MODE><<<grid, kThreads, 0, s>>>(p);
+  } else {
+    selected_reader_kernel<2, MODE><<<grid, kThreads, 0, s>>>(p);
+  }
+  FL_CHECK_LAUNCH(who);
+  return FL_OK;
+}
+
+}  // namespace
+
+extern "C" int fl_sparse_attention_delta(const fl_layer* layer, int32_t loop, const void* query,
+                                         const void* current_key, const void* current_value,
+                                         const int32_t* indices, const uint8_t* valid,
+                                         int64_t capacity, const float* source_output,
+                                         const float* global_mass, float scaling, float* output,
+                                         float* current_logits, void* workspace,
+                                         size_t workspace_bytes, fl_cuda_stream stream) {
+  const char* who = "fl_sparse_attention_delta";
+  if (int rc = validate_layer(layer, loop, who)) return rc;
+  FL_REQUIRE(query && current_key && current_value && indices && valid && source_output && global_mass && output,
+             "%s: null argument", who);
+  FL_REQUIRE(aligned16(query) && aligned16(current_key) && aligned16(current_value),
+             "%s: vectors must be 16-byte aligned", who);
+  FL_REQUIRE(capacity > 0 && capacity < (1 << 24), "%s: capacity out of range", who);
+  ReaderParams p{};
+  if (int rc = fill_common(p, layer, loop, workspace, workspace_bytes, 0, who)) return rc;
+  p.q = static_cast<const __nv_bfloat16*>(query);
+  p.kcur = static_cast<const __nv_bfloat16*>(current_key);
+  p.vcur = static_cast<const __nv_bfloat16*>(current_value);
+  p.scaling = scaling;
+  p.scaling_log2 = scaling * 1.4426950408889634f;
+  p.out = output;
+  p.indices = indices;
+  p.valid = valid;
+  p.capacity = static_cast<int>(capacity);
+  p.source_out = source_output;
+  p.mass = global_mass;
+  p.cur_logits = current_logits;
+  return launch_selected<kModeDelta>(layer, p, static_cast<cudaStream_t>(stream), who);
+}
+
+extern "C" int fl_selected_pv(const fl_layer* layer, int32_t loop, const float* weights,
+                              const int32_t* indices, const uint8_t* valid, int64_t capacity,
+                              const void* current_value, float* output, void* workspace,
+                              size_t workspace_bytes, fl_cuda_stream stream) {
+  const char* who = "fl_selected_pv";
+  if (int rc = validate_layer(layer, loop, who)) return rc;
+  FL_REQUIRE(weights && indices && output, "%s: null argument", who);
+  FL_REQUIRE(!current_value || aligned16(current_value), "%s: current_value must be 16-byte aligned", who);
+  FL_REQUIRE(capacity > 0 && capacity < (1 << 24), "%s: capacity out of range", who);
+  ReaderParams p{};
+  if (int rc = fill_common(p, layer, loop, workspace, workspace_bytes, 0, who)) return rc;
+  p.vcur = static_cast<const __nv_bfloat16*>(current_value);
+  p.out = output;
+  p.indices = indices;
+  p.valid = valid;
+  p.capacity = static_cast<int>(capacity);
+  p.weights = weights;
+  return launch_selected<kModePV>(layer, p, static_cast<cudaStream_t>(stream), who);
+}
+
+extern "C" int fl_selected_qk(const fl_layer* layer, int32_t loop, const void* query,
+                              const int32_t* indices, const uint8_t* valid, int64_t capacity,
+                              const void* current_key, float* logits, fl_cuda_stream stream) {
+  const char* who = "fl_selected_qk";
+  if (int rc = validate_layer(layer, loop, who)) return rc;
+  FL_REQUIRE(query && indices && logits, "%s: null argument", who);
+  FL_REQUIRE(aligned16(query) && (!current_key || aligned16(current_key)),
+             "%s: vectors must be 16-byte aligned", who);
+  FL_REQUIRE(capacity > 0 && capacity < (1 << 24), "%s: capacity out of range", who);
+  ReaderParams p{};
+  p.L = make_view(*layer);
+  p.loop = loop;
+  p.q = static_cast<const __nv_bfloat16*>(query);
+  p.kcur = static_cast<const __nv_bfloat16*>(current_key);
+  p.scaling = 1.f;
+  p.scaling_log2 = 1.f;
+  p.logits = logits;
+  p.indices = indices;
+  p.valid = valid;
+  p.capacity = static_cast<int>(capacity);
+  p.max_chunks = kMaxSplits;
+  return launch_selected<kModeQK>(layer, p, static_cast<cudaStream_t>(stream), who);
+}

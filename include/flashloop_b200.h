@@ -1,0 +1,228 @@
+/*
+ * flashloop_b200 -- C ABI of the B200 (sm_100a) kernels for FlashLoop's late-loop decode path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, launches on that
+ * stream without synchronising, allocates nothing, and returns FL_OK or a negative status
+ * (fl_last_error() holds the message of the calling thread's last failure).  Outputs and the
+ * scratch workspace are caller-provided, so a decode step built from these calls can be
+ * captured in a CUDA graph.
+ *
+ * Each declaration cites the interface of the reference project (paths relative to its root)
+ * that it replaces.  Where the reference is batch-one with scalar lengths, the replacement is
+ * batched: per-sequence lengths live in device memory (fl_layer.seq_state).
+ *
+ * Fixed by the reference and by these kernels: head_dim 128, quantisation group 64
+ * (flashloop/config.py:40-43, flashloop/kivi_backend.py:174-175).
+ */
+#ifndef FLASHLOOP_B200_H
+#define FLASHLOOP_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FL_HEAD_DIM 128
+#define FL_GROUP 64
+#define FL_STREAMS 4
+#define FL_STATE_WORDS 8
+
+/* status codes */
+#define FL_OK 0
+#define FL_ERR_ARGUMENT (-1)
+#define FL_ERR_CUDA (-2)
+#define FL_ERR_WORKSPACE (-3)
+#define FL_ERR_UNSUPPORTED (-4)
+
+/* element types of floating-point inputs */
+#define FL_DTYPE_BF16 0
+#define FL_DTYPE_F16 1
+#define FL_DTYPE_F32 2
+
+/* words of fl_layer.seq_state[b] */
+#define FL_STATE_QUANT_TOKENS 0 /* tokens held in the packed streams (multiple of 64)          */
+#define FL_STATE_TAIL_LEN 1     /* tokens held in the BF16 tail                                */
+#define FL_STATE_TAIL_START 2   /* ring slot of the oldest tail token                           */
+#define FL_STATE_ROWS2 3        /* rows in use in stream 2 (multiple of 64 between rollovers)   */
+#define FL_STATE_ROWS3 4        /* rows in use in stream 3                                      */
+
+typedef void* fl_cuda_stream; /* a cudaStream_t */
+
+/*
+ * One physical cache layer: the anchor stream and three delta streams of K and of V for every
+ * (sequence, head), the four BF16 tails and the per-sequence state.  Replaces the tensors held
+ * by CrossLoopKVLayer (flashloop/cache.py:628-657): _packed_keys/_packed_values, rank_maps,
+ * _tail_keys/_tail_values, _tail_active, quantized_tokens, _tail_length.
+ *
+ * Streams use the row layout of flashloop/packing.py:49-54, 71-99 (one token per row, even
+ * channel in the low nibble; 2-bit rows hold four channels per byte).  K metadata is one
+ * float16 minimum and scale per channel per 64-row group (packing.py:146-170); V metadata is
+ * one minimum and scale per token per 64-channel group (packing.py:173-197), stored
+ * interleaved so that one token's four values share a 8-byte word.
+ *
+ * Rows of (b, h) in stream s start at row_base[s][b*heads + h]; their K metadata groups start
+ * at group_base[s][b*heads + h]; row r belongs to group r / 64.  Streams 2 and 3 hold only
+ * the rows retained by loops 3 and 4: rank[s-2][rank_base[b] + t] is the row of logical token
+ * t, or -1.  A rollover appends one 64-row block to every stream, so a compact stream's rows
+ * of one metadata group are contiguous and never share a group with another block
+ * (the row layout's append rule, flashloop/cache.py:202-242).
+ *
+ * The struct itself lives in host memory; all pointers in it are device pointers.
+ */
+typedef struct fl_layer {
+  int32_t batch;
+  int32_t heads;
+  int32_t bits;          /* 4 or 2 */
+  int32_t tail_capacity; /* ring size in tokens, >= 128 */
+  void* k_codes[FL_STREAMS];           /* uint8 [rows][16*bits]            */
+  void* k_min[FL_STREAMS];             /* float16 [groups][128]            */
+  void* k_scale[FL_STREAMS];           /* float16 [groups][128]            */
+  void* v_codes[FL_STREAMS];           /* uint8 [rows][16*bits]            */
+  void* v_meta[FL_STREAMS];            /* float16 [rows][4]: min0 min1 scale0 scale1 */
+  const int64_t* row_base[FL_STREAMS]; /* [batch*heads]                    */
+  const int64_t* group_base[FL_STREAMS];
+  int32_t* rank[2];                    /* streams 2 and 3                  */
+  const int64_t* rank_base;            /* [batch]                          */
+  void* tail_k[FL_STREAMS];            /* bfloat16 [batch*heads][tail_capacity][128], per loop */
+  void* tail_v[FL_STREAMS];
+  uint8_t* tail_active[2];             /* [batch][tail_capacity] loop-3 / loop-4 retention   */
+  int32_t* seq_state;                  /* [batch][FL_STATE_WORDS]          */
+} fl_layer;
+
+const char* fl_last_error(void);
+int fl_version(void);
+
+/* ---------------------------------------------------------------------------------------
+ * Quantise + pack.  Bit-exact with the reference's CPU codecs on the same input.
+ * ------------------------------------------------------------------------------------- */
+
+/* flashloop/packing.py:146-170 pack_k_per_channel.  values [bh][tokens][128] of `dtype`;
+ * codes [bh][tokens][16*bits]; minimum/scale float16 [bh][ceil(tokens/64)][128]. */
+int fl_pack_k_rows(const void* values, int32_t dtype, int64_t batch_heads, int64_t tokens,
+                   int32_t bits, void* codes, void* minimum, void* scale, fl_cuda_stream stream);
+
+/* flashloop/packing.py:173-197 pack_v_per_token.  minimum/scale float16, element (bh, t, g) at
+ * [(bh*tokens + t)*meta_stride + g]; meta_stride 2 gives the reference's [bh][tokens][2]. */
+int fl_pack_v_rows(const void* values, int32_t dtype, int64_t batch_heads, int64_t tokens,
+                   int32_t bits, void* codes, void* minimum, void* scale, int64_t meta_stride,
+                   fl_cuda_stream stream);
+
+/* flashloop/kivi_backend.py:404-438 pack_kivi_k_per_channel (and its GPU twin
+ * _triton_pack_kivi, :162-256).  payload int32 [bh][ceil(tokens/8)][128]. */
+int fl_pack_kivi_k(const void* values, int32_t dtype, int64_t batch_heads, int64_t tokens,
+                   void* payload, void* minimum, void* scale, fl_cuda_stream stream);
+
+/* flashloop/kivi_backend.py:441-475 pack_kivi_v_per_token.  payload int32 [bh][16][tokens];
+ * minimum/scale float16 [bh][2][tokens]. */
+int fl_pack_kivi_v(const void* values, int32_t dtype, int64_t batch_heads, int64_t tokens,
+                   void* payload, void* minimum, void* scale, fl_cuda_stream stream);
+
+/* Packed4Bit.decode (flashloop/packing.py:108-132): code*scale + minimum in float32, rounded
+ * to bfloat16.  per_channel != 0 selects K metadata ([bh][groups][128]); otherwise V metadata
+ * with meta_stride as in fl_pack_v_rows.  out bfloat16 [bh][tokens][128]. */
+int fl_decode_rows(const void* codes, const void* minimum, const void* scale, int32_t per_channel,
+                   int64_t meta_stride, int64_t batch_heads, int64_t tokens, int32_t bits,
+                   void* out, fl_cuda_stream stream);
+
+/* Re-arrange a KIVI word stream (flashloop/kivi_backend.py:286-322) into the row layout; the
+ * codes and metadata values are unchanged.  K: payload int32 [bh][ceil(tokens/8)][128] ->
+ * codes [bh][tokens][64].  V: payload [bh][16][tokens] -> codes; metadata [bh][2][tokens] ->
+ * [bh][tokens][meta_stride]. */
+int fl_kivi_to_rows_k(const void* payload, int64_t batch_heads, int64_t tokens, void* codes,
+                      fl_cuda_stream stream);
+int fl_kivi_to_rows_v(const void* payload, const void* minimum, const void* scale,
+                      int64_t batch_heads, int64_t tokens, void* codes, void* out_minimum,
+                      void* out_scale, int64_t meta_stride, fl_cuda_stream stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Readers.
+ * ------------------------------------------------------------------------------------- */
+
+/* Bytes of scratch needed by the readers for `batch_heads` (b,h) pairs and contexts of at most
+ * `max_context_tokens`.  The workspace must be zero-filled once before its first use
+ * (fl_workspace_init); the readers leave it ready for the next call.  Calls that share one
+ * workspace must not overlap on the GPU. */
+size_t fl_reader_workspace_bytes(int64_t batch_heads, int64_t max_context_tokens);
+int fl_workspace_init(void* workspace, size_t bytes, fl_cuda_stream stream);
+
+/* Synchronises `stream` and copies the workspace's status word to *status (host memory):
+ * 0, or 1 when a reader launched with this workspace for `batch_heads` pairs gave up waiting
+ * for one of its own asynchronous copies (its output is then undefined).  The reference has
+ * no counterpart: its kernels never wait on anything. */
+int fl_workspace_status(const void* workspace, int64_t batch_heads, int32_t* status,
+                        fl_cuda_stream stream);
+
+/* CrossLoopKVLayer.dense_source_attention (flashloop/cache.py:1644-1756) ->
+ * dense_source_attention_cuda (flashloop/csrc/kivi_outer_gemv_cuda.cu:1914-2076, kernels :722,
+ * :813, :870) as ONE launch: softmax(scaling * q [K_loop; K_tail; k_cur]^T) [V_loop; V_tail;
+ * v_cur], K_loop = sum of dequantised streams 0..loop (loop 0..3; the reference stops at 1).
+ * query/current_key/current_value bfloat16 [bh][128]; output float32 [bh][128]; logits
+ * (nullable) float32 [bh][logits_stride] receives the scaled logits of the quant+tail+1 keys
+ * of each sequence, as the reference returns for loop 1.  max_context_tokens bounds
+ * quant+tail over the batch (host-known; sizes the grid). */
+int fl_dense_source_attention(const fl_layer* layer, int32_t loop, const void* query,
+                              const void* current_key, const void* current_value, float scaling,
+                              float* output, float* logits, int64_t logits_stride,
+                              int64_t max_context_tokens, void* workspace, size_t workspace_bytes,
+                              fl_cuda_stream stream);
+
+/* CrossLoopKVLayer.cached_mass_sparse_attention_delta (flashloop/cache.py:1517-1642) ->
+ * sparse_attention_delta_cuda (kivi_outer_gemv_cuda.cu:1711-1912, kernels :1015, :813, :1146)
+ * as ONE launch: over the valid selected logical indices (prefix rows through the rank maps,
+ * tail rows, or the current token at index quant+tail) compute the subset softmax target and
+ * return global_mass * (target - source_output).  indices int32 / valid uint8 [bh][capacity];
+ * source_output float32 [bh][128]; global_mass float32 [bh]; output float32 [bh][128];
+ * current_logits (nullable) float32 [bh] receives the scaled logit of the current token. */
+int fl_sparse_attention_delta(const fl_layer* layer, int32_t loop, const void* query,
+                              const void* current_key, const void* current_value,
+                              const int32_t* indices, const uint8_t* valid, int64_t capacity,
+                              const float* source_output, const float* global_mass, float scaling,
+                              float* output, float* current_logits, void* workspace,
+                              size_t workspace_bytes, fl_cuda_stream stream);
+
+/* CrossLoopKVLayer.pv (flashloop/cache.py:1358-1515) -> pv_cross_loop_cuda
+ * (kivi_outer_gemv_cuda.cu:1625-1709) fused with the current-token term of
+ * FlashLoopEngine._selected_value_aggregate (flashloop/engine.py:346-371):
+ * output = sum_j weights[j] * V_loop[indices[j]], the row of index quant+tail being
+ * current_value (nullable: then that index contributes nothing).  weights float32
+ * [bh][capacity]; valid nullable. */
+int fl_selected_pv(const fl_layer* layer, int32_t loop, const float* weights,
+                   const int32_t* indices, const uint8_t* valid, int64_t capacity,
+                   const void* current_value, float* output, void* workspace,
+                   size_t workspace_bytes, fl_cuda_stream stream);
+
+/* CrossLoopKVLayer.qk (flashloop/cache.py:1202-1356) -> qk_cross_loop_cuda
+ * (kivi_outer_gemv_cuda.cu:1541-1623): unscaled logits of the selected logical rows;
+ * index quant+tail reads current_key (nullable).  logits float32 [bh][capacity]; slots that
+ * are invalid or out of range receive 0. */
+int fl_selected_qk(const fl_layer* layer, int32_t loop, const void* query, const int32_t* indices,
+                   const uint8_t* valid, int64_t capacity, const void* current_key, float* logits,
+                   fl_cuda_stream stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Selection.
+ * ------------------------------------------------------------------------------------- */
+
+/* select_decode_keys (flashloop/selection.py:72-88) and the inline selection of
+ * FlashLoopEngine.decode (flashloop/engine.py:438-481: softmax, topk, sort, gather, pad,
+ * mass, renormalise) as ONE launch per call: per (b,h) pick the budget = min(N, max(1,
+ * ceil(N*fraction))) largest of N float32 values (ties: lower index first), emit their indices
+ * in ascending order padded with zeros to `capacity`, the validity mask, the selected global
+ * softmax mass and (nullable) the selected weights divided by that mass.
+ * values [bh][values_stride]; if values_are_logits != 0 they are scaled logits and the weights
+ * are their softmax over the N keys, else they are the weights themselves.
+ * N = n_keys when seq_state is NULL, else quant+tail+1 of each sequence.
+ * capacity must be >= (budget/64 + 1)*64 for the largest N (engine.py:100). */
+int fl_select_decode_keys(const float* values, int64_t values_stride, int32_t batch, int32_t heads,
+                          int32_t n_keys, const int32_t* seq_state, double fraction,
+                          int32_t values_are_logits, int32_t* indices, uint8_t* valid,
+                          int64_t capacity, int32_t* counts, float* global_mass,
+                          float* selected_weights, fl_cuda_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FLASHLOOP_B200_H */
