@@ -1,0 +1,380 @@
+#!/usr/bin/env python3
+"""Decode-path benchmark: tokens/s of the int4 KV-residual attention hot path.
+
+Workload (BASELINE configs[1], "sparse late-loop decode"): per GPU a batch of 8 sequences,
+16 heads x 128, context 8192, four loops, 4-bit K/V in groups of 64 with a 64-token BF16 tail,
+held for the 24 layers of an Ouro-1.4B-shaped decoder.  One step decodes one token per
+sequence through the KV-attention path of every layer: dense reader loop 1, dense reader
+loop 2 (+ logits), top-10 % key selection, selected-value aggregate, cached-mass sparse reader
+loops 3 and 4, then the append of the token's four K/V rows to the tail (with the 64-token
+rollover when the tail reaches 128).  Queries and current K/V are synthetic (there is no
+model in front of the path); the cache is synthetic K/V of the named shape.
+
+Prints ONE JSON line (rank 0).  ``--impl reference`` times the CPU oracle port of the same
+step on the host cores instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HEADS, HEAD_DIM, CONTEXT, LAYERS, BATCH = 16, 128, 8192, 24, 8
+KEY_FRACTION = 0.10
+SCALING = HEAD_DIM ** -0.5
+METRIC = "decode tok/s (Ouro-1.4B-shape R4)"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--batch", type=int, default=BATCH)
+    ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--bits", type=int, default=4)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def workload_name(args) -> str:
+    return (f"configs[1] sparse late-loop decode: batch {args.batch}/GPU, {HEADS} heads x {HEAD_DIM}, "
+            f"context {args.context}, 4 loops, {args.bits}-bit K/V group 64, 64-token BF16 tail, "
+            f"top-10% keys in loops 3-4, {args.layers} layers")
+
+
+# ----------------------------------------------------------------------------- algorithmic bytes
+
+
+def stream_bytes_per_token(bits: int) -> int:
+    """K codes + V codes + K metadata (512 B per 64 tokens) + V metadata (8 B) per token."""
+    return 2 * 16 * bits + 8 + 8
+
+
+def dense_bytes(batch_heads: int, loop: int, quant: int, tail: int, bits: int) -> int:
+    """Dense reader, loop index 0..3: streams 0..loop of the packed prefix, K+V tail rows,
+    query / current K / current V (bf16) and the float32 output."""
+    return batch_heads * ((loop + 1) * stream_bytes_per_token(bits) * quant + tail * 512 + 1280)
+
+
+def sparse_bytes(batch_heads: int, loop: int, keys: int, quant: int, bits: int) -> int:
+    """Gathered reader: selected rows of every stream (codes + V metadata), the K metadata of
+    every group, 13 B of index / validity / rank lookups per key, vectors in and out."""
+    per_stream = keys * (2 * 16 * bits + 8) + 512 * (quant // 64)
+    return batch_heads * ((loop + 1) * per_stream + keys * 13 + 1280)
+
+
+# ----------------------------------------------------------------------------- clocks
+
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.path = tempfile.NamedTemporaryFile(prefix="fl_clocks_", suffix=".csv", delete=False).name
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in Path(self.path).read_text().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[3:7]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ----------------------------------------------------------------------------- the CPU oracle leg
+
+
+def _oracle_head_step(seed: int, context: int, bits: int) -> float:
+    """One head of one sequence of one layer through the oracle's decode step; returns seconds.
+    (The only place outside tests/ where the oracle runs: it is the CPU baseline.)"""
+
+    import numpy as np
+
+    from flashloop_b200.synthetic import make_loop_kv, make_query
+    from oracle import selection as osel
+    from oracle.cache import LayerOracle
+
+    keys, values = make_loop_kv(1, context, seed=seed)
+    import torch
+
+    torch.set_num_threads(1)
+    to_np = lambda t: t.float().numpy()
+    ones = np.ones(context, bool)
+    layer = LayerOracle.from_prefill([to_np(k) for k in keys], [to_np(v) for v in values],
+                                     mask_loop3=ones, mask_loop4=ones, bits=bits)
+    q, ck, cv = (to_np(t) for t in make_query(1, seed=seed))
+    start = time.perf_counter()
+    layer.dense_source_attention(0, query=q, current_key=ck, current_value=cv, scaling=SCALING)
+    _, logits = layer.dense_source_attention(1, query=q, current_key=ck, current_value=cv, scaling=SCALING)
+    sel = osel.select_from_logits(logits, fraction=KEY_FRACTION)
+    src = layer.selected_value_aggregate(1, selected_indices=sel["indices"], selected_weights=sel["selected_weights"],
+                                         current_value=cv, past_tokens=context)
+    for loop in (2, 3):
+        layer.cached_mass_sparse_attention_delta(
+            loop, query=q, current_key=ck, current_value=cv, current_position=context, indices=sel["indices"],
+            valid=sel["valid"], source_selected_output=src, global_mass=sel["global_mass"], scaling=SCALING)
+    layer.append_decode_token([ck] * 4, [cv] * 4)
+    return time.perf_counter() - start
+
+
+def cpu_oracle_tokens_per_second(args, tasks_per_core: int = 1) -> dict:
+    """Time the oracle on every host core at once (one head-step task per core per round) and
+    scale to whole decode tokens: one token = HEADS heads x layers."""
+
+    import multiprocessing
+    from concurrent.futures import ProcessPoolExecutor
+
+    cores = min(os.cpu_count() or 1, 32)
+    tasks = cores * tasks_per_core
+    start = time.perf_counter()
+    # spawn, not fork: the parent may hold a CUDA context and OpenMP threads
+    with ProcessPoolExecutor(max_workers=cores, mp_context=multiprocessing.get_context("spawn")) as pool:
+        seconds = list(pool.map(_oracle_head_step, range(tasks), [args.context] * tasks, [args.bits] * tasks))
+    wall = time.perf_counter() - start
+    # all workers run at once: aggregate rate = workers / mean seconds per head-step
+    head_steps_per_s = cores / (sum(seconds) / len(seconds))
+    return {
+        "value": head_steps_per_s / (HEADS * args.layers),
+        "unit": "tok/s",
+        "cores": cores,
+        "kind": "port",
+        "sample": (f"{tasks} head-steps (1 sequence x 1 head x 1 layer each, context {args.context}) on {cores} "
+                   f"processes, mean {sum(seconds) / len(seconds):.2f} s per head-step (cache build excluded, "
+                   f"{wall:.1f} s wall with it), scaled by {HEADS} heads x {args.layers} layers per token"),
+    }
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rounds = max(1, min(args.steps, 4))
+    for _ in range(min(args.warmup, 1)):
+        cpu_oracle_tokens_per_second(args)
+    results = [cpu_oracle_tokens_per_second(args) for _ in range(rounds)]
+    best = max(results, key=lambda r: r["value"])
+    line = {
+        "impl": "reference", "metric": METRIC, "value": best["value"], "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / best["value"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args)}, "cpu_baseline": best,
+        "e2e": {"value": best["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------- the GPU leg
+
+
+def run_b200(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from flashloop_b200 import _native
+    from flashloop_b200.cache import CrossLoopKVLayer
+    from flashloop_b200.synthetic import make_loop_kv
+
+    _native.load()  # fail loudly when the CUDA library is missing
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    B, H, T, NL = args.batch, HEADS, args.context, args.layers
+    steps_total = args.warmup + args.steps
+    # ---- build the cache: NL layers, B sequences (seed distinct per rank / sequence / layer)
+    layers = []
+    ones = torch.ones(B, T, dtype=torch.bool, device=device)
+    for layer_index in range(NL):
+        keys = [[] for _ in range(4)]
+        values = [[] for _ in range(4)]
+        for b in range(B):
+            k, v = make_loop_kv(H, T, seed=(rank * 1000 + layer_index) * 100 + b, device=device)
+            for r in range(4):
+                keys[r].append(k[r])
+                values[r].append(v[r])
+        keys = [torch.cat(k) for k in keys]
+        values = [torch.cat(v) for v in values]
+        layers.append(CrossLoopKVLayer.from_prefill(keys, values, mask_loop3=ones, mask_loop4=ones,
+                                                    bits=args.bits, max_new_tokens=2 * steps_total + 64))
+        del keys, values
+    quant, tail = layers[0].quantized_tokens, layers[0].tail_tokens
+
+    # ---- per-step inputs: query / current K / current V of every (layer, loop), bf16
+    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    host_inputs = torch.randn((3, NL, 4, B, H, 1, HEAD_DIM), generator=gen).to(torch.bfloat16).pin_memory()
+    dev_inputs = host_inputs.to(device)
+    out = torch.empty((NL, 4, B, H, 1, HEAD_DIM), dtype=torch.float32, device=device)
+    host_out = torch.empty(out.shape, dtype=torch.float32).pin_memory()
+    launches = [0]
+    probe = []  # CUDA event pairs around the dominant kernel (dense reader, loop 2)
+
+    def step(inputs, timed_probe: bool) -> None:
+        q_all, k_all, v_all = inputs[0], inputs[1], inputs[2]
+        for li, layer in enumerate(layers):
+            q, k, v = q_all[li], k_all[li], v_all[li]
+            layer.dense_source_attention(0, query=q[0], current_key=k[0], current_value=v[0], scaling=SCALING,
+                                         return_logits=False, out=out[li, 0])
+            if timed_probe:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            _, logits = layer.dense_source_attention(1, query=q[1], current_key=k[1], current_value=v[1],
+                                                     scaling=SCALING, return_logits=True, out=out[li, 1])
+            if timed_probe:
+                e1.record()
+                probe.append((e0, e1))
+            sel = layer.select_decode_keys(logits, fraction=KEY_FRACTION)
+            src = layer.pv(1, sel.selected_weights, sel.indices, current_value=v[1], valid=sel.valid,
+                           validate_indices=False)
+            for loop in (2, 3):
+                layer.cached_mass_sparse_attention_delta(
+                    loop, query=q[loop], current_key=k[loop], current_value=v[loop], indices=sel.indices,
+                    valid=sel.valid, source_selected_output=src, global_mass=sel.global_mass, scaling=SCALING,
+                    out=out[li, loop])
+            layer.append_decode_token([k[r] for r in range(4)], [v[r] for r in range(4)])
+            launches[0] += 6
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, count: int) -> float:
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(count):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # ---- device-resident leg
+    for _ in range(args.warmup):
+        step(dev_inputs, False)
+    launches[0] = 0
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms_total = timed(lambda: step(dev_inputs, True), args.steps)
+    clocks = sampler.stop() if sampler else {}
+    timed_launches = launches[0]
+    probe_ms = [a.elapsed_time(b) for a, b in probe]
+    tokens = B * world * args.steps
+    value = tokens / (ms_total * 1e-3)
+
+    # ---- end-to-end leg: the same step through the public API with HOST buffers
+    def e2e_step():
+        dev = host_inputs.to(device, non_blocking=True)
+        step(dev, False)
+        host_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = max(2, min(args.steps, 16))
+    e2e_step()
+    e2e_ms = timed(e2e_step, e2e_steps)
+    e2e_value = B * world * e2e_steps / (e2e_ms * 1e-3)
+    status = max(layer.reader_status() for layer in layers)
+
+    if rank == 0:
+        peaks = {}
+        peaks_path = ROOT / "MEASURED_PEAKS.json"
+        if peaks_path.exists():
+            peaks = json.loads(peaks_path.read_text())
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        peak_kind = "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback 6650 GB/s"
+        bh = B * H
+        algo = dense_bytes(bh, 1, quant, tail, args.bits)
+        avg_ms = statistics.mean(probe_ms) if probe_ms else float("nan")
+        achieved = algo / (avg_ms * 1e-3) / 1e9
+        keys = math.ceil((T + 1) * KEY_FRACTION)
+        step_bytes = NL * (dense_bytes(bh, 0, quant, tail, args.bits) + algo
+                           + sparse_bytes(bh, 1, keys, quant, args.bits) - bh * 1280  # selected PV, loop 2
+                           + sparse_bytes(bh, 2, keys, quant, args.bits) + sparse_bytes(bh, 3, keys, quant, args.bits))
+        line = {
+            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16" if True else "", "data": "synthetic",
+            "config": {"workload": workload_name(args), "global_batch": B * world,
+                       "l2": "inputs larger than L2: each step streams ~%.1f GB of packed cache per GPU" %
+                             (step_bytes / 1e9),
+                       "parallelism": f"batch-sharded x{world}, no data-path collective"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": int(host_inputs.numel() * 2),
+                    "d2h_bytes_per_step": int(host_out.numel() * 4), "steps": e2e_steps},
+            "gpu_launches": timed_launches,
+            "roofline": {"bound": "hbm", "kernel": "dense_reader_kernel<4> (loop 2: anchor + delta-2 streams)",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "frac_of_nominal_8000": achieved / 8000.0, "peak_source": peak_kind,
+                         "algorithmic_bytes_per_launch": algo, "avg_launch_ms": avg_ms,
+                         "launches_timed": len(probe_ms), "traffic": None,
+                         "step_algorithmic_GBps": step_bytes / (ms_total / args.steps * 1e-3) / 1e9},
+            "reader_status": status,
+        }
+        line["dtype"] = "f16"  # codes are dequantised and multiplied in float16 pairs, accumulated in float32
+        if not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_oracle_tokens_per_second(args)
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -537,8 +537,9 @@ def test_full_size_properties(fl):
                                                           source_selected_output=zero, global_mass=one,
                                                           scaling=SCALING)
         assert float((dense - sparse).abs().max()) < 5e-3, float((dense - sparse).abs().max())
-    # (5) constant V rows: softmax weights sum to one, so the output is that row
-    const = torch.randn(1, heads, 1, 128, generator=g, device="cuda").to(torch.bfloat16)
+    # (5) V rows that are one constant per 64-channel group quantise exactly (span 0); softmax
+    # weights sum to one, so the output is that row
+    const = torch.randn(1, heads, 1, 2, generator=g, device="cuda").to(torch.bfloat16).repeat_interleave(64, dim=-1)
     flat = [const.expand(batch, heads, tokens, 128).contiguous() for _ in range(4)]
     layer2 = CrossLoopKVLayer.from_prefill(keys, flat, mask_loop3=ones, mask_loop4=ones)
     for loop in (0, 3):
