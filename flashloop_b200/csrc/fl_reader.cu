@@ -1336,3 +1336,4 @@ extern "C" int fl_selected_qk(const fl_layer* layer, int32_t loop, const void* q
   p.max_chunks = kMaxSplits;
   return launch_selected<kModeQK>(layer, p, static_cast<cudaStream_t>(stream), who);
 }
+

@@ -140,7 +140,9 @@ int fl_kivi_to_rows_v(const void* payload, const void* minimum, const void* scal
  * Readers.
  * ------------------------------------------------------------------------------------- */
 
-/* Bytes of scratch needed by the readers for `batch_heads` (b,h) pairs and contexts of at most
+/* The reference allocates its logits / probability scratch inside every call with torch::empty
+ * (flashloop/csrc/kivi_outer_gemv_cuda.cu:2016-2020); here the caller owns it.  Bytes of scratch
+ * needed by the readers for `batch_heads` (b,h) pairs and contexts of at most
  * `max_context_tokens`.  The workspace must be zero-filled once before its first use
  * (fl_workspace_init); the readers leave it ready for the next call.  Calls that share one
  * workspace must not overlap on the GPU. */

@@ -546,7 +546,9 @@ def test_full_size_properties(fl):
         out, _ = layer2.dense_source_attention(loop, query=q, current_key=ck,
                                                current_value=const.expand(batch, heads, 1, 128).contiguous(),
                                                scaling=SCALING, return_logits=False)
-        assert float((out - const.float()).abs().max()) < 2e-3
+        # a zero span is stored as scale 1, so the centred codes contribute -8 * p and the bias
+        # +8 * p in float16: the two cancel to within float16 rounding of 8, not of the value
+        assert float((out - const.float()).abs().max()) < 2e-2
     assert layer.reader_status() == 0 and layer2.reader_status() == 0
 
 
