@@ -52,6 +52,8 @@ SIGNATURES = {
     "fl_workspace_status": (C.c_int, [_vp, _i64, C.POINTER(_i32), _vp]),
     "fl_dense_source_attention": (C.c_int, [C.POINTER(FlLayer), _i32, _vp, _vp, _vp, _f32, _vp, _vp,
                                             _i64, _i64, _vp, _sz, _vp]),
+    "fl_dense_source_attention_static": (C.c_int, [C.POINTER(FlLayer), _i32, _vp, _vp, _vp, _f32, _vp, _vp,
+                                                   _i64, _i64, _vp]),
     "fl_sparse_attention_delta": (C.c_int, [C.POINTER(FlLayer), _i32, _vp, _vp, _vp, _vp, _vp, _i64,
                                             _vp, _vp, _f32, _vp, _vp, _vp, _sz, _vp]),
     "fl_selected_pv": (C.c_int, [C.POINTER(FlLayer), _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),

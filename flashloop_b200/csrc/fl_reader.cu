@@ -1337,3 +1337,129 @@ extern "C" int fl_selected_qk(const fl_layer* layer, int32_t loop, const void* q
   return launch_selected<kModeQK>(layer, p, static_cast<cudaStream_t>(stream), who);
 }
 
+// ------------------------------------------------------------------------------ scratch-free variant
+//
+// fl_dense_source_attention_static: the dense reader for callers that cannot hand over a
+// scratch buffer because they cannot allocate device memory at the point of the call -- code
+// running inside a stream capture, a plugin loaded into a server whose memory is owned by a
+// fixed pool it has no handle to, a host language binding without a device allocator.  The
+// scratch (tickets, status word, work queue, split partials) lives in the file-scope device
+// array below, which every GPU that loads this library holds until the process exits.
+
+namespace fl {
+namespace {
+
+constexpr int64_t kStaticMaxBatchHeads = 128;
+constexpr int64_t kStaticMaxContext = 16384;
+// partial slots per (b,h): one per 512-token chunk plus the tail item
+constexpr int kStaticSlots = static_cast<int>(kStaticMaxContext / (kGroup * kDenseWarps)) + 1;
+constexpr size_t kStaticHeaderBytes = ((kStaticMaxBatchHeads + 3) * sizeof(int) + 255) / 256 * 256;
+constexpr size_t kStaticBytes =
+    kStaticHeaderBytes + static_cast<size_t>(kStaticMaxBatchHeads) * kStaticSlots * kPartialStride * sizeof(float);
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_address[kMaxDevices] = {};
+
+// The array's name is only a host-side handle: the device address has to be asked for, once
+// per device, with that device current.  The header words are cleared here so that a first
+// call starts from zero whatever a previous, failed launch may have left behind.
+int static_scratch_address(void** address, cudaStream_t stream) {
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess || device < 0 || device >= kMaxDevices) {
+    set_error("fl_dense_source_attention_static: cannot identify the current device");
+    return FL_ERR_CUDA;
+  }
+  if (g_static_address[device] == nullptr) {
+    void* ptr = nullptr;
+    err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (err != cudaSuccess || ptr == nullptr) {
+      set_error("fl_dense_source_attention_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(err));
+      return FL_ERR_CUDA;
+    }
+    err = cudaMemsetAsync(ptr, 0, kStaticHeaderBytes, stream);
+    if (err != cudaSuccess) {
+      set_error("fl_dense_source_attention_static: clearing the scratch header failed: %s",
+                cudaGetErrorString(err));
+      return FL_ERR_CUDA;
+    }
+    g_static_address[device] = ptr;
+  }
+  *address = g_static_address[device];
+  return FL_OK;
+}
+
+}  // namespace
+}  // namespace fl
+
+extern "C" int fl_dense_source_attention_static(const fl_layer* layer, int32_t loop, const void* query,
+                                                const void* current_key, const void* current_value,
+                                                float scaling, float* output, float* logits,
+                                                int64_t logits_stride, int64_t max_context_tokens,
+                                                fl_cuda_stream stream) {
+  const char* who = "fl_dense_source_attention_static";
+  if (int rc = validate_layer(layer, loop, who)) return rc;
+  FL_REQUIRE(query && current_key && current_value && output, "%s: null vector", who);
+  FL_REQUIRE(aligned16(query) && aligned16(current_key) && aligned16(current_value),
+             "%s: vectors must be 16-byte aligned", who);
+  FL_REQUIRE(!logits || logits_stride > max_context_tokens, "%s: logits_stride must exceed max_context_tokens", who);
+  const int64_t bh = static_cast<int64_t>(layer->batch) * layer->heads;
+  if (bh > kStaticMaxBatchHeads || max_context_tokens < 0 || max_context_tokens > kStaticMaxContext) {
+    set_error("%s: batch*heads %lld (limit %lld) or max_context_tokens %lld (limit %lld) exceeds the built-in "
+              "scratch; use fl_dense_source_attention with a caller-provided workspace",
+              who, static_cast<long long>(bh), static_cast<long long>(kStaticMaxBatchHeads),
+              static_cast<long long>(max_context_tokens), static_cast<long long>(kStaticMaxContext));
+    return FL_ERR_UNSUPPORTED;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  void* scratch = nullptr;
+  if (int rc = static_scratch_address(&scratch, s)) return rc;
+
+  ReaderParams p{};
+  p.L = make_view(*layer);
+  p.loop = loop;
+  p.tickets = static_cast<int*>(scratch);
+  p.status = p.tickets + kStaticMaxBatchHeads;
+  p.queue = p.tickets + kStaticMaxBatchHeads + 1;
+  p.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + kStaticHeaderBytes);
+  p.max_chunks = kStaticSlots;
+  p.q = static_cast<const __nv_bfloat16*>(query);
+  p.kcur = static_cast<const __nv_bfloat16*>(current_key);
+  p.vcur = static_cast<const __nv_bfloat16*>(current_value);
+  p.scaling = scaling;
+  p.scaling_log2 = scaling * 1.4426950408889634f;
+  p.out = output;
+  p.logits = logits;
+  p.logits_stride = logits_stride;
+  p.chunk_tokens = kGroup * kDenseWarps;
+  p.grid_chunks = static_cast<int>((max_context_tokens + p.chunk_tokens - 1) / p.chunk_tokens) + 1;
+  int device = 0, sm_count = 0;
+  cudaGetDevice(&device);
+  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+  if (sm_count <= 0) sm_count = 148;
+  const int64_t items = bh * p.grid_chunks;
+  const unsigned grid = static_cast<unsigned>(items < 2 * sm_count ? items : 2 * sm_count);
+  if (layer->bits == 4) {
+    constexpr int kSmem = kDenseWarps * kStages * Stage<4>::kBytes;
+    const cudaError_t attr =
+        cudaFuncSetAttribute(dense_reader_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (attr != cudaSuccess) {
+      set_error("%s: %s", who, cudaGetErrorString(attr));
+      return FL_ERR_CUDA;
+    }
+    dense_reader_kernel<4><<<grid, kDenseThreads, kSmem, s>>>(p);
+  } else {
+    constexpr int kSmem = kDenseWarps * kStages * Stage<2>::kBytes;
+    const cudaError_t attr =
+        cudaFuncSetAttribute(dense_reader_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (attr != cudaSuccess) {
+      set_error("%s: %s", who, cudaGetErrorString(attr));
+      return FL_ERR_CUDA;
+    }
+    dense_reader_kernel<2><<<grid, kDenseThreads, kSmem, s>>>(p);
+  }
+  FL_CHECK_LAUNCH(who);
+  return FL_OK;
+}

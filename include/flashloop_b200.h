@@ -170,6 +170,23 @@ int fl_dense_source_attention(const fl_layer* layer, int32_t loop, const void* q
                               int64_t max_context_tokens, void* workspace, size_t workspace_bytes,
                               fl_cuda_stream stream);
 
+/* fl_dense_source_attention without a workspace argument.  It has no counterpart in the
+ * reference.  It is for callers that cannot allocate device memory where they call the reader:
+ * code inside a stream capture, a plugin inside a server whose device memory belongs to a
+ * fixed pool, a language binding with no device allocator at hand.  The scratch is a static
+ * device array of about 2.2 MB that every GPU loading this library keeps until exit; nothing
+ * is allocated or freed by the call.  Limits: batch*heads <= 128 and max_context_tokens <=
+ * 16384 (FL_ERR_UNSUPPORTED beyond them).  The first call on each device looks up the array's
+ * device address and clears its header, so make that call outside any stream capture.  All
+ * calls on a device share the array: calls that may overlap on the GPU (different streams)
+ * race and must be serialised by the caller.  Results are identical to
+ * fl_dense_source_attention. */
+int fl_dense_source_attention_static(const fl_layer* layer, int32_t loop, const void* query,
+                                     const void* current_key, const void* current_value,
+                                     float scaling, float* output, float* logits,
+                                     int64_t logits_stride, int64_t max_context_tokens,
+                                     fl_cuda_stream stream);
+
 /* CrossLoopKVLayer.cached_mass_sparse_attention_delta (flashloop/cache.py:1517-1642) ->
  * sparse_attention_delta_cuda (kivi_outer_gemv_cuda.cu:1711-1912, kernels :1015, :813, :1146)
  * as ONE launch: over the valid selected logical indices (prefix rows through the rank maps,
