@@ -58,6 +58,7 @@ SIGNATURES = {
                                             _vp, _vp, _f32, _vp, _vp, _vp, _sz, _vp]),
     "fl_selected_pv": (C.c_int, [C.POINTER(FlLayer), _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
     "fl_selected_qk": (C.c_int, [C.POINTER(FlLayer), _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp]),
+    "fl_append_decode_token": (C.c_int, [C.POINTER(FlLayer), C.POINTER(_vp), C.POINTER(_vp), _vp]),
     "fl_select_decode_keys": (C.c_int, [_vp, _i64, _i32, _i32, _i32, _vp, _f64, _i32, _vp, _vp, _i64,
                                         _vp, _vp, _vp, _vp]),
 }

@@ -139,9 +139,9 @@ class CrossLoopKVLayer:
         self._tail_active = torch.zeros((2, self.batch, TAIL_CAPACITY), dtype=torch.uint8, device=dev)
         self._state_host = torch.zeros((self.batch, _native.FL_STATE_WORDS), dtype=torch.int32)
         self._seq_state = torch.zeros((self.batch, _native.FL_STATE_WORDS), dtype=torch.int32, device=dev)
-        # logical positions held by the compact streams, per sequence (host lists of tensors)
-        self._override_positions = [[torch.empty(0, dtype=torch.int32, device=dev) for _ in range(2)]
-                                    for _ in range(self.batch)]
+        # host mirrors: rows held by the compact streams and the tail's retention flags
+        self._compact_counts = [[0, 0] for _ in range(self.batch)]
+        self._tail_active_host: list[list[list[bool]]] = [[[], []] for _ in range(self.batch)]
         self._native = self._make_native()
 
     # ------------------------------------------------------------------ native descriptor
@@ -302,7 +302,7 @@ class CrossLoopKVLayer:
                     raise ValueError("rank maps must cover the packed prefix")
                 if rank.numel():
                     layer._rank[i][base:base + quant] = rank
-                    layer._override_positions[b][i] = torch.nonzero(rank >= 0, as_tuple=False).flatten().to(torch.int32)
+                    layer._compact_counts[b][i] = int((rank >= 0).sum().item())
             st = layer._state_host[b]
             st[_native.STATE_QUANT_TOKENS] = quant
             st[_native.STATE_ROWS2] = _round_up(counts[2], GROUP)
@@ -326,6 +326,7 @@ class CrossLoopKVLayer:
                 bool((self._state_host[:, _native.STATE_TAIL_START] != 0).any()):
             self._state_host[:, _native.STATE_TAIL_LEN] = tail
             self._state_host[:, _native.STATE_TAIL_START] = 0
+            self._tail_active_host = [[[False] * tail, [False] * tail] for _ in range(self.batch)]
             self._push_state()
 
     def _encode_block(self, keys, values, mask3, mask4):
@@ -376,7 +377,7 @@ class CrossLoopKVLayer:
                     self._store_stream(s, b, 0, sk[s], sv[s])
             base = self._rank_base_host[b]
             for i in range(2):
-                self._override_positions[b][i] = positions[i]
+                self._compact_counts[b][i] = int(positions[i].numel())
                 self._rank[i][base:base + packed] = _rank_map(packed, positions[i], self._device)
                 rows[i] = _round_up(int(positions[i].numel()), GROUP)
         st[_native.STATE_ROWS2], st[_native.STATE_ROWS3] = rows
@@ -391,6 +392,7 @@ class CrossLoopKVLayer:
             self._tail_v[r, sl, :tail].copy_(values[r][0, :, packed:])
         self._tail_active[0, b, :tail].copy_(mask3[packed:].to(torch.uint8))
         self._tail_active[1, b, :tail].copy_(mask4[packed:].to(torch.uint8))
+        self._tail_active_host[b] = [mask3[packed:].tolist(), mask4[packed:].tolist()]
 
     # ------------------------------------------------------------------ bookkeeping
 
@@ -417,7 +419,8 @@ class CrossLoopKVLayer:
 
     @property
     def max_context_tokens(self) -> int:
-        return max(self.token_counts())
+        st = self._state_host
+        return int((st[:, _native.STATE_QUANT_TOKENS] + st[:, _native.STATE_TAIL_LEN]).max())
 
     @property
     def storage_bytes(self) -> int:
@@ -427,7 +430,7 @@ class CrossLoopKVLayer:
         total = 0
         for b in range(self.batch):
             q = self.quantized_tokens_of(b)
-            n = [q, q, int(self._override_positions[b][0].numel()), int(self._override_positions[b][1].numel())]
+            n = [q, q, self._compact_counts[b][0], self._compact_counts[b][1]]
             for s in range(4):
                 groups = -(-n[s] // GROUP)
                 total += self.heads * (2 * n[s] * row_bytes + 2 * groups * HEAD_DIM * 2 + n[s] * 8)
@@ -534,7 +537,7 @@ class CrossLoopKVLayer:
             if logits_out is not None:
                 logits = logits_out
                 stride = int(logits.shape[-1])
-            elif len(set(self.token_counts())) == 1:
+            elif self.batch == 1 or len(set(self.token_counts())) == 1:
                 logits = torch.empty((self.batch, self.heads, 1, stride), dtype=torch.float32, device=self._device)
             else:
                 logits = torch.full((self.batch, self.heads, 1, stride), float("-inf"),
@@ -666,59 +669,47 @@ class CrossLoopKVLayer:
     def append_decode_token(self, keys: Sequence[torch.Tensor], values: Sequence[torch.Tensor]) -> None:
         """Append the four loops' K/V of one decoded token per sequence to the BF16 tail
         and roll the oldest 64 tail tokens into the packed streams when the tail reaches
-        128 (flashloop/cache.py:1758-1838)."""
+        128 (flashloop/cache.py:1758-1838).  Three launches of ``fl_append_decode_token``,
+        no host synchronisation: the device advances ``seq_state`` itself and the host
+        mirror below follows by the same arithmetic."""
 
         shape = _validate_loop_tensors(keys, values)
         if shape != (self.batch, self.heads, 1, HEAD_DIM):
             raise ValueError("decode K/V shape does not match the cache")
-        bh = self.batch * self.heads
-        slots = torch.empty(self.batch, dtype=torch.long)
+        if keys[0].dtype != torch.bfloat16:
+            raise ValueError("decode K/V must be bfloat16")
+        _native.require_cuda(*keys, *values)
+        full = self.residual_length + self.group_size
         for b in range(self.batch):
             st = self._state_host[b]
-            slots[b] = (int(st[_native.STATE_TAIL_START]) + int(st[_native.STATE_TAIL_LEN])) % TAIL_CAPACITY
-        slot_bh = slots.repeat_interleave(self.heads).to(self._device)
-        rows = torch.arange(bh, device=self._device)
-        for r in range(4):
-            self._tail_k[r, rows, slot_bh] = keys[r].reshape(bh, HEAD_DIM)
-            self._tail_v[r, rows, slot_bh] = values[r].reshape(bh, HEAD_DIM)
-        seq = torch.arange(self.batch, device=self._device)
-        self._tail_active[:, seq, slots.to(self._device)] = 1
+            if int(st[_native.STATE_TAIL_LEN]) + 1 >= full:
+                room = (int(st[_native.STATE_QUANT_TOKENS]) + GROUP <= self._caps[0][b]
+                        and int(st[_native.STATE_ROWS2]) + GROUP <= self._caps[2][b]
+                        and int(st[_native.STATE_ROWS3]) + GROUP <= self._caps[3][b])
+                if not room:
+                    raise RuntimeError("the preallocated cache is full; raise max_new_tokens")
+        ks = [k.contiguous() for k in keys]
+        vs = [v.contiguous() for v in values]
+        key_table = (C.c_void_p * 4)(*[k.data_ptr() for k in ks])
+        value_table = (C.c_void_p * 4)(*[v.data_ptr() for v in vs])
+        _native.check(_native.load().fl_append_decode_token(
+            C.byref(self._native), key_table, value_table, _native.current_stream(self._device)),
+            "fl_append_decode_token")
         for b in range(self.batch):
-            self._state_host[b, _native.STATE_TAIL_LEN] += 1
-            while int(self._state_host[b, _native.STATE_TAIL_LEN]) >= self.residual_length + self.group_size:
-                self._roll_one_group(b)
-        self._push_state()
-
-    def _roll_one_group(self, b: int) -> None:
-        st = self._state_host[b]
-        start = int(st[_native.STATE_TAIL_START])
-        quant = int(st[_native.STATE_QUANT_TOKENS])
-        slots = (start + torch.arange(GROUP, device=self._device)) % TAIL_CAPACITY
-        sl = slice(b * self.heads, (b + 1) * self.heads)
-        keys = [self._tail_k[r, sl].index_select(1, slots).unsqueeze(0) for r in range(4)]
-        values = [self._tail_v[r, sl].index_select(1, slots).unsqueeze(0) for r in range(4)]
-        mask3 = self._tail_active[0, b].index_select(0, slots).bool()
-        mask4 = self._tail_active[1, b].index_select(0, slots).bool()
-        sk, sv, positions = self._encode_block(keys, values, mask3, mask4)
-        row0 = [quant, quant, int(st[_native.STATE_ROWS2]), int(st[_native.STATE_ROWS3])]
-        if quant + GROUP > self._caps[0][b]:
-            raise RuntimeError("the preallocated cache is full; raise max_new_tokens")
-        for s in range(4):
-            if sk[s] is not None:
-                self._store_stream(s, b, row0[s], sk[s], sv[s])
-        base = self._rank_base_host[b]
-        for i in range(2):
-            rank = _rank_map(GROUP, positions[i], self._device)
-            rank = torch.where(rank >= 0, rank + row0[2 + i], rank)
-            self._rank[i][base + quant:base + quant + GROUP] = rank
-            self._override_positions[b][i] = torch.cat(
-                [self._override_positions[b][i], positions[i] + quant]).to(torch.int32)
-        self._tail_active[:, b, slots] = 0
-        st[_native.STATE_QUANT_TOKENS] = quant + GROUP
-        st[_native.STATE_ROWS2] = row0[2] + GROUP
-        st[_native.STATE_ROWS3] = row0[3] + GROUP
-        st[_native.STATE_TAIL_LEN] -= GROUP
-        st[_native.STATE_TAIL_START] = (start + GROUP) % TAIL_CAPACITY
+            st = self._state_host[b]
+            for i in range(2):
+                self._tail_active_host[b][i].append(True)
+            st[_native.STATE_TAIL_LEN] += 1
+            if int(st[_native.STATE_TAIL_LEN]) >= full:
+                for i in range(2):
+                    flags = self._tail_active_host[b][i]
+                    self._compact_counts[b][i] += sum(flags[:GROUP])
+                    del flags[:GROUP]
+                st[_native.STATE_QUANT_TOKENS] += GROUP
+                st[_native.STATE_ROWS2] += GROUP
+                st[_native.STATE_ROWS3] += GROUP
+                st[_native.STATE_TAIL_LEN] -= GROUP
+                st[_native.STATE_TAIL_START] = (int(st[_native.STATE_TAIL_START]) + GROUP) % TAIL_CAPACITY
 
 
 class CrossLoopKVCache:

@@ -499,6 +499,8 @@ __device__ __forceinline__ Span block_span(const LayerView& L, int s, int b, int
 struct ItemDesc {
   int id;  // -1: the queue is empty
   int bh, b, chunk, nchunks, quant, tail_len, tail_start, blk_begin, blk_end;
+  int64_t row_base[4];    // first row / first K metadata group of this (b,h) in every stream
+  int64_t group_base[4];
 };
 
 // Take the next valid item from the global queue (one thread per CTA calls this).
@@ -529,6 +531,10 @@ __device__ __forceinline__ void draw_item(const ReaderParams& p, ItemDesc* d) {
     d->blk_begin = chunk * (p.chunk_tokens / kGroup);
     d->blk_end = chunk == nq_chunks ? d->blk_begin
                                     : min(d->blk_begin + p.chunk_tokens / kGroup, quant / kGroup);
+    for (int s = 0; s <= p.loop; ++s) {
+      d->row_base[s] = L.row_base[s][bh];
+      d->group_base[s] = L.group_base[s][bh];
+    }
     d->id = id;
     return;
   }
@@ -588,8 +594,12 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   bool timed_out = false;
 
   for (int k = 0;; ++k) {
-    const ItemDesc cur = s_item[k % 3];
-    if (cur.id < 0) break;
+    const ItemDesc* curp = &s_item[k % 3];
+    if (curp->id < 0) break;
+    struct {
+      int bh, b, chunk, nchunks, quant, tail_len, tail_start, blk_begin, blk_end;
+    } cur = {curp->bh, curp->b, curp->chunk, curp->nchunks, curp->quant, curp->tail_len,
+             curp->tail_start, curp->blk_begin, curp->blk_end};
     // Look ahead: thread 0 draws item k+2; the upper half of the CTA fetches the query of item
     // k+1.  Both become visible to the other warps at this item's merge barrier.
     if (tid == 0) draw_item(p, &s_item[(k + 2) % 3]);
@@ -630,7 +640,6 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
               iss_j = 0;
               continue;
             }
-            const int64_t ibh = it->bh;
             const int iblk = it->blk_begin + warp + iss_blk * kDenseWarps;
             const bool iv = iss_j >= streams;
             const int is = iv ? iss_j - streams : iss_j;
@@ -642,11 +651,11 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
               if (sp.m == 0) {
                 mbar_arrive(bar);
               } else {
-                const int64_t row = L.row_base[is][ibh] + sp.r0;
+                const int64_t row = it->row_base[is] + sp.r0;
                 const uint32_t code_bytes = static_cast<uint32_t>(sp.m) * kRowBytes;
                 if (!iv) {
                   const int g0 = sp.r0 >> 6, g1 = (sp.r0 + sp.m - 1) >> 6;
-                  const int64_t grp = L.group_base[is][ibh] + g0;
+                  const int64_t grp = it->group_base[is] + g0;
                   const uint32_t ng = g1 - g0 + 1;
                   mbar_arrive_expect_tx(bar, code_bytes + ng * 512u);
                   bulk_copy_g2s(dst, L.k_codes[is] + row * kRowBytes, code_bytes, bar);
@@ -728,9 +737,10 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   #pragma unroll
             for (int it = 0; it < 8; ++it) lg[it] += k_dot_fast<BITS>(c[it], mult) + kbias0;
           } else if (sp.m > 0) {
-  #pragma unroll
+  #pragma unroll 1
             for (int it = 0; it < 8; ++it) {
               const int r = rank[it * 8 + quad];
+              const float add = 0.f;
               if (r >= 0) {
                 const int gi = (r >> 6) - g0;
                 __half2 mult[16];
@@ -743,7 +753,9 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
                 }
                 const Codes<BITS> c =
                     load_codes_shared<BITS>(stage + (r - sp.r0) * kRowBytes + sub * kLaneBytes);
-                lg[it] += k_dot_fast<BITS>(c, mult) + (gi == 0 ? kbias0 : kbias1);
+                const float dot = k_dot_fast<BITS>(c, mult) + (gi == 0 ? kbias0 : kbias1);
+  #pragma unroll
+                for (int k = 0; k < 8; ++k) lg[k] += (k == it) ? dot : add;
               }
             }
           }
@@ -767,7 +779,7 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
             for (int i = 0; i < 16; ++i) hacc[i] = __floats2half2_rn(0.f, 0.f);
           }
         } else {
-          const int64_t row = L.row_base[s][bh] + sp.r0;
+          const int64_t row = curp->row_base[s] + sp.r0;
           const uint8_t* meta = stage + St::kCodes + static_cast<int>(row & 1) * 8;
           // my channel group's minimum / scale, duplicated into both halves
           const uint32_t pick = (sub < 2) ? 0x1010u : 0x3232u;
@@ -794,16 +806,19 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
               }
             }
           } else if (sp.m > 0) {
-  #pragma unroll
+  #pragma unroll 1
             for (int it = 0; it < 8; ++it) {
               const int r = rank[it * 8 + quad];
               if (r >= 0) {
                 const int ri = r - sp.r0;
+                float pr = 0.f;
+  #pragma unroll
+                for (int k = 0; k < 8; ++k) pr = (k == it) ? lg[k] : pr;
                 const Codes<BITS> c = load_codes_shared<BITS>(stage + ri * kRowBytes + sub * kLaneBytes);
                 const uint2 mt = *reinterpret_cast<const uint2*>(meta + ri * 8);
                 const __half2 vm2 = as_half2(__byte_perm(mt.x, 0u, pick));
                 const __half2 vs2 = as_half2(__byte_perm(mt.y, 0u, pick));
-                const __half2 p2 = __float2half2_rn(lg[it]);
+                const __half2 p2 = __float2half2_rn(pr);
                 hbias = __hfma2(p2, __hfma2(centre2, vs2, vm2), hbias);
                 v_accumulate<BITS>(c, __hmul2(p2, vs2), hacc);
               }
@@ -1080,7 +1095,7 @@ int choose_chunk_tokens(int64_t batch_heads, int64_t max_context_tokens) {
   // that gives every CTA more than ~32 items, then two or four blocks per warp.
   const int64_t ctas = 148 * 2;
   int chunk = kGroup * kDenseWarps;
-  while (chunk < 2048 && batch_heads * ((max_context_tokens + chunk - 1) / chunk) > 32 * ctas) chunk *= 2;
+  while (chunk < 2048 && batch_heads * ((max_context_tokens + chunk - 1) / chunk) > 6 * ctas) chunk *= 2;
   if (const char* env = getenv("FL_CHUNK")) chunk = atoi(env);
   return chunk;
 }

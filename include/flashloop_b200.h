@@ -221,6 +221,22 @@ int fl_selected_qk(const fl_layer* layer, int32_t loop, const void* query, const
                    fl_cuda_stream stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Append.
+ * ------------------------------------------------------------------------------------- */
+
+/* CrossLoopKVLayer.append_decode_token + _roll_one_group (flashloop/cache.py:1758-1838) and the
+ * block re-encode they trigger (from_prefill / _encode_initial_prefix, cache.py:752-817,
+ * 1008-1074), for every sequence at once and with no host round trip: the four loops' K and V
+ * rows of one decoded token per sequence (keys[r], values[r]: bfloat16 [batch*heads][128],
+ * r = 0..3; the two tables are host arrays of device pointers) go into the BF16 tail rings;
+ * every sequence whose tail thereby reaches 128 tokens has its oldest 64 tail tokens turned into
+ * one new 64-row block of all eight streams (anchor, delta-2, delta-3/4 of the retained rows,
+ * bfloat16 residual arithmetic and codes bit-exact with the reference), its rank maps extended
+ * and its seq_state advanced.  The caller guarantees room for the new block in every stream. */
+int fl_append_decode_token(const fl_layer* layer, const void* const* keys, const void* const* values,
+                           fl_cuda_stream stream);
+
+/* ---------------------------------------------------------------------------------------
  * Selection.
  * ------------------------------------------------------------------------------------- */
 
