@@ -142,6 +142,7 @@ class CrossLoopKVLayer:
         # host mirrors: rows held by the compact streams and the tail's retention flags
         self._compact_counts = [[0, 0] for _ in range(self.batch)]
         self._tail_active_host: list[list[list[bool]]] = [[[], []] for _ in range(self.batch)]
+        self.context_bound: int | None = None
         self._native = self._make_native()
 
     # ------------------------------------------------------------------ native descriptor
@@ -419,6 +420,12 @@ class CrossLoopKVLayer:
 
     @property
     def max_context_tokens(self) -> int:
+        """Longest context of the batch, or ``context_bound`` when one is set.  Launch
+        geometry and buffer sizes derive from this number only, so a decode step recorded
+        in a CUDA graph with a bound stays valid while contexts grow up to it."""
+
+        if self.context_bound is not None:
+            return self.context_bound
         st = self._state_host
         return int((st[:, _native.STATE_QUANT_TOKENS] + st[:, _native.STATE_TAIL_LEN]).max())
 
@@ -695,6 +702,14 @@ class CrossLoopKVLayer:
         _native.check(_native.load().fl_append_decode_token(
             C.byref(self._native), key_table, value_table, _native.current_stream(self._device)),
             "fl_append_decode_token")
+        self.advance_host_state()
+
+    def advance_host_state(self) -> None:
+        """Host mirror of what one ``fl_append_decode_token`` does to ``seq_state``.  Called
+        by :meth:`append_decode_token`; a caller that replays a captured decode step calls
+        it once per replay."""
+
+        full = self.residual_length + self.group_size
         for b in range(self.batch):
             st = self._state_host[b]
             for i in range(2):
