@@ -934,7 +934,7 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
 enum { kModeDelta = 0, kModePV = 1, kModeQK = 2 };
 
 template <int BITS, int MODE>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)
 selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   constexpr int kRowBytes = 16 * BITS;
   __shared__ __align__(16) float s_qf[kHeadDim];
@@ -980,99 +980,147 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   const __nv_bfloat16* tk = L.tail_k[p.loop] + bh * L.tail_capacity * kHeadDim;
   const __nv_bfloat16* tv = L.tail_v[p.loop] + bh * L.tail_capacity * kHeadDim;
 
-  for (int j0 = slot_begin + warp * 8; j0 < slot_end; j0 += kWarps * 8) {
-    const int j = j0 + quad;
-    const bool in_range = j < slot_end;
-    int idx = -1;
-    if (in_range && (!valid_row || valid_row[j])) idx = idx_row[j];
-    // kind: 0 nothing, 1 packed prefix, 2 tail, 3 current token
-    int kind = 0;
-    const __nv_bfloat16* krow = nullptr;
-    const __nv_bfloat16* vrow = nullptr;
-    if (idx >= 0) {
-      if (idx == cur_pos) {
-        if constexpr (MODE == kModePV) {
-          kind = p.vcur ? 3 : 0;
-        } else {
-          kind = p.kcur ? 3 : 0;
-        }
-        krow = p.kcur ? p.kcur + bh * kHeadDim : nullptr;
-        vrow = p.vcur ? p.vcur + bh * kHeadDim : nullptr;
-      } else if (idx >= quant) {
-        if (idx - quant < tail_len) {
-          kind = 2;
-          const int slot = (tail_start + idx - quant) % L.tail_capacity;
-          krow = tk + slot * kHeadDim;
-          vrow = tv + slot * kHeadDim;
-        }
-      } else {
-        kind = 1;
-      }
-    }
-    int rows[4];
+  // Slots are staged through shared memory in batches: index, validity and the two rank-map
+  // lookups of every slot are fetched by the whole CTA at once, so the gather loop below has a
+  // single level of dependent loads (the rows themselves).
+  constexpr int kSlotBatch = 256;
+  __shared__ int s_idx[kSlotBatch];      // logical index, or -1
+  __shared__ int s_row[2][kSlotBatch];   // rows in streams 2 and 3, or -1
+  __shared__ int64_t s_base[2][4];       // row_base / group_base of this (b,h)
+  if (threadIdx.x < 8) {
+    const int s4 = threadIdx.x & 3;
+    s_base[threadIdx.x >> 2][s4] = s4 <= p.loop ? ((threadIdx.x >> 2) ? L.group_base[s4][bh] : L.row_base[s4][bh]) : 0;
+  }
+  __half2 hacc[16];
 #pragma unroll
-    for (int s = 0; s < 4; ++s) {
-      rows[s] = -1;
-      if (kind == 1 && s <= p.loop) {
-        rows[s] = s < 2 ? idx : L.rank[s - 2][L.rank_base[b] + idx];
-      }
-    }
+  for (int i = 0; i < 16; ++i) hacc[i] = __floats2half2_rn(0.f, 0.f);
 
-    float pr = 0.f;
-    if constexpr (MODE != kModePV) {
-      float dot = 0.f;
-      if (kind == 1) {
-#pragma unroll
-        for (int s = 0; s < 4; ++s) {
-          if (rows[s] >= 0) {
-            const int64_t row = L.row_base[s][bh] + rows[s];
-            const int64_t g = L.group_base[s][bh] + (rows[s] >> 6);
-            const Codes<BITS> c = load_codes<BITS>(L.k_codes[s] + row * kRowBytes, sub);
-            dot += k_dot_meta<BITS>(c, L.k_scale[s] + g * kHeadDim + sub * 32,
-                                    L.k_min[s] + g * kHeadDim + sub * 32, q2);
+  for (int batch_begin = slot_begin; batch_begin < slot_end; batch_begin += kSlotBatch) {
+    const int batch_n = min(kSlotBatch, slot_end - batch_begin);
+    __syncthreads();
+    for (int t = threadIdx.x; t < batch_n; t += kThreads) {
+      const int j = batch_begin + t;
+      int idx = -1;
+      if (!valid_row || valid_row[j]) idx = idx_row[j];
+      int r2 = -1, r3 = -1;
+      if (idx >= 0 && idx < quant) {
+        if (p.loop >= 2) r2 = L.rank[0][L.rank_base[b] + idx];
+        if (p.loop >= 3) r3 = L.rank[1][L.rank_base[b] + idx];
+      }
+      s_idx[t] = idx;
+      s_row[0][t] = r2;
+      s_row[1][t] = r3;
+    }
+    __syncthreads();
+
+    for (int t0 = warp * 8; t0 < batch_n; t0 += kWarps * 8) {
+      const int t = t0 + quad;
+      const bool in_range = t < batch_n;
+      const int j = batch_begin + t;
+      const int idx = in_range ? s_idx[t] : -1;
+      // kind: 0 nothing, 1 packed prefix, 2 tail, 3 current token
+      int kind = 0;
+      const __nv_bfloat16* krow = nullptr;
+      const __nv_bfloat16* vrow = nullptr;
+      if (idx >= 0) {
+        if (idx == cur_pos) {
+          if constexpr (MODE == kModePV) {
+            kind = p.vcur ? 3 : 0;
+          } else {
+            kind = p.kcur ? 3 : 0;
           }
+          krow = p.kcur ? p.kcur + bh * kHeadDim : nullptr;
+          vrow = p.vcur ? p.vcur + bh * kHeadDim : nullptr;
+        } else if (idx >= quant) {
+          if (idx - quant < tail_len) {
+            kind = 2;
+            const int slot = (tail_start + idx - quant) % L.tail_capacity;
+            krow = tk + slot * kHeadDim;
+            vrow = tv + slot * kHeadDim;
+          }
+        } else {
+          kind = 1;
         }
-      } else if (kind >= 2) {
-        dot = bf16_row_dot<BITS>(krow, sub, s_qf);
       }
-      dot = quad_sum(dot);
-      if constexpr (MODE == kModeQK) {
-        if (in_range && sub == 0) p.logits[bh * p.capacity + j] = kind ? dot : 0.f;
-        continue;
-      }
-      if (kind == 3 && p.cur_logits && sub == 0) p.cur_logits[bh] = dot * p.scaling;
-      const float x = kind ? dot * p.scaling_log2 : -INFINITY;
-      const float mx = across_quads_max(x);
-      if (mx > -INFINITY) state_raise(S, mx);
-      pr = kind ? exp2f(x - S.m) : 0.f;
-      S.l += pr;
-    } else {
-      pr = kind ? p.weights[bh * p.capacity + j] : 0.f;
-    }
+      int rows[4];
+      rows[0] = (kind == 1) ? idx : -1;
+      rows[1] = (kind == 1 && p.loop >= 1) ? idx : -1;
+      rows[2] = (kind == 1) ? s_row[0][in_range ? t : 0] : -1;
+      rows[3] = (kind == 1) ? s_row[1][in_range ? t : 0] : -1;
 
-    if (kind == 1) {
-      __half2 hacc[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) hacc[i] = __floats2half2_rn(0.f, 0.f);
+      // ---- issue every row load of this token before using any of them
+      Codes<BITS> kc[4], vc[4];
+      uint2 vmeta[4];
 #pragma unroll
       for (int s = 0; s < 4; ++s) {
         if (rows[s] >= 0) {
-          const int64_t row = L.row_base[s][bh] + rows[s];
-          const Codes<BITS> c = load_codes<BITS>(L.v_codes[s] + row * kRowBytes, sub);
-          const uint2 mt = ldg64(L.v_meta[s] + row * 4);
-          const __half2 mins = as_half2(mt.x), scales = as_half2(mt.y);
-          const float vs = (sub < 2) ? __low2float(scales) : __high2float(scales);
-          const float vm = (sub < 2) ? __low2float(mins) : __high2float(mins);
-          S.vbias = fmaf(pr, fmaf(float(kCentre<BITS>), vs, vm), S.vbias);
-          const __half wh = __float2half_rn(pr * vs);
-          v_accumulate<BITS>(c, __halves2half2(wh, wh), hacc);
+          const int64_t row = s_base[0][s] + rows[s];
+          if constexpr (MODE != kModePV) kc[s] = load_codes<BITS>(L.k_codes[s] + row * kRowBytes, sub);
+          if constexpr (MODE != kModeQK) {
+            vc[s] = load_codes<BITS>(L.v_codes[s] + row * kRowBytes, sub);
+            vmeta[s] = ldg64(L.v_meta[s] + row * 4);
+          }
         }
       }
-      flush_pairs(hacc, S.acc);
-    } else if (kind >= 2) {
-      bf16_row_accumulate<BITS>(vrow, sub, pr, S.acc);
+
+      float pr = 0.f;
+      if constexpr (MODE != kModePV) {
+        float dot = 0.f;
+        if (kind == 1) {
+#pragma unroll
+          for (int s = 0; s < 4; ++s) {
+            if (rows[s] >= 0) {
+              const int64_t g = s_base[1][s] + (rows[s] >> 6);
+              dot += k_dot_meta<BITS>(kc[s], L.k_scale[s] + g * kHeadDim + sub * 32,
+                                      L.k_min[s] + g * kHeadDim + sub * 32, q2);
+            }
+          }
+        } else if (kind >= 2) {
+          dot = bf16_row_dot<BITS>(krow, sub, s_qf);
+        }
+        dot = quad_sum(dot);
+        if constexpr (MODE == kModeQK) {
+          if (in_range && sub == 0) p.logits[bh * p.capacity + j] = kind ? dot : 0.f;
+          continue;
+        }
+        if (kind == 3 && p.cur_logits && sub == 0) p.cur_logits[bh] = dot * p.scaling;
+        const float x = kind ? dot * p.scaling_log2 : -INFINITY;
+        const float mx = across_quads_max(x);
+        if (mx > S.m) {
+          flush_pairs(hacc, S.acc);  // the float16 partial sums belong to the old maximum
+          state_raise(S, mx);
+        }
+        pr = kind ? exp2f(x - S.m) : 0.f;
+        S.l += pr;
+      } else {
+        pr = kind ? p.weights[bh * p.capacity + j] : 0.f;
+      }
+
+      if constexpr (MODE != kModeQK) {
+        if (kind == 1) {
+          const uint32_t pick = (sub < 2) ? 0x1010u : 0x3232u;
+          const __half2 centre2 = __floats2half2_rn(float(kCentre<BITS>), float(kCentre<BITS>));
+          const __half2 p2 = __float2half2_rn(pr);
+          __half2 hb = __floats2half2_rn(0.f, 0.f);
+#pragma unroll
+          for (int s = 0; s < 4; ++s) {
+            if (rows[s] >= 0) {
+              const __half2 vm2 = as_half2(__byte_perm(vmeta[s].x, 0u, pick));
+              const __half2 vs2 = as_half2(__byte_perm(vmeta[s].y, 0u, pick));
+              hb = __hfma2(centre2, vs2, __hadd2(vm2, hb));
+              v_accumulate<BITS>(vc[s], __hmul2(p2, vs2), hacc);
+            }
+          }
+          S.vbias = fmaf(pr, __low2float(hb), S.vbias);
+        } else if (kind >= 2) {
+          bf16_row_accumulate<BITS>(vrow, sub, pr, S.acc);
+        }
+      }
+      // at most 4 streams x 4 steps = 16 float16 terms per accumulator before widening
+      if (((t0 / (kWarps * 8)) & 3) == 3) flush_pairs(hacc, S.acc);
     }
   }
+  flush_pairs(hacc, S.acc);
   if constexpr (MODE == kModeQK) return;
 
   state_store<BITS>(S, lane, s_merge[warp]);

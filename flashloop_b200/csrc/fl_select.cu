@@ -11,12 +11,16 @@
 namespace fl {
 namespace {
 
-constexpr int kSelThreads = 512;
+constexpr int kSelThreads = 1024;
 constexpr int kSelWarps = kSelThreads / 32;
+constexpr int kSelMaxSharedKeys = 50 * 1024;  // keys held in shared memory (200 KiB)
 
 __device__ __forceinline__ uint32_t sortable(float v) {
   const uint32_t b = __float_as_uint(v);
   return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float unsortable(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
 }
 
 __device__ __forceinline__ float block_reduce(float v, float* s_red, bool is_max) {
@@ -45,13 +49,16 @@ struct SelectParams {
   float* weights;
 };
 
+// SHARED: the keys of this (b,h) are staged once in shared memory (n <= kSelMaxSharedKeys);
+// otherwise every pass re-reads the values from global memory (L2).
+template <bool SHARED>
 __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams p) {
+  extern __shared__ uint32_t s_keys[];
   __shared__ int s_hist[256];
   __shared__ float s_red[kSelWarps];
   __shared__ int s_wgt[kSelWarps], s_weq[kSelWarps];
   __shared__ uint32_t s_prefix;
   __shared__ int s_need;
-  __shared__ int s_base_gt, s_base_eq;
 
   const int64_t bh = blockIdx.x;
   const int b = static_cast<int>(bh / p.heads);
@@ -65,107 +72,155 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
   uint8_t* out_valid = p.valid ? p.valid + bh * p.capacity : nullptr;
   float* out_w = p.weights ? p.weights + bh * p.capacity : nullptr;
   const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  auto key_at = [&](int i) -> uint32_t { return SHARED ? s_keys[i] : sortable(v[i]); };
 
   // budget = min(n, max(1, ceil(n * fraction))) in double, as Python computes it
   int budget = static_cast<int>(ceil(static_cast<double>(n) * p.fraction));
   budget = min(n, max(1, budget));
   if (budget > p.capacity) budget = static_cast<int>(p.capacity);  // guarded on the host
 
-  // softmax statistics when the inputs are logits
+  // stage the keys; softmax statistics when the inputs are logits
   float vmax = 0.f, inv_z = 1.f;
-  if (p.is_logits) {
+  {
     float m = -INFINITY;
-    for (int i = tid; i < n; i += kSelThreads) m = fmaxf(m, v[i]);
-    vmax = block_reduce(m, s_red, true);
-    float z = 0.f;
-    for (int i = tid; i < n; i += kSelThreads) z += expf(v[i] - vmax);
-    inv_z = 1.f / block_reduce(z, s_red, false);
+    for (int i = tid; i < n; i += kSelThreads) {
+      const float x = v[i];
+      if (SHARED) s_keys[i] = sortable(x);
+      m = fmaxf(m, x);
+    }
+    if (p.is_logits) {
+      vmax = block_reduce(m, s_red, true);
+      float z = 0.f;
+      for (int i = tid; i < n; i += kSelThreads) z += expf(unsortable(key_at(i)) - vmax);
+      inv_z = 1.f / block_reduce(z, s_red, false);
+    }
   }
-
-  // radix select: the sortable key of rank `budget` (descending)
   if (tid == 0) {
     s_prefix = 0u;
     s_need = budget;
   }
+
+  // radix select: the sortable key of rank `budget` (descending), 8 bits per pass.  Float keys
+  // share their high bits, so the lanes that hold lane 0's digit are counted with one ballot and
+  // one atomic; only the others fall back to their own atomics.
   for (int pass = 3; pass >= 0; --pass) {
     for (int i = tid; i < 256; i += kSelThreads) s_hist[i] = 0;
     __syncthreads();
     const uint32_t prefix = s_prefix;
     const uint32_t himask = pass == 3 ? 0u : (0xFFFFFFFFu << (8 * (pass + 1)));
-    for (int i = tid; i < n; i += kSelThreads) {
-      const uint32_t key = sortable(v[i]);
-      if ((key & himask) == prefix) atomicAdd(&s_hist[(key >> (8 * pass)) & 0xFF], 1);
+    for (int i0 = 0; i0 < n; i0 += kSelThreads) {
+      const int i = i0 + tid;
+      int digit = -1;  // not a candidate
+      if (i < n) {
+        const uint32_t key = key_at(i);
+        if ((key & himask) == prefix) digit = (key >> (8 * pass)) & 0xFF;
+      }
+      const uint32_t cand = __ballot_sync(0xffffffffu, digit >= 0);
+      if (cand == 0u) continue;
+      const int lead = __shfl_sync(0xffffffffu, digit, __ffs(cand) - 1);
+      const uint32_t same = __ballot_sync(0xffffffffu, digit == lead);
+      if (digit == lead) {
+        if (lane == __ffs(same) - 1) atomicAdd(&s_hist[lead], __popc(same));
+      } else if (digit >= 0) {
+        atomicAdd(&s_hist[digit], 1);
+      }
     }
     __syncthreads();
-    if (tid == 0) {
-      int need = s_need;
-      int bin = 255;
-      for (; bin > 0; --bin) {
-        const int cnt = s_hist[bin];
-        if (cnt >= need) break;
-        need -= cnt;
+    if (warp == 0) {
+      // suffix sums over the 256 bins, 8 bins per lane: find the bin holding rank `need`
+      int local[8], sum = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        local[k] = s_hist[255 - (lane * 8 + k)];  // lane 0 holds the highest bins
+        sum += local[k];
       }
-      s_need = need;
-      s_prefix = prefix | (static_cast<uint32_t>(bin) << (8 * pass));
+      int incl = sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      const int need = s_need;
+      int before = incl - sum;  // keys in higher bins than mine
+      int found_bin = -1, found_need = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (found_bin < 0 && before < need && before + local[k] >= need) {
+          found_bin = 255 - (lane * 8 + k);
+          found_need = need - before;
+        }
+        before += local[k];
+      }
+      const uint32_t who = __ballot_sync(0xffffffffu, found_bin >= 0);
+      if (who != 0u && lane == __ffs(who) - 1) {
+        s_need = found_need;
+        s_prefix = prefix | (static_cast<uint32_t>(found_bin) << (8 * pass));
+      }
     }
     __syncthreads();
   }
   const uint32_t threshold = s_prefix;  // key of the budget-th largest value
   const int need_eq = s_need;           // how many equal to it are taken, lowest index first
-  if (tid == 0) {
-    s_base_gt = 0;
-    s_base_eq = 0;
+
+  // ordered compaction: thread t owns the contiguous keys [t*per, (t+1)*per); one block-wide
+  // exclusive scan of the (greater, equal) counts gives every thread its output position
+  const int per = (n + kSelThreads - 1) / kSelThreads;
+  const int begin = min(n, tid * per), end = min(n, begin + per);
+  int my_gt = 0, my_eq = 0;
+  for (int i = begin; i < end; ++i) {
+    const uint32_t key = key_at(i);
+    my_gt += key > threshold;
+    my_eq += key == threshold;
+  }
+  int inc_gt = my_gt, inc_eq = my_eq;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int ug = __shfl_up_sync(0xffffffffu, inc_gt, o);
+    const int ue = __shfl_up_sync(0xffffffffu, inc_eq, o);
+    if (lane >= o) {
+      inc_gt += ug;
+      inc_eq += ue;
+    }
+  }
+  if (lane == 31) {
+    s_wgt[warp] = inc_gt;
+    s_weq[warp] = inc_eq;
   }
   __syncthreads();
-
-  // ordered compaction
-  const int lane = tid & 31, warp = tid >> 5;
+  if (warp == 0) {
+    int wg = s_wgt[lane], we = s_weq[lane];
+    const int tg = wg, te = we;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int ug = __shfl_up_sync(0xffffffffu, wg, o);
+      const int ue = __shfl_up_sync(0xffffffffu, we, o);
+      if (lane >= o) {
+        wg += ug;
+        we += ue;
+      }
+    }
+    s_wgt[lane] = wg - tg;  // exclusive
+    s_weq[lane] = we - te;
+  }
+  __syncthreads();
+  int gt_before = s_wgt[warp] + inc_gt - my_gt;
+  int eq_before = s_weq[warp] + inc_eq - my_eq;
   float mass_part = 0.f;
-  for (int i0 = 0; i0 < n; i0 += kSelThreads) {
-    const int i = i0 + tid;
-    float val = 0.f;
-    bool gt = false, eq = false;
-    if (i < n) {
-      val = v[i];
-      const uint32_t key = sortable(val);
-      gt = key > threshold;
-      eq = key == threshold;
-    }
-    const uint32_t bgt = __ballot_sync(0xffffffffu, gt);
-    const uint32_t beq = __ballot_sync(0xffffffffu, eq);
-    if (lane == 0) {
-      s_wgt[warp] = __popc(bgt);
-      s_weq[warp] = __popc(beq);
-    }
-    __syncthreads();
-    int gt_before = s_base_gt, eq_before = s_base_eq;
-    for (int w = 0; w < warp; ++w) {
-      gt_before += s_wgt[w];
-      eq_before += s_weq[w];
-    }
-    const uint32_t lt = (1u << lane) - 1u;
-    gt_before += __popc(bgt & lt);
-    eq_before += __popc(beq & lt);
-    const bool take = gt || (eq && eq_before < need_eq);
-    if (take) {
+  for (int i = begin; i < end; ++i) {
+    const uint32_t key = key_at(i);
+    const bool gt = key > threshold, eq = key == threshold;
+    if (gt || (eq && eq_before < need_eq)) {
       const int pos = gt_before + min(eq_before, need_eq);
+      const float val = unsortable(key);
       const float w = p.is_logits ? expf(val - vmax) * inv_z : val;
       out_idx[pos] = i;
       if (out_valid) out_valid[pos] = 1;
       if (out_w) out_w[pos] = w;
       mass_part += w;
     }
-    __syncthreads();
-    if (tid == 0) {
-      int tg = 0, te = 0;
-      for (int w = 0; w < kSelWarps; ++w) {
-        tg += s_wgt[w];
-        te += s_weq[w];
-      }
-      s_base_gt += tg;
-      s_base_eq += te;
-    }
-    __syncthreads();
+    gt_before += gt;
+    eq_before += eq;
   }
   const float mass = block_reduce(mass_part, s_red, false);
   if (tid == 0) {
@@ -224,7 +279,18 @@ extern "C" int fl_select_decode_keys(const float* values, int64_t values_stride,
   p.counts = counts;
   p.mass = global_mass;
   p.weights = selected_weights;
-  select_kernel<<<static_cast<unsigned>(batch) * heads, kSelThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  // keys per head are bounded by the stride of the values (or by n_keys when it is given)
+  const int64_t bound = seq_state ? values_stride : n_keys;
+  const unsigned grid = static_cast<unsigned>(batch) * heads;
+  if (bound <= kSelMaxSharedKeys) {
+    const size_t smem = static_cast<size_t>(bound) * sizeof(uint32_t);
+    static const cudaError_t attr = cudaFuncSetAttribute(
+        select_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSelMaxSharedKeys * sizeof(uint32_t));
+    (void)attr;
+    select_kernel<true><<<grid, kSelThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  } else {
+    select_kernel<false><<<grid, kSelThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  }
   FL_CHECK_LAUNCH(who);
   return FL_OK;
 }
