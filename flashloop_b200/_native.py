@@ -61,6 +61,10 @@ SIGNATURES = {
     "fl_append_decode_token": (C.c_int, [C.POINTER(FlLayer), C.POINTER(_vp), C.POINTER(_vp), _vp]),
     "fl_select_decode_keys": (C.c_int, [_vp, _i64, _i32, _i32, _i32, _vp, _f64, _i32, _vp, _vp, _i64,
                                         _vp, _vp, _vp, _vp]),
+    "fl_hidden_delta_score": (C.c_int, [_vp, _vp, _i64, _i32, _vp, _vp]),
+    "fl_select_prefill_tokens": (C.c_int, [_vp, _vp, _i32, _i32, _f64, _i32, _vp, _vp, _vp, _vp, _vp]),
+    "fl_gather_rows": (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _i32, _vp]),
+    "fl_scatter_rows": (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _i32, _vp]),
 }
 
 _LIB = None

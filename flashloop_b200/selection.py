@@ -118,7 +118,8 @@ def select_prefill_tokens(scores: torch.Tensor, *, fraction: float,
                           force_last_token: bool = True) -> torch.Tensor:
     """Select a global ceil budget, optionally nested in a prior-loop mask
     (flashloop/selection.py:26-69).  Runs once per loop boundary of the prefill, on
-    whatever device ``scores`` lives on; ties go to the lower index."""
+    the GPU as one launch (``fl_select_prefill_tokens``) for CUDA scores; host tensors take
+    the Torch path below.  Ties go to the lower index."""
 
     fraction = _validate_fraction(fraction)
     if scores.ndim != 2 or scores.shape[1] == 0:
@@ -133,6 +134,13 @@ def select_prefill_tokens(scores: torch.Tensor, *, fraction: float,
     budget = max(1, math.ceil(tokens * fraction))
     if bool((~eligible).all(dim=1).any()):
         raise ValueError("eligible contains an empty batch row")
+    if force_last_token and not bool(eligible[:, -1].all()):
+        raise ValueError("the forced final token must be eligible")
+    if scores.is_cuda:
+        from .compaction import retain_tokens
+
+        return retain_tokens(scores, fraction=fraction, eligible=eligible,
+                             force_last_token=force_last_token).mask
     work = scores.float().masked_fill(~eligible, float("-inf"))
     forced = 0
     if force_last_token:

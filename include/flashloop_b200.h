@@ -256,6 +256,40 @@ int fl_select_decode_keys(const float* values, int64_t values_stride, int32_t ba
                           int64_t capacity, int32_t* counts, float* global_mass,
                           float* selected_weights, fl_cuda_stream stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Token retention (sparse late loops of the prefill).
+ * ------------------------------------------------------------------------------------- */
+
+/* _hidden_delta_score (flashloop/engine.py:78-81): ||h_r - h_{r-1}|| / max(||h_r||, 1e-12) per
+ * token row, float32.  current/previous bfloat16 [rows][hidden], hidden a multiple of 8. */
+int fl_hidden_delta_score(const void* current, const void* previous, int64_t rows, int32_t hidden,
+                          float* scores, fl_cuda_stream stream);
+
+/* select_prefill_tokens (flashloop/selection.py:26-69) fused with the position list and rank
+ * map built around it (flashloop/engine.py:276-277, flashloop/cache.py:281-289): per sequence
+ * keep min(max(1, ceil(tokens*fraction)), eligible) tokens, the last token first when forced,
+ * then the highest scores among the other eligible tokens (ties: lower index).  scores float32
+ * [batch][tokens]; eligible uint8 [batch][tokens] or NULL; mask uint8 [batch][tokens];
+ * positions int32 [batch][tokens] = kept positions ascending then -1; rank int32
+ * [batch][tokens] = index into positions or -1; count int32 [batch]. */
+int fl_select_prefill_tokens(const float* scores, const uint8_t* eligible, int32_t batch,
+                             int32_t tokens, double fraction, int32_t force_last_token,
+                             uint8_t* mask, int32_t* positions, int32_t* rank, int32_t* count,
+                             fl_cuda_stream stream);
+
+/* The row movement of the sparse prefill loops (flashloop/prefill.py:144, 154-158, 193-194,
+ * 237, 252-254: index_select of active rows, index_copy_ of their results).  full is
+ * [outer][full_rows][row_bytes], compact is [outer][compact_rows][row_bytes]; sequence
+ * outer / per_sequence owns positions[seq*positions_stride + r], r < count[seq].
+ * fl_gather_rows: compact[r] = full[positions[r]]; fl_scatter_rows: full[positions[r]] = compact[r].
+ * row_bytes must be a multiple of 16. */
+int fl_gather_rows(const void* full, void* compact, const int32_t* positions, const int32_t* count,
+                   int64_t positions_stride, int64_t outer, int32_t per_sequence, int64_t full_rows,
+                   int64_t compact_rows, int32_t row_bytes, fl_cuda_stream stream);
+int fl_scatter_rows(void* full, const void* compact, const int32_t* positions, const int32_t* count,
+                    int64_t positions_stride, int64_t outer, int32_t per_sequence, int64_t full_rows,
+                    int64_t compact_rows, int32_t row_bytes, fl_cuda_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

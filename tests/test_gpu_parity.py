@@ -574,3 +574,69 @@ def layer_decode(layer, s, kind, tokens):
             sc = p.scale.float().repeat_interleave(64, dim=3)
         outs.append(codes * sc + mn)
     return torch.cat(outs)
+
+
+# ------------------------------------------------------------------------------ token retention
+
+
+def test_token_retention_vs_reference_vectors_and_oracle(fl, golden):
+    from flashloop_b200 import compaction, selection
+
+    h1 = torch.from_numpy(bf(golden["retain.h1"])).to(torch.bfloat16).cuda()
+    h2 = torch.from_numpy(bf(golden["retain.h2"])).to(torch.bfloat16).cuda()
+    score = compaction.hidden_delta_score(h2, h1)
+    np.testing.assert_allclose(score.cpu().numpy(), golden["retain.score3"], rtol=2e-5)
+    s3 = torch.from_numpy(golden["retain.score3"]).cuda()
+    s4 = torch.from_numpy(golden["retain.score4"]).cuda()
+    r3 = compaction.retain_tokens(s3, fraction=0.25)
+    assert torch.equal(r3.mask.cpu(), torch.from_numpy(golden["retain.mask3"]))
+    r4 = compaction.retain_tokens(s4, fraction=0.10, eligible=r3.mask)
+    assert torch.equal(r4.mask.cpu(), torch.from_numpy(golden["retain.mask4"]))
+    assert torch.equal(selection.select_prefill_tokens(s4, fraction=0.10, eligible=r3.mask), r4.mask)
+    for r in (r3, r4):
+        m = r.mask[0].cpu().numpy()
+        pos, rank = osel.positions_and_rank_map(m, m.size)
+        n = int(r.count[0])
+        assert n == pos.size
+        np.testing.assert_array_equal(r.positions[0, :n].cpu().numpy(), pos)
+        assert bool((r.positions[0, n:] == -1).all())
+        np.testing.assert_array_equal(r.rank[0].cpu().numpy(), rank)
+
+
+@pytest.mark.parametrize("tokens,fraction", [(1, 0.25), (7, 0.1), (2048, 0.25), (8192, 0.10), (5000, 1.0)])
+def test_token_retention_and_row_movement_vs_oracle(fl, tokens, fraction):
+    from flashloop_b200 import compaction
+
+    g = torch.Generator().manual_seed(tokens)
+    batch = 3
+    scores = torch.rand(batch, tokens, generator=g)
+    if tokens > 16:
+        scores[1, 3] = scores[1, 11]  # a tie: the lower index wins
+    eligible = torch.rand(batch, tokens, generator=g) < 0.6
+    eligible[:, -1] = True
+    for elig in (None, eligible):
+        want = osel.select_prefill_tokens(scores.numpy(), fraction=fraction,
+                                          eligible=None if elig is None else elig.numpy())
+        got = compaction.retain_tokens(scores.cuda(), fraction=fraction,
+                                       eligible=None if elig is None else elig.cuda())
+        np.testing.assert_array_equal(got.mask.cpu().numpy(), want)
+        for b in range(batch):
+            pos, rank = osel.positions_and_rank_map(want[b], tokens)
+            assert int(got.count[b]) == pos.size
+            np.testing.assert_array_equal(got.positions[b, :pos.size].cpu().numpy(), pos)
+            np.testing.assert_array_equal(got.rank[b].cpu().numpy(), rank)
+    # gather the retained rows of a [B*H, T, 128] array, scatter them back into zeros
+    heads = 2
+    full = torch.randn(batch * heads, tokens, 128, generator=g).to(torch.bfloat16).cuda()
+    rows = int(got.count.max())
+    compact = compaction.gather_rows(full, got.positions, got.count, rows=rows, per_sequence=heads)
+    back = torch.zeros_like(full)
+    compaction.scatter_rows(back, compact, got.positions, got.count, per_sequence=heads)
+    for o in range(batch * heads):
+        b = o // heads
+        n = int(got.count[b])
+        pos = got.positions[b, :n].long()
+        assert torch.equal(compact[o, :n], full[o].index_select(0, pos))
+        expect = torch.zeros_like(full[o])
+        expect[pos] = full[o, pos]
+        assert torch.equal(back[o], expect)
