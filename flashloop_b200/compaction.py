@@ -74,6 +74,15 @@ def retain_tokens(scores: torch.Tensor, *, fraction: float, eligible: torch.Tens
     return RetainedTokens(mask=mask, positions=positions, rank=rank, count=count)
 
 
+def retained_from_mask(mask: torch.Tensor) -> RetainedTokens:
+    """Positions, rank map and counts of an externally chosen retention mask [B, T]."""
+
+    if mask.ndim != 2 or mask.dtype != torch.bool:
+        raise ValueError("mask must be bool [batch, tokens]")
+    scores = torch.zeros(mask.shape, dtype=torch.float32, device=mask.device)
+    return retain_tokens(scores, fraction=1.0, eligible=mask, force_last_token=False)
+
+
 def _move(gather: bool, full: torch.Tensor, compact: torch.Tensor, positions: torch.Tensor,
           count: torch.Tensor, per_sequence: int) -> None:
     if full.ndim != 3 or compact.ndim != 3 or full.shape[0] != compact.shape[0] or full.shape[2] != compact.shape[2]:

@@ -1,0 +1,323 @@
+"""Batched Ouro-style four-loop inference orchestration.
+
+Mirrors flashloop/engine.py:112-607 (``FlashLoopEngine.prefill / decode / generate / reset``,
+``EngineState``, ``PrefillOutput``, ``DecodeOutput``, ``DecodeReceipt``) with a batch dimension:
+the reference is batch-one (engine.py:176-177, 376-377); here every sequence of the batch has
+its own cache state inside one ``CrossLoopKVLayer`` per physical layer and all sequences share
+every launch.  Prompts of one call have equal length.
+
+Decode per layer and loop (engine.py:393-537): loops 1-2 run the dense reader; after loop 2 the
+top ``decode_key_fraction`` keys are selected from its logits and their loop-2 value aggregate
+is cached; loops 3-4 run the cached-mass sparse reader over those keys and add the projected
+correction to the loop-2 attention output.  After the four loops the token's K/V of every loop
+are appended (``fl_append_decode_token``).  With ``use_cuda_graph=True`` the whole decode step
+(model GEMMs included) is recorded once and replayed.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .cache import CrossLoopKVCache, CrossLoopKVLayer
+from .compaction import RetainedTokens, hidden_delta_score, retain_tokens
+from .config import FlashLoopConfig, validate_ouro_model
+from .selection import decode_budget
+from .prefill import PrefillReceipt, apply_rope, dense_prefill_loop, sparse_prefill_loop
+from .weights import fused_mlp, project_qkv, repack_projection_weights
+
+
+@dataclass(frozen=True)
+class EngineState:
+    cache: CrossLoopKVCache
+    next_position: int
+    mask_loop3: torch.Tensor
+    mask_loop4: torch.Tensor
+    prefill_receipts: tuple
+
+
+@dataclass(frozen=True)
+class PrefillOutput:
+    logits: torch.Tensor
+    state: EngineState
+
+
+@dataclass(frozen=True)
+class DecodeReceipt:
+    dense_attention_calls: int
+    sparse_attention_calls: int
+    dense_late_loop_calls: int
+    selected_keys_per_layer: tuple
+
+
+@dataclass(frozen=True)
+class DecodeOutput:
+    logits: torch.Tensor
+    state: EngineState
+    receipt: DecodeReceipt
+
+
+class FlashLoopEngine:
+    """Narrow adapter that reuses an Ouro-style model's weights without copying them."""
+
+    def __init__(self, model: torch.nn.Module, *, config: FlashLoopConfig | None = None,
+                 validate_model: bool = True, max_new_tokens: int = 512, use_cuda_graph: bool = False,
+                 reference_loop4_scores: bool = True) -> None:
+        if validate_model:
+            validate_ouro_model(model)
+        elif int(getattr(model.config, "total_ut_steps", 0)) != 4:
+            raise ValueError("FlashLoop requires exactly four recurrent loops")
+        self.model = model.eval()
+        self.config = config or FlashLoopConfig()
+        self.layers = self.model.model.layers
+        self.backbone = self.model.model
+        if self.config.fuse_projection_weights:
+            repack_projection_weights(self.layers)
+        self.max_new_tokens = int(max_new_tokens)
+        self.use_cuda_graph = bool(use_cuda_graph)
+        self.reference_loop4_scores = bool(reference_loop4_scores)
+        self._state: EngineState | None = None
+        self._graph = None
+        self._graph_io = None
+        self._graph_warm = False
+        self._decode_limit = 0
+
+    @classmethod
+    def from_pretrained(cls, model_path: str, *, config: FlashLoopConfig | None = None,
+                        torch_dtype: torch.dtype = torch.bfloat16, device: str | torch.device = "cuda",
+                        **kwargs) -> "FlashLoopEngine":
+        """engine.py:134-150: load an Ouro checkpoint with its remote modelling code."""
+
+        from transformers import AutoModelForCausalLM
+
+        model = AutoModelForCausalLM.from_pretrained(model_path, trust_remote_code=True,
+                                                     torch_dtype=torch_dtype).to(device)
+        return cls(model, config=config, validate_model=True, **kwargs)
+
+    @property
+    def state(self) -> EngineState:
+        if self._state is None:
+            raise RuntimeError("engine cache is not initialized")
+        return self._state
+
+    def reset(self) -> None:
+        self._state = None
+        self._graph = None
+        self._graph_io = None
+        self._graph_warm = False
+        self._decode_limit = 0
+
+    # ------------------------------------------------------------------ prefill
+
+    def _retain(self, loop: int, scores: torch.Tensor, fraction: float,
+                eligible: torch.Tensor | None) -> RetainedTokens:
+        """Retention decision of ``loop`` (3 or 4); a subclass may substitute its own policy."""
+
+        return retain_tokens(scores, fraction=fraction, eligible=eligible)
+
+    @torch.inference_mode()
+    def prefill(self, input_ids: torch.Tensor, attention_mask: torch.Tensor | None = None) -> PrefillOutput:
+        """engine.py:162-344 for a batch of equally long prompts [B, T]."""
+
+        if self._state is not None:
+            raise RuntimeError("engine cache is already initialized; call reset()")
+        if input_ids.ndim != 2 or input_ids.shape[1] <= 0:
+            raise ValueError("prefill requires input_ids [batch, tokens] with at least one token")
+        if attention_mask is not None and not bool(attention_mask.bool().all().item()):
+            raise ValueError("padding is not supported: prompts of one call have equal length")
+        batch, tokens = (int(v) for v in input_ids.shape)
+        hidden = self.backbone.embed_tokens(input_ids)
+        positions = torch.arange(tokens, device=input_ids.device).unsqueeze(0).expand(batch, -1)
+        rope = self.backbone.rotary_emb(hidden, positions)
+        norm = self.backbone.norm
+
+        loop1 = dense_prefill_loop(self.layers, hidden, position_embeddings=rope, final_norm=norm, loop=1)
+        loop2 = dense_prefill_loop(self.layers, loop1.hidden_states, position_embeddings=rope, final_norm=norm,
+                                   loop=2)
+        fraction3, fraction4 = self.config.effective_prefill_fractions
+        keep3 = self._retain(3, hidden_delta_score(loop2.hidden_states, loop1.hidden_states), fraction3, None)
+        loop3 = sparse_prefill_loop(self.layers, loop2.hidden_states, retained=keep3,
+                                    composite_cache=loop2.composite_cache, position_embeddings=rope,
+                                    final_norm=norm, loop=3)
+        if self.reference_loop4_scores:
+            # engine.py:258-275 runs Loop 3 with consume_inputs=True, so prefill.py:236-237,254
+            # write the Loop-3 rows into the Loop-2 tensor itself and the score of
+            # engine.py:271-272 compares that tensor with itself: every Loop-4 score is 0 and
+            # the retained set is decided by the tie rule alone (here: lowest positions first).
+            score4 = torch.zeros((batch, tokens), dtype=torch.float32, device=input_ids.device)
+        else:
+            score4 = hidden_delta_score(loop3.hidden_states, loop2.hidden_states)
+        keep4 = self._retain(4, score4, fraction4, keep3.mask)
+        loop4 = sparse_prefill_loop(self.layers, loop3.hidden_states, retained=keep4,
+                                    composite_cache=loop3.composite_cache, position_embeddings=rope,
+                                    final_norm=norm, loop=4)
+
+        physical = CrossLoopKVCache(num_layers=len(self.layers))
+        loops = (loop1, loop2, loop3, loop4)
+        for index in range(len(self.layers)):
+            physical.set_layer(index, CrossLoopKVLayer.from_prefill(
+                [lp.composite_cache.keys[index] for lp in loops],
+                [lp.composite_cache.values[index] for lp in loops],
+                mask_loop3=keep3.mask, mask_loop4=keep4.mask, group_size=self.config.group_size,
+                residual_length=self.config.residual_length, bits=self.config.kv_bits,
+                max_new_tokens=self.max_new_tokens))
+            for lp in loops:  # release the dense K/V of this layer
+                lp.composite_cache.keys[index] = None
+                lp.composite_cache.values[index] = None
+        self._decode_limit = tokens + self.max_new_tokens
+        self._state = EngineState(cache=physical, next_position=tokens, mask_loop3=keep3.mask,
+                                  mask_loop4=keep4.mask,
+                                  prefill_receipts=tuple(lp.receipt for lp in loops))
+        logits = self.model.lm_head(loop4.hidden_states[:, -1]).float()
+        return PrefillOutput(logits=logits, state=self._state)
+
+    # ------------------------------------------------------------------ decode
+
+    def _decode_step(self, token_ids: torch.Tensor, position_ids: torch.Tensor) -> torch.Tensor:
+        """The device work of one decode step; returns float32 logits [B, vocab]."""
+
+        cache = self.state.cache
+        fraction = self.config.effective_decode_key_fraction
+        hidden = self.backbone.embed_tokens(token_ids)
+        batch = int(token_ids.shape[0])
+        cos, sin = self.backbone.rotary_emb(hidden, position_ids)
+        n_layers = len(self.layers)
+        keys = [[None] * 4 for _ in range(n_layers)]
+        values = [[None] * 4 for _ in range(n_layers)]
+        sources = [None] * n_layers
+        for loop in range(4):
+            for index, layer in enumerate(self.layers):
+                attention = layer.self_attn
+                head_dim = int(attention.head_dim)
+                physical = cache.layers[index]
+                q, k, v = project_qkv(attention, layer.input_layernorm(hidden))
+                heads = q.shape[-1] // head_dim
+                q = q.view(batch, 1, heads, head_dim).transpose(1, 2)
+                k = k.view(batch, 1, heads, head_dim).transpose(1, 2)
+                v = v.view(batch, 1, heads, head_dim).transpose(1, 2).contiguous()
+                q, k = apply_rope(q, k, cos, sin)
+                q, k = q.contiguous(), k.contiguous()
+                keys[index][loop], values[index][loop] = k, v
+                scaling = float(attention.scaling)
+                if loop < 2 or not self.config.enable_sparse_decode:
+                    want_logits = loop == 1 and self.config.enable_sparse_decode
+                    out, logits = physical.dense_source_attention(loop, query=q, current_key=k, current_value=v,
+                                                                  scaling=scaling, return_logits=want_logits)
+                    projected = attention.o_proj(out.to(q.dtype).transpose(1, 2).reshape(batch, 1, -1))
+                    if want_logits:
+                        sel = physical.select_decode_keys(logits, fraction=fraction)
+                        aggregate = physical.pv(1, sel.selected_weights, sel.indices, current_value=v,
+                                                valid=sel.valid, validate_indices=False)
+                        sources[index] = (projected, sel, aggregate)
+                else:
+                    projected0, sel, aggregate = sources[index]
+                    delta = physical.cached_mass_sparse_attention_delta(
+                        loop, query=q, current_key=k, current_value=v, indices=sel.indices, valid=sel.valid,
+                        source_selected_output=aggregate, global_mass=sel.global_mass, scaling=scaling)
+                    projected = projected0 + attention.o_proj(
+                        delta.to(v.dtype).transpose(1, 2).reshape(batch, 1, -1))
+                residual = hidden
+                hidden = residual + layer.input_layernorm_2(projected)
+                hidden = hidden + layer.post_attention_layernorm_2(
+                    fused_mlp(layer.mlp, layer.post_attention_layernorm(hidden)))
+            hidden = self.backbone.norm(hidden)
+        for index in range(n_layers):
+            cache.layers[index].append_decode_token(keys[index], values[index])
+        return self.model.lm_head(hidden[:, -1]).float()
+
+    def _graph_decode(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """Decode through a recorded CUDA graph.  The first call runs eagerly with the launch
+        geometry fixed to the longest context this engine can reach (it creates every lazily
+        allocated buffer), the second records the step, later ones replay it."""
+
+        state = self.state
+        layers = state.cache.layers
+        if self._graph_io is None:
+            for layer in layers:
+                layer.context_bound = self._decode_limit
+            self._graph_io = (token_ids.clone(), torch.empty_like(token_ids, dtype=torch.long), None)
+        static_ids, static_pos, static_logits = self._graph_io
+        static_ids.copy_(token_ids)
+        static_pos.fill_(state.next_position)
+        if self._graph is None and not self._graph_warm:
+            self._graph_warm = True
+            return self._decode_step(static_ids, static_pos)
+        if self._graph is None:
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_logits = self._decode_step(static_ids, static_pos)
+            # recording advanced the host mirror of the cache state but ran nothing on the
+            # device: one replay brings the device in line
+            graph.replay()
+            self._graph = graph
+            self._graph_io = (static_ids, static_pos, static_logits)
+            return static_logits.clone()
+        self._graph.replay()
+        for layer in layers:
+            layer.advance_host_state()
+        return static_logits.clone()
+
+    @torch.inference_mode()
+    def decode(self, token_ids: torch.Tensor) -> DecodeOutput:
+        """engine.py:373-570 for one token per sequence, token_ids [B, 1]."""
+
+        state = self.state
+        layers = state.cache.layers
+        batch = layers[0].batch
+        if tuple(token_ids.shape) != (batch, 1):
+            raise ValueError("decode requires exactly one token per sequence")
+        if state.next_position >= self._decode_limit:
+            raise RuntimeError("the preallocated cache is full; raise max_new_tokens")
+        if self.use_cuda_graph:
+            logits = self._graph_decode(token_ids)
+        else:
+            position_ids = torch.full((batch, 1), state.next_position, device=token_ids.device, dtype=torch.long)
+            logits = self._decode_step(token_ids, position_ids)
+        self._state = EngineState(cache=state.cache, next_position=state.next_position + 1,
+                                  mask_loop3=state.mask_loop3, mask_loop4=state.mask_loop4,
+                                  prefill_receipts=state.prefill_receipts)
+        sparse = self.config.enable_sparse_decode
+        n = len(self.layers)
+        budget = decode_budget(state.next_position + 1, self.config.effective_decode_key_fraction)
+        receipt = DecodeReceipt(dense_attention_calls=(2 if sparse else 4) * n,
+                                sparse_attention_calls=(2 if sparse else 0) * n,
+                                dense_late_loop_calls=(0 if sparse else 2) * n,
+                                selected_keys_per_layer=tuple([budget] * n) if sparse else ())
+        return DecodeOutput(logits=logits, state=self._state, receipt=receipt)
+
+    # ------------------------------------------------------------------ generate
+
+    @torch.inference_mode()
+    def generate(self, input_ids: torch.Tensor, *, max_new_tokens: int, eos_token_id: int | None = None,
+                 stop_token_sequences: tuple = ()) -> torch.Tensor:
+        """Greedy generation (engine.py:572-607).  With a batch, generation stops when every
+        sequence has produced ``eos_token_id`` (finished sequences keep emitting it)."""
+
+        if int(max_new_tokens) <= 0:
+            raise ValueError("max_new_tokens must be positive")
+        if int(max_new_tokens) > self.max_new_tokens:
+            raise ValueError("max_new_tokens exceeds the room preallocated by the engine")
+        if eos_token_id is None:
+            eos_token_id = getattr(self.model.config, "eos_token_id", None)
+        logits = self.prefill(input_ids).logits
+        generated = input_ids
+        finished = torch.zeros(input_ids.shape[0], dtype=torch.bool, device=input_ids.device)
+        completions: list[list[int]] = [[] for _ in range(input_ids.shape[0])] if stop_token_sequences else []
+        for step in range(int(max_new_tokens)):
+            next_token = torch.argmax(logits, dim=-1, keepdim=True)
+            if eos_token_id is not None:
+                next_token = torch.where(finished[:, None], torch.full_like(next_token, int(eos_token_id)), next_token)
+                finished = finished | (next_token[:, 0] == int(eos_token_id))
+            generated = torch.cat([generated, next_token], dim=1)
+            if stop_token_sequences:
+                for b, tok in enumerate(next_token[:, 0].tolist()):
+                    completions[b].append(tok)
+                    if any(seq and tuple(completions[b][-len(seq):]) == tuple(seq) for seq in stop_token_sequences):
+                        finished[b] = True
+            if (eos_token_id is not None or stop_token_sequences) and bool(finished.all().item()):
+                break
+            if step + 1 < int(max_new_tokens):
+                logits = self.decode(next_token).logits
+        return generated

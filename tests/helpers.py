@@ -59,3 +59,28 @@ def assert_kivi_equal(packed: PackedKivi | None, ref, *, what=""):
                                   err_msg=what + " minimum")
     np.testing.assert_array_equal(packed.scale.view(np.uint16), ref["scale"].view(np.uint16),
                                   err_msg=what + " scale")
+
+
+TINY_OURO = dict(vocab_size=256, hidden_size=256, intermediate_size=384, num_hidden_layers=2,
+                 num_attention_heads=2)
+
+
+def tiny_ouro_model(seed: int = 11):
+    """A two-layer, two-head Ouro-shaped model whose weights come from numpy's legacy
+    RandomState, so the golden script and the tests build the same bfloat16 tensors on any
+    machine and any torch version."""
+
+    import torch
+
+    from flashloop_b200.ouro_shape import OuroShapedConfig, OuroShapedForCausalLM
+
+    model = OuroShapedForCausalLM(OuroShapedConfig(**TINY_OURO))
+    rng = np.random.RandomState(seed)
+    with torch.no_grad():
+        for name, param in sorted(model.named_parameters()):
+            if param.ndim >= 2:
+                w = rng.standard_normal(param.shape).astype(np.float32) * (0.08 if "embed" not in name else 1.0)
+            else:
+                w = 1.0 + 0.1 * rng.standard_normal(param.shape).astype(np.float32)
+            param.copy_(torch.from_numpy(w).to(param.dtype))
+    return model.eval()
