@@ -215,7 +215,7 @@ def run_b200(args) -> None:
     import torch
     import torch.distributed as dist
 
-    from flashloop_b200 import _native
+    from flashloop_b200 import _native, sharding
     from flashloop_b200.cache import CrossLoopKVLayer
     from flashloop_b200.synthetic import make_loop_kv
 
@@ -237,7 +237,7 @@ def run_b200(args) -> None:
         keys = [[] for _ in range(4)]
         values = [[] for _ in range(4)]
         for b in range(B):
-            k, v = make_loop_kv(H, T, seed=(rank * 1000 + layer_index) * 100 + b, device=device)
+            k, v = make_loop_kv(H, T, seed=sharding.sequence_seed(rank, layer_index, b), device=device)
             for r in range(4):
                 keys[r].append(k[r])
                 values[r].append(v[r])
@@ -280,9 +280,7 @@ def run_b200(args) -> None:
             layer.append_decode_token([k[r] for r in range(4)], [v[r] for r in range(4)])
 
     def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+        sharding.barrier(device)
 
     def timed(fn, count: int) -> float:
         barrier()
@@ -292,10 +290,7 @@ def run_b200(args) -> None:
             fn()
         e1.record()
         barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+        return sharding.max_over_ranks(e0.elapsed_time(e1), device)
 
     # ---- warm-up (eager), then record one step as a CUDA graph over static input buffers
     for _ in range(args.warmup):
@@ -325,8 +320,8 @@ def run_b200(args) -> None:
     torch.cuda.profiler.stop()
     clocks = sampler.stop() if sampler else {}
     timed_launches = kernels_per_layer * NL * args.steps
-    tokens = B * world * args.steps
-    value = tokens / (ms_total * 1e-3)
+    # every rank decodes its own B sequences: tokens of all ranks over the slowest rank's time
+    value = sharding.sum_over_ranks(B * args.steps, device) / (ms_total * 1e-3)
 
     # ---- the dominant kernel alone: the loop-2 dense reader of every layer, same arguments as in
     # the step, timed with CUDA events on the launching stream right after the timed region
@@ -355,7 +350,7 @@ def run_b200(args) -> None:
     e2e_steps = max(2, min(args.steps, 16))
     e2e_step()
     e2e_ms = timed(e2e_step, e2e_steps)
-    e2e_value = B * world * e2e_steps / (e2e_ms * 1e-3)
+    e2e_value = sharding.sum_over_ranks(B * e2e_steps, device) / (e2e_ms * 1e-3)
     status = max(layer.reader_status() for layer in layers)
 
     if rank == 0:

@@ -28,7 +28,7 @@ class FlLayer(C.Structure):
     _fields_ = [
         ("batch", _i32), ("heads", _i32), ("bits", _i32), ("tail_capacity", _i32),
         ("k_codes", _vp * FL_STREAMS), ("k_min", _vp * FL_STREAMS), ("k_scale", _vp * FL_STREAMS),
-        ("v_codes", _vp * FL_STREAMS), ("v_meta", _vp * FL_STREAMS),
+        ("v_rows", _vp * FL_STREAMS),
         ("row_base", _vp * FL_STREAMS), ("group_base", _vp * FL_STREAMS),
         ("rank", _vp * 2), ("rank_base", _vp),
         ("tail_k", _vp * FL_STREAMS), ("tail_v", _vp * FL_STREAMS),

@@ -109,7 +109,7 @@ class CrossLoopKVLayer:
                 [_round_up(c[1], GROUP) for c in compact_capacities]]
         self._caps = caps
         dev = self._device
-        self._k_codes, self._k_min, self._k_scale, self._v_codes, self._v_meta = [], [], [], [], []
+        self._k_codes, self._k_min, self._k_scale, self._v_rows, self._v_codes, self._v_meta = [], [], [], [], [], []
         self._row_base, self._group_base, self._row_base_host = [], [], []
         for s in range(4):
             bases, off = [], 0
@@ -119,10 +119,13 @@ class CrossLoopKVLayer:
                 off += self.heads * caps[s][b]
             total = max(off, GROUP)
             self._k_codes.append(torch.zeros((total, row_bytes), dtype=torch.uint8, device=dev))
-            self._v_codes.append(torch.zeros((total, row_bytes), dtype=torch.uint8, device=dev))
+            # V records: codes, then float16 min0 min1 scale0 scale1, then 8 bytes of padding
+            records = torch.zeros((total, row_bytes + 16), dtype=torch.uint8, device=dev)
+            self._v_rows.append(records)
+            self._v_codes.append(records[:, :row_bytes])
+            self._v_meta.append(records[:, row_bytes:row_bytes + 8].view(torch.float16))
             self._k_min.append(torch.zeros((total // GROUP, HEAD_DIM), dtype=torch.float16, device=dev))
             self._k_scale.append(torch.zeros((total // GROUP, HEAD_DIM), dtype=torch.float16, device=dev))
-            self._v_meta.append(torch.zeros((total, 4), dtype=torch.float16, device=dev))
             self._row_base_host.append(bases)
             self._row_base.append(torch.tensor(bases, dtype=torch.int64, device=dev))
             self._group_base.append(torch.tensor([x // GROUP for x in bases], dtype=torch.int64, device=dev))
@@ -154,8 +157,7 @@ class CrossLoopKVLayer:
             n.k_codes[s] = self._k_codes[s].data_ptr()
             n.k_min[s] = self._k_min[s].data_ptr()
             n.k_scale[s] = self._k_scale[s].data_ptr()
-            n.v_codes[s] = self._v_codes[s].data_ptr()
-            n.v_meta[s] = self._v_meta[s].data_ptr()
+            n.v_rows[s] = self._v_rows[s].data_ptr()
             n.row_base[s] = self._row_base[s].data_ptr()
             n.group_base[s] = self._group_base[s].data_ptr()
             n.tail_k[s] = self._tail_k[s].data_ptr()

@@ -25,8 +25,7 @@ struct AppendParams {
   uint8_t* k_codes[4];
   __half* k_min[4];
   __half* k_scale[4];
-  uint8_t* v_codes[4];
-  __half* v_meta[4];
+  uint8_t* v_rows[4];
   int32_t* rank[2];
   __nv_bfloat16* tail_k[4];
   __nv_bfloat16* tail_v[4];
@@ -173,15 +172,16 @@ __global__ void __launch_bounds__(128) rollover_kernel(const AppendParams p) {
         }
         const int j = s < 2 ? i : s_rank[s - 2][i];
         const int64_t row = p.L.row_base[s][bh] + row0[s] + j;
-        uint8_t* dst = p.v_codes[s] + row * kRowBytes;
+        uint8_t* dst = p.v_rows[s] + row * (kRowBytes + 16);
         if constexpr (BITS == 4) {
           reinterpret_cast<uint16_t*>(dst)[lane] = static_cast<uint16_t>(packed);
         } else {
           dst[lane] = static_cast<uint8_t>(packed);
         }
         if ((lane & 15) == 0) {
-          p.v_meta[s][row * 4 + g] = mn16;
-          p.v_meta[s][row * 4 + 2 + g] = sc16;
+          __half* meta = reinterpret_cast<__half*>(dst + kRowBytes);
+          meta[g] = mn16;
+          meta[2 + g] = sc16;
         }
       }
     }
@@ -252,8 +252,7 @@ extern "C" int fl_append_decode_token(const fl_layer* layer, const void* const* 
     p.k_codes[s] = static_cast<uint8_t*>(layer->k_codes[s]);
     p.k_min[s] = static_cast<__half*>(layer->k_min[s]);
     p.k_scale[s] = static_cast<__half*>(layer->k_scale[s]);
-    p.v_codes[s] = static_cast<uint8_t*>(layer->v_codes[s]);
-    p.v_meta[s] = static_cast<__half*>(layer->v_meta[s]);
+    p.v_rows[s] = static_cast<uint8_t*>(layer->v_rows[s]);
     p.tail_k[s] = static_cast<__nv_bfloat16*>(layer->tail_k[s]);
     p.tail_v[s] = static_cast<__nv_bfloat16*>(layer->tail_v[s]);
     p.keys[s] = static_cast<const __nv_bfloat16*>(keys[s]);

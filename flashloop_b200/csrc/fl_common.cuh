@@ -46,8 +46,7 @@ struct LayerView {
   const uint8_t* k_codes[4];
   const __half* k_min[4];
   const __half* k_scale[4];
-  const uint8_t* v_codes[4];
-  const __half* v_meta[4];
+  const uint8_t* v_rows[4];  // records of FL_V_RECORD_BYTES(bits): codes, min0 min1 scale0 scale1, padding
   const int64_t* row_base[4];
   const int64_t* group_base[4];
   const int32_t* rank[2];
@@ -68,8 +67,7 @@ inline LayerView make_view(const fl_layer& l) {
     v.k_codes[s] = static_cast<const uint8_t*>(l.k_codes[s]);
     v.k_min[s] = static_cast<const __half*>(l.k_min[s]);
     v.k_scale[s] = static_cast<const __half*>(l.k_scale[s]);
-    v.v_codes[s] = static_cast<const uint8_t*>(l.v_codes[s]);
-    v.v_meta[s] = static_cast<const __half*>(l.v_meta[s]);
+    v.v_rows[s] = static_cast<const uint8_t*>(l.v_rows[s]);
     v.row_base[s] = l.row_base[s];
     v.group_base[s] = l.group_base[s];
     v.tail_k[s] = static_cast<const __nv_bfloat16*>(l.tail_k[s]);
@@ -105,6 +103,9 @@ __device__ __forceinline__ float warp_min(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
+
+__device__ __forceinline__ int warp_min_int(int v) { return __reduce_min_sync(0xffffffffu, v); }
+__device__ __forceinline__ int warp_max_int(int v) { return __reduce_max_sync(0xffffffffu, v); }
 
 // (a & mask) | orv in one LOP3.
 __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t orv) {

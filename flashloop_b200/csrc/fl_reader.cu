@@ -406,19 +406,12 @@ __device__ __forceinline__ void bf16_row_accumulate(const __nv_bfloat16* row, in
   }
 }
 
-__device__ __forceinline__ void load_query(const ReaderParams& p, int64_t bh, float* s_qf, __half* s_qh) {
-  const int c = threadIdx.x;
-  const float q = __bfloat162float(p.q[bh * kHeadDim + c]);
-  s_qf[c] = q;
-  s_qh[c] = __float2half_rn(q);
-}
-
 // ------------------------------------------------------------------------------ dense reader
 //
 // Eight warps per CTA; each warp owns whole 64-token blocks of the chunk and runs its own
-// two-stage shared-memory ring.  A "unit" is one (block, stream, K|V) piece: the 64 packed rows
-// (4 KiB at 4 bits) plus their metadata (K: the scale/min rows of the one or two 64-row groups
-// the rows live in; V: the rows' 8-byte scale/min words).  Lane 0 of the warp arms the stage's
+// two-stage shared-memory ring.  A "unit" is one (block, stream, K|V) piece: for K the 64 packed
+// rows (4 KiB at 4 bits) plus the scale/min rows of the one or two 64-row groups they live in,
+// for V the 64 records (codes and metadata together, one copy).  Lane 0 of the warp arms the stage's
 // mbarrier with the byte count and issues the TMA bulk copies (cp.async.bulk, global ->
 // shared); the warp then waits on the barrier's phase, computes from shared memory, and
 // re-issues the unit two places ahead into the stage it has just drained.  No CTA-wide
@@ -434,9 +427,11 @@ constexpr uint32_t kSuspendNs = 100000;
 template <int BITS>
 struct Stage {
   static constexpr int kRowBytes = 16 * BITS;
-  static constexpr int kCodes = kGroup * kRowBytes;
-  static constexpr int kMeta = 1024;  // K: scale/min of two groups; V: up to 66 rows of 8 bytes
-  static constexpr int kBytes = kCodes + kMeta;
+  static constexpr int kRecord = kRowBytes + 16;     // V record: codes, 8 bytes of metadata, padding
+  static constexpr int kCodes = kGroup * kRowBytes;  // K unit: 64 code rows, then ...
+  static constexpr int kMeta = 1024;                 // ... the scale/min rows of up to two groups
+  static constexpr int kBytes = kCodes + kMeta;      // a V unit is 64 records: the same size
+  static_assert(kGroup * kRecord <= kBytes, "a V unit must fit the stage");
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* ptr) {
@@ -665,11 +660,9 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
                                   bar);
                   }
                 } else {
-                  const int64_t even = row & ~int64_t(1);
-                  const uint32_t meta_rows = static_cast<uint32_t>(((row + sp.m + 1) & ~int64_t(1)) - even);
-                  mbar_arrive_expect_tx(bar, code_bytes + meta_rows * 8u);
-                  bulk_copy_g2s(dst, L.v_codes[is] + row * kRowBytes, code_bytes, bar);
-                  bulk_copy_g2s(dst + St::kCodes, L.v_meta[is] + even * 4, meta_rows * 8u, bar);
+                  const uint32_t record_bytes = static_cast<uint32_t>(sp.m) * St::kRecord;
+                  mbar_arrive_expect_tx(bar, record_bytes);
+                  bulk_copy_g2s(dst, L.v_rows[is] + row * St::kRecord, record_bytes, bar);
                 }
               }
             }
@@ -779,13 +772,12 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
             for (int i = 0; i < 16; ++i) hacc[i] = __floats2half2_rn(0.f, 0.f);
           }
         } else {
-          const int64_t row = curp->row_base[s] + sp.r0;
-          const uint8_t* meta = stage + St::kCodes + static_cast<int>(row & 1) * 8;
+          const uint8_t* meta = stage + kRowBytes;  // of record 0
           // my channel group's minimum / scale, duplicated into both halves
           const uint32_t pick = (sub < 2) ? 0x1010u : 0x3232u;
           const __half2 centre2 = __floats2half2_rn(float(kCentre<BITS>), float(kCentre<BITS>));
           if (full) {
-            const uint8_t* piece = stage + quad * kRowBytes + sub * kLaneBytes;
+            const uint8_t* piece = stage + quad * St::kRecord + sub * kLaneBytes;
   #pragma unroll
             for (int half_block = 0; half_block < 2; ++half_block) {
               Codes<BITS> c[4];
@@ -793,8 +785,8 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   #pragma unroll
               for (int k = 0; k < 4; ++k) {
                 const int it = half_block * 4 + k;
-                c[k] = load_codes_shared<BITS>(piece + it * 8 * kRowBytes);
-                mt[k] = *reinterpret_cast<const uint2*>(meta + (it * 8 + quad) * 8);
+                c[k] = load_codes_shared<BITS>(piece + it * 8 * St::kRecord);
+                mt[k] = *reinterpret_cast<const uint2*>(meta + (it * 8 + quad) * St::kRecord);
               }
   #pragma unroll
               for (int k = 0; k < 4; ++k) {
@@ -814,8 +806,8 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
                 float pr = 0.f;
   #pragma unroll
                 for (int k = 0; k < 8; ++k) pr = (k == it) ? lg[k] : pr;
-                const Codes<BITS> c = load_codes_shared<BITS>(stage + ri * kRowBytes + sub * kLaneBytes);
-                const uint2 mt = *reinterpret_cast<const uint2*>(meta + ri * 8);
+                const Codes<BITS> c = load_codes_shared<BITS>(stage + ri * St::kRecord + sub * kLaneBytes);
+                const uint2 mt = *reinterpret_cast<const uint2*>(meta + ri * St::kRecord);
                 const __half2 vm2 = as_half2(__byte_perm(mt.x, 0u, pick));
                 const __half2 vs2 = as_half2(__byte_perm(mt.y, 0u, pick));
                 const __half2 p2 = __float2half2_rn(pr);
@@ -930,16 +922,70 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
 }
 
 // ------------------------------------------------------------------------------ selected readers
+//
+// Block-major gather with a per-warp asynchronous prefetch.  The selected indices arrive sorted,
+// so the slots that fall into one 64-token block are consecutive: a "run".  A warp takes whole
+// runs and walks them in passes of eight tokens, one per lane quad.  While it computes pass i
+// from shared memory, the rows of pass i+1 (K row and V record of every stream, and the K
+// metadata of a new run) are already on their way there as 16-byte cp.async copies that each
+// lane issues for the pieces it will read itself, so no registers are tied up by loads in flight
+// and a warp meets memory latency once per pipeline fill instead of once per pass.
+//
+// For a run the warp builds the block's query-folded K tables exactly as the dense reader does
+// (w_c = q_c * scale_c in float16, bias in float32; a second table where the compact rows of a
+// block straddle a metadata group), so K metadata is read once per run and stream and the
+// per-token arithmetic is the dense reader's fast path.
+//
+// Indices need not be sorted for correctness (an unsorted list only makes more, shorter runs).
 
 enum { kModeDelta = 0, kModePV = 1, kModeQK = 2 };
+constexpr int kSlotBatch = 2 * kThreads;  // slots staged per round: two per thread
+constexpr int kTailKey = INT_MAX;
+
+template <int BYTES>
+__device__ __forceinline__ void cp_async(void* dst_shared, const void* src_global) {
+  const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(dst_shared));
+  if constexpr (BYTES == 16) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src_global) : "memory");
+  } else {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(dst), "l"(src_global), "n"(BYTES) : "memory");
+  }
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <int BITS, int MODE>
-__global__ void __launch_bounds__(kThreads, 4)
+struct GatherSmem {
+  static constexpr int kRowBytes = 16 * BITS;
+  static constexpr int kRecord = kRowBytes + 16;
+  static constexpr int kKBytes = MODE == kModePV ? 0 : kRowBytes;
+  static constexpr int kVBytes = MODE == kModeQK ? 0 : kRecord;
+  static constexpr int kToken = kKBytes + kVBytes;           // one token of one stream
+  static constexpr int kMetaBytes = MODE == kModePV ? 0 : 512;  // scale[128], min[128] of one group
+  static constexpr int kBuffer = 8 * 4 * kToken + 4 * kMetaBytes;
+  static constexpr int kWarp = 2 * kBuffer;
+};
+
+template <int BITS, int MODE>
+__global__ void __launch_bounds__(kThreads, 3)
 selected_reader_kernel(const __grid_constant__ ReaderParams p) {
-  constexpr int kRowBytes = 16 * BITS;
+  using G = GatherSmem<BITS, MODE>;
+  constexpr int kRowBytes = G::kRowBytes;
+  constexpr int kLaneBytes = kRowBytes / 4;
+  extern __shared__ __align__(128) uint8_t s_gather[];  // [warp][2][rows of 8 tokens x 4 streams | K metadata]
   __shared__ __align__(16) float s_qf[kHeadDim];
-  __shared__ __align__(16) __half s_qh[kHeadDim];
+  __shared__ __align__(16) __half s_wtab[kWarps][4][2][kHeadDim];
+  __shared__ float s_kbias[kWarps][4][2];
+  __shared__ int s_g0[kWarps][2][4];      // per buffer: first K metadata group of the run, per stream
+  __shared__ int s_ng[kWarps][2][4];      // ... and how many groups (0, 1 or 2) its rows touch
   __shared__ __align__(16) float s_merge[kWarps][kPartialStride];
+  __shared__ int s_idx[kSlotBatch];       // logical index, or -1
+  __shared__ int s_row[2][kSlotBatch];    // rows in streams 2 and 3, or -1
+  __shared__ int s_key[kSlotBatch];       // 64-token block of the slot, kTailKey, or -1 (nothing to read)
+  __shared__ int s_run[kSlotBatch + 1];   // first slot of every run, then the end
+  __shared__ int s_warp_runs[2][kWarps];
+  __shared__ int64_t s_base[2][4];        // row_base / group_base of this (b,h)
   __shared__ int s_last;
 
   const LayerView& L = p.L;
@@ -955,21 +1001,21 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   const int slot_begin = split * p.slots_per_cta;
   const int slot_end = min(p.capacity, slot_begin + p.slots_per_cta);
 
-  const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
   const int quad = lane >> 2;
   const int sub = lane & 3;
-  __half2 q2[16];
+  uint8_t* const my_gather = s_gather + warp * G::kWarp;
+  float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);  // query channels 4*lane .. 4*lane+3
   if constexpr (MODE != kModePV) {
-    load_query(p, bh, s_qf, s_qh);
-    __syncthreads();
-    const uint4* src = reinterpret_cast<const uint4*>(&s_qh[sub * 32]);
-#pragma unroll
-    for (int v = 0; v < 4; ++v) {
-      const uint4 x = src[v];
-      q2[4 * v + 0] = as_half2(x.x); q2[4 * v + 1] = as_half2(x.y);
-      q2[4 * v + 2] = as_half2(x.z); q2[4 * v + 3] = as_half2(x.w);
-    }
+    s_qf[tid] = __bfloat162float(p.q[bh * kHeadDim + tid]);
+    const uint2 raw = ldg64(p.q + bh * kHeadDim + 4 * lane);
+    q4 = make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
+  }
+  if (tid < 8) {
+    const int s4 = tid & 3;
+    s_base[tid >> 2][s4] = s4 <= p.loop ? ((tid >> 2) ? L.group_base[s4][bh] : L.row_base[s4][bh]) : 0;
   }
 
   OnlineState S;
@@ -979,125 +1025,283 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   const uint8_t* valid_row = p.valid ? p.valid + bh * p.capacity : nullptr;
   const __nv_bfloat16* tk = L.tail_k[p.loop] + bh * L.tail_capacity * kHeadDim;
   const __nv_bfloat16* tv = L.tail_v[p.loop] + bh * L.tail_capacity * kHeadDim;
-
-  // Slots are staged through shared memory in batches: index, validity and the two rank-map
-  // lookups of every slot are fetched by the whole CTA at once, so the gather loop below has a
-  // single level of dependent loads (the rows themselves).
-  constexpr int kSlotBatch = 256;
-  __shared__ int s_idx[kSlotBatch];      // logical index, or -1
-  __shared__ int s_row[2][kSlotBatch];   // rows in streams 2 and 3, or -1
-  __shared__ int64_t s_base[2][4];       // row_base / group_base of this (b,h)
-  if (threadIdx.x < 8) {
-    const int s4 = threadIdx.x & 3;
-    s_base[threadIdx.x >> 2][s4] = s4 <= p.loop ? ((threadIdx.x >> 2) ? L.group_base[s4][bh] : L.row_base[s4][bh]) : 0;
-  }
   __half2 hacc[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) hacc[i] = __floats2half2_rn(0.f, 0.f);
+  int passes = 0;
 
   for (int batch_begin = slot_begin; batch_begin < slot_end; batch_begin += kSlotBatch) {
     const int batch_n = min(kSlotBatch, slot_end - batch_begin);
-    __syncthreads();
-    for (int t = threadIdx.x; t < batch_n; t += kThreads) {
-      const int j = batch_begin + t;
-      int idx = -1;
-      if (!valid_row || valid_row[j]) idx = idx_row[j];
-      int r2 = -1, r3 = -1;
-      if (idx >= 0 && idx < quant) {
-        if (p.loop >= 2) r2 = L.rank[0][L.rank_base[b] + idx];
-        if (p.loop >= 3) r3 = L.rank[1][L.rank_base[b] + idx];
+    __syncthreads();  // the previous round's lists are no longer read
+    // ---- stage this round's slots: index, rank-map rows, run key
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int t = tid + half * kThreads;
+      int idx = -1, r2 = -1, r3 = -1, key = -1;
+      if (t < batch_n) {
+        const int j = batch_begin + t;
+        if (!valid_row || valid_row[j]) idx = idx_row[j];
+        if (idx >= 0 && idx < quant) {
+          key = idx >> 6;
+          if (p.loop >= 2) r2 = L.rank[0][L.rank_base[b] + idx];
+          if (p.loop >= 3) r3 = L.rank[1][L.rank_base[b] + idx];
+        } else if (idx >= quant) {
+          const bool has_current = (MODE == kModePV) ? p.vcur != nullptr : p.kcur != nullptr;
+          if (idx - quant < tail_len || (idx == cur_pos && has_current)) key = kTailKey;
+        }
+        if constexpr (MODE == kModeQK) {
+          if (key < 0) p.logits[bh * p.capacity + j] = 0.f;
+        }
       }
       s_idx[t] = idx;
       s_row[0][t] = r2;
       s_row[1][t] = r3;
+      s_key[t] = key;
     }
     __syncthreads();
-
-    for (int t0 = warp * 8; t0 < batch_n; t0 += kWarps * 8) {
-      const int t = t0 + quad;
-      const bool in_range = t < batch_n;
-      const int j = batch_begin + t;
-      const int idx = in_range ? s_idx[t] : -1;
-      // kind: 0 nothing, 1 packed prefix, 2 tail, 3 current token
-      int kind = 0;
-      const __nv_bfloat16* krow = nullptr;
-      const __nv_bfloat16* vrow = nullptr;
-      if (idx >= 0) {
-        if (idx == cur_pos) {
-          if constexpr (MODE == kModePV) {
-            kind = p.vcur ? 3 : 0;
-          } else {
-            kind = p.kcur ? 3 : 0;
-          }
-          krow = p.kcur ? p.kcur + bh * kHeadDim : nullptr;
-          vrow = p.vcur ? p.vcur + bh * kHeadDim : nullptr;
-        } else if (idx >= quant) {
-          if (idx - quant < tail_len) {
-            kind = 2;
-            const int slot = (tail_start + idx - quant) % L.tail_capacity;
-            krow = tk + slot * kHeadDim;
-            vrow = tv + slot * kHeadDim;
-          }
-        } else {
-          kind = 1;
-        }
+    // ---- runs: maximal ranges of consecutive slots with the same key
+    bool head[2];
+    uint32_t heads[2];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int t = tid + half * kThreads;
+      head[half] = t < batch_n && (t == 0 || s_key[t - 1] != s_key[t]);
+      heads[half] = __ballot_sync(0xffffffffu, head[half]);
+      if (lane == 0) s_warp_runs[half][warp] = __popc(heads[half]);
+    }
+    __syncthreads();
+    int nruns = 0;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      int run_base = 0;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        if (half == 1) run_base += s_warp_runs[0][w];
+        if (w < warp) run_base += s_warp_runs[half][w];
+        nruns += s_warp_runs[half][w];
       }
-      int rows[4];
-      rows[0] = (kind == 1) ? idx : -1;
-      rows[1] = (kind == 1 && p.loop >= 1) ? idx : -1;
-      rows[2] = (kind == 1) ? s_row[0][in_range ? t : 0] : -1;
-      rows[3] = (kind == 1) ? s_row[1][in_range ? t : 0] : -1;
+      if (head[half]) s_run[run_base + __popc(heads[half] & ((1u << lane) - 1u))] = tid + half * kThreads;
+    }
+    if (tid == 0) s_run[nruns] = batch_n;
+    __syncthreads();
 
-      // ---- issue every row load of this token before using any of them
-      Codes<BITS> kc[4], vc[4];
-      uint2 vmeta[4];
+    // ---- the warp's passes: (run, first slot) pairs, walked with one pass of look-ahead
+    struct Pass {
+      int r, t0, run_a, run_e, key;  // r >= nruns: no more passes
+    };
+    auto next_run = [&](Pass& ps) {
+      for (ps.r += kWarps; ps.r < nruns; ps.r += kWarps) {
+        ps.run_a = s_run[ps.r];
+        ps.run_e = s_run[ps.r + 1];
+        ps.key = s_key[ps.run_a];
+        ps.t0 = ps.run_a;
+        if (ps.key >= 0) return;
+      }
+    };
+    auto advance = [&](Pass& ps) {
+      ps.t0 += 8;
+      if (ps.t0 >= ps.run_e) next_run(ps);
+    };
+    // Issue the asynchronous copies of a packed pass into buffer `buf` (one commit group).
+    auto issue = [&](const Pass& ps, int buf) {
+      uint8_t* dst = my_gather + buf * G::kBuffer;
+      const int t = ps.t0 + quad;
+      const bool on = t < ps.run_e;
+      int rows[4];
+      rows[0] = on ? s_idx[t] : -1;
+      rows[1] = p.loop >= 1 ? rows[0] : -1;
+      rows[2] = on ? s_row[0][t] : -1;
+      rows[3] = on ? s_row[1][t] : -1;
 #pragma unroll
       for (int s = 0; s < 4; ++s) {
         if (rows[s] >= 0) {
           const int64_t row = s_base[0][s] + rows[s];
-          if constexpr (MODE != kModePV) kc[s] = load_codes<BITS>(L.k_codes[s] + row * kRowBytes, sub);
+          uint8_t* token = dst + (quad * 4 + s) * G::kToken;
+          if constexpr (MODE != kModePV) {
+            cp_async<kLaneBytes>(token + sub * kLaneBytes, L.k_codes[s] + row * kRowBytes + sub * kLaneBytes);
+          }
           if constexpr (MODE != kModeQK) {
-            vc[s] = load_codes<BITS>(L.v_codes[s] + row * kRowBytes, sub);
-            vmeta[s] = ldg64(L.v_meta[s] + row * 4);
+            const uint8_t* record = L.v_rows[s] + row * G::kRecord;
+            cp_async<kLaneBytes>(token + G::kKBytes + sub * kLaneBytes, record + sub * kLaneBytes);
+            if (sub == 0) cp_async<16>(token + G::kKBytes + kRowBytes, record + kRowBytes);
           }
         }
       }
-
-      float pr = 0.f;
       if constexpr (MODE != kModePV) {
-        float dot = 0.f;
-        if (kind == 1) {
+        if (ps.t0 == ps.run_a) {
+          // first pass of a run: its K metadata (group 0 of every stream) travels with the rows
+          int g0[4] = {ps.key, ps.key, 0, 0};
+          int ng[4] = {1, p.loop >= 1 ? 1 : 0, 0, 0};
+#pragma unroll
+          for (int s = 2; s < 4; ++s) {
+            if (s <= p.loop) {
+              // rows of the run in a compact stream ascend with the slots: first and last present
+              int lo = INT_MAX, hi = -1;
+              for (int u = ps.run_a + lane; u < ps.run_e; u += 32) {
+                const int rr = s_row[s - 2][u];
+                if (rr >= 0) {
+                  lo = min(lo, rr);
+                  hi = max(hi, rr);
+                }
+              }
+              lo = warp_min_int(lo);
+              hi = warp_max_int(hi);
+              g0[s] = hi >= 0 ? lo >> 6 : 0;
+              ng[s] = hi >= 0 ? (hi >> 6) - g0[s] + 1 : 0;
+            }
+          }
+          uint8_t* meta = dst + 8 * 4 * G::kToken;
+#pragma unroll
+          for (int s = 0; s < 4; ++s) {
+            if (ng[s] > 0) {
+              const int64_t g = s_base[1][s] + g0[s];
+              cp_async<8>(meta + s * 512 + lane * 8, L.k_scale[s] + g * kHeadDim + 4 * lane);
+              cp_async<8>(meta + s * 512 + 256 + lane * 8, L.k_min[s] + g * kHeadDim + 4 * lane);
+            }
+            if (lane == 0) {
+              s_g0[warp][buf][s] = g0[s];
+              s_ng[warp][buf][s] = ng[s];
+            }
+          }
+        }
+      }
+      cp_async_commit();
+    };
+
+    Pass cur{warp - kWarps, 0, 0, 0, -1};
+    next_run(cur);
+    int buf = 0;             // the buffer that holds (or will hold) the current packed pass
+    int run_g0[2] = {0, 0};  // first K metadata group of the current run in streams 2 and 3
+    if (cur.r < nruns && cur.key != kTailKey) issue(cur, buf);
+    while (cur.r < nruns) {
+      Pass nxt = cur;
+      advance(nxt);
+      const bool prefetch = nxt.r < nruns && nxt.key != kTailKey;
+      __syncwarp();  // every lane is done with the buffer the next pass is copied into
+      if (prefetch) issue(nxt, buf ^ 1);
+
+      if (cur.key == kTailKey) {
+        // ---- BF16 rows: tail tokens and the current token (read directly)
+        const int t = cur.t0 + quad;
+        const bool on = t < cur.run_e;
+        const int idx = on ? s_idx[t] : -1;
+        const bool is_cur = idx == cur_pos;
+        const int slot = on && !is_cur ? (tail_start + idx - quant) % L.tail_capacity : 0;
+        float pr = 0.f;
+        bool skip_v = false;
+        if constexpr (MODE != kModePV) {
+          const __nv_bfloat16* krow = is_cur ? p.kcur + bh * kHeadDim : tk + slot * kHeadDim;
+          float dot = on ? bf16_row_dot<BITS>(krow, sub, s_qf) : 0.f;
+          dot = quad_sum(dot);
+          if constexpr (MODE == kModeQK) {
+            if (on && sub == 0) p.logits[bh * p.capacity + batch_begin + t] = dot;
+            skip_v = true;
+          } else {
+            if (on && is_cur && p.cur_logits && sub == 0) p.cur_logits[bh] = dot * p.scaling;
+            const float x = on ? dot * p.scaling_log2 : -INFINITY;
+            const float mx = across_quads_max(x);
+            if (mx > S.m) {
+              flush_pairs(hacc, S.acc);  // the float16 partial sums belong to the old maximum
+              state_raise(S, mx);
+            }
+            pr = on ? exp2f(x - S.m) : 0.f;
+            S.l += pr;
+          }
+        } else {
+          pr = on ? p.weights[bh * p.capacity + batch_begin + t] : 0.f;
+        }
+        if constexpr (MODE != kModeQK) {
+          const __nv_bfloat16* vrow = is_cur ? p.vcur + bh * kHeadDim : tv + slot * kHeadDim;
+          if (on && !skip_v) bf16_row_accumulate<BITS>(vrow, sub, pr, S.acc);
+        }
+      } else {
+        // ---- a pass inside one packed 64-token block, from shared memory
+        if (prefetch) cp_async_wait<1>(); else cp_async_wait<0>();
+        __syncwarp();  // a quad shares the V metadata piece that its first lane copied
+        const uint8_t* src = my_gather + buf * G::kBuffer;
+        const int t = cur.t0 + quad;
+        const bool on = t < cur.run_e;
+        int rows[4];
+        rows[0] = on ? s_idx[t] : -1;
+        rows[1] = p.loop >= 1 ? rows[0] : -1;
+        rows[2] = on ? s_row[0][t] : -1;
+        rows[3] = on ? s_row[1][t] : -1;
+
+        float pr = 0.f;
+        if constexpr (MODE != kModePV) {
+          if (cur.t0 == cur.run_a) {
+            // ---- the run's K tables: w_c = q_c * scale_c, bias = sum_c q_c * (min_c + centre * scale_c)
+            __syncwarp();  // every lane has left the previous run: its tables may be overwritten
+            const uint8_t* meta = src + 8 * 4 * G::kToken;
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+              const int ng = s_ng[warp][buf][s];
+              for (int gi = 0; gi < ng && gi < 2; ++gi) {
+                uint2 sc, mn;
+                if (gi == 0) {
+                  sc = *reinterpret_cast<const uint2*>(meta + s * 512 + lane * 8);
+                  mn = *reinterpret_cast<const uint2*>(meta + s * 512 + 256 + lane * 8);
+                } else {
+                  const int64_t g = s_base[1][s] + s_g0[warp][buf][s] + 1;
+                  sc = ldg64(L.k_scale[s] + g * kHeadDim + 4 * lane);
+                  mn = ldg64(L.k_min[s] + g * kHeadDim + 4 * lane);
+                }
+                const float2 sc01 = __half22float2(as_half2(sc.x)), sc23 = __half22float2(as_half2(sc.y));
+                const float2 mn01 = __half22float2(as_half2(mn.x)), mn23 = __half22float2(as_half2(mn.y));
+                const float kcn = float(kCentre<BITS>);
+                float bias = q4.x * fmaf(kcn, sc01.x, mn01.x);
+                bias = fmaf(q4.y, fmaf(kcn, sc01.y, mn01.y), bias);
+                bias = fmaf(q4.z, fmaf(kcn, sc23.x, mn23.x), bias);
+                bias = fmaf(q4.w, fmaf(kcn, sc23.y, mn23.y), bias);
+                __half* tab = &s_wtab[warp][s][gi][(4 * lane) & ~31];
+                const int cc = (4 * lane) & 31;
+                tab[channel_slot<BITS>(cc + 0)] = __float2half_rn(q4.x * sc01.x);
+                tab[channel_slot<BITS>(cc + 1)] = __float2half_rn(q4.y * sc01.y);
+                tab[channel_slot<BITS>(cc + 2)] = __float2half_rn(q4.z * sc23.x);
+                tab[channel_slot<BITS>(cc + 3)] = __float2half_rn(q4.w * sc23.y);
+                bias = 0.25f * warp_sum(bias);  // added in each of the four lanes of a quad
+                if (lane == 0) s_kbias[warp][s][gi] = bias;
+              }
+            }
+            run_g0[0] = s_g0[warp][buf][2];
+            run_g0[1] = s_g0[warp][buf][3];
+            __syncwarp();
+          }
+          float dot = 0.f;
 #pragma unroll
           for (int s = 0; s < 4; ++s) {
             if (rows[s] >= 0) {
-              const int64_t g = s_base[1][s] + (rows[s] >> 6);
-              dot += k_dot_meta<BITS>(kc[s], L.k_scale[s] + g * kHeadDim + sub * 32,
-                                      L.k_min[s] + g * kHeadDim + sub * 32, q2);
+              const int gi = s >= 2 ? min(1, (rows[s] >> 6) - run_g0[s - 2]) : 0;
+              __half2 mult[16];
+              const uint4* tab = reinterpret_cast<const uint4*>(&s_wtab[warp][s][gi][sub * 32]);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                const uint4 x = tab[v];
+                mult[4 * v + 0] = as_half2(x.x); mult[4 * v + 1] = as_half2(x.y);
+                mult[4 * v + 2] = as_half2(x.z); mult[4 * v + 3] = as_half2(x.w);
+              }
+              const Codes<BITS> kc = load_codes_shared<BITS>(src + (quad * 4 + s) * G::kToken + sub * kLaneBytes);
+              dot += k_dot_fast<BITS>(kc, mult) + s_kbias[warp][s][gi];
             }
           }
-        } else if (kind >= 2) {
-          dot = bf16_row_dot<BITS>(krow, sub, s_qf);
+          dot = quad_sum(dot);
+          if constexpr (MODE == kModeQK) {
+            if (on && sub == 0) p.logits[bh * p.capacity + batch_begin + t] = dot;
+          } else {
+            const float x = on ? dot * p.scaling_log2 : -INFINITY;
+            const float mx = across_quads_max(x);
+            if (mx > S.m) {
+              flush_pairs(hacc, S.acc);
+              state_raise(S, mx);
+            }
+            pr = on ? exp2f(x - S.m) : 0.f;
+            S.l += pr;
+          }
+        } else {
+          pr = on ? p.weights[bh * p.capacity + batch_begin + t] : 0.f;
         }
-        dot = quad_sum(dot);
-        if constexpr (MODE == kModeQK) {
-          if (in_range && sub == 0) p.logits[bh * p.capacity + j] = kind ? dot : 0.f;
-          continue;
-        }
-        if (kind == 3 && p.cur_logits && sub == 0) p.cur_logits[bh] = dot * p.scaling;
-        const float x = kind ? dot * p.scaling_log2 : -INFINITY;
-        const float mx = across_quads_max(x);
-        if (mx > S.m) {
-          flush_pairs(hacc, S.acc);  // the float16 partial sums belong to the old maximum
-          state_raise(S, mx);
-        }
-        pr = kind ? exp2f(x - S.m) : 0.f;
-        S.l += pr;
-      } else {
-        pr = kind ? p.weights[bh * p.capacity + j] : 0.f;
-      }
 
-      if constexpr (MODE != kModeQK) {
-        if (kind == 1) {
+        if constexpr (MODE != kModeQK) {
           const uint32_t pick = (sub < 2) ? 0x1010u : 0x3232u;
           const __half2 centre2 = __floats2half2_rn(float(kCentre<BITS>), float(kCentre<BITS>));
           const __half2 p2 = __float2half2_rn(pr);
@@ -1105,23 +1309,31 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
 #pragma unroll
           for (int s = 0; s < 4; ++s) {
             if (rows[s] >= 0) {
-              const __half2 vm2 = as_half2(__byte_perm(vmeta[s].x, 0u, pick));
-              const __half2 vs2 = as_half2(__byte_perm(vmeta[s].y, 0u, pick));
+              const uint8_t* record = src + (quad * 4 + s) * G::kToken + G::kKBytes;
+              const Codes<BITS> vc = load_codes_shared<BITS>(record + sub * kLaneBytes);
+              const uint2 vmeta = *reinterpret_cast<const uint2*>(record + kRowBytes);
+              const __half2 vm2 = as_half2(__byte_perm(vmeta.x, 0u, pick));
+              const __half2 vs2 = as_half2(__byte_perm(vmeta.y, 0u, pick));
               hb = __hfma2(centre2, vs2, __hadd2(vm2, hb));
-              v_accumulate<BITS>(vc[s], __hmul2(p2, vs2), hacc);
+              v_accumulate<BITS>(vc, __hmul2(p2, vs2), hacc);
             }
           }
           S.vbias = fmaf(pr, __low2float(hb), S.vbias);
-        } else if (kind >= 2) {
-          bf16_row_accumulate<BITS>(vrow, sub, pr, S.acc);
+          // at most 4 streams x 4 passes = 16 float16 terms per accumulator before widening
+          if ((++passes & 3) == 0) flush_pairs(hacc, S.acc);
         }
+        buf ^= 1;
       }
-      // at most 4 streams x 4 steps = 16 float16 terms per accumulator before widening
-      if (((t0 / (kWarps * 8)) & 3) == 3) flush_pairs(hacc, S.acc);
+      if (cur.key == kTailKey && prefetch) {
+        // the prefetched pass was issued into buf ^ 1 and the tail pass used no buffer
+        buf ^= 1;
+      }
+      cur = nxt;
     }
+    cp_async_wait<0>();
   }
-  flush_pairs(hacc, S.acc);
   if constexpr (MODE == kModeQK) return;
+  flush_pairs(hacc, S.acc);
 
   state_store<BITS>(S, lane, s_merge[warp]);
   float total, denom;
@@ -1149,7 +1361,9 @@ int choose_chunk_tokens(int64_t batch_heads, int64_t max_context_tokens) {
 }
 
 int choose_slots_per_cta(int64_t batch_heads, int64_t capacity) {
-  const int64_t budget = 148 * 6;
+  // One wave: three CTAs of the gather kernel are resident per SM, so the grid is kept within
+  // 148 * 3 CTAs where the capacity allows it (a second, partial wave would cost a whole round).
+  const int64_t budget = 148 * 3;
   int64_t slots = 32;
   while ((batch_heads * ((capacity + slots - 1) / slots) > budget || (capacity + slots - 1) / slots > kMaxSplits) &&
          slots < capacity)
@@ -1177,11 +1391,11 @@ int validate_layer(const fl_layer* layer, int loop, const char* who) {
   FL_REQUIRE(layer->tail_capacity >= 1, "%s: tail_capacity must be positive", who);
   FL_REQUIRE(layer->seq_state != nullptr, "%s: seq_state is null", who);
   for (int s = 0; s <= loop; ++s) {
-    FL_REQUIRE(layer->k_codes[s] && layer->k_min[s] && layer->k_scale[s] && layer->v_codes[s] &&
-                   layer->v_meta[s] && layer->row_base[s] && layer->group_base[s],
+    FL_REQUIRE(layer->k_codes[s] && layer->k_min[s] && layer->k_scale[s] && layer->v_rows[s] &&
+                   layer->row_base[s] && layer->group_base[s],
                "%s: stream %d has a null pointer", who, s);
-    FL_REQUIRE(aligned16(layer->k_codes[s]) && aligned16(layer->v_codes[s]) && aligned16(layer->k_min[s]) &&
-                   aligned16(layer->k_scale[s]) && aligned16(layer->v_meta[s]),
+    FL_REQUIRE(aligned16(layer->k_codes[s]) && aligned16(layer->v_rows[s]) && aligned16(layer->k_min[s]) &&
+                   aligned16(layer->k_scale[s]),
                "%s: stream %d is not 16-byte aligned", who, s);
   }
   if (loop >= 2) {
@@ -1308,6 +1522,15 @@ extern "C" int fl_dense_source_attention(const fl_layer* layer, int32_t loop, co
 
 namespace {
 
+template <int BITS, int MODE>
+void launch_selected_bits(const dim3 grid, const ReaderParams& p, cudaStream_t s) {
+  constexpr int kSmem = GatherSmem<BITS, MODE>::kWarp * kWarps;
+  static const cudaError_t attr = cudaFuncSetAttribute(
+      selected_reader_kernel<BITS, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  (void)attr;
+  selected_reader_kernel<BITS, MODE><<<grid, kThreads, kSmem, s>>>(p);
+}
+
 template <int MODE>
 int launch_selected(const fl_layer* layer, ReaderParams& p, cudaStream_t s, const char* who) {
   const int64_t bh = static_cast<int64_t>(layer->batch) * layer->heads;
@@ -1315,9 +1538,9 @@ int launch_selected(const fl_layer* layer, ReaderParams& p, cudaStream_t s, cons
   const int splits = (p.capacity + p.slots_per_cta - 1) / p.slots_per_cta;
   const dim3 grid(splits, static_cast<unsigned>(bh));
   if (layer->bits == 4) {
-    selected_reader_kernel<4, MODE><<<grid, kThreads, 0, s>>>(p);
+    launch_selected_bits<4, MODE>(grid, p, s);
   } else {
-    selected_reader_kernel<2, MODE><<<grid, kThreads, 0, s>>>(p);
+    launch_selected_bits<2, MODE>(grid, p, s);
   }
   FL_CHECK_LAUNCH(who);
   return FL_OK;

@@ -27,6 +27,8 @@ extern "C" {
 #define FL_HEAD_DIM 128
 #define FL_GROUP 64
 #define FL_STREAMS 4
+/* bytes of one V record in the cache: codes, 8 bytes of metadata, 8 bytes of padding */
+#define FL_V_RECORD_BYTES(bits) (16 * (bits) + 16)
 #define FL_STATE_WORDS 8
 
 /* status codes */
@@ -59,8 +61,10 @@ typedef void* fl_cuda_stream; /* a cudaStream_t */
  * Streams use the row layout of flashloop/packing.py:49-54, 71-99 (one token per row, even
  * channel in the low nibble; 2-bit rows hold four channels per byte).  K metadata is one
  * float16 minimum and scale per channel per 64-row group (packing.py:146-170); V metadata is
- * one minimum and scale per token per 64-channel group (packing.py:173-197), stored
- * interleaved so that one token's four values share a 8-byte word.
+ * one minimum and scale per token per 64-channel group (packing.py:173-197), stored in the
+ * same record as the token's V codes: a V record is 16*bits bytes of codes, then float16
+ * min0 min1 scale0 scale1, then 8 bytes of padding (FL_V_RECORD_BYTES(bits) in all), so that a
+ * gathered read of one token's V is one contiguous request.
  *
  * Rows of (b, h) in stream s start at row_base[s][b*heads + h]; their K metadata groups start
  * at group_base[s][b*heads + h]; row r belongs to group r / 64.  Streams 2 and 3 hold only
@@ -79,8 +83,7 @@ typedef struct fl_layer {
   void* k_codes[FL_STREAMS];           /* uint8 [rows][16*bits]            */
   void* k_min[FL_STREAMS];             /* float16 [groups][128]            */
   void* k_scale[FL_STREAMS];           /* float16 [groups][128]            */
-  void* v_codes[FL_STREAMS];           /* uint8 [rows][16*bits]            */
-  void* v_meta[FL_STREAMS];            /* float16 [rows][4]: min0 min1 scale0 scale1 */
+  void* v_rows[FL_STREAMS];            /* uint8 [rows][FL_V_RECORD_BYTES(bits)]: codes, metadata */
   const int64_t* row_base[FL_STREAMS]; /* [batch*heads]                    */
   const int64_t* group_base[FL_STREAMS];
   int32_t* rank[2];                    /* streams 2 and 3                  */
