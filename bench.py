@@ -34,6 +34,10 @@ HEADS, HEAD_DIM, CONTEXT, LAYERS, BATCH = 16, 128, 8192, 24, 8
 KEY_FRACTION = 0.10
 SCALING = HEAD_DIM ** -0.5
 METRIC = "decode tok/s (Ouro-1.4B-shape R4)"
+# DRAM bytes per token and stream of the dense reader, from one ncu capture of a smaller case
+# (dram__bytes_read.sum + dram__bytes_write.sum = 165.7 MB for 64 (b,h) x 8128 tokens x 2 streams);
+# every packed byte is read once, so traffic grows in proportion to the tokens a launch covers.
+DENSE_TRAFFIC_PER_TOKEN_STREAM = {4: 165.7e6 / (64 * 8128 * 2)}
 
 
 def parse_args():
@@ -42,16 +46,29 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="hotpath", choices=["hotpath", "e2e"],
+                    help="hotpath: configs[1], the KV-attention path of every layer on synthetic vectors; "
+                         "e2e: configs[3], the Ouro-1.4B-shaped model decoding through the engine")
     ap.add_argument("--layers", type=int, default=LAYERS)
-    ap.add_argument("--batch", type=int, default=BATCH)
-    ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--batch", type=int, default=None, help="sequences per GPU (default 8 hotpath, 16 e2e)")
+    ap.add_argument("--context", type=int, default=None, help="context / prompt length (default 8192 hotpath, 2048 e2e)")
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
-    return ap.parse_args()
+    args = ap.parse_args()
+    if args.batch is None:
+        args.batch = BATCH if args.workload == "hotpath" else 16
+    if args.context is None:
+        args.context = CONTEXT if args.workload == "hotpath" else 2048
+    return args
 
 
 def workload_name(args) -> str:
+    if args.workload == "e2e":
+        return (f"configs[3] end-to-end Ouro-1.4B-shaped decoder (random-init bf16, {args.layers} layers x 4 loops, "
+                f"hidden 2048, {HEADS} heads x {HEAD_DIM}, SwiGLU 5632, vocab 49152): batch {args.batch}/GPU, "
+                f"{args.context}-token random prompts, greedy decode, loops 1-2 dense, 25%/10% token retention, "
+                f"10% key retention, {args.bits}-bit K/V group 64")
     return (f"configs[1] sparse late-loop decode: batch {args.batch}/GPU, {HEADS} heads x {HEAD_DIM}, "
             f"context {args.context}, 4 loops, {args.bits}-bit K/V group 64, 64-token BF16 tail, "
             f"top-10% keys in loops 3-4, {args.layers} layers")
@@ -193,9 +210,10 @@ def run_reference(args) -> None:
     if rank != 0:
         return
     rounds = max(1, min(args.steps, 4))
+    measure = cpu_e2e_tokens_per_second if args.workload == "e2e" else cpu_oracle_tokens_per_second
     for _ in range(min(args.warmup, 1)):
-        cpu_oracle_tokens_per_second(args)
-    results = [cpu_oracle_tokens_per_second(args) for _ in range(rounds)]
+        measure(args)
+    results = [measure(args) for _ in range(rounds)]
     best = max(results, key=lambda r: r["value"])
     line = {
         "impl": "reference", "metric": METRIC, "value": best["value"], "unit": "tok/s", "n_gpus": args.gpus,
@@ -385,7 +403,11 @@ def run_b200(args) -> None:
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "frac_of_nominal_8000": achieved / 8000.0, "peak_source": peak_kind,
                          "algorithmic_bytes_per_launch": algo, "avg_launch_ms": avg_ms,
-                         "launches_timed": len(probe_ms), "traffic": None,
+                         "launches_timed": len(probe_ms),
+                         "traffic": DENSE_TRAFFIC_PER_TOKEN_STREAM[args.bits] * bh * quant * 2
+                         if args.bits in DENSE_TRAFFIC_PER_TOKEN_STREAM else None,
+                         "traffic_source": "ncu dram__bytes_read+write of the batch-4 capture in profiles/"
+                                           "dense_reader_loop2_batch4_ctx8192.md, scaled by (b,h) pairs x tokens",
                          "step_algorithmic_GBps": step_bytes / (ms_total / args.steps * 1e-3) / 1e9},
             "reader_status": status,
         }
@@ -398,10 +420,171 @@ def run_b200(args) -> None:
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------- the end-to-end workload
+
+
+def cpu_e2e_tokens_per_second(args) -> dict:
+    """CPU stand-in for one decode token of the model: the oracle's KV-attention step (per head,
+    scaled) plus the projection / MLP GEMVs of two Ouro-shaped layers in torch on the host cores
+    (scaled to ``layers`` x 4 loops)."""
+
+    import torch
+
+    from flashloop_b200.ouro_shape import OuroShapedConfig, OuroShapedForCausalLM
+    from flashloop_b200.weights import fused_mlp, project_qkv
+
+    kv = cpu_oracle_tokens_per_second(args)
+    torch.set_num_threads(os.cpu_count() or 1)
+    model = OuroShapedForCausalLM(OuroShapedConfig(num_hidden_layers=2, vocab_size=1024), dtype=torch.float32)
+    x = torch.randn(1, 1, 2048)
+    with torch.inference_mode():
+        def layers_once():
+            h = x
+            for layer in model.model.layers:
+                q, _, _ = project_qkv(layer.self_attn, layer.input_layernorm(h))
+                h = h + layer.input_layernorm_2(layer.self_attn.o_proj(q))
+                h = h + layer.post_attention_layernorm_2(fused_mlp(layer.mlp, layer.post_attention_layernorm(h)))
+            return h
+        layers_once()
+        start = time.perf_counter()
+        reps = 5
+        for _ in range(reps):
+            layers_once()
+        per_layer = (time.perf_counter() - start) / reps / 2
+    seconds = 1.0 / kv["value"] + per_layer * args.layers * 4
+    return {"value": 1.0 / seconds, "unit": "tok/s", "cores": kv["cores"], "kind": "port",
+            "sample": (f"KV attention: {kv['sample']}; model side: float32 torch GEMVs of 2 layers on "
+                       f"{os.cpu_count()} threads, {per_layer * 1e3:.2f} ms per layer, scaled by {args.layers} layers x 4 loops")}
+
+
+def run_e2e(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from flashloop_b200 import FlashLoopConfig, FlashLoopEngine, _native, sharding
+    from flashloop_b200.ouro_shape import OuroShapedConfig, OuroShapedForCausalLM
+
+    _native.load()  # fail loudly when the CUDA library is missing
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    B, T, NL = args.batch, args.context, args.layers
+    e2e_steps = max(2, min(args.steps, 16))
+    budget = args.warmup + args.steps + e2e_steps + 8
+    cfg = OuroShapedConfig(num_hidden_layers=NL)
+    model = OuroShapedForCausalLM(cfg, seed=0, device=device)
+    engine = FlashLoopEngine(model, config=FlashLoopConfig(kv_bits=args.bits), validate_model=NL in (24, 48),
+                             max_new_tokens=budget, use_cuda_graph=not args.no_graph)
+    gen = torch.Generator().manual_seed(100 + rank)
+    prompts = torch.randint(0, cfg.vocab_size, (B, T), generator=gen).to(device)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    logits = engine.prefill(prompts).logits
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+    state = {"token": logits.argmax(-1, keepdim=True)}
+
+    def run_step():
+        state["token"] = engine.decode(state["token"]).logits.argmax(-1, keepdim=True)
+
+    def timed(fn, count: int) -> float:
+        sharding.barrier(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(count):
+            fn()
+        e1.record()
+        sharding.barrier(device)
+        return sharding.max_over_ranks(e0.elapsed_time(e1), device)
+
+    for _ in range(args.warmup):
+        run_step()
+    sampler = ClockSampler(local) if rank == 0 else None
+    torch.cuda.profiler.start()
+    ms_total = timed(run_step, args.steps)
+    torch.cuda.profiler.stop()
+    clocks = sampler.stop() if sampler else {}
+    value = sharding.sum_over_ranks(B * args.steps, device) / (ms_total * 1e-3)
+
+    # ---- end to end: token ids come from pinned host memory, the chosen token goes back to it
+    host_token = state["token"].cpu().pin_memory()
+    dev_token = torch.empty_like(state["token"])
+
+    def e2e_step():
+        dev_token.copy_(host_token, non_blocking=True)
+        out = engine.decode(dev_token).logits.argmax(-1, keepdim=True)
+        host_token.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_ms = timed(e2e_step, e2e_steps)
+    e2e_value = sharding.sum_over_ranks(B * e2e_steps, device) / (e2e_ms * 1e-3)
+
+    # ---- the dominant kernel of the path alone: the loop-2 dense reader of every layer
+    layers = engine.state.cache.layers
+    H = cfg.num_attention_heads
+    q, k, v = (torch.randn((B, H, 1, HEAD_DIM), device=device).to(torch.bfloat16) for _ in range(3))
+    probe = []
+    for rep in range(3):
+        for layer in layers:
+            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            layer.dense_source_attention(1, query=q, current_key=k, current_value=v, scaling=SCALING,
+                                         return_logits=True)
+            b_.record()
+            if rep:
+                probe.append((a, b_))
+    torch.cuda.synchronize()
+    probe_ms = [a.elapsed_time(b_) for a, b_ in probe]
+    status = max(layer.reader_status() for layer in layers)
+    quant, tail = layers[0].quantized_tokens, layers[0].tail_tokens
+
+    if rank == 0:
+        peaks_path = ROOT / "MEASURED_PEAKS.json"
+        peaks = json.loads(peaks_path.read_text()) if peaks_path.exists() else {}
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        algo = dense_bytes(B * H, 1, quant, tail, args.bits)
+        avg_ms = statistics.mean(probe_ms)
+        achieved = algo / (avg_ms * 1e-3) / 1e9
+        weights = sum(p.numel() for n, p in model.named_parameters() if "embed" not in n) * 2
+        line = {
+            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": workload_name(args), "global_batch": B * world,
+                       "l2": "inputs larger than L2: each step streams the layer weights four times "
+                             "(%.1f GB) and the packed cache" % (4 * weights / 1e9),
+                       "parallelism": f"batch-data-parallel replicas x{world}, no collective",
+                       "launch": "eager" if args.no_graph else "one CUDA graph replay per step",
+                       "prefill_seconds": prefill_s, "context_at_end": quant + tail},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": int(host_token.numel() * 8),
+                    "d2h_bytes_per_step": int(host_token.numel() * 8), "steps": e2e_steps},
+            "gpu_launches": 9 * NL * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "dense_reader_kernel<%d> (loop 2: anchor + delta-2 streams)" % args.bits,
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback 6650 GB/s",
+                         "algorithmic_bytes_per_launch": algo, "avg_launch_ms": avg_ms,
+                         "launches_timed": len(probe_ms), "traffic": None},
+            "reader_status": status,
+        }
+        if not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_e2e_tokens_per_second(args)
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main() -> None:
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "e2e":
+        run_e2e(args)
     else:
         run_b200(args)
 

@@ -109,16 +109,20 @@ class Backbone(nn.Module):
 
 
 class OuroShapedForCausalLM(nn.Module):
-    """Random-init (normal, std 0.02) four-loop decoder of the given widths."""
+    """Random-init (normal, std 0.02) four-loop decoder of the given widths.  With ``device`` the
+    parameters are created and drawn there (a 1.4B-parameter model takes a second on a GPU)."""
 
-    def __init__(self, cfg: OuroShapedConfig, *, seed: int = 0, dtype: torch.dtype = torch.bfloat16) -> None:
+    def __init__(self, cfg: OuroShapedConfig, *, seed: int = 0, dtype: torch.dtype = torch.bfloat16,
+                 device: str | torch.device | None = None) -> None:
         super().__init__()
         self.config = cfg
-        self.model = Backbone(cfg)
-        self.lm_head = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False)
-        gen = torch.Generator().manual_seed(seed)
+        device = torch.device(device) if device is not None else torch.device("cpu")
+        with torch.device(device):
+            self.model = Backbone(cfg)
+            self.lm_head = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False)
+        self.to(dtype)
+        gen = torch.Generator(device=device).manual_seed(seed)
         with torch.no_grad():
             for name, param in self.named_parameters():
                 if param.ndim >= 2:
-                    param.copy_(torch.randn(param.shape, generator=gen) * 0.02)
-        self.to(dtype)
+                    param.copy_(torch.randn(param.shape, generator=gen, device=device, dtype=torch.float32) * 0.02)
