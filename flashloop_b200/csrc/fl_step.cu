@@ -1,0 +1,219 @@
+// Elementwise glue of one decode step around the KV readers, one launch each instead of the
+// five to eight tensor ops a framework issues: RMSNorm, residual add + RMSNorm (+ the next
+// RMSNorm), the Q/K/V split with rotate-half RoPE, and SwiGLU.
+//
+// These restate the module arithmetic the reference's decode loop calls on an Ouro-style model
+// (flashloop/engine.py:396-437 input_layernorm / project_qkv / _apply_rope, :533-537 the
+// sandwich norms and fused_mlp; flashloop/weights.py:108-117) with the roundings of bfloat16
+// tensor ops: every elementwise result is rounded to bfloat16 where the tensor op would have
+// produced a bfloat16 tensor, reductions run in float32.
+#include "fl_common.cuh"
+
+namespace fl {
+namespace {
+
+constexpr int kStepThreads = 256;
+constexpr int kMaxChunks = 4;  // 8 elements per thread per chunk: rows up to 8192 wide
+
+__device__ __forceinline__ float bf16_round_f(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__device__ __forceinline__ void unpack8(const uint4& x, float (&f)[8]) {
+  const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    f[2 * k] = bf16_lo(w[k]);
+    f[2 * k + 1] = bf16_hi(w[k]);
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+    w[k] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Sum over the CTA; every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* s_part) {
+  v = warp_sum(v);
+  __syncthreads();  // s_part may still be read from a previous call
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int w = 0; w < kStepThreads / 32; ++w) total += s_part[w];
+  return total;
+}
+
+struct NormParams {
+  const __nv_bfloat16* x;         // [rows][width]: the tensor to normalise
+  const __nv_bfloat16* residual;  // [rows][width] or null
+  const __nv_bfloat16* weight;    // [width]
+  const __nv_bfloat16* weight2;   // [width] or null: a second norm applied to the sum
+  float eps, eps2;
+  int width;
+  __nv_bfloat16* out;   // [rows][width]: norm(x) (+ residual)
+  __nv_bfloat16* out2;  // [rows][width] or null: norm2(out)
+};
+
+// out = [residual +] w * bf16(x * rsqrt(mean(x^2) + eps));  out2 = w2 * bf16(out * rsqrt(mean(out^2) + eps2))
+__global__ void __launch_bounds__(kStepThreads) norm_kernel(const NormParams p) {
+  __shared__ float s_part[kStepThreads / 32];
+  const int64_t row = blockIdx.x;
+  const __nv_bfloat16* x = p.x + row * p.width;
+  float v[kMaxChunks][8];
+  float sq = 0.f;
+#pragma unroll
+  for (int c = 0; c < kMaxChunks; ++c) {
+    const int e = (c * kStepThreads + threadIdx.x) * 8;
+    if (e < p.width) {
+      unpack8(ldg128(x + e), v[c]);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) sq = fmaf(v[c][k], v[c][k], sq);
+    }
+  }
+  float inv = rsqrtf(block_sum(sq, s_part) / float(p.width) + p.eps);
+  sq = 0.f;
+#pragma unroll
+  for (int c = 0; c < kMaxChunks; ++c) {
+    const int e = (c * kStepThreads + threadIdx.x) * 8;
+    if (e < p.width) {
+      float w[8], r[8];
+      unpack8(ldg128(p.weight + e), w);
+      if (p.residual) unpack8(ldg128(p.residual + row * p.width + e), r);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        float y = bf16_round_f(w[k] * bf16_round_f(v[c][k] * inv));
+        if (p.residual) y = bf16_round_f(r[k] + y);
+        v[c][k] = y;
+        sq = fmaf(y, y, sq);
+      }
+      *reinterpret_cast<uint4*>(p.out + row * p.width + e) = pack8(v[c]);
+    }
+  }
+  if (p.out2 == nullptr) return;
+  inv = rsqrtf(block_sum(sq, s_part) / float(p.width) + p.eps2);
+#pragma unroll
+  for (int c = 0; c < kMaxChunks; ++c) {
+    const int e = (c * kStepThreads + threadIdx.x) * 8;
+    if (e < p.width) {
+      float w[8];
+      unpack8(ldg128(p.weight2 + e), w);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[c][k] = w[k] * bf16_round_f(v[c][k] * inv);
+      *reinterpret_cast<uint4*>(p.out2 + row * p.width + e) = pack8(v[c]);
+    }
+  }
+}
+
+// One token per row: q/k get rotate-half RoPE, v is copied; outputs are [rows][heads*128].
+__global__ void __launch_bounds__(kStepThreads)
+rope_split_kernel(const __nv_bfloat16* __restrict__ q_in, const __nv_bfloat16* __restrict__ k_in,
+                  const __nv_bfloat16* __restrict__ v_in, int64_t in_stride,
+                  const __nv_bfloat16* __restrict__ cosv, const __nv_bfloat16* __restrict__ sinv, int heads,
+                  __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out,
+                  __nv_bfloat16* __restrict__ v_out) {
+  const int64_t row = blockIdx.x;
+  const int width = heads * kHeadDim;
+  const __nv_bfloat16* cs = cosv + row * kHeadDim;
+  const __nv_bfloat16* sn = sinv + row * kHeadDim;
+  // a thread handles 8 channels of the first half of a head and their partners in the second
+  for (int t = threadIdx.x; t < heads * 8; t += kStepThreads) {
+    const int head = t >> 3, c = (t & 7) * 8;
+    float c1[8], c2[8], s1[8], s2[8];
+    unpack8(ldg128(cs + c), c1);
+    unpack8(ldg128(cs + 64 + c), c2);
+    unpack8(ldg128(sn + c), s1);
+    unpack8(ldg128(sn + 64 + c), s2);
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      const __nv_bfloat16* src = (which ? k_in : q_in) + row * in_stride + head * kHeadDim;
+      __nv_bfloat16* dst = (which ? k_out : q_out) + row * width + head * kHeadDim;
+      float a[8], b[8], lo[8], hi[8];
+      unpack8(ldg128(src + c), a);
+      unpack8(ldg128(src + 64 + c), b);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        // x * cos + rotate_half(x) * sin with rotate_half = (-second half, first half)
+        lo[k] = bf16_round_f(a[k] * c1[k]) + bf16_round_f(-b[k] * s1[k]);
+        hi[k] = bf16_round_f(b[k] * c2[k]) + bf16_round_f(a[k] * s2[k]);
+      }
+      *reinterpret_cast<uint4*>(dst + c) = pack8(lo);
+      *reinterpret_cast<uint4*>(dst + 64 + c) = pack8(hi);
+    }
+  }
+  for (int e = threadIdx.x * 8; e < width; e += kStepThreads * 8) {
+    *reinterpret_cast<uint4*>(v_out + row * width + e) = ldg128(v_in + row * in_stride + e);
+  }
+}
+
+// out = bf16(silu(gate)) * up, gate_up = [rows][2 * width]
+__global__ void __launch_bounds__(kStepThreads)
+swiglu_kernel(const __nv_bfloat16* __restrict__ gate_up, int width, __nv_bfloat16* __restrict__ out) {
+  const int64_t row = blockIdx.y;
+  const int e = (blockIdx.x * kStepThreads + threadIdx.x) * 8;
+  if (e >= width) return;
+  float g[8], u[8];
+  unpack8(ldg128(gate_up + row * 2 * width + e), g);
+  unpack8(ldg128(gate_up + row * 2 * width + width + e), u);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) g[k] = bf16_round_f(g[k] / (1.f + expf(-g[k]))) * u[k];
+  *reinterpret_cast<uint4*>(out + row * width + e) = pack8(g);
+}
+
+}  // namespace
+}  // namespace fl
+
+using namespace fl;
+
+extern "C" int fl_rmsnorm(const void* x, const void* residual, const void* weight, float eps,
+                          const void* weight2, float eps2, int64_t rows, int32_t width, void* out, void* out2,
+                          fl_cuda_stream stream) {
+  FL_REQUIRE(x && weight && out, "fl_rmsnorm: null argument");
+  FL_REQUIRE(rows >= 0 && width > 0 && width % 8 == 0 && width <= kMaxChunks * kStepThreads * 8,
+             "fl_rmsnorm: width must be a multiple of 8 up to %d, got %d", kMaxChunks * kStepThreads * 8, width);
+  FL_REQUIRE((weight2 == nullptr) == (out2 == nullptr), "fl_rmsnorm: weight2 and out2 go together");
+  FL_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(out) && aligned16(residual) && aligned16(weight2) &&
+                 aligned16(out2),
+             "fl_rmsnorm: pointers must be 16-byte aligned");
+  if (rows == 0) return FL_OK;
+  NormParams p{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
+               static_cast<const __nv_bfloat16*>(weight), static_cast<const __nv_bfloat16*>(weight2),
+               eps, eps2, width, static_cast<__nv_bfloat16*>(out), static_cast<__nv_bfloat16*>(out2)};
+  norm_kernel<<<static_cast<unsigned>(rows), kStepThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  FL_CHECK_LAUNCH("fl_rmsnorm");
+  return FL_OK;
+}
+
+extern "C" int fl_rope_split(const void* q_in, const void* k_in, const void* v_in, int64_t in_stride,
+                             const void* cosv, const void* sinv, int64_t rows, int32_t heads, void* q_out,
+                             void* k_out, void* v_out, fl_cuda_stream stream) {
+  FL_REQUIRE(q_in && k_in && v_in && cosv && sinv && q_out && k_out && v_out, "fl_rope_split: null argument");
+  FL_REQUIRE(rows >= 0 && heads > 0 && in_stride >= heads * kHeadDim && in_stride % 8 == 0,
+             "fl_rope_split: bad sizes");
+  FL_REQUIRE(aligned16(q_in) && aligned16(k_in) && aligned16(v_in) && aligned16(cosv) && aligned16(sinv) &&
+                 aligned16(q_out) && aligned16(k_out) && aligned16(v_out),
+             "fl_rope_split: pointers must be 16-byte aligned");
+  if (rows == 0) return FL_OK;
+  rope_split_kernel<<<static_cast<unsigned>(rows), kStepThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(q_in), static_cast<const __nv_bfloat16*>(k_in),
+      static_cast<const __nv_bfloat16*>(v_in), in_stride, static_cast<const __nv_bfloat16*>(cosv),
+      static_cast<const __nv_bfloat16*>(sinv), heads, static_cast<__nv_bfloat16*>(q_out),
+      static_cast<__nv_bfloat16*>(k_out), static_cast<__nv_bfloat16*>(v_out));
+  FL_CHECK_LAUNCH("fl_rope_split");
+  return FL_OK;
+}
+
+extern "C" int fl_swiglu(const void* gate_up, int64_t rows, int32_t width, void* out, fl_cuda_stream stream) {
+  FL_REQUIRE(gate_up && out, "fl_swiglu: null argument");
+  FL_REQUIRE(rows >= 0 && rows <= 65535 && width > 0 && width % 8 == 0, "fl_swiglu: bad sizes");
+  FL_REQUIRE(aligned16(gate_up) && aligned16(out), "fl_swiglu: pointers must be 16-byte aligned");
+  if (rows == 0) return FL_OK;
+  const dim3 grid((width / 8 + kStepThreads - 1) / kStepThreads, static_cast<unsigned>(rows));
+  swiglu_kernel<<<grid, kStepThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate_up), width, static_cast<__nv_bfloat16*>(out));
+  FL_CHECK_LAUNCH("fl_swiglu");
+  return FL_OK;
+}

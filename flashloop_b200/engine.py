@@ -25,6 +25,7 @@ from .compaction import RetainedTokens, hidden_delta_score, retain_tokens
 from .config import FlashLoopConfig, validate_ouro_model
 from .selection import decode_budget
 from .prefill import PrefillReceipt, apply_rope, dense_prefill_loop, sparse_prefill_loop
+from . import step_ops
 from .weights import fused_mlp, project_qkv, repack_projection_weights
 
 
@@ -63,7 +64,7 @@ class FlashLoopEngine:
 
     def __init__(self, model: torch.nn.Module, *, config: FlashLoopConfig | None = None,
                  validate_model: bool = True, max_new_tokens: int = 512, use_cuda_graph: bool = False,
-                 reference_loop4_scores: bool = True) -> None:
+                 reference_loop4_scores: bool = True, fuse_decode_ops: bool = True) -> None:
         if validate_model:
             validate_ouro_model(model)
         elif int(getattr(model.config, "total_ut_steps", 0)) != 4:
@@ -77,6 +78,7 @@ class FlashLoopEngine:
         self.max_new_tokens = int(max_new_tokens)
         self.use_cuda_graph = bool(use_cuda_graph)
         self.reference_loop4_scores = bool(reference_loop4_scores)
+        self.fuse_decode_ops = bool(fuse_decode_ops) and self._modules_are_fusable()
         self._state: EngineState | None = None
         self._graph = None
         self._graph_io = None
@@ -174,11 +176,110 @@ class FlashLoopEngine:
 
     # ------------------------------------------------------------------ decode
 
+    @staticmethod
+    def _norm_eps(norm) -> float | None:
+        for name in ("eps", "variance_epsilon"):
+            if hasattr(norm, name):
+                return float(getattr(norm, name))
+        return None
+
+    def _modules_are_fusable(self) -> bool:
+        """True when every layer is the plain Ouro block the one-launch glue kernels restate:
+        weight-only RMSNorms, repacked bias-free projections, SiLU-gated MLP, equal Q/K/V widths."""
+
+        norms = [self.backbone.norm]
+        for layer in self.layers:
+            attention, mlp = layer.self_attn, layer.mlp
+            if not hasattr(attention, "_flashloop_qkv_weight") or not hasattr(mlp, "_flashloop_gate_up_weight"):
+                return False
+            if len(set(attention._flashloop_qkv_splits)) != 1 or len(set(mlp._flashloop_gate_up_splits)) != 1:
+                return False
+            if int(attention.head_dim) != 128 or "silu" not in type(mlp.act_fn).__name__.lower():
+                return False
+            if attention.o_proj.bias is not None or mlp.down_proj.bias is not None:
+                return False
+            norms += [layer.input_layernorm, layer.input_layernorm_2, layer.post_attention_layernorm,
+                      layer.post_attention_layernorm_2]
+        for norm in norms:
+            weight = getattr(norm, "weight", None)
+            if weight is None or weight.dtype != torch.bfloat16 or getattr(norm, "bias", None) is not None:
+                return False
+            if self._norm_eps(norm) is None or len(list(norm.parameters())) != 1:
+                return False
+        return True
+
     def _decode_step(self, token_ids: torch.Tensor, position_ids: torch.Tensor) -> torch.Tensor:
         """The device work of one decode step; returns float32 logits [B, vocab]."""
 
+        if self.fuse_decode_ops and token_ids.is_cuda:
+            return self._decode_step_fused(token_ids, position_ids)
+        return self._decode_step_modules(token_ids, position_ids)
+
+    def _attend(self, loop: int, index: int, q, k, v, scaling: float, sources: list, o_proj, batch: int):
+        """The cache-facing part of one layer and loop (engine.py:422-531): returns the projected
+        attention output [B, 1, hidden]."""
+
+        physical = self.state.cache.layers[index]
+        if loop < 2 or not self.config.enable_sparse_decode:
+            want_logits = loop == 1 and self.config.enable_sparse_decode
+            out, logits = physical.dense_source_attention(loop, query=q, current_key=k, current_value=v,
+                                                          scaling=scaling, return_logits=want_logits)
+            projected = o_proj(out.to(q.dtype).view(batch, 1, -1))
+            if want_logits:
+                sel = physical.select_decode_keys(logits, fraction=self.config.effective_decode_key_fraction)
+                aggregate = physical.pv(1, sel.selected_weights, sel.indices, current_value=v,
+                                        valid=sel.valid, validate_indices=False)
+                sources[index] = (projected, sel, aggregate)
+            return projected
+        projected0, sel, aggregate = sources[index]
+        delta = physical.cached_mass_sparse_attention_delta(
+            loop, query=q, current_key=k, current_value=v, indices=sel.indices, valid=sel.valid,
+            source_selected_output=aggregate, global_mass=sel.global_mass, scaling=scaling)
+        return projected0 + o_proj(delta.to(v.dtype).view(batch, 1, -1))
+
+    def _decode_step_fused(self, token_ids: torch.Tensor, position_ids: torch.Tensor) -> torch.Tensor:
+        """One decode step with the elementwise glue as one-launch kernels (``step_ops``): per layer
+        and loop four GEMMs, the Q/K/V split + RoPE, the readers, two add + norm launches and
+        SwiGLU.  Same arithmetic, op by op, as :meth:`_decode_step_modules`."""
+
+        F = torch.nn.functional
         cache = self.state.cache
-        fraction = self.config.effective_decode_key_fraction
+        hidden = self.backbone.embed_tokens(token_ids)
+        batch = int(token_ids.shape[0])
+        cos, sin = self.backbone.rotary_emb(hidden, position_ids)
+        cos, sin = cos.contiguous(), sin.contiguous()
+        n_layers = len(self.layers)
+        keys = [[None] * 4 for _ in range(n_layers)]
+        values = [[None] * 4 for _ in range(n_layers)]
+        sources = [None] * n_layers
+        eps = self._norm_eps
+        first = self.layers[0].input_layernorm
+        for loop in range(4):
+            x = step_ops.rmsnorm(hidden, first.weight, eps(first))
+            for index, layer in enumerate(self.layers):
+                attention, mlp = layer.self_attn, layer.mlp
+                q, k, v = F.linear(x, attention._flashloop_qkv_weight).split(attention._flashloop_qkv_splits, dim=-1)
+                heads = q.shape[-1] // 128
+                q, k, v = step_ops.rope_split(q, k, v, cos, sin, heads=heads)
+                keys[index][loop], values[index][loop] = k, v
+                projected = self._attend(loop, index, q, k, v, float(attention.scaling), sources,
+                                         attention.o_proj, batch)
+                n2, n3, n4 = layer.input_layernorm_2, layer.post_attention_layernorm, layer.post_attention_layernorm_2
+                hidden, x = step_ops.rmsnorm(projected, n2.weight, eps(n2), residual=hidden,
+                                             weight2=n3.weight, eps2=eps(n3))
+                m = mlp.down_proj(step_ops.swiglu(F.linear(x, mlp._flashloop_gate_up_weight)))
+                following = self.backbone.norm if index == n_layers - 1 else self.layers[index + 1].input_layernorm
+                hidden, x = step_ops.rmsnorm(m, n4.weight, eps(n4), residual=hidden,
+                                             weight2=following.weight, eps2=eps(following))
+            hidden = x  # the final norm of this loop
+        for index in range(n_layers):
+            cache.layers[index].append_decode_token(keys[index], values[index])
+        return self.model.lm_head(hidden[:, -1]).float()
+
+    def _decode_step_modules(self, token_ids: torch.Tensor, position_ids: torch.Tensor) -> torch.Tensor:
+        """One decode step through the model's own modules (any Ouro-style block)."""
+
+        cache = self.state.cache
         hidden = self.backbone.embed_tokens(token_ids)
         batch = int(token_ids.shape[0])
         cos, sin = self.backbone.rotary_emb(hidden, position_ids)
@@ -190,7 +291,6 @@ class FlashLoopEngine:
             for index, layer in enumerate(self.layers):
                 attention = layer.self_attn
                 head_dim = int(attention.head_dim)
-                physical = cache.layers[index]
                 q, k, v = project_qkv(attention, layer.input_layernorm(hidden))
                 heads = q.shape[-1] // head_dim
                 q = q.view(batch, 1, heads, head_dim).transpose(1, 2)
@@ -199,24 +299,8 @@ class FlashLoopEngine:
                 q, k = apply_rope(q, k, cos, sin)
                 q, k = q.contiguous(), k.contiguous()
                 keys[index][loop], values[index][loop] = k, v
-                scaling = float(attention.scaling)
-                if loop < 2 or not self.config.enable_sparse_decode:
-                    want_logits = loop == 1 and self.config.enable_sparse_decode
-                    out, logits = physical.dense_source_attention(loop, query=q, current_key=k, current_value=v,
-                                                                  scaling=scaling, return_logits=want_logits)
-                    projected = attention.o_proj(out.to(q.dtype).transpose(1, 2).reshape(batch, 1, -1))
-                    if want_logits:
-                        sel = physical.select_decode_keys(logits, fraction=fraction)
-                        aggregate = physical.pv(1, sel.selected_weights, sel.indices, current_value=v,
-                                                valid=sel.valid, validate_indices=False)
-                        sources[index] = (projected, sel, aggregate)
-                else:
-                    projected0, sel, aggregate = sources[index]
-                    delta = physical.cached_mass_sparse_attention_delta(
-                        loop, query=q, current_key=k, current_value=v, indices=sel.indices, valid=sel.valid,
-                        source_selected_output=aggregate, global_mass=sel.global_mass, scaling=scaling)
-                    projected = projected0 + attention.o_proj(
-                        delta.to(v.dtype).transpose(1, 2).reshape(batch, 1, -1))
+                projected = self._attend(loop, index, q, k, v, float(attention.scaling), sources,
+                                         attention.o_proj, batch)
                 residual = hidden
                 hidden = residual + layer.input_layernorm_2(projected)
                 hidden = hidden + layer.post_attention_layernorm_2(

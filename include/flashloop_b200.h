@@ -293,6 +293,31 @@ int fl_scatter_rows(void* full, const void* compact, const int32_t* positions, c
                     int64_t positions_stride, int64_t outer, int32_t per_sequence, int64_t full_rows,
                     int64_t compact_rows, int32_t row_bytes, fl_cuda_stream stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Elementwise glue of one decode step around the readers (bfloat16 rows, one token per row).
+ * Each restates module arithmetic of the reference's decode loop with the roundings of
+ * bfloat16 tensor ops and replaces five to eight framework launches by one.
+ * ------------------------------------------------------------------------------------- */
+
+/* The RMSNorm modules of flashloop/engine.py:396 (input_layernorm) and :533-537 (the sandwich
+ * norms around attention and MLP):  out = [residual +] weight * bf16(x * rsqrt(mean(x^2) + eps));
+ * with weight2/out2 also out2 = weight2 * bf16(out * rsqrt(mean(out^2) + eps2)), i.e. the next
+ * norm of the residual stream in the same launch.  x, residual, out, out2: [rows][width]. */
+int fl_rmsnorm(const void* x, const void* residual, const void* weight, float eps, const void* weight2,
+               float eps2, int64_t rows, int32_t width, void* out, void* out2, fl_cuda_stream stream);
+
+/* The view/transpose of the Q/K/V projections and _apply_rope (flashloop/engine.py:59-75,
+ * 410-419) for one token per row: q_out/k_out = x * cos + rotate_half(x) * sin, v_out = v.
+ * q_in/k_in/v_in: rows of heads*128 values, in_stride elements apart (three slices of one
+ * fused projection or three separate tensors); cos/sin [rows][128]; outputs [rows][heads*128]. */
+int fl_rope_split(const void* q_in, const void* k_in, const void* v_in, int64_t in_stride, const void* cosv,
+                  const void* sinv, int64_t rows, int32_t heads, void* q_out, void* k_out, void* v_out,
+                  fl_cuda_stream stream);
+
+/* fused_mlp's activation (flashloop/weights.py:108-117): out = bf16(silu(gate)) * up with
+ * gate_up = [rows][2*width] (gate then up), out [rows][width]. */
+int fl_swiglu(const void* gate_up, int64_t rows, int32_t width, void* out, fl_cuda_stream stream);
+
 #ifdef __cplusplus
 }
 #endif
