@@ -46,10 +46,11 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="hotpath", choices=["hotpath", "e2e"],
+    ap.add_argument("--workload", default="hotpath", choices=["hotpath", "ragged", "e2e"],
                     help="hotpath: configs[1], the KV-attention path of every layer on synthetic vectors; "
+                         "ragged: configs[2], the same path over 32 sequences of 1024..32768 tokens (one layer); "
                          "e2e: configs[3], the Ouro-1.4B-shaped model decoding through the engine")
-    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--layers", type=int, default=None, help="physical layers (default 24; 1 for ragged)")
     ap.add_argument("--batch", type=int, default=None, help="sequences per GPU (default 8 hotpath, 16 e2e)")
     ap.add_argument("--context", type=int, default=None, help="context / prompt length (default 8192 hotpath, 2048 e2e)")
     ap.add_argument("--bits", type=int, default=4)
@@ -57,9 +58,11 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.batch is None:
-        args.batch = BATCH if args.workload == "hotpath" else 16
+        args.batch = {"hotpath": BATCH, "ragged": 32, "e2e": 16}[args.workload]
     if args.context is None:
-        args.context = CONTEXT if args.workload == "hotpath" else 2048
+        args.context = {"hotpath": CONTEXT, "ragged": 32768, "e2e": 2048}[args.workload]
+    if args.layers is None:
+        args.layers = 1 if args.workload == "ragged" else LAYERS
     return args
 
 
@@ -69,6 +72,10 @@ def workload_name(args) -> str:
                 f"hidden 2048, {HEADS} heads x {HEAD_DIM}, SwiGLU 5632, vocab 49152): batch {args.batch}/GPU, "
                 f"{args.context}-token random prompts, greedy decode, loops 1-2 dense, 25%/10% token retention, "
                 f"10% key retention, {args.bits}-bit K/V group 64")
+    if args.workload == "ragged":
+        return (f"configs[2] ragged batched decode: batch {args.batch}/GPU, context lengths uniform in "
+                f"[1024, {args.context}] (seeded), {HEADS} heads x {HEAD_DIM}, 4 loops, {args.bits}-bit K/V group 64, "
+                f"64-token BF16 tail, top-10% keys in loops 3-4, {args.layers} layer(s)")
     return (f"configs[1] sparse late-loop decode: batch {args.batch}/GPU, {HEADS} heads x {HEAD_DIM}, "
             f"context {args.context}, 4 loops, {args.bits}-bit K/V group 64, 64-token BF16 tail, "
             f"top-10% keys in loops 3-4, {args.layers} layers")
@@ -250,21 +257,21 @@ def run_b200(args) -> None:
     steps_total = args.warmup + args.steps
     # ---- build the cache: NL layers, B sequences (seed distinct per rank / sequence / layer)
     layers = []
-    ones = torch.ones(B, T, dtype=torch.bool, device=device)
+    if args.workload == "ragged":
+        lengths = torch.randint(1024, T + 1, (B,), generator=torch.Generator().manual_seed(rank)).tolist()
+    else:
+        lengths = [T] * B
     for layer_index in range(NL):
-        keys = [[] for _ in range(4)]
-        values = [[] for _ in range(4)]
+        sequences = []
         for b in range(B):
-            k, v = make_loop_kv(H, T, seed=sharding.sequence_seed(rank, layer_index, b), device=device)
-            for r in range(4):
-                keys[r].append(k[r])
-                values[r].append(v[r])
-        keys = [torch.cat(k) for k in keys]
-        values = [torch.cat(v) for v in values]
-        layers.append(CrossLoopKVLayer.from_prefill(keys, values, mask_loop3=ones, mask_loop4=ones,
-                                                    bits=args.bits, max_new_tokens=2 * steps_total + 192))
-        del keys, values
-    quant, tail = layers[0].quantized_tokens, layers[0].tail_tokens
+            k, v = make_loop_kv(H, lengths[b], seed=sharding.sequence_seed(rank, layer_index, b), device=device)
+            ones = torch.ones(lengths[b], dtype=torch.bool, device=device)
+            sequences.append((k, v, ones, ones))
+        layers.append(CrossLoopKVLayer.from_prefill_ragged(sequences, bits=args.bits,
+                                                           max_new_tokens=2 * steps_total + 192))
+        del sequences
+    quants = [layers[0].quantized_tokens_of(b) for b in range(B)]
+    tails = [layers[0].tail_tokens_of(b) for b in range(B)]
 
     # ---- per-step inputs: query / current K / current V of every (layer, loop), bf16
     gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
@@ -274,7 +281,7 @@ def run_b200(args) -> None:
     host_out = torch.empty(out.shape, dtype=torch.float32).pin_memory()
     probe = []  # CUDA event pairs around the dominant kernel (dense reader, loop 2)
 
-    bound = T + steps_total + 64
+    bound = max(lengths) + steps_total + 64
     for layer in layers:
         layer.context_bound = bound  # fixed launch geometry: the step can be replayed as a CUDA graph
     kernels_per_layer = 9  # 2 dense + select + selected PV + 2 sparse + 3 append/rollover/state
@@ -379,13 +386,15 @@ def run_b200(args) -> None:
         peak = float(peaks.get("hbm_gbs", 6650.0))
         peak_kind = "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback 6650 GB/s"
         bh = B * H
-        algo = dense_bytes(bh, 1, quant, tail, args.bits)
+        algo = sum(dense_bytes(H, 1, q_, t_, args.bits) for q_, t_ in zip(quants, tails))
         avg_ms = statistics.mean(probe_ms) if probe_ms else float("nan")
         achieved = algo / (avg_ms * 1e-3) / 1e9
-        keys = math.ceil((T + 1) * KEY_FRACTION)
-        step_bytes = NL * (dense_bytes(bh, 0, quant, tail, args.bits) + algo
-                           + sparse_bytes(bh, 1, keys, quant, args.bits) - bh * 1280  # selected PV, loop 2
-                           + sparse_bytes(bh, 2, keys, quant, args.bits) + sparse_bytes(bh, 3, keys, quant, args.bits))
+        step_bytes = 0
+        for q_, t_ in zip(quants, tails):
+            keys = math.ceil((q_ + t_ + 1) * KEY_FRACTION)
+            step_bytes += NL * (dense_bytes(H, 0, q_, t_, args.bits) + dense_bytes(H, 1, q_, t_, args.bits)
+                                + sparse_bytes(H, 1, keys, q_, args.bits) - H * 1280  # selected PV, loop 2
+                                + sparse_bytes(H, 2, keys, q_, args.bits) + sparse_bytes(H, 3, keys, q_, args.bits))
         line = {
             "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
@@ -404,7 +413,7 @@ def run_b200(args) -> None:
                          "frac_of_nominal_8000": achieved / 8000.0, "peak_source": peak_kind,
                          "algorithmic_bytes_per_launch": algo, "avg_launch_ms": avg_ms,
                          "launches_timed": len(probe_ms),
-                         "traffic": DENSE_TRAFFIC_PER_TOKEN_STREAM[args.bits] * bh * quant * 2
+                         "traffic": DENSE_TRAFFIC_PER_TOKEN_STREAM[args.bits] * H * sum(quants) * 2
                          if args.bits in DENSE_TRAFFIC_PER_TOKEN_STREAM else None,
                          "traffic_source": "ncu dram__bytes_read+write of the batch-4 capture in profiles/"
                                            "dense_reader_loop2_batch4_ctx8192.md, scaled by (b,h) pairs x tokens",
@@ -540,7 +549,8 @@ def run_e2e(args) -> None:
     torch.cuda.synchronize()
     probe_ms = [a.elapsed_time(b_) for a, b_ in probe]
     status = max(layer.reader_status() for layer in layers)
-    quant, tail = layers[0].quantized_tokens, layers[0].tail_tokens
+    quants = [layers[0].quantized_tokens_of(b) for b in range(B)]
+    tails = [layers[0].tail_tokens_of(b) for b in range(B)]
 
     if rank == 0:
         peaks_path = ROOT / "MEASURED_PEAKS.json"
