@@ -549,8 +549,7 @@ def run_e2e(args) -> None:
     torch.cuda.synchronize()
     probe_ms = [a.elapsed_time(b_) for a, b_ in probe]
     status = max(layer.reader_status() for layer in layers)
-    quants = [layers[0].quantized_tokens_of(b) for b in range(B)]
-    tails = [layers[0].tail_tokens_of(b) for b in range(B)]
+    quant, tail = layers[0].quantized_tokens, layers[0].tail_tokens
 
     if rank == 0:
         peaks_path = ROOT / "MEASURED_PEAKS.json"

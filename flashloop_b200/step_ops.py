@@ -74,3 +74,4 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     _native.check(_native.load().fl_swiglu(_native.ptr(gate_up), rows, double // 2, _native.ptr(out),
                                            _native.current_stream(gate_up.device)), "fl_swiglu")
     return out
+

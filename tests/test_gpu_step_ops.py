@@ -104,3 +104,4 @@ def test_unfusable_model_falls_back_to_modules():
     model = tiny_ouro_model().cuda()
     model.model.layers[0].mlp.act_fn = torch.nn.GELU()
     assert FlashLoopEngine(model, validate_model=False).fuse_decode_ops is False
+
