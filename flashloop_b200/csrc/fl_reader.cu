@@ -73,19 +73,6 @@ struct Codes<2> {
 };
 
 template <int BITS>
-__device__ __forceinline__ Codes<BITS> load_codes(const uint8_t* row, int sub) {
-  Codes<BITS> c;
-  if constexpr (BITS == 4) {
-    const uint4 v = ldg128(row + sub * 16);
-    c.w[0] = v.x; c.w[1] = v.y; c.w[2] = v.z; c.w[3] = v.w;
-  } else {
-    const uint2 v = ldg64(row + sub * 8);
-    c.w[0] = v.x; c.w[1] = v.y;
-  }
-  return c;
-}
-
-template <int BITS>
 __device__ __forceinline__ Codes<BITS> load_codes_shared(const uint8_t* piece) {
   Codes<BITS> c;
   if constexpr (BITS == 4) {
@@ -154,39 +141,6 @@ __device__ __forceinline__ void unpack_centred(const Codes<BITS>& c, __half2 (&h
   }
 }
 
-// The lane's 32 codes as 16 half2 of exact integers in natural channel order (2k, 2k+1).
-template <int BITS>
-__device__ __forceinline__ void unpack_natural(const Codes<BITS>& c, __half2 (&h)[16]) {
-  if constexpr (BITS == 4) {
-    const __half2 kMul = __floats2half2_rn(1.f, 0.0625f);
-    const __half2 kAdd = __floats2half2_rn(-1024.f, -64.f);
-#pragma unroll
-    for (int wd = 0; wd < 4; ++wd) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        // bytes [b_j, 0x64, b_j, 0x64]; keep the low nibble in the low half, the high nibble
-        // in the high half: {1024 + n_even, 1024 + 16 * n_odd}.
-        const uint32_t v = __byte_perm(c.w[wd], 0x64646464u, 0x4040u | (j << 8) | j) & 0xFFF0FF0Fu;
-        h[4 * wd + j] = __hfma2(as_half2(v), kMul, kAdd);
-      }
-    }
-  } else {
-    const __half2 kMulA = __floats2half2_rn(1.f, 0.25f);
-    const __half2 kAddA = __floats2half2_rn(-1024.f, -256.f);
-    const __half2 kMulB = __floats2half2_rn(0.0625f, 0.015625f);
-    const __half2 kAddB = __floats2half2_rn(-64.f, -16.f);
-#pragma unroll
-    for (int wd = 0; wd < 2; ++wd) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t rep = __byte_perm(c.w[wd], 0x64646464u, 0x4040u | (j << 8) | j);
-        h[8 * wd + 2 * j + 0] = __hfma2(as_half2(rep & 0xFF0CFF03u), kMulA, kAddA);
-        h[8 * wd + 2 * j + 1] = __hfma2(as_half2(rep & 0xFFC0FF30u), kMulB, kAddB);
-      }
-    }
-  }
-}
-
 // K, fast path: sum over the lane's 32 channels of w_c * (code_c - centre).
 template <int BITS>
 __device__ __forceinline__ float k_dot_fast(const Codes<BITS>& c, const __half2 (&mult)[16]) {
@@ -198,34 +152,6 @@ __device__ __forceinline__ float k_dot_fast(const Codes<BITS>& c, const __half2 
   for (int p = 2; p < 16; p += 2) {
     a0 = __hfma2(h[p], mult[p], a0);
     a1 = __hfma2(h[p + 1], mult[p + 1], a1);
-  }
-  const float2 f0 = __half22float2(a0);
-  const float2 f1 = __half22float2(a1);
-  return (f0.x + f0.y) + (f1.x + f1.y);
-}
-
-// K, gather path: dequantise the lane's 32 channels against metadata read from memory
-// (natural channel order) and dot them with the query.
-template <int BITS>
-__device__ __forceinline__ float k_dot_meta(const Codes<BITS>& c, const __half* __restrict__ scale,
-                                            const __half* __restrict__ minimum,
-                                            const __half2 (&q2)[16]) {
-  __half2 h[16];
-  unpack_natural<BITS>(c, h);
-  __half2 a0 = __floats2half2_rn(0.f, 0.f), a1 = a0;
-#pragma unroll
-  for (int v = 0; v < 4; ++v) {
-    const uint4 s4 = ldg128(scale + 8 * v);
-    const uint4 m4 = ldg128(minimum + 8 * v);
-    const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w};
-    const uint32_t mw[4] = {m4.x, m4.y, m4.z, m4.w};
-#pragma unroll
-    for (int k = 0; k < 4; k += 2) {
-      const __half2 k0 = __hfma2(h[4 * v + k], as_half2(sw[k]), as_half2(mw[k]));
-      const __half2 k1 = __hfma2(h[4 * v + k + 1], as_half2(sw[k + 1]), as_half2(mw[k + 1]));
-      a0 = __hfma2(k0, q2[4 * v + k], a0);
-      a1 = __hfma2(k1, q2[4 * v + k + 1], a1);
-    }
   }
   const float2 f0 = __half22float2(a0);
   const float2 f1 = __half22float2(a1);
@@ -973,6 +899,7 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   using G = GatherSmem<BITS, MODE>;
   constexpr int kRowBytes = G::kRowBytes;
   constexpr int kLaneBytes = kRowBytes / 4;
+  constexpr uint32_t kFull = 0xffffffffu;
   extern __shared__ __align__(128) uint8_t s_gather[];  // [warp][2][rows of 8 tokens x 4 streams | K metadata]
   __shared__ __align__(16) float s_qf[kHeadDim];
   __shared__ __align__(16) __half s_wtab[kWarps][4][2][kHeadDim];
@@ -981,11 +908,10 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   __shared__ int s_ng[kWarps][2][4];      // ... and how many groups (0, 1 or 2) its rows touch
   __shared__ __align__(16) float s_merge[kWarps][kPartialStride];
   __shared__ int s_idx[kSlotBatch];       // logical index, or -1
-  __shared__ int s_row[2][kSlotBatch];    // rows in streams 2 and 3, or -1
+  __shared__ int s_grow[4][kSlotBatch];   // row of the slot in every stream, counted from the head's first row, or -1
   __shared__ int s_key[kSlotBatch];       // 64-token block of the slot, kTailKey, or -1 (nothing to read)
   __shared__ int s_run[kSlotBatch + 1];   // first slot of every run, then the end
   __shared__ int s_warp_runs[2][kWarps];
-  __shared__ int64_t s_base[2][4];        // row_base / group_base of this (b,h)
   __shared__ int s_last;
 
   const LayerView& L = p.L;
@@ -1000,6 +926,7 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   const int split = blockIdx.x;
   const int slot_begin = split * p.slots_per_cta;
   const int slot_end = min(p.capacity, slot_begin + p.slots_per_cta);
+  const int streams = p.loop + 1;
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -1013,9 +940,12 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
     const uint2 raw = ldg64(p.q + bh * kHeadDim + 4 * lane);
     q4 = make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
   }
-  if (tid < 8) {
-    const int s4 = tid & 3;
-    s_base[tid >> 2][s4] = s4 <= p.loop ? ((tid >> 2) ? L.group_base[s4][bh] : L.row_base[s4][bh]) : 0;
+  // rows / K metadata groups of this (b,h) start here in every stream (the counts fit 31 bits)
+  int row_base[4], group_base[4];
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    row_base[s] = s < streams ? static_cast<int>(L.row_base[s][bh]) : 0;
+    group_base[s] = s < streams ? static_cast<int>(L.group_base[s][bh]) : 0;
   }
 
   OnlineState S;
@@ -1033,18 +963,21 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   for (int batch_begin = slot_begin; batch_begin < slot_end; batch_begin += kSlotBatch) {
     const int batch_n = min(kSlotBatch, slot_end - batch_begin);
     __syncthreads();  // the previous round's lists are no longer read
-    // ---- stage this round's slots: index, rank-map rows, run key
+    // ---- stage this round's slots: index, the row in every stream, run key
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int t = tid + half * kThreads;
-      int idx = -1, r2 = -1, r3 = -1, key = -1;
+      int idx = -1, key = -1;
+      int rows[4] = {-1, -1, -1, -1};
       if (t < batch_n) {
         const int j = batch_begin + t;
         if (!valid_row || valid_row[j]) idx = idx_row[j];
         if (idx >= 0 && idx < quant) {
           key = idx >> 6;
-          if (p.loop >= 2) r2 = L.rank[0][L.rank_base[b] + idx];
-          if (p.loop >= 3) r3 = L.rank[1][L.rank_base[b] + idx];
+          rows[0] = idx;
+          if (streams >= 2) rows[1] = idx;
+          if (streams >= 3) rows[2] = L.rank[0][L.rank_base[b] + idx];
+          if (streams >= 4) rows[3] = L.rank[1][L.rank_base[b] + idx];
         } else if (idx >= quant) {
           const bool has_current = (MODE == kModePV) ? p.vcur != nullptr : p.kcur != nullptr;
           if (idx - quant < tail_len || (idx == cur_pos && has_current)) key = kTailKey;
@@ -1054,8 +987,8 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
         }
       }
       s_idx[t] = idx;
-      s_row[0][t] = r2;
-      s_row[1][t] = r3;
+#pragma unroll
+      for (int s = 0; s < 4; ++s) s_grow[s][t] = rows[s];
       s_key[t] = key;
     }
     __syncthreads();
@@ -1066,7 +999,7 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
     for (int half = 0; half < 2; ++half) {
       const int t = tid + half * kThreads;
       head[half] = t < batch_n && (t == 0 || s_key[t - 1] != s_key[t]);
-      heads[half] = __ballot_sync(0xffffffffu, head[half]);
+      heads[half] = __ballot_sync(kFull, head[half]);
       if (lane == 0) s_warp_runs[half][warp] = __popc(heads[half]);
     }
     __syncthreads();
@@ -1105,62 +1038,61 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
     // Issue the asynchronous copies of a packed pass into buffer `buf` (one commit group).
     auto issue = [&](const Pass& ps, int buf) {
       uint8_t* dst = my_gather + buf * G::kBuffer;
-      const int t = ps.t0 + quad;
-      const bool on = t < ps.run_e;
-      int rows[4];
-      rows[0] = on ? s_idx[t] : -1;
-      rows[1] = p.loop >= 1 ? rows[0] : -1;
-      rows[2] = on ? s_row[0][t] : -1;
-      rows[3] = on ? s_row[1][t] : -1;
+      const int t = min(ps.t0 + quad, ps.run_e - 1);  // idle quads repeat the run's last token
+      uint8_t* token = dst + quad * 4 * G::kToken + sub * kLaneBytes;
 #pragma unroll
       for (int s = 0; s < 4; ++s) {
-        if (rows[s] >= 0) {
-          const int64_t row = s_base[0][s] + rows[s];
-          uint8_t* token = dst + (quad * 4 + s) * G::kToken;
-          if constexpr (MODE != kModePV) {
-            cp_async<kLaneBytes>(token + sub * kLaneBytes, L.k_codes[s] + row * kRowBytes + sub * kLaneBytes);
-          }
-          if constexpr (MODE != kModeQK) {
-            const uint8_t* record = L.v_rows[s] + row * G::kRecord;
-            cp_async<kLaneBytes>(token + G::kKBytes + sub * kLaneBytes, record + sub * kLaneBytes);
-            if (sub == 0) cp_async<16>(token + G::kKBytes + kRowBytes, record + kRowBytes);
+        if (s < streams) {
+          const int local = s_grow[s][t];
+          if (local >= 0) {
+            const int row = row_base[s] + local;
+            if constexpr (MODE != kModePV) {
+              cp_async<kLaneBytes>(token + s * G::kToken,
+                                   L.k_codes[s] + static_cast<int64_t>(row) * kRowBytes + sub * kLaneBytes);
+            }
+            if constexpr (MODE != kModeQK) {
+              const uint8_t* record = L.v_rows[s] + static_cast<int64_t>(row) * G::kRecord + sub * kLaneBytes;
+              cp_async<kLaneBytes>(token + s * G::kToken + G::kKBytes, record);
+              if (sub == 0) cp_async<16>(token + s * G::kToken + G::kKBytes + kRowBytes, record + kRowBytes);
+            }
           }
         }
       }
       if constexpr (MODE != kModePV) {
         if (ps.t0 == ps.run_a) {
-          // first pass of a run: its K metadata (group 0 of every stream) travels with the rows
-          int g0[4] = {ps.key, ps.key, 0, 0};
-          int ng[4] = {1, p.loop >= 1 ? 1 : 0, 0, 0};
-#pragma unroll
-          for (int s = 2; s < 4; ++s) {
-            if (s <= p.loop) {
-              // rows of the run in a compact stream ascend with the slots: first and last present
-              int lo = INT_MAX, hi = -1;
-              for (int u = ps.run_a + lane; u < ps.run_e; u += 32) {
-                const int rr = s_row[s - 2][u];
-                if (rr >= 0) {
-                  lo = min(lo, rr);
-                  hi = max(hi, rr);
-                }
-              }
-              lo = warp_min_int(lo);
-              hi = warp_max_int(hi);
-              g0[s] = hi >= 0 ? lo >> 6 : 0;
-              ng[s] = hi >= 0 ? (hi >> 6) - g0[s] + 1 : 0;
-            }
-          }
+          // first pass of a run: its K metadata (first group of every stream) travels with the rows
           uint8_t* meta = dst + 8 * 4 * G::kToken;
 #pragma unroll
           for (int s = 0; s < 4; ++s) {
-            if (ng[s] > 0) {
-              const int64_t g = s_base[1][s] + g0[s];
-              cp_async<8>(meta + s * 512 + lane * 8, L.k_scale[s] + g * kHeadDim + 4 * lane);
-              cp_async<8>(meta + s * 512 + 256 + lane * 8, L.k_min[s] + g * kHeadDim + 4 * lane);
-            }
-            if (lane == 0) {
-              s_g0[warp][buf][s] = g0[s];
-              s_ng[warp][buf][s] = ng[s];
+            if (s < streams) {
+              int g0, ng;
+              if (s < 2) {
+                g0 = s_grow[s][ps.run_a] >> 6;
+                ng = 1;
+              } else {
+                // rows of the run in a compact stream ascend with the slots: first and last present
+                int lo = INT_MAX, hi = -1;
+                for (int u = ps.run_a + lane; u < ps.run_e; u += 32) {
+                  const int rr = s_grow[s][u];
+                  if (rr >= 0) {
+                    lo = min(lo, rr);
+                    hi = max(hi, rr);
+                  }
+                }
+                lo = warp_min_int(lo);
+                hi = warp_max_int(hi);
+                g0 = hi >= 0 ? lo >> 6 : 0;
+                ng = hi >= 0 ? (hi >> 6) - g0 + 1 : 0;
+              }
+              if (ng > 0) {
+                const int64_t g = group_base[s] + g0;
+                cp_async<8>(meta + s * 512 + lane * 8, L.k_scale[s] + g * kHeadDim + 4 * lane);
+                cp_async<8>(meta + s * 512 + 256 + lane * 8, L.k_min[s] + g * kHeadDim + 4 * lane);
+              }
+              if (lane == 0) {
+                s_g0[warp][buf][s] = g0;
+                s_ng[warp][buf][s] = ng;
+              }
             }
           }
         }
@@ -1219,13 +1151,22 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
         if (prefetch) cp_async_wait<1>(); else cp_async_wait<0>();
         __syncwarp();  // a quad shares the V metadata piece that its first lane copied
         const uint8_t* src = my_gather + buf * G::kBuffer;
-        const int t = cur.t0 + quad;
-        const bool on = t < cur.run_e;
-        int rows[4];
-        rows[0] = on ? s_idx[t] : -1;
-        rows[1] = p.loop >= 1 ? rows[0] : -1;
-        rows[2] = on ? s_row[0][t] : -1;
-        rows[3] = on ? s_row[1][t] : -1;
+        const uint8_t* token = src + quad * 4 * G::kToken;
+        const bool on = cur.t0 + quad < cur.run_e;
+        const int t = min(cur.t0 + quad, cur.run_e - 1);
+        // which streams hold this token (idle quads: none); `any` is the same for the whole warp
+        uint32_t mine = 0, any = 0;
+        int rows23[2] = {-1, -1};
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          if (s < streams) {
+            const int row = s_grow[s][t];
+            if (s >= 2) rows23[s - 2] = row;
+            const bool have = on && row >= 0;
+            mine |= have ? 1u << s : 0u;
+            any |= __any_sync(kFull, have) ? 1u << s : 0u;
+          }
+        }
 
         float pr = 0.f;
         if constexpr (MODE != kModePV) {
@@ -1235,43 +1176,47 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
             const uint8_t* meta = src + 8 * 4 * G::kToken;
 #pragma unroll
             for (int s = 0; s < 4; ++s) {
-              const int ng = s_ng[warp][buf][s];
-              for (int gi = 0; gi < ng && gi < 2; ++gi) {
-                uint2 sc, mn;
-                if (gi == 0) {
-                  sc = *reinterpret_cast<const uint2*>(meta + s * 512 + lane * 8);
-                  mn = *reinterpret_cast<const uint2*>(meta + s * 512 + 256 + lane * 8);
-                } else {
-                  const int64_t g = s_base[1][s] + s_g0[warp][buf][s] + 1;
-                  sc = ldg64(L.k_scale[s] + g * kHeadDim + 4 * lane);
-                  mn = ldg64(L.k_min[s] + g * kHeadDim + 4 * lane);
+              if (s < streams) {
+                const int ng = s_ng[warp][buf][s];
+                for (int gi = 0; gi < ng && gi < 2; ++gi) {
+                  uint2 sc, mn;
+                  if (gi == 0) {
+                    sc = *reinterpret_cast<const uint2*>(meta + s * 512 + lane * 8);
+                    mn = *reinterpret_cast<const uint2*>(meta + s * 512 + 256 + lane * 8);
+                  } else {
+                    const int64_t g = group_base[s] + s_g0[warp][buf][s] + 1;
+                    sc = ldg64(L.k_scale[s] + g * kHeadDim + 4 * lane);
+                    mn = ldg64(L.k_min[s] + g * kHeadDim + 4 * lane);
+                  }
+                  const float2 sc01 = __half22float2(as_half2(sc.x)), sc23 = __half22float2(as_half2(sc.y));
+                  const float2 mn01 = __half22float2(as_half2(mn.x)), mn23 = __half22float2(as_half2(mn.y));
+                  const float kcn = float(kCentre<BITS>);
+                  float bias = q4.x * fmaf(kcn, sc01.x, mn01.x);
+                  bias = fmaf(q4.y, fmaf(kcn, sc01.y, mn01.y), bias);
+                  bias = fmaf(q4.z, fmaf(kcn, sc23.x, mn23.x), bias);
+                  bias = fmaf(q4.w, fmaf(kcn, sc23.y, mn23.y), bias);
+                  __half* tab = &s_wtab[warp][s][gi][(4 * lane) & ~31];
+                  const int cc = (4 * lane) & 31;
+                  tab[channel_slot<BITS>(cc + 0)] = __float2half_rn(q4.x * sc01.x);
+                  tab[channel_slot<BITS>(cc + 1)] = __float2half_rn(q4.y * sc01.y);
+                  tab[channel_slot<BITS>(cc + 2)] = __float2half_rn(q4.z * sc23.x);
+                  tab[channel_slot<BITS>(cc + 3)] = __float2half_rn(q4.w * sc23.y);
+                  bias = 0.25f * warp_sum(bias);  // added in each of the four lanes of a quad
+                  if (lane == 0) s_kbias[warp][s][gi] = bias;
                 }
-                const float2 sc01 = __half22float2(as_half2(sc.x)), sc23 = __half22float2(as_half2(sc.y));
-                const float2 mn01 = __half22float2(as_half2(mn.x)), mn23 = __half22float2(as_half2(mn.y));
-                const float kcn = float(kCentre<BITS>);
-                float bias = q4.x * fmaf(kcn, sc01.x, mn01.x);
-                bias = fmaf(q4.y, fmaf(kcn, sc01.y, mn01.y), bias);
-                bias = fmaf(q4.z, fmaf(kcn, sc23.x, mn23.x), bias);
-                bias = fmaf(q4.w, fmaf(kcn, sc23.y, mn23.y), bias);
-                __half* tab = &s_wtab[warp][s][gi][(4 * lane) & ~31];
-                const int cc = (4 * lane) & 31;
-                tab[channel_slot<BITS>(cc + 0)] = __float2half_rn(q4.x * sc01.x);
-                tab[channel_slot<BITS>(cc + 1)] = __float2half_rn(q4.y * sc01.y);
-                tab[channel_slot<BITS>(cc + 2)] = __float2half_rn(q4.z * sc23.x);
-                tab[channel_slot<BITS>(cc + 3)] = __float2half_rn(q4.w * sc23.y);
-                bias = 0.25f * warp_sum(bias);  // added in each of the four lanes of a quad
-                if (lane == 0) s_kbias[warp][s][gi] = bias;
               }
             }
             run_g0[0] = s_g0[warp][buf][2];
             run_g0[1] = s_g0[warp][buf][3];
             __syncwarp();
           }
+          // Every lane runs every stream some lane needs; a lane without the row computes on
+          // whatever its buffer holds and drops the result (unpacked codes are always finite).
           float dot = 0.f;
 #pragma unroll
           for (int s = 0; s < 4; ++s) {
-            if (rows[s] >= 0) {
-              const int gi = s >= 2 ? min(1, (rows[s] >> 6) - run_g0[s - 2]) : 0;
+            if (any & (1u << s)) {
+              const int gi = s >= 2 ? max(0, min(1, (rows23[s >= 2 ? s - 2 : 0] >> 6) - run_g0[s >= 2 ? s - 2 : 0])) : 0;
               __half2 mult[16];
               const uint4* tab = reinterpret_cast<const uint4*>(&s_wtab[warp][s][gi][sub * 32]);
 #pragma unroll
@@ -1280,8 +1225,9 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
                 mult[4 * v + 0] = as_half2(x.x); mult[4 * v + 1] = as_half2(x.y);
                 mult[4 * v + 2] = as_half2(x.z); mult[4 * v + 3] = as_half2(x.w);
               }
-              const Codes<BITS> kc = load_codes_shared<BITS>(src + (quad * 4 + s) * G::kToken + sub * kLaneBytes);
-              dot += k_dot_fast<BITS>(kc, mult) + s_kbias[warp][s][gi];
+              const Codes<BITS> kc = load_codes_shared<BITS>(token + s * G::kToken + sub * kLaneBytes);
+              const float kd = k_dot_fast<BITS>(kc, mult) + s_kbias[warp][s][gi];
+              dot += (mine & (1u << s)) ? kd : 0.f;
             }
           }
           dot = quad_sum(dot);
@@ -1304,16 +1250,18 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
         if constexpr (MODE != kModeQK) {
           const uint32_t pick = (sub < 2) ? 0x1010u : 0x3232u;
           const __half2 centre2 = __floats2half2_rn(float(kCentre<BITS>), float(kCentre<BITS>));
+          const __half2 zero2 = __floats2half2_rn(0.f, 0.f);
           const __half2 p2 = __float2half2_rn(pr);
-          __half2 hb = __floats2half2_rn(0.f, 0.f);
+          __half2 hb = zero2;
 #pragma unroll
           for (int s = 0; s < 4; ++s) {
-            if (rows[s] >= 0) {
-              const uint8_t* record = src + (quad * 4 + s) * G::kToken + G::kKBytes;
+            if (any & (1u << s)) {
+              const bool have = mine & (1u << s);
+              const uint8_t* record = token + s * G::kToken + G::kKBytes;
               const Codes<BITS> vc = load_codes_shared<BITS>(record + sub * kLaneBytes);
               const uint2 vmeta = *reinterpret_cast<const uint2*>(record + kRowBytes);
-              const __half2 vm2 = as_half2(__byte_perm(vmeta.x, 0u, pick));
-              const __half2 vs2 = as_half2(__byte_perm(vmeta.y, 0u, pick));
+              const __half2 vm2 = as_half2(have ? __byte_perm(vmeta.x, 0u, pick) : 0u);
+              const __half2 vs2 = as_half2(have ? __byte_perm(vmeta.y, 0u, pick) : 0u);
               hb = __hfma2(centre2, vs2, __hadd2(vm2, hb));
               v_accumulate<BITS>(vc, __hmul2(p2, vs2), hacc);
             }
