@@ -55,6 +55,9 @@ def parse_args():
     ap.add_argument("--context", type=int, default=None, help="context / prompt length (default 8192 hotpath, 2048 e2e)")
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tp", action="store_true",
+                    help="e2e workload: shard heads and FFN columns over the ranks (NCCL all-reduce after o_proj "
+                         "and the MLP) instead of running one replica per rank")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.batch is None:
@@ -472,6 +475,7 @@ def run_e2e(args) -> None:
 
     from flashloop_b200 import FlashLoopConfig, FlashLoopEngine, _native, sharding
     from flashloop_b200.ouro_shape import OuroShapedConfig, OuroShapedForCausalLM
+    from flashloop_b200.tensor_parallel import shard_ouro_model
 
     _native.load()  # fail loudly when the CUDA library is missing
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -486,9 +490,13 @@ def run_e2e(args) -> None:
     budget = args.warmup + args.steps + e2e_steps + 8
     cfg = OuroShapedConfig(num_hidden_layers=NL)
     model = OuroShapedForCausalLM(cfg, seed=0, device=device)
-    engine = FlashLoopEngine(model, config=FlashLoopConfig(kv_bits=args.bits), validate_model=NL in (24, 48),
-                             max_new_tokens=budget, use_cuda_graph=not args.no_graph)
-    gen = torch.Generator().manual_seed(100 + rank)
+    tp = args.tp and world > 1
+    if tp:
+        shard_ouro_model(model, rank, world)  # this rank's heads and FFN columns
+    engine = FlashLoopEngine(model, config=FlashLoopConfig(kv_bits=args.bits), validate_model=False,
+                             max_new_tokens=budget, use_cuda_graph=not (args.no_graph or tp),
+                             tp_group=dist.group.WORLD if tp else None)
+    gen = torch.Generator().manual_seed(100 + (0 if tp else rank))
     prompts = torch.randint(0, cfg.vocab_size, (B, T), generator=gen).to(device)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -517,7 +525,8 @@ def run_e2e(args) -> None:
     ms_total = timed(run_step, args.steps)
     torch.cuda.profiler.stop()
     clocks = sampler.stop() if sampler else {}
-    value = sharding.sum_over_ranks(B * args.steps, device) / (ms_total * 1e-3)
+    job_tokens = (lambda n: float(B * n)) if tp else (lambda n: sharding.sum_over_ranks(B * n, device))
+    value = job_tokens(args.steps) / (ms_total * 1e-3)
 
     # ---- end to end: token ids come from pinned host memory, the chosen token goes back to it
     host_token = state["token"].cpu().pin_memory()
@@ -530,11 +539,11 @@ def run_e2e(args) -> None:
         torch.cuda.current_stream().synchronize()
 
     e2e_ms = timed(e2e_step, e2e_steps)
-    e2e_value = sharding.sum_over_ranks(B * e2e_steps, device) / (e2e_ms * 1e-3)
+    e2e_value = job_tokens(e2e_steps) / (e2e_ms * 1e-3)
 
     # ---- the dominant kernel of the path alone: the loop-2 dense reader of every layer
     layers = engine.state.cache.layers
-    H = cfg.num_attention_heads
+    H = cfg.num_attention_heads // (world if tp else 1)
     q, k, v = (torch.randn((B, H, 1, HEAD_DIM), device=device).to(torch.bfloat16) for _ in range(3))
     probe = []
     for rep in range(3):
@@ -562,12 +571,14 @@ def run_e2e(args) -> None:
         line = {
             "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": workload_name(args), "global_batch": B * world,
+            "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": workload_name(args), "global_batch": B if tp else B * world,
                        "l2": "inputs larger than L2: each step streams the layer weights four times "
                              "(%.1f GB) and the packed cache" % (4 * weights / 1e9),
-                       "parallelism": f"batch-data-parallel replicas x{world}, no collective",
-                       "launch": "eager" if args.no_graph else "one CUDA graph replay per step",
+                       "parallelism": (f"tensor parallel x{world}: heads and FFN columns sharded, NCCL all-reduce "
+                                       f"after o_proj and the MLP" if tp else
+                                       f"batch-data-parallel replicas x{world}, no collective"),
+                       "launch": "eager" if (args.no_graph or tp) else "one CUDA graph replay per step",
                        "prefill_seconds": prefill_s, "context_at_end": quant + tail},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": int(host_token.numel() * 8),

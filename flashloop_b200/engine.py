@@ -26,6 +26,7 @@ from .config import FlashLoopConfig, validate_ouro_model
 from .selection import decode_budget
 from .prefill import PrefillReceipt, apply_rope, dense_prefill_loop, sparse_prefill_loop
 from . import step_ops
+from .tensor_parallel import PartialSum
 from .weights import fused_mlp, project_qkv, repack_projection_weights
 
 
@@ -64,7 +65,7 @@ class FlashLoopEngine:
 
     def __init__(self, model: torch.nn.Module, *, config: FlashLoopConfig | None = None,
                  validate_model: bool = True, max_new_tokens: int = 512, use_cuda_graph: bool = False,
-                 reference_loop4_scores: bool = True, fuse_decode_ops: bool = True) -> None:
+                 reference_loop4_scores: bool = True, fuse_decode_ops: bool = True, tp_group=None) -> None:
         if validate_model:
             validate_ouro_model(model)
         elif int(getattr(model.config, "total_ut_steps", 0)) != 4:
@@ -78,6 +79,11 @@ class FlashLoopEngine:
         self.max_new_tokens = int(max_new_tokens)
         self.use_cuda_graph = bool(use_cuda_graph)
         self.reference_loop4_scores = bool(reference_loop4_scores)
+        # tensor parallelism: the model holds this rank's heads / FFN columns (see tensor_parallel.py)
+        # and the partial o_proj / down_proj outputs are summed over ``tp_group``
+        if tp_group is not None and use_cuda_graph:
+            raise ValueError("the tensor-parallel decode step is launched eagerly: use_cuda_graph=False")
+        self._reduce = PartialSum(tp_group) if tp_group is not None else (lambda t: t)
         self.fuse_decode_ops = bool(fuse_decode_ops) and self._modules_are_fusable()
         self._state: EngineState | None = None
         self._graph = None
@@ -134,14 +140,15 @@ class FlashLoopEngine:
         rope = self.backbone.rotary_emb(hidden, positions)
         norm = self.backbone.norm
 
-        loop1 = dense_prefill_loop(self.layers, hidden, position_embeddings=rope, final_norm=norm, loop=1)
+        loop1 = dense_prefill_loop(self.layers, hidden, position_embeddings=rope, final_norm=norm, loop=1,
+                                   reduce=self._reduce)
         loop2 = dense_prefill_loop(self.layers, loop1.hidden_states, position_embeddings=rope, final_norm=norm,
-                                   loop=2)
+                                   loop=2, reduce=self._reduce)
         fraction3, fraction4 = self.config.effective_prefill_fractions
         keep3 = self._retain(3, hidden_delta_score(loop2.hidden_states, loop1.hidden_states), fraction3, None)
         loop3 = sparse_prefill_loop(self.layers, loop2.hidden_states, retained=keep3,
                                     composite_cache=loop2.composite_cache, position_embeddings=rope,
-                                    final_norm=norm, loop=3)
+                                    final_norm=norm, loop=3, reduce=self._reduce)
         if self.reference_loop4_scores:
             # engine.py:258-275 runs Loop 3 with consume_inputs=True, so prefill.py:236-237,254
             # write the Loop-3 rows into the Loop-2 tensor itself and the score of
@@ -153,7 +160,7 @@ class FlashLoopEngine:
         keep4 = self._retain(4, score4, fraction4, keep3.mask)
         loop4 = sparse_prefill_loop(self.layers, loop3.hidden_states, retained=keep4,
                                     composite_cache=loop3.composite_cache, position_embeddings=rope,
-                                    final_norm=norm, loop=4)
+                                    final_norm=norm, loop=4, reduce=self._reduce)
 
         physical = CrossLoopKVCache(num_layers=len(self.layers))
         loops = (loop1, loop2, loop3, loop4)
@@ -224,7 +231,7 @@ class FlashLoopEngine:
             want_logits = loop == 1 and self.config.enable_sparse_decode
             out, logits = physical.dense_source_attention(loop, query=q, current_key=k, current_value=v,
                                                           scaling=scaling, return_logits=want_logits)
-            projected = o_proj(out.to(q.dtype).view(batch, 1, -1))
+            projected = self._reduce(o_proj(out.to(q.dtype).view(batch, 1, -1)))
             if want_logits:
                 sel = physical.select_decode_keys(logits, fraction=self.config.effective_decode_key_fraction)
                 aggregate = physical.pv(1, sel.selected_weights, sel.indices, current_value=v,
@@ -235,7 +242,7 @@ class FlashLoopEngine:
         delta = physical.cached_mass_sparse_attention_delta(
             loop, query=q, current_key=k, current_value=v, indices=sel.indices, valid=sel.valid,
             source_selected_output=aggregate, global_mass=sel.global_mass, scaling=scaling)
-        return projected0 + o_proj(delta.to(v.dtype).view(batch, 1, -1))
+        return projected0 + self._reduce(o_proj(delta.to(v.dtype).view(batch, 1, -1)))
 
     def _decode_step_fused(self, token_ids: torch.Tensor, position_ids: torch.Tensor) -> torch.Tensor:
         """One decode step with the elementwise glue as one-launch kernels (``step_ops``): per layer
@@ -267,7 +274,7 @@ class FlashLoopEngine:
                 n2, n3, n4 = layer.input_layernorm_2, layer.post_attention_layernorm, layer.post_attention_layernorm_2
                 hidden, x = step_ops.rmsnorm(projected, n2.weight, eps(n2), residual=hidden,
                                              weight2=n3.weight, eps2=eps(n3))
-                m = mlp.down_proj(step_ops.swiglu(F.linear(x, mlp._flashloop_gate_up_weight)))
+                m = self._reduce(mlp.down_proj(step_ops.swiglu(F.linear(x, mlp._flashloop_gate_up_weight))))
                 following = self.backbone.norm if index == n_layers - 1 else self.layers[index + 1].input_layernorm
                 hidden, x = step_ops.rmsnorm(m, n4.weight, eps(n4), residual=hidden,
                                              weight2=following.weight, eps2=eps(following))
@@ -304,7 +311,7 @@ class FlashLoopEngine:
                 residual = hidden
                 hidden = residual + layer.input_layernorm_2(projected)
                 hidden = hidden + layer.post_attention_layernorm_2(
-                    fused_mlp(layer.mlp, layer.post_attention_layernorm(hidden)))
+                    self._reduce(fused_mlp(layer.mlp, layer.post_attention_layernorm(hidden))))
             hidden = self.backbone.norm(hidden)
         for index in range(n_layers):
             cache.layers[index].append_decode_token(keys[index], values[index])

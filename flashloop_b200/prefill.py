@@ -70,14 +70,20 @@ def _heads(x: torch.Tensor, heads: int, head_dim: int) -> torch.Tensor:
     return x.view(batch, rows, heads, head_dim).transpose(1, 2)
 
 
-def _layer_tail(layer: nn.Module, residual: torch.Tensor, attention_output: torch.Tensor) -> torch.Tensor:
+def _identity(t: torch.Tensor) -> torch.Tensor:
+    return t
+
+
+def _layer_tail(layer: nn.Module, residual: torch.Tensor, attention_output: torch.Tensor, reduce) -> torch.Tensor:
     hidden = residual + layer.input_layernorm_2(attention_output)
-    return hidden + layer.post_attention_layernorm_2(fused_mlp(layer.mlp, layer.post_attention_layernorm(hidden)))
+    mlp_out = reduce(fused_mlp(layer.mlp, layer.post_attention_layernorm(hidden)))
+    return hidden + layer.post_attention_layernorm_2(mlp_out)
 
 
 def dense_prefill_loop(layers: Sequence[nn.Module], hidden_states: torch.Tensor, *, position_embeddings,
-                       final_norm: nn.Module, loop: int) -> PrefillLoopOutput:
-    """One dense recurrent loop: every row is recomputed (prefill.py:275-304)."""
+                       final_norm: nn.Module, loop: int, reduce=_identity) -> PrefillLoopOutput:
+    """One dense recurrent loop: every row is recomputed (prefill.py:275-304).  ``reduce`` completes
+    the row-parallel partial sums of ``o_proj`` / ``down_proj`` under tensor parallelism."""
 
     batch, tokens, hidden_size = hidden_states.shape
     cos, sin = position_embeddings
@@ -94,8 +100,8 @@ def dense_prefill_loop(layers: Sequence[nn.Module], hidden_states: torch.Tensor,
         keys.append(k)
         values.append(v)
         out = F.scaled_dot_product_attention(q, k, v, dropout_p=0.0, is_causal=True)
-        out = attention.o_proj(out.transpose(1, 2).reshape(batch, tokens, hidden_size))
-        hidden = _layer_tail(layer, hidden, out)
+        out = reduce(attention.o_proj(out.transpose(1, 2).reshape(batch, tokens, -1)))
+        hidden = _layer_tail(layer, hidden, out, reduce)
     hidden = final_norm(hidden)
     n = len(layers)
     receipt = PrefillReceipt(loop, batch * tokens, batch * tokens, 3 * batch * tokens * n, batch * tokens * n,
@@ -105,7 +111,7 @@ def dense_prefill_loop(layers: Sequence[nn.Module], hidden_states: torch.Tensor,
 
 def sparse_prefill_loop(layers: Sequence[nn.Module], hidden_states: torch.Tensor, *, retained: RetainedTokens,
                         composite_cache: PrefillCompositeCache, position_embeddings, final_norm: nn.Module,
-                        loop: int) -> PrefillLoopOutput:
+                        loop: int, reduce=_identity) -> PrefillLoopOutput:
     """A late loop over the retained rows only (prefill.py:307-342).  Returns new full
     composites (retained rows replaced, the others carried over from ``composite_cache``)."""
 
@@ -144,8 +150,8 @@ def sparse_prefill_loop(layers: Sequence[nn.Module], hidden_states: torch.Tensor
         keys.append(full_k)
         values.append(full_v)
         out = F.scaled_dot_product_attention(q, full_k, full_v, attn_mask=attn_mask, dropout_p=0.0)
-        out = attention.o_proj(out.transpose(1, 2).reshape(batch, rows, hidden_size))
-        active = _layer_tail(layer, active, out)
+        out = reduce(attention.o_proj(out.transpose(1, 2).reshape(batch, rows, -1)))
+        active = _layer_tail(layer, active, out, reduce)
     active = final_norm(active)
     scatter_rows(hidden, active.contiguous(), positions, count)
     n = len(layers)
