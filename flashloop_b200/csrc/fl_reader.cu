@@ -521,9 +521,10 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
       int bh, b, chunk, nchunks, quant, tail_len, tail_start, blk_begin, blk_end;
     } cur = {curp->bh, curp->b, curp->chunk, curp->nchunks, curp->quant, curp->tail_len,
              curp->tail_start, curp->blk_begin, curp->blk_end};
-    // Look ahead: thread 0 draws item k+2; the upper half of the CTA fetches the query of item
-    // k+1.  Both become visible to the other warps at this item's merge barrier.
-    if (tid == 0) draw_item(p, &s_item[(k + 2) % 3]);
+    // Look ahead: one thread of the upper half of the CTA (the warps that sit out the merge) draws
+    // item k+2, the upper half fetches the query of item k+1.  Both become visible to the other
+    // warps at this item's merge barrier.
+    if (tid == kHeadDim) draw_item(p, &s_item[(k + 2) % 3]);
     if (tid >= kHeadDim) {
       const int next_id = s_item[(k + 1) % 3].id;
       if (next_id >= 0) {
@@ -973,7 +974,8 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
         const int j = batch_begin + t;
         if (!valid_row || valid_row[j]) idx = idx_row[j];
         if (idx >= 0 && idx < quant) {
-          key = idx >> 6;
+          // K tables belong to a 64-token block; without K (weighted PV) any eight slots make a pass
+          key = MODE == kModePV ? (t >> 3) : (idx >> 6);
           rows[0] = idx;
           if (streams >= 2) rows[1] = idx;
           if (streams >= 3) rows[2] = L.rank[0][L.rank_base[b] + idx];
