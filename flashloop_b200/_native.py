@@ -65,6 +65,7 @@ SIGNATURES = {
     "fl_select_prefill_tokens": (C.c_int, [_vp, _vp, _i32, _i32, _f64, _i32, _vp, _vp, _vp, _vp, _vp]),
     "fl_gather_rows": (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _i32, _vp]),
     "fl_scatter_rows": (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _i32, _vp]),
+    "fl_encode_prefill": (C.c_int, [_vp, _i32, _i32, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp]),
     "fl_rmsnorm": (C.c_int, [_vp, _vp, _vp, _f32, _vp, _f32, _i64, _i32, _vp, _vp, _vp]),
     "fl_rope_split": (C.c_int, [_vp, _vp, _vp, _i64, _vp, _vp, _i64, _i32, _vp, _vp, _vp, _vp]),
     "fl_swiglu": (C.c_int, [_vp, _i64, _i32, _vp, _vp]),

@@ -25,7 +25,7 @@ from typing import Sequence
 import torch
 
 from . import _native
-from .packing import Packed4Bit, pack_k_per_channel, pack_v_per_token
+from .packing import Packed4Bit
 from .selection import PaddedDecodeSelection, select_decode_keys_padded
 
 GROUP = 64
@@ -51,15 +51,6 @@ def reader_workspace(device: torch.device, batch_heads: int, max_context_tokens:
 
 def _round_up(value: int, multiple: int) -> int:
     return -(-int(value) // multiple) * multiple
-
-
-def _rank_map(tokens: int, positions: torch.Tensor, device: torch.device) -> torch.Tensor:
-    """flashloop/cache.py:281-289."""
-
-    result = torch.full((tokens,), -1, dtype=torch.int32, device=device)
-    if positions.numel():
-        result[positions.long()] = torch.arange(positions.numel(), dtype=torch.int32, device=device)
-    return result
 
 
 def _validate_loop_tensors(keys: Sequence[torch.Tensor], values: Sequence[torch.Tensor]):
@@ -183,23 +174,6 @@ class CrossLoopKVLayer:
         t = tensor_list[s]
         return t[start:start + count].view(self.heads, cap // per_row, *t.shape[1:])
 
-    def _store_stream(self, s: int, b: int, row0: int, key: Packed4Bit, value: Packed4Bit) -> None:
-        """Copy one packed K/V segment of sequence ``b`` into rows ``row0 ..`` of stream ``s``."""
-
-        n = key.original_shape[2]
-        if row0 % GROUP:
-            raise RuntimeError("stream segments must start on a group boundary")
-        if row0 + n > self._caps[s][b]:
-            raise RuntimeError(f"stream {s} of sequence {b} is full ({row0 + n} > {self._caps[s][b]} rows)")
-        groups = key.minimum.shape[2]
-        self._rows(self._k_codes, s, b)[:, row0:row0 + n].copy_(key.payload[0])
-        self._rows(self._k_min, s, b, GROUP)[:, row0 // GROUP:row0 // GROUP + groups].copy_(key.minimum[0])
-        self._rows(self._k_scale, s, b, GROUP)[:, row0 // GROUP:row0 // GROUP + groups].copy_(key.scale[0])
-        self._rows(self._v_codes, s, b)[:, row0:row0 + n].copy_(value.payload[0])
-        meta = self._rows(self._v_meta, s, b)[:, row0:row0 + n]
-        meta[..., 0:2].copy_(value.minimum[0])
-        meta[..., 2:4].copy_(value.scale[0])
-
     # ------------------------------------------------------------------ construction
 
     @classmethod
@@ -222,10 +196,23 @@ class CrossLoopKVLayer:
             raise ValueError("unknown KV reader backend")
         if mask_loop3.shape != (batch, tokens) or mask_loop4.shape != (batch, tokens):
             raise ValueError("prefill masks must have shape [batch, tokens]")
-        sequences = [([k[b:b + 1] for k in keys], [v[b:b + 1] for v in values],
-                      mask_loop3[b], mask_loop4[b]) for b in range(batch)]
-        return cls.from_prefill_ragged(sequences, group_size=group_size, residual_length=residual_length,
-                                       bits=bits, max_new_tokens=max_new_tokens)
+        device = keys[0].device
+        mask3 = mask_loop3.to(device=device, dtype=torch.bool).contiguous()
+        mask4 = mask_loop4.to(device=device, dtype=torch.bool).contiguous()
+        if not bool(torch.all(~mask4 | mask3).item()):
+            raise ValueError("Loop-4 overrides must be nested in Loop-3 overrides")
+        packed = max(0, ((tokens - residual_length) // group_size) * group_size)
+        counts3 = mask3[:, :packed].sum(1).tolist()
+        counts4 = mask4[:, :packed].sum(1).tolist()
+        extra = _round_up(max_new_tokens, GROUP) + 2 * GROUP
+        layer = cls(batch=batch, heads=heads, token_capacities=[packed + extra] * batch,
+                    compact_capacities=[(_round_up(n3, GROUP) + extra, _round_up(n4, GROUP) + extra)
+                                        for n3, n4 in zip(counts3, counts4)],
+                    bits=bits, group_size=group_size, residual_length=residual_length, device=device,
+                    dtype=keys[0].dtype)
+        layer._encode_sequences(0, keys, values, mask3, mask4, packed, counts3, counts4)
+        layer._push_state()
+        return layer
 
     @classmethod
     def from_prefill_ragged(cls, sequences, *, group_size: int = 64, residual_length: int = 64,
@@ -263,7 +250,8 @@ class CrossLoopKVLayer:
                     compact_capacities=compact_caps, bits=bits, group_size=group_size,
                     residual_length=residual_length, device=device, dtype=dtype)
         for b, (keys, values, mask3, mask4, packed) in enumerate(prepared):
-            layer._encode_sequence(b, keys, values, mask3, mask4, packed)
+            layer._encode_sequences(b, keys, values, mask3[None], mask4[None], packed,
+                                    [int(mask3[:packed].sum().item())], [int(mask4[:packed].sum().item())])
         layer._push_state()
         return layer
 
@@ -332,70 +320,61 @@ class CrossLoopKVLayer:
             self._tail_active_host = [[[False] * tail, [False] * tail] for _ in range(self.batch)]
             self._push_state()
 
-    def _encode_block(self, keys, values, mask3, mask4):
-        """The residual chain of flashloop/cache.py:1008-1074 on one token block
-        ([1, H, n, 128] per loop): returns the four packed K/V streams and the active
-        positions of streams 2 and 3.  Every subtraction/addition is a bfloat16 tensor
-        operation, as in the reference; the codecs are the CUDA kernels."""
+    def _encode_sequences(self, first: int, keys, values, mask3: torch.Tensor, mask4: torch.Tensor, packed: int,
+                          counts3, counts4) -> None:
+        """Encode sequences ``first .. first + n`` from their prompts: keys/values are four
+        [n, H, T, 128] tensors, masks bool [n, T], ``packed`` the quantised prefix length of all
+        of them, counts the retained tokens inside the prefix.  One ``fl_encode_prefill`` call
+        (three launches) runs the residual chain of flashloop/cache.py:1008-1074 and writes the
+        streams; rank maps, tails and state words are filled around it."""
 
-        bits = self.bits
-        streams_k: list[Packed4Bit | None] = [None] * 4
-        streams_v: list[Packed4Bit | None] = [None] * 4
-        streams_k[0] = pack_k_per_channel(keys[0], bits=bits)
-        streams_v[0] = pack_v_per_token(values[0], bits=bits)
-        recon_k = streams_k[0].decode()
-        recon_v = streams_v[0].decode()
-        streams_k[1] = pack_k_per_channel(keys[1] - recon_k, bits=bits)
-        streams_v[1] = pack_v_per_token(values[1] - recon_v, bits=bits)
-        recon_k = recon_k + streams_k[1].decode()
-        recon_v = recon_v + streams_v[1].decode()
-        positions = []
-        for s, mask in ((2, mask3), (3, mask4)):
-            pos = torch.nonzero(mask, as_tuple=False).flatten()
-            positions.append(pos.to(torch.int32))
-            if pos.numel() == 0:
-                continue
-            dk = keys[s].index_select(2, pos) - recon_k.index_select(2, pos)
-            dv = values[s].index_select(2, pos) - recon_v.index_select(2, pos)
-            streams_k[s] = pack_k_per_channel(dk, bits=bits)
-            streams_v[s] = pack_v_per_token(dv, bits=bits)
-            if s == 2:
-                recon_k = recon_k.clone()
-                recon_v = recon_v.clone()
-                recon_k.index_add_(2, pos, streams_k[s].decode())
-                recon_v.index_add_(2, pos, streams_v[s].decode())
-        return streams_k, streams_v, positions
+        from .compaction import retained_from_mask
 
-    def _encode_sequence(self, b: int, keys, values, mask3, mask4, packed: int) -> None:
-        tokens = int(keys[0].shape[2])
-        st = self._state_host[b]
-        st[_native.STATE_QUANT_TOKENS] = packed
-        rows = [0, 0]
-        if packed:
-            sk, sv, positions = self._encode_block([k[:, :, :packed] for k in keys],
-                                                   [v[:, :, :packed] for v in values],
-                                                   mask3[:packed], mask4[:packed])
-            for s in range(4):
-                if sk[s] is not None:
-                    self._store_stream(s, b, 0, sk[s], sv[s])
-            base = self._rank_base_host[b]
-            for i in range(2):
-                self._compact_counts[b][i] = int(positions[i].numel())
-                self._rank[i][base:base + packed] = _rank_map(packed, positions[i], self._device)
-                rows[i] = _round_up(int(positions[i].numel()), GROUP)
-        st[_native.STATE_ROWS2], st[_native.STATE_ROWS3] = rows
+        n, tokens = int(keys[0].shape[0]), int(keys[0].shape[2])
         tail = tokens - packed
         if tail > TAIL_CAPACITY:
             raise RuntimeError("tail longer than the ring")
-        st[_native.STATE_TAIL_LEN] = tail
-        st[_native.STATE_TAIL_START] = 0
-        sl = slice(b * self.heads, (b + 1) * self.heads)
+        _native.require_cuda(*keys, *values)
+        if keys[0].dtype != torch.bfloat16:
+            raise ValueError("prefill K/V must be bfloat16")
+        for i in range(n):
+            b = first + i
+            if packed > self._caps[0][b] or _round_up(counts3[i], GROUP) > self._caps[2][b] \
+                    or _round_up(counts4[i], GROUP) > self._caps[3][b]:
+                raise RuntimeError(f"sequence {b} does not fit its preallocated streams")
+            st = self._state_host[b]
+            st[_native.STATE_QUANT_TOKENS] = packed
+            st[_native.STATE_ROWS2] = _round_up(int(counts3[i]), GROUP)
+            st[_native.STATE_ROWS3] = _round_up(int(counts4[i]), GROUP)
+            st[_native.STATE_TAIL_LEN] = tail
+            st[_native.STATE_TAIL_START] = 0
+            self._compact_counts[b] = [int(counts3[i]), int(counts4[i])]
+        self._seq_state[first:first + n].copy_(self._state_host[first:first + n])  # the kernels read the prefix length
+        if packed:
+            kept3, kept4 = retained_from_mask(mask3), retained_from_mask(mask4)
+            for i in range(n):
+                base = self._rank_base_host[first + i]
+                self._rank[0][base:base + packed].copy_(kept3.rank[i, :packed])
+                self._rank[1][base:base + packed].copy_(kept4.rank[i, :packed])
+            ks = [k.contiguous() for k in keys]
+            vs = [v.contiguous() for v in values]
+            recon_k, recon_v = torch.empty_like(ks[0]), torch.empty_like(vs[0])
+            key_table = (C.c_void_p * 4)(*[k.data_ptr() for k in ks])
+            value_table = (C.c_void_p * 4)(*[v.data_ptr() for v in vs])
+            _native.check(_native.load().fl_encode_prefill(
+                C.byref(self._native), first, n, tokens, key_table, value_table, _native.ptr(kept3.positions),
+                _native.ptr(kept4.positions), tokens, _native.ptr(recon_k), _native.ptr(recon_v),
+                _native.current_stream(self._device)), "fl_encode_prefill")
+        heads = self.heads
+        sl = slice(first * heads, (first + n) * heads)
         for r in range(4):
-            self._tail_k[r, sl, :tail].copy_(keys[r][0, :, packed:])
-            self._tail_v[r, sl, :tail].copy_(values[r][0, :, packed:])
-        self._tail_active[0, b, :tail].copy_(mask3[packed:].to(torch.uint8))
-        self._tail_active[1, b, :tail].copy_(mask4[packed:].to(torch.uint8))
-        self._tail_active_host[b] = [mask3[packed:].tolist(), mask4[packed:].tolist()]
+            self._tail_k[r, sl, :tail].copy_(keys[r][:, :, packed:].reshape(n * heads, tail, HEAD_DIM))
+            self._tail_v[r, sl, :tail].copy_(values[r][:, :, packed:].reshape(n * heads, tail, HEAD_DIM))
+        self._tail_active[0, first:first + n, :tail].copy_(mask3[:, packed:].to(torch.uint8))
+        self._tail_active[1, first:first + n, :tail].copy_(mask4[:, packed:].to(torch.uint8))
+        flags3, flags4 = mask3[:, packed:].tolist(), mask4[:, packed:].tolist()
+        for i in range(n):
+            self._tail_active_host[first + i] = [flags3[i], flags4[i]]
 
     # ------------------------------------------------------------------ bookkeeping
 

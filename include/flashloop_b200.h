@@ -293,6 +293,22 @@ int fl_scatter_rows(void* full, const void* compact, const int32_t* positions, c
                     int64_t positions_stride, int64_t outer, int32_t per_sequence, int64_t full_rows,
                     int64_t compact_rows, int32_t row_bytes, fl_cuda_stream stream);
 
+/* The prefill-time residual encoder: CrossLoopKVLayerBuilder.from_loop1 / add_loop2 /
+ * _install_sparse_streams / finalize and _encode_initial_prefix (flashloop/cache.py:343-397,
+ * 415-439, 469-508, 510-625, 1008-1074) in three launches.  keys / values: four pointers (loops
+ * 1-4) to bfloat16 [sequence_count][heads][tokens][128] of sequences sequence_begin .. of the
+ * layer.  The first seq_state[b][FL_STATE_QUANT_TOKENS] tokens of every sequence are encoded:
+ * stream 0 = loop 1, stream 1 = loop 2 - decode(stream 0), streams 2 / 3 = loops 3 / 4 minus the
+ * running reconstruction at the retained positions, 64 compact rows per K metadata group; every
+ * subtraction and add-back rounded to bfloat16 as the reference's tensor ops round.  positions3 /
+ * positions4: int32 [sequence_count][positions_stride], retained positions ascending then -1
+ * (both NULL: no compact streams).  recon_k / recon_v: scratch of the size of one K / V input.
+ * Rank maps, tails and state words are the caller's to fill. */
+int fl_encode_prefill(const fl_layer* layer, int32_t sequence_begin, int32_t sequence_count, int64_t tokens,
+                      const void* const* keys, const void* const* values, const int32_t* positions3,
+                      const int32_t* positions4, int64_t positions_stride, void* recon_k, void* recon_v,
+                      fl_cuda_stream stream);
+
 /* ---------------------------------------------------------------------------------------
  * Elementwise glue of one decode step around the readers (bfloat16 rows, one token per row).
  * Each restates module arithmetic of the reference's decode loop with the roundings of
