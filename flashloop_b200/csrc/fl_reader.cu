@@ -866,53 +866,54 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
 // Indices need not be sorted for correctness (an unsorted list only makes more, shorter runs).
 
 enum { kModeDelta = 0, kModePV = 1, kModeQK = 2 };
-constexpr int kSlotBatch = 2 * kThreads;  // slots staged per round: two per thread
+constexpr int kSlotBatch = kThreads;  // slots staged per round: one per thread
 constexpr int kTailKey = INT_MAX;
 
 template <int BYTES>
-__device__ __forceinline__ void cp_async(void* dst_shared, const void* src_global) {
-  const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(dst_shared));
+__device__ __forceinline__ void cp_async(uint32_t dst_shared, const void* src_global) {
   if constexpr (BYTES == 16) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src_global) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_shared), "l"(src_global) : "memory");
   } else {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(dst), "l"(src_global), "n"(BYTES) : "memory");
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(dst_shared), "l"(src_global), "n"(BYTES)
+                 : "memory");
   }
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// Per-warp shared memory of the gather: two row buffers (8 tokens x 4 streams) and one K
+// metadata buffer (scale[128], min[128] of one group per stream).
 template <int BITS, int MODE>
 struct GatherSmem {
   static constexpr int kRowBytes = 16 * BITS;
   static constexpr int kRecord = kRowBytes + 16;
   static constexpr int kKBytes = MODE == kModePV ? 0 : kRowBytes;
   static constexpr int kVBytes = MODE == kModeQK ? 0 : kRecord;
-  static constexpr int kToken = kKBytes + kVBytes;           // one token of one stream
-  static constexpr int kMetaBytes = MODE == kModePV ? 0 : 512;  // scale[128], min[128] of one group
-  static constexpr int kBuffer = 8 * 4 * kToken + 4 * kMetaBytes;
-  static constexpr int kWarp = 2 * kBuffer;
+  static constexpr int kToken = kKBytes + kVBytes;  // one token of one stream
+  static constexpr int kRows = 8 * 4 * kToken;
+  static constexpr int kMeta = MODE == kModePV ? 0 : 4 * 512;
+  static constexpr int kWarp = 2 * kRows + kMeta;
+  static_assert(kWarps * kWarp >= kWarps * kPartialStride * 4, "the merge buffer reuses this memory");
 };
 
 template <int BITS, int MODE>
-__global__ void __launch_bounds__(kThreads, 3)
+__global__ void __launch_bounds__(kThreads, 4)
 selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   using G = GatherSmem<BITS, MODE>;
   constexpr int kRowBytes = G::kRowBytes;
   constexpr int kLaneBytes = kRowBytes / 4;
   constexpr uint32_t kFull = 0xffffffffu;
-  extern __shared__ __align__(128) uint8_t s_gather[];  // [warp][2][rows of 8 tokens x 4 streams | K metadata]
+  extern __shared__ __align__(128) uint8_t s_gather[];  // [warp][row buffer 0 | row buffer 1 | K metadata]
   __shared__ __align__(16) float s_qf[kHeadDim];
-  __shared__ __align__(16) __half s_wtab[kWarps][4][2][kHeadDim];
-  __shared__ float s_kbias[kWarps][4][2];
-  __shared__ int s_g0[kWarps][2][4];      // per buffer: first K metadata group of the run, per stream
-  __shared__ int s_ng[kWarps][2][4];      // ... and how many groups (0, 1 or 2) its rows touch
-  __shared__ __align__(16) float s_merge[kWarps][kPartialStride];
+  __shared__ __align__(16) __half s_wtab[kWarps][4][kHeadDim];  // the current run's K table of every stream
+  __shared__ float s_kbias[kWarps][4];
+  __shared__ int s_g0[kWarps][4];         // first K metadata group of the run whose metadata is in the buffer
   __shared__ int s_idx[kSlotBatch];       // logical index, or -1
   __shared__ int s_grow[4][kSlotBatch];   // row of the slot in every stream, counted from the head's first row, or -1
   __shared__ int s_key[kSlotBatch];       // 64-token block of the slot, kTailKey, or -1 (nothing to read)
   __shared__ int s_run[kSlotBatch + 1];   // first slot of every run, then the end
-  __shared__ int s_warp_runs[2][kWarps];
+  __shared__ int s_warp_runs[kWarps];
   __shared__ int s_last;
 
   const LayerView& L = p.L;
@@ -935,6 +936,8 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   const int quad = lane >> 2;
   const int sub = lane & 3;
   uint8_t* const my_gather = s_gather + warp * G::kWarp;
+  const uint32_t my_gather_u32 = smem_u32(my_gather);
+  const uint8_t* const my_meta = my_gather + 2 * G::kRows;
   float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);  // query channels 4*lane .. 4*lane+3
   if constexpr (MODE != kModePV) {
     s_qf[tid] = __bfloat162float(p.q[bh * kHeadDim + tid]);
@@ -961,21 +964,39 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   for (int i = 0; i < 16; ++i) hacc[i] = __floats2half2_rn(0.f, 0.f);
   int passes = 0;
 
+  // The K table of stream s for one metadata group: w_c = q_c * scale_c in pair order and
+  // bias = sum_c q_c * (min_c + centre * scale_c), from this lane's four channels.
+  auto build_table = [&](int s, uint2 sc, uint2 mn) {
+    const float2 sc01 = __half22float2(as_half2(sc.x)), sc23 = __half22float2(as_half2(sc.y));
+    const float2 mn01 = __half22float2(as_half2(mn.x)), mn23 = __half22float2(as_half2(mn.y));
+    const float kcn = float(kCentre<BITS>);
+    float bias = q4.x * fmaf(kcn, sc01.x, mn01.x);
+    bias = fmaf(q4.y, fmaf(kcn, sc01.y, mn01.y), bias);
+    bias = fmaf(q4.z, fmaf(kcn, sc23.x, mn23.x), bias);
+    bias = fmaf(q4.w, fmaf(kcn, sc23.y, mn23.y), bias);
+    __half* tab = &s_wtab[warp][s][(4 * lane) & ~31];
+    const int cc = (4 * lane) & 31;
+    tab[channel_slot<BITS>(cc + 0)] = __float2half_rn(q4.x * sc01.x);
+    tab[channel_slot<BITS>(cc + 1)] = __float2half_rn(q4.y * sc01.y);
+    tab[channel_slot<BITS>(cc + 2)] = __float2half_rn(q4.z * sc23.x);
+    tab[channel_slot<BITS>(cc + 3)] = __float2half_rn(q4.w * sc23.y);
+    bias = 0.25f * warp_sum(bias);  // added in each of the four lanes of a quad
+    if (lane == 0) s_kbias[warp][s] = bias;
+  };
+
   for (int batch_begin = slot_begin; batch_begin < slot_end; batch_begin += kSlotBatch) {
     const int batch_n = min(kSlotBatch, slot_end - batch_begin);
     __syncthreads();  // the previous round's lists are no longer read
     // ---- stage this round's slots: index, the row in every stream, run key
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int t = tid + half * kThreads;
+    {
       int idx = -1, key = -1;
       int rows[4] = {-1, -1, -1, -1};
-      if (t < batch_n) {
-        const int j = batch_begin + t;
+      if (tid < batch_n) {
+        const int j = batch_begin + tid;
         if (!valid_row || valid_row[j]) idx = idx_row[j];
         if (idx >= 0 && idx < quant) {
           // K tables belong to a 64-token block; without K (weighted PV) any eight slots make a pass
-          key = MODE == kModePV ? (t >> 3) : (idx >> 6);
+          key = MODE == kModePV ? (tid >> 3) : (idx >> 6);
           rows[0] = idx;
           if (streams >= 2) rows[1] = idx;
           if (streams >= 3) rows[2] = L.rank[0][L.rank_base[b] + idx];
@@ -988,35 +1009,24 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
           if (key < 0) p.logits[bh * p.capacity + j] = 0.f;
         }
       }
-      s_idx[t] = idx;
+      s_idx[tid] = idx;
 #pragma unroll
-      for (int s = 0; s < 4; ++s) s_grow[s][t] = rows[s];
-      s_key[t] = key;
+      for (int s = 0; s < 4; ++s) s_grow[s][tid] = rows[s];
+      s_key[tid] = key;
     }
     __syncthreads();
     // ---- runs: maximal ranges of consecutive slots with the same key
-    bool head[2];
-    uint32_t heads[2];
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int t = tid + half * kThreads;
-      head[half] = t < batch_n && (t == 0 || s_key[t - 1] != s_key[t]);
-      heads[half] = __ballot_sync(kFull, head[half]);
-      if (lane == 0) s_warp_runs[half][warp] = __popc(heads[half]);
-    }
+    const bool head = tid < batch_n && (tid == 0 || s_key[tid - 1] != s_key[tid]);
+    const uint32_t heads = __ballot_sync(kFull, head);
+    if (lane == 0) s_warp_runs[warp] = __popc(heads);
     __syncthreads();
-    int nruns = 0;
+    int run_base = 0, nruns = 0;
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      int run_base = 0;
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) {
-        if (half == 1) run_base += s_warp_runs[0][w];
-        if (w < warp) run_base += s_warp_runs[half][w];
-        nruns += s_warp_runs[half][w];
-      }
-      if (head[half]) s_run[run_base + __popc(heads[half] & ((1u << lane) - 1u))] = tid + half * kThreads;
+    for (int w = 0; w < kWarps; ++w) {
+      if (w < warp) run_base += s_warp_runs[w];
+      nruns += s_warp_runs[w];
     }
+    if (head) s_run[run_base + __popc(heads & ((1u << lane) - 1u))] = tid;
     if (tid == 0) s_run[nruns] = batch_n;
     __syncthreads();
 
@@ -1037,11 +1047,12 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
       ps.t0 += 8;
       if (ps.t0 >= ps.run_e) next_run(ps);
     };
-    // Issue the asynchronous copies of a packed pass into buffer `buf` (one commit group).
+    // Issue the asynchronous copies of a packed pass into row buffer `buf` (one commit group).
+    // The first pass of a run also brings the run's K metadata (first group of every stream) into
+    // the metadata buffer, which the previous run has finished with by then.
     auto issue = [&](const Pass& ps, int buf) {
-      uint8_t* dst = my_gather + buf * G::kBuffer;
       const int t = min(ps.t0 + quad, ps.run_e - 1);  // idle quads repeat the run's last token
-      uint8_t* token = dst + quad * 4 * G::kToken + sub * kLaneBytes;
+      const uint32_t token = my_gather_u32 + buf * G::kRows + quad * 4 * G::kToken + sub * kLaneBytes;
 #pragma unroll
       for (int s = 0; s < 4; ++s) {
         if (s < streams) {
@@ -1062,39 +1073,29 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
       }
       if constexpr (MODE != kModePV) {
         if (ps.t0 == ps.run_a) {
-          // first pass of a run: its K metadata (first group of every stream) travels with the rows
-          uint8_t* meta = dst + 8 * 4 * G::kToken;
+          const uint32_t meta = my_gather_u32 + 2 * G::kRows + lane * 8;
 #pragma unroll
           for (int s = 0; s < 4; ++s) {
             if (s < streams) {
-              int g0, ng;
+              int g0;
               if (s < 2) {
                 g0 = s_grow[s][ps.run_a] >> 6;
-                ng = 1;
               } else {
-                // rows of the run in a compact stream ascend with the slots: first and last present
-                int lo = INT_MAX, hi = -1;
+                // rows of the run in a compact stream ascend with the slots: the first present one
+                int lo = INT_MAX;
                 for (int u = ps.run_a + lane; u < ps.run_e; u += 32) {
                   const int rr = s_grow[s][u];
-                  if (rr >= 0) {
-                    lo = min(lo, rr);
-                    hi = max(hi, rr);
-                  }
+                  if (rr >= 0) lo = min(lo, rr);
                 }
                 lo = warp_min_int(lo);
-                hi = warp_max_int(hi);
-                g0 = hi >= 0 ? lo >> 6 : 0;
-                ng = hi >= 0 ? (hi >> 6) - g0 + 1 : 0;
+                g0 = lo == INT_MAX ? -1 : lo >> 6;
               }
-              if (ng > 0) {
+              if (g0 >= 0) {
                 const int64_t g = group_base[s] + g0;
-                cp_async<8>(meta + s * 512 + lane * 8, L.k_scale[s] + g * kHeadDim + 4 * lane);
-                cp_async<8>(meta + s * 512 + 256 + lane * 8, L.k_min[s] + g * kHeadDim + 4 * lane);
+                cp_async<8>(meta + s * 512, L.k_scale[s] + g * kHeadDim + 4 * lane);
+                cp_async<8>(meta + s * 512 + 256, L.k_min[s] + g * kHeadDim + 4 * lane);
               }
-              if (lane == 0) {
-                s_g0[warp][buf][s] = g0;
-                s_ng[warp][buf][s] = ng;
-              }
+              if (lane == 0) s_g0[warp][s] = g0;
             }
           }
         }
@@ -1104,17 +1105,36 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
 
     Pass cur{warp - kWarps, 0, 0, 0, -1};
     next_run(cur);
-    int buf = 0;             // the buffer that holds (or will hold) the current packed pass
-    int run_g0[2] = {0, 0};  // first K metadata group of the current run in streams 2 and 3
+    int buf = 0;               // the row buffer that holds (or will hold) the current packed pass
+    int run_g[2] = {-1, -1};   // K metadata group the tables of streams 2 and 3 were built for
     if (cur.r < nruns && cur.key != kTailKey) issue(cur, buf);
     while (cur.r < nruns) {
       Pass nxt = cur;
       advance(nxt);
       const bool prefetch = nxt.r < nruns && nxt.key != kTailKey;
-      __syncwarp();  // every lane is done with the buffer the next pass is copied into
-      if (prefetch) issue(nxt, buf ^ 1);
+      const bool packed_pass = cur.key != kTailKey;
+      if (packed_pass) {
+        cp_async_wait<0>();  // only the current pass is in flight here
+        __syncwarp();        // a quad shares the V metadata piece that its first lane copied
+        if constexpr (MODE != kModePV) {
+          if (cur.t0 == cur.run_a) {
+            // ---- the run's K tables, before the next run's metadata may overwrite the buffer
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+              if (s < streams && s_g0[warp][s] >= 0) {
+                build_table(s, *reinterpret_cast<const uint2*>(my_meta + s * 512 + lane * 8),
+                            *reinterpret_cast<const uint2*>(my_meta + s * 512 + 256 + lane * 8));
+              }
+            }
+            run_g[0] = s_g0[warp][2];
+            run_g[1] = s_g0[warp][3];
+          }
+        }
+      }
+      __syncwarp();  // tables written; every lane is done with the row buffer the next pass is copied into
+      if (prefetch) issue(nxt, packed_pass ? buf ^ 1 : buf);
 
-      if (cur.key == kTailKey) {
+      if (!packed_pass) {
         // ---- BF16 rows: tail tokens and the current token (read directly)
         const int t = cur.t0 + quad;
         const bool on = t < cur.run_e;
@@ -1150,21 +1170,18 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
         }
       } else {
         // ---- a pass inside one packed 64-token block, from shared memory
-        if (prefetch) cp_async_wait<1>(); else cp_async_wait<0>();
-        __syncwarp();  // a quad shares the V metadata piece that its first lane copied
-        const uint8_t* src = my_gather + buf * G::kBuffer;
-        const uint8_t* token = src + quad * 4 * G::kToken;
+        const uint8_t* token = my_gather + buf * G::kRows + quad * 4 * G::kToken;
         const bool on = cur.t0 + quad < cur.run_e;
         const int t = min(cur.t0 + quad, cur.run_e - 1);
         // which streams hold this token (idle quads: none); `any` is the same for the whole warp
         uint32_t mine = 0, any = 0;
-        int rows23[2] = {-1, -1};
+        int group23[2] = {-1, -1};
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
           if (s < streams) {
             const int row = s_grow[s][t];
-            if (s >= 2) rows23[s - 2] = row;
             const bool have = on && row >= 0;
+            if (s >= 2) group23[s - 2] = have ? row >> 6 : -1;
             mine |= have ? 1u << s : 0u;
             any |= __any_sync(kFull, have) ? 1u << s : 0u;
           }
@@ -1172,64 +1189,47 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
 
         float pr = 0.f;
         if constexpr (MODE != kModePV) {
-          if (cur.t0 == cur.run_a) {
-            // ---- the run's K tables: w_c = q_c * scale_c, bias = sum_c q_c * (min_c + centre * scale_c)
-            __syncwarp();  // every lane has left the previous run: its tables may be overwritten
-            const uint8_t* meta = src + 8 * 4 * G::kToken;
-#pragma unroll
-            for (int s = 0; s < 4; ++s) {
-              if (s < streams) {
-                const int ng = s_ng[warp][buf][s];
-                for (int gi = 0; gi < ng && gi < 2; ++gi) {
-                  uint2 sc, mn;
-                  if (gi == 0) {
-                    sc = *reinterpret_cast<const uint2*>(meta + s * 512 + lane * 8);
-                    mn = *reinterpret_cast<const uint2*>(meta + s * 512 + 256 + lane * 8);
-                  } else {
-                    const int64_t g = group_base[s] + s_g0[warp][buf][s] + 1;
-                    sc = ldg64(L.k_scale[s] + g * kHeadDim + 4 * lane);
-                    mn = ldg64(L.k_min[s] + g * kHeadDim + 4 * lane);
-                  }
-                  const float2 sc01 = __half22float2(as_half2(sc.x)), sc23 = __half22float2(as_half2(sc.y));
-                  const float2 mn01 = __half22float2(as_half2(mn.x)), mn23 = __half22float2(as_half2(mn.y));
-                  const float kcn = float(kCentre<BITS>);
-                  float bias = q4.x * fmaf(kcn, sc01.x, mn01.x);
-                  bias = fmaf(q4.y, fmaf(kcn, sc01.y, mn01.y), bias);
-                  bias = fmaf(q4.z, fmaf(kcn, sc23.x, mn23.x), bias);
-                  bias = fmaf(q4.w, fmaf(kcn, sc23.y, mn23.y), bias);
-                  __half* tab = &s_wtab[warp][s][gi][(4 * lane) & ~31];
-                  const int cc = (4 * lane) & 31;
-                  tab[channel_slot<BITS>(cc + 0)] = __float2half_rn(q4.x * sc01.x);
-                  tab[channel_slot<BITS>(cc + 1)] = __float2half_rn(q4.y * sc01.y);
-                  tab[channel_slot<BITS>(cc + 2)] = __float2half_rn(q4.z * sc23.x);
-                  tab[channel_slot<BITS>(cc + 3)] = __float2half_rn(q4.w * sc23.y);
-                  bias = 0.25f * warp_sum(bias);  // added in each of the four lanes of a quad
-                  if (lane == 0) s_kbias[warp][s][gi] = bias;
-                }
-              }
-            }
-            run_g0[0] = s_g0[warp][buf][2];
-            run_g0[1] = s_g0[warp][buf][3];
-            __syncwarp();
-          }
           // Every lane runs every stream some lane needs; a lane without the row computes on
           // whatever its buffer holds and drops the result (unpacked codes are always finite).
           float dot = 0.f;
 #pragma unroll
           for (int s = 0; s < 4; ++s) {
             if (any & (1u << s)) {
-              const int gi = s >= 2 ? max(0, min(1, (rows23[s >= 2 ? s - 2 : 0] >> 6) - run_g0[s >= 2 ? s - 2 : 0])) : 0;
-              __half2 mult[16];
-              const uint4* tab = reinterpret_cast<const uint4*>(&s_wtab[warp][s][gi][sub * 32]);
-#pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                const uint4 x = tab[v];
-                mult[4 * v + 0] = as_half2(x.x); mult[4 * v + 1] = as_half2(x.y);
-                mult[4 * v + 2] = as_half2(x.z); mult[4 * v + 3] = as_half2(x.w);
-              }
               const Codes<BITS> kc = load_codes_shared<BITS>(token + s * G::kToken + sub * kLaneBytes);
-              const float kd = k_dot_fast<BITS>(kc, mult) + s_kbias[warp][s][gi];
-              dot += (mine & (1u << s)) ? kd : 0.f;
+              bool take = mine & (1u << s);
+              // The compact rows of one block may straddle two metadata groups: tokens of the
+              // first group use the table as built, then the table moves on to the second.
+              for (int round = 0; round < 2; ++round) {
+                bool now = take;
+                if (s >= 2) {
+                  const int g = group23[s >= 2 ? s - 2 : 0];
+                  now = take && g == run_g[s >= 2 ? s - 2 : 0];
+                  if (round == 1) {
+                    const bool later = take && g > run_g[s >= 2 ? s - 2 : 0];
+                    if (!__any_sync(kFull, later)) break;
+                    __syncwarp();
+                    const int next = run_g[s >= 2 ? s - 2 : 0] + 1;
+                    const int64_t gg = group_base[s] + next;
+                    build_table(s, ldg64(L.k_scale[s] + gg * kHeadDim + 4 * lane),
+                                ldg64(L.k_min[s] + gg * kHeadDim + 4 * lane));
+                    run_g[s >= 2 ? s - 2 : 0] = next;
+                    __syncwarp();
+                    now = later;
+                  }
+                } else if (round == 1) {
+                  break;
+                }
+                __half2 mult[16];
+                const uint4* tab = reinterpret_cast<const uint4*>(&s_wtab[warp][s][sub * 32]);
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                  const uint4 x = tab[v];
+                  mult[4 * v + 0] = as_half2(x.x); mult[4 * v + 1] = as_half2(x.y);
+                  mult[4 * v + 2] = as_half2(x.z); mult[4 * v + 3] = as_half2(x.w);
+                }
+                const float kd = k_dot_fast<BITS>(kc, mult) + s_kbias[warp][s];
+                dot += now ? kd : 0.f;
+              }
             }
           }
           dot = quad_sum(dot);
@@ -1252,9 +1252,8 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
         if constexpr (MODE != kModeQK) {
           const uint32_t pick = (sub < 2) ? 0x1010u : 0x3232u;
           const __half2 centre2 = __floats2half2_rn(float(kCentre<BITS>), float(kCentre<BITS>));
-          const __half2 zero2 = __floats2half2_rn(0.f, 0.f);
           const __half2 p2 = __float2half2_rn(pr);
-          __half2 hb = zero2;
+          __half2 hb = __floats2half2_rn(0.f, 0.f);
 #pragma unroll
           for (int s = 0; s < 4; ++s) {
             if (any & (1u << s)) {
@@ -1274,10 +1273,6 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
         }
         buf ^= 1;
       }
-      if (cur.key == kTailKey && prefetch) {
-        // the prefetched pass was issued into buf ^ 1 and the tail pass used no buffer
-        buf ^= 1;
-      }
       cur = nxt;
     }
     cp_async_wait<0>();
@@ -1285,6 +1280,8 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   if constexpr (MODE == kModeQK) return;
   flush_pairs(hacc, S.acc);
 
+  __syncthreads();  // every warp has left its gather buffers: they become the merge buffer
+  float (*s_merge)[kPartialStride] = reinterpret_cast<float (*)[kPartialStride]>(s_gather);
   state_store<BITS>(S, lane, s_merge[warp]);
   float total, denom;
   if (merge_and_publish<kWarps>(p, s_merge, &s_last, bh, split, nsplits, total, denom)) {
@@ -1311,9 +1308,9 @@ int choose_chunk_tokens(int64_t batch_heads, int64_t max_context_tokens) {
 }
 
 int choose_slots_per_cta(int64_t batch_heads, int64_t capacity) {
-  // One wave: three CTAs of the gather kernel are resident per SM, so the grid is kept within
-  // 148 * 3 CTAs where the capacity allows it (a second, partial wave would cost a whole round).
-  const int64_t budget = 148 * 3;
+  // One wave: four CTAs of the gather kernel are resident per SM, so the grid is kept within
+  // 148 * 4 CTAs where the capacity allows it (a second, partial wave would cost a whole round).
+  const int64_t budget = 148 * 4;
   int64_t slots = 32;
   while ((batch_heads * ((capacity + slots - 1) / slots) > budget || (capacity + slots - 1) / slots > kMaxSplits) &&
          slots < capacity)
