@@ -188,7 +188,7 @@ def _oracle_head_step(seed: int, context: int, bits: int) -> float:
     return time.perf_counter() - start
 
 
-def cpu_oracle_tokens_per_second(args, tasks_per_core: int = 1) -> dict:
+def cpu_oracle_tokens_per_second(args, tasks_per_core: int = 3) -> dict:
     """Time the oracle on every host core at once (one head-step task per core per round) and
     scale to whole decode tokens: one token = HEADS heads x layers."""
 

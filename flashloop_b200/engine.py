@@ -27,7 +27,7 @@ from .selection import decode_budget
 from .prefill import PrefillReceipt, apply_rope, dense_prefill_loop, sparse_prefill_loop
 from . import step_ops
 from .tensor_parallel import PartialSum
-from .weights import fused_mlp, project_qkv, repack_projection_weights
+from .weights import fused_mlp, project_qkv, project_value, repack_projection_weights
 
 
 @dataclass(frozen=True)
@@ -85,6 +85,7 @@ class FlashLoopEngine:
             raise ValueError("the tensor-parallel decode step is launched eagerly: use_cuda_graph=False")
         self._reduce = PartialSum(tp_group) if tp_group is not None else (lambda t: t)
         self.fuse_decode_ops = bool(fuse_decode_ops) and self._modules_are_fusable()
+        self._reuse = self.config.reuse_selected_probabilities and self.config.enable_sparse_decode
         self._state: EngineState | None = None
         self._graph = None
         self._graph_io = None
@@ -239,6 +240,12 @@ class FlashLoopEngine:
                 sources[index] = (projected, sel, aggregate)
             return projected
         projected0, sel, aggregate = sources[index]
+        if self.config.reuse_selected_probabilities:
+            # engine.py:502-513: the loop-2 probabilities are reused, only V is read
+            target = physical.pv(loop, sel.selected_weights, sel.indices, current_value=v, valid=sel.valid,
+                                 validate_indices=False)
+            delta = sel.global_mass.view(batch, -1, 1, 1) * (target - aggregate)
+            return projected0 + self._reduce(o_proj(delta.to(v.dtype).view(batch, 1, -1)))
         delta = physical.cached_mass_sparse_attention_delta(
             loop, query=q, current_key=k, current_value=v, indices=sel.indices, valid=sel.valid,
             source_selected_output=aggregate, global_mass=sel.global_mass, scaling=scaling)
@@ -265,9 +272,14 @@ class FlashLoopEngine:
             x = step_ops.rmsnorm(hidden, first.weight, eps(first))
             for index, layer in enumerate(self.layers):
                 attention, mlp = layer.self_attn, layer.mlp
-                q, k, v = F.linear(x, attention._flashloop_qkv_weight).split(attention._flashloop_qkv_splits, dim=-1)
-                heads = q.shape[-1] // 128
-                q, k, v = step_ops.rope_split(q, k, v, cos, sin, heads=heads)
+                if loop >= 2 and self._reuse:
+                    # engine.py:401-408: no Q/K in the late loops; the loop-2 key stands in for the append
+                    v = project_value(attention, x).view(batch, -1, 1, 128)
+                    q, k = None, keys[index][1]
+                else:
+                    q, k, v = F.linear(x, attention._flashloop_qkv_weight).split(attention._flashloop_qkv_splits,
+                                                                                  dim=-1)
+                    q, k, v = step_ops.rope_split(q, k, v, cos, sin, heads=q.shape[-1] // 128)
                 keys[index][loop], values[index][loop] = k, v
                 projected = self._attend(loop, index, q, k, v, float(attention.scaling), sources,
                                          attention.o_proj, batch)
@@ -298,13 +310,18 @@ class FlashLoopEngine:
             for index, layer in enumerate(self.layers):
                 attention = layer.self_attn
                 head_dim = int(attention.head_dim)
-                q, k, v = project_qkv(attention, layer.input_layernorm(hidden))
-                heads = q.shape[-1] // head_dim
-                q = q.view(batch, 1, heads, head_dim).transpose(1, 2)
-                k = k.view(batch, 1, heads, head_dim).transpose(1, 2)
-                v = v.view(batch, 1, heads, head_dim).transpose(1, 2).contiguous()
-                q, k = apply_rope(q, k, cos, sin)
-                q, k = q.contiguous(), k.contiguous()
+                if loop >= 2 and self._reuse:
+                    v = project_value(attention, layer.input_layernorm(hidden))
+                    v = v.view(batch, 1, -1, head_dim).transpose(1, 2).contiguous()
+                    q, k = None, keys[index][1]
+                else:
+                    q, k, v = project_qkv(attention, layer.input_layernorm(hidden))
+                    heads = q.shape[-1] // head_dim
+                    q = q.view(batch, 1, heads, head_dim).transpose(1, 2)
+                    k = k.view(batch, 1, heads, head_dim).transpose(1, 2)
+                    v = v.view(batch, 1, heads, head_dim).transpose(1, 2).contiguous()
+                    q, k = apply_rope(q, k, cos, sin)
+                    q, k = q.contiguous(), k.contiguous()
                 keys[index][loop], values[index][loop] = k, v
                 projected = self._attend(loop, index, q, k, v, float(attention.scaling), sources,
                                          attention.o_proj, batch)

@@ -47,6 +47,16 @@ def project_qkv(attention: nn.Module, values: torch.Tensor):
     return tuple(F.linear(values, weight).split(attention._flashloop_qkv_splits, dim=-1))
 
 
+def project_value(attention: nn.Module, values: torch.Tensor) -> torch.Tensor:
+    """weights.py:91-105: only V, from the packed QKV weight without copying it."""
+
+    weight = getattr(attention, "_flashloop_qkv_weight", None)
+    if weight is None:
+        return attention.v_proj(values)
+    q_features, k_features, v_features = attention._flashloop_qkv_splits
+    return F.linear(values, weight.narrow(0, q_features + k_features, v_features))
+
+
 def fused_mlp(mlp: nn.Module, values: torch.Tensor) -> torch.Tensor:
     """weights.py:108-117."""
 

@@ -156,6 +156,21 @@ for p in range(2):
     out[f"p{p}.final_quantized_tokens"] = np.asarray(layer0.quantized_tokens)
     out[f"p{p}.final_tail_tokens"] = np.asarray(layer0.tail_tokens)
 
+# --- the reuse_selected_probabilities option (engine.py:401-408, 502-513): prompt 0, 24 steps ---
+from flashloop.config import FlashLoopConfig as RefConfig  # noqa: E402
+
+tracing.update(on=False)
+engine = RefEngine(tiny_ouro_model(), validate_model=False, config=RefConfig(reuse_selected_probabilities=True))
+logits = engine.prefill(torch.from_numpy(prompts[0:1])).logits.reshape(1, -1)
+tokens, step_logits = [], []
+for _ in range(24):
+    token = logits.argmax(-1, keepdim=True)
+    tokens.append(int(token))
+    logits = engine.decode(token.view(1, 1)).logits.reshape(1, -1)
+    step_logits.append(logits.float().reshape(-1).numpy())
+out["reuse.tokens"] = np.asarray(tokens, dtype=np.int64)
+out["reuse.decode_logits"] = np.stack(step_logits)
+
 np.savez_compressed(HERE / "engine_vectors.npz", **out)
 np.savez_compressed(HERE / "engine_trace.npz", **trace)
 print("trace:", len(trace), "arrays,", (HERE / "engine_trace.npz").stat().st_size / 1e6, "MB")

@@ -22,6 +22,7 @@ def test_config_defaults_and_fractions():
     assert FlashLoopConfig(enable_token_sparse_prefill=False).effective_prefill_fractions == (1.0, 1.0)
     assert FlashLoopConfig(enable_sparse_decode=False).effective_decode_key_fraction == 1.0
     assert FlashLoopConfig(kv_bits=2).kv_bits == 2
+    assert FlashLoopConfig(reuse_selected_probabilities=True).reuse_selected_probabilities
 
 
 @pytest.mark.parametrize("kwargs", [

@@ -259,3 +259,29 @@ def test_decode_trace_replay(eg):
     assert np.median(sparse_errors) < 1e-2 and worst["sparse"] < 1e-1, (np.median(sparse_errors), worst)
     assert layers[0].quantized_tokens == 192 and layers[0].tail_tokens == 78
     assert all(layer.reader_status() == 0 for layer in layers)
+
+
+class _Prompt0MaskEngine(FlashLoopEngine):
+    golden = None
+
+    def _retain(self, loop, scores, fraction, eligible):
+        return retained_from_mask(torch.from_numpy(self.golden[f"p0.mask{loop}"][None]).cuda())
+
+
+@pytest.mark.parametrize("fuse", [True, False])
+def test_reuse_selected_probabilities_follows_reference(eg, fuse):
+    """The reference's reuse_selected_probabilities option (engine.py:401-408, 502-513): loops 3-4
+    skip Q/K and re-weight the loop-2 probabilities over the late loops' values."""
+
+    _Prompt0MaskEngine.golden = eg
+    engine = _Prompt0MaskEngine(tiny_ouro_model().cuda(), validate_model=False, max_new_tokens=32,
+                                config=FlashLoopConfig(reuse_selected_probabilities=True), fuse_decode_ops=fuse)
+    engine.prefill(torch.from_numpy(eg["prompts"][:1]).cuda())
+    ref = eg["reuse.decode_logits"]
+    got = np.stack([engine.decode(torch.tensor([[int(t)]], device="cuda")).logits[0].cpu().numpy()
+                    for t in eg["reuse.tokens"]])
+    per_step = np.abs(got - ref).mean(axis=1)
+    assert np.median(per_step) < 0.1 and per_step.mean() < 0.15 and per_step.max() < 0.6, per_step
+    assert np.corrcoef(got.ravel(), ref.ravel())[0, 1] > 0.99
+    # the option changes the result: it must not be the default path in disguise
+    assert np.abs(ref[:20] - eg["p0.decode_logits"][:20]).mean() > 0.05
