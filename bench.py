@@ -46,10 +46,11 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="hotpath", choices=["hotpath", "ragged", "e2e"],
+    ap.add_argument("--workload", default="hotpath", choices=["hotpath", "ragged", "e2e", "e2e-2.6b"],
                     help="hotpath: configs[1], the KV-attention path of every layer on synthetic vectors; "
                          "ragged: configs[2], the same path over 32 sequences of 1024..32768 tokens (one layer); "
-                         "e2e: configs[3], the Ouro-1.4B-shaped model decoding through the engine")
+                         "e2e: configs[3], the Ouro-1.4B-shaped model decoding through the engine; "
+                         "e2e-2.6b: one GPU's share of configs[4] (48 layers, 8 of the 64 sequences, 8192-token prompts)")
     ap.add_argument("--layers", type=int, default=None, help="physical layers (default 24; 1 for ragged)")
     ap.add_argument("--batch", type=int, default=None, help="sequences per GPU (default 8 hotpath, 16 e2e)")
     ap.add_argument("--context", type=int, default=None, help="context / prompt length (default 8192 hotpath, 2048 e2e)")
@@ -60,6 +61,12 @@ def parse_args():
                          "and the MLP) instead of running one replica per rank")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
+    args.config_index = 3
+    if args.workload == "e2e-2.6b":
+        args.workload, args.config_index = "e2e", 4
+        args.layers = args.layers or 48
+        args.batch = args.batch or 8
+        args.context = args.context or 8192
     if args.batch is None:
         args.batch = {"hotpath": BATCH, "ragged": 32, "e2e": 16}[args.workload]
     if args.context is None:
@@ -71,7 +78,9 @@ def parse_args():
 
 def workload_name(args) -> str:
     if args.workload == "e2e":
-        return (f"configs[3] end-to-end Ouro-1.4B-shaped decoder (random-init bf16, {args.layers} layers x 4 loops, "
+        which = ("configs[3] end-to-end Ouro-1.4B-shaped decoder" if args.config_index == 3 else
+                 "configs[4] Ouro-2.6B-shaped decoder, one GPU's share of the batch of 64,")
+        return (f"{which} (random-init bf16, {args.layers} layers x 4 loops, "
                 f"hidden 2048, {HEADS} heads x {HEAD_DIM}, SwiGLU 5632, vocab 49152): batch {args.batch}/GPU, "
                 f"{args.context}-token random prompts, greedy decode, loops 1-2 dense, 25%/10% token retention, "
                 f"10% key retention, {args.bits}-bit K/V group 64")
