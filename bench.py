@@ -46,10 +46,11 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="hotpath", choices=["hotpath", "ragged", "e2e", "e2e-2.6b"],
+    ap.add_argument("--workload", default="hotpath", choices=["hotpath", "ragged", "e2e", "e2e-2.6b", "kernels"],
                     help="hotpath: configs[1], the KV-attention path of every layer on synthetic vectors; "
                          "ragged: configs[2], the same path over 32 sequences of 1024..32768 tokens (one layer); "
                          "e2e: configs[3], the Ouro-1.4B-shaped model decoding through the engine; "
+                         "kernels: every kernel of the path alone at the configs[1] shapes, with its bytes and fraction of peak; "
                          "e2e-2.6b: one GPU's share of configs[4] (48 layers, 8 of the 64 sequences, 8192-token prompts)")
     ap.add_argument("--layers", type=int, default=None, help="physical layers (default 24; 1 for ragged)")
     ap.add_argument("--batch", type=int, default=None, help="sequences per GPU (default 8 hotpath, 16 e2e)")
@@ -68,9 +69,9 @@ def parse_args():
         args.batch = args.batch or 8
         args.context = args.context or 8192
     if args.batch is None:
-        args.batch = {"hotpath": BATCH, "ragged": 32, "e2e": 16}[args.workload]
+        args.batch = {"hotpath": BATCH, "ragged": 32, "e2e": 16, "kernels": BATCH}[args.workload]
     if args.context is None:
-        args.context = {"hotpath": CONTEXT, "ragged": 32768, "e2e": 2048}[args.workload]
+        args.context = {"hotpath": CONTEXT, "ragged": 32768, "e2e": 2048, "kernels": CONTEXT}[args.workload]
     if args.layers is None:
         args.layers = 1 if args.workload == "ragged" else LAYERS
     return args
@@ -441,6 +442,163 @@ def run_b200(args) -> None:
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------- per-kernel table
+
+
+def run_kernel_table(args) -> None:
+    """Every kernel of the path timed alone (CUDA events around a graph of back-to-back launches
+    over six different layers, so that no launch finds its input in L2), with its algorithmic
+    bytes and the fraction of the measured copy bandwidth.  One JSON line."""
+
+    import torch
+
+    from flashloop_b200 import _native
+    from flashloop_b200.cache import CrossLoopKVLayer
+    from flashloop_b200.compaction import gather_rows, hidden_delta_score, retain_tokens, scatter_rows
+    from flashloop_b200.kivi_backend import kivi_to_rows, pack_kivi_k_per_channel, pack_kivi_v_per_token
+    from flashloop_b200.packing import pack_k_per_channel, pack_v_per_token
+    from flashloop_b200.synthetic import make_loop_kv
+
+    _native.load()
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    B, H, T, bits, NL = args.batch, HEADS, args.context, args.bits, 6
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    peaks = json.loads(peaks_path.read_text()) if peaks_path.exists() else {}
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    rows = []
+
+    def timeit(fn, reps: int = 12) -> float:
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(reps):
+                fn(i)
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (3 * reps) * 1e3
+
+    def add(name: str, us: float, nbytes: float, note: str = "") -> None:
+        gbs = nbytes / us / 1e3
+        rows.append({"kernel": name, "us": round(us, 1), "algorithmic_MB": round(nbytes / 1e6, 1),
+                     "GBps": round(gbs), "frac_of_peak": round(gbs / peak, 3), "note": note})
+
+    # ---- inputs: NL layers of B sequences
+    ones = torch.ones(B, T, dtype=torch.bool, device=device)
+    kv = []
+    for layer_index in range(NL):
+        keys, values = [[] for _ in range(4)], [[] for _ in range(4)]
+        for b in range(B):
+            k, v = make_loop_kv(H, T, seed=layer_index * 100 + b, device=device)
+            for r in range(4):
+                keys[r].append(k[r])
+                values[r].append(v[r])
+        kv.append(([torch.cat(k) for k in keys], [torch.cat(v) for v in values]))
+    elems = B * H * T * HEAD_DIM
+    # ---- codecs (per launch: one [B,H,T,128] bf16 tensor in, packed codes + metadata out)
+    code_bytes = elems * bits / 8
+    add("pack_k rows (fl_pack_k_rows)", timeit(lambda i: pack_k_per_channel(kv[i % NL][0][0], bits=bits)),
+        2 * elems + code_bytes + elems / 64 * 4)
+    add("pack_v rows (fl_pack_v_rows)", timeit(lambda i: pack_v_per_token(kv[i % NL][1][0], bits=bits)),
+        2 * elems + code_bytes + elems / 64 * 4)
+    if bits == 4:
+        add("pack_k KIVI words (fl_pack_kivi_k)", timeit(lambda i: pack_kivi_k_per_channel(kv[i % NL][0][0])),
+            2 * elems + code_bytes + elems / 64 * 4)
+        add("pack_v KIVI words (fl_pack_kivi_v)", timeit(lambda i: pack_kivi_v_per_token(kv[i % NL][1][0])),
+            2 * elems + code_bytes + elems / 64 * 4)
+        packed = [pack_kivi_k_per_channel(kv[i][0][0]) for i in range(NL)]
+        add("KIVI words -> rows, K (fl_kivi_to_rows_k)", timeit(lambda i: kivi_to_rows(packed[i % NL])), 2 * code_bytes)
+        del packed
+    # ---- prefill encoder: four loops of K and V in, all streams out
+    def build(i):
+        return CrossLoopKVLayer.from_prefill(kv[i % NL][0], kv[i % NL][1], mask_loop3=ones, mask_loop4=ones, bits=bits,
+                                             max_new_tokens=256)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    layers = [build(i) for i in range(NL)]
+    torch.cuda.synchronize()
+    add("prefill encoder, all-token masks (fl_encode_prefill + tails, host included)",
+        (time.perf_counter() - t0) / NL * 1e6, 8 * 2 * elems + 4 * 2 * (code_bytes + elems / 64 * 4),
+        "wall clock per layer including the Python around the three launches")
+    quant, tail = layers[0].quantized_tokens, layers[0].tail_tokens
+    for layer in layers:
+        layer.context_bound = T + 256
+    bh = B * H
+    gen = torch.Generator(device=device).manual_seed(1)
+    q, ck, cv = (torch.randn(B, H, 1, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16) for _ in range(3))
+    out = torch.empty(B, H, 1, HEAD_DIM, device=device)
+    for loop in range(4):
+        us = timeit(lambda i: layers[i % NL].dense_source_attention(loop, query=q, current_key=ck, current_value=cv,
+                                                                   scaling=SCALING, return_logits=loop == 1, out=out))
+        add(f"dense reader loop {loop + 1} (fl_dense_source_attention)", us, dense_bytes(bh, loop, quant, tail, bits))
+    _, logits = layers[0].dense_source_attention(1, query=q, current_key=ck, current_value=cv, scaling=SCALING,
+                                                 return_logits=True)
+    keys_n = math.ceil((T + 1) * KEY_FRACTION)
+    add("decode key selection (fl_select_decode_keys)",
+        timeit(lambda i: layers[0].select_decode_keys(logits, fraction=KEY_FRACTION)), bh * (4 * (T + 1) + 6 * keys_n),
+        "latency bound: one CTA per head")
+    sel = layers[0].select_decode_keys(logits, fraction=KEY_FRACTION)
+    pv_bytes = bh * (2 * keys_n * (16 * bits + 8) + keys_n * 13 + 1280)
+    add("selected value aggregate, loop 2 (fl_selected_pv)",
+        timeit(lambda i: layers[i % NL].pv(1, sel.selected_weights, sel.indices, current_value=cv, valid=sel.valid,
+                                           validate_indices=False, out=out)), pv_bytes)
+    add("selected logits, loop 2 (fl_selected_qk)",
+        timeit(lambda i: layers[i % NL].qk(1, q, sel.indices, validate_indices=False, current_key=ck)),
+        bh * (2 * (keys_n * 16 * bits + 512 * (quant // 64)) + keys_n * 8 + 512))
+    src = layers[0].pv(1, sel.selected_weights, sel.indices, current_value=cv, valid=sel.valid, validate_indices=False)
+    for loop in (2, 3):
+        us = timeit(lambda i: layers[i % NL].cached_mass_sparse_attention_delta(
+            loop, query=q, current_key=ck, current_value=cv, indices=sel.indices, valid=sel.valid,
+            source_selected_output=src, global_mass=sel.global_mass, scaling=SCALING, out=out))
+        add(f"sparse delta loop {loop + 1} (fl_sparse_attention_delta)", us, sparse_bytes(bh, loop, keys_n, quant, bits))
+    # ---- append: plain step, and the step that rolls 64 tokens over (timed once per layer, eagerly)
+    k4, v4 = [ck] * 4, [cv] * 4
+    def timed_append(layer) -> float:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        layer.append_decode_token(k4, v4)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3
+    plain, rolled = [], []
+    for layer in layers:
+        while layer.tail_tokens < 126:
+            layer.append_decode_token(k4, v4)
+        plain.append(timed_append(layer))   # tail 126 -> 127
+        rolled.append(timed_append(layer))  # tail 127 -> 128: rollover
+    add("append, no rollover (fl_append_decode_token, 3 launches, eager)", statistics.median(plain), bh * 8 * 256 * 2)
+    add("append with 64-token rollover (3 launches, eager)", statistics.median(rolled),
+        bh * (4 * 2 * 64 * 256 + 4 * 64 * (2 * 16 * bits + 24)))
+    # ---- token retention (prefill time): hidden [B, T, 2048]
+    h1 = torch.randn(B, T, 2048, generator=gen, device=device).to(torch.bfloat16)
+    h2 = (h1.float() + 0.1 * torch.randn(B, T, 2048, generator=gen, device=device)).to(torch.bfloat16)
+    add("hidden-delta score (fl_hidden_delta_score)", timeit(lambda i: hidden_delta_score(h2, h1)), 2 * h1.numel() * 2)
+    score = hidden_delta_score(h2, h1)
+    add("token retention (fl_select_prefill_tokens)", timeit(lambda i: retain_tokens(score, fraction=0.25)),
+        B * T * (4 + 1 + 4 + 4), "latency bound: one CTA per sequence")
+    kept = retain_tokens(score, fraction=0.25)
+    n = int(kept.count[0])
+    compact = gather_rows(h2, kept.positions, kept.count, rows=n)
+    add("gather retained rows (fl_gather_rows)", timeit(lambda i: gather_rows(h2, kept.positions, kept.count, rows=n)),
+        2 * compact.numel() * 2)
+    add("scatter retained rows (fl_scatter_rows)", timeit(lambda i: scatter_rows(h2, compact, kept.positions, kept.count)),
+        2 * compact.numel() * 2)
+    line = {"metric": "kernel table: achieved GB/s per kernel of the path", "unit": "GB/s", "n_gpus": 1,
+            "peak_GBps": peak, "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback 6650 GB/s",
+            "config": {"workload": f"every kernel alone at batch {B}, {H} heads x {HEAD_DIM}, context {T}, {bits}-bit, "
+                                   f"all-token masks; timed as graphs of 12 launches over 6 layers"},
+            "kernels": rows}
+    print(json.dumps(line))
+
+
 # ----------------------------------------------------------------------------- the end-to-end workload
 
 
@@ -614,6 +772,8 @@ def main() -> None:
         run_reference(args)
     elif args.workload == "e2e":
         run_e2e(args)
+    elif args.workload == "kernels":
+        run_kernel_table(args)
     else:
         run_b200(args)
 

@@ -152,8 +152,8 @@ rope_split_kernel(const __nv_bfloat16* __restrict__ q_in, const __nv_bfloat16* _
 // out = bf16(silu(gate)) * up, gate_up = [rows][2 * width]
 __global__ void __launch_bounds__(kStepThreads)
 swiglu_kernel(const __nv_bfloat16* __restrict__ gate_up, int width, __nv_bfloat16* __restrict__ out) {
-  const int64_t row = blockIdx.y;
-  const int e = (blockIdx.x * kStepThreads + threadIdx.x) * 8;
+  const int64_t row = blockIdx.x;
+  const int e = (blockIdx.y * kStepThreads + threadIdx.x) * 8;
   if (e >= width) return;
   float g[8], u[8];
   unpack8(ldg128(gate_up + row * 2 * width + e), g);
@@ -208,10 +208,12 @@ extern "C" int fl_rope_split(const void* q_in, const void* k_in, const void* v_i
 
 extern "C" int fl_swiglu(const void* gate_up, int64_t rows, int32_t width, void* out, fl_cuda_stream stream) {
   FL_REQUIRE(gate_up && out, "fl_swiglu: null argument");
-  FL_REQUIRE(rows >= 0 && rows <= 65535 && width > 0 && width % 8 == 0, "fl_swiglu: bad sizes");
+  FL_REQUIRE(rows >= 0 && rows < (int64_t(1) << 31) && width > 0 && width % 8 == 0 &&
+                 width <= 65535 * kStepThreads * 8,
+             "fl_swiglu: bad sizes");
   FL_REQUIRE(aligned16(gate_up) && aligned16(out), "fl_swiglu: pointers must be 16-byte aligned");
   if (rows == 0) return FL_OK;
-  const dim3 grid((width / 8 + kStepThreads - 1) / kStepThreads, static_cast<unsigned>(rows));
+  const dim3 grid(static_cast<unsigned>(rows), (width / 8 + kStepThreads - 1) / kStepThreads);
   swiglu_kernel<<<grid, kStepThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(gate_up), width, static_cast<__nv_bfloat16*>(out));
   FL_CHECK_LAUNCH("fl_swiglu");
