@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(128) rollover_kernel(const AppendParams p) {
         mx = fmaxf(mx, x);
       }
       const float sc = quant_scale(mn, mx, kLevels);
+      const float inv = quant_inverse(sc);
       const __half mn16 = __float2half_rn(mn), sc16 = __float2half_rn(sc);
       const int64_t group = p.L.group_base[s][bh] + row0[s] / kGroup;
       p.k_min[s][group * kHeadDim + c] = mn16;
@@ -119,7 +120,7 @@ __global__ void __launch_bounds__(128) rollover_kernel(const AppendParams p) {
         float x = __bfloat162float(src[((start + i) % cap) * kHeadDim]);
         const float base = s > 0 ? __bfloat162float(s_recon[i][c]) : 0.f;
         if (s > 0) x = bf16_round(x - base);
-        const uint32_t code = quant_code(x, mn, sc, kLevels);
+        const uint32_t code = quant_code(x, mn, sc, inv, kLevels);
         const int j = s < 2 ? i : s_rank[s - 2][i];
         s_tile[j][c] = static_cast<uint8_t>(code);
         const float dec = bf16_round(dequant_f32(code, sc16, mn16));
@@ -161,11 +162,12 @@ __global__ void __launch_bounds__(128) rollover_kernel(const AppendParams p) {
           mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         }
         const float sc = quant_scale(mn, mx, kLevels);
+        const float inv = quant_inverse(sc);
         const __half mn16 = __float2half_rn(mn), sc16 = __float2half_rn(sc);
         uint32_t packed = 0;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const uint32_t code = quant_code(x[k], mn, sc, kLevels);
+          const uint32_t code = quant_code(x[k], mn, sc, inv, kLevels);
           packed |= code << (BITS * k);
           const float dec = bf16_round(dequant_f32(code, sc16, mn16));
           recon[k] = s > 0 ? bf16_round(recon[k] + dec) : dec;

@@ -186,9 +186,22 @@ __device__ __forceinline__ float quant_scale(float minimum, float maximum, float
   const float span = __fsub_rn(maximum, minimum);
   return span > 0.f ? __fdiv_rn(span, levels) : 1.f;
 }
-__device__ __forceinline__ uint32_t quant_code(float x, float minimum, float scale, float levels) {
-  const float q = __fdiv_rn(__fsub_rn(x, minimum), scale);
-  const float r = fminf(fmaxf(rintf(q), 0.f), levels);
+// The reciprocal the quantiser multiplies by on its fast path; 0 where the reciprocal would
+// lose bits (scale far outside the range K/V values live in), which sends every element through
+// the division.
+__device__ __forceinline__ float quant_inverse(float scale) {
+  return (scale > 1e-30f && scale < 1e30f) ? __frcp_rn(scale) : 0.f;
+}
+// The reference divides: q = (x - min) / scale, IEEE, then rounds half to even.  (x - min) * (1 /
+// scale) is within 3e-6 of that quotient for codes up to 15, so unless it sits within 1e-4 of a
+// rounding boundary both give the same code; at a boundary the division decides.  Same bits as
+// the reference at a fraction of the arithmetic.
+__device__ __forceinline__ uint32_t quant_code(float x, float minimum, float scale, float inverse, float levels) {
+  const float d = __fsub_rn(x, minimum);
+  const float q = __fmul_rn(d, inverse);
+  float r = rintf(q);
+  if (!(fabsf(fabsf(q - r) - 0.5f) > 1e-4f) || inverse == 0.f) r = rintf(__fdiv_rn(d, scale));
+  r = fminf(fmaxf(r, 0.f), levels);
   return static_cast<uint32_t>(r);
 }
 // code * scale + minimum in float32 (two roundings, as torch computes it), then bf16 RNE.

@@ -69,11 +69,12 @@ __device__ __forceinline__ void encode_v_row(const float (&x)[4], uint8_t* recor
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   }
   const float sc = quant_scale(mn, mx, kLevels);
+  const float inv = quant_inverse(sc);
   const __half mn16 = __float2half_rn(mn), sc16 = __float2half_rn(sc);
   uint32_t packed = 0;
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
-    const uint32_t code = quant_code(x[k], mn, sc, kLevels);
+    const uint32_t code = quant_code(x[k], mn, sc, inv, kLevels);
     packed |= code << (BITS * k);
     dec[k] = bf16_round(dequant_f32(code, sc16, mn16));
   }
@@ -98,6 +99,27 @@ __device__ __forceinline__ void store4(__nv_bfloat16* dst, const float (&x)[4]) 
   *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
 }
 
+// Rows of 128 bfloat16 between global and shared memory, 16 bytes per thread and step.
+// `row_of(i)` gives the global row index of tile row i.
+template <typename RowOf>
+__device__ __forceinline__ void load_rows(__nv_bfloat16 (*tile)[kHeadDim], const __nv_bfloat16* base, int rows,
+                                          RowOf row_of) {
+  for (int idx = threadIdx.x; idx < rows * 16; idx += 128) {
+    const int i = idx >> 4, piece = idx & 15;
+    *reinterpret_cast<uint4*>(&tile[i][piece * 8]) =
+        ldg128(base + static_cast<int64_t>(row_of(i)) * kHeadDim + piece * 8);
+  }
+}
+template <typename RowOf>
+__device__ __forceinline__ void store_rows(const __nv_bfloat16 (*tile)[kHeadDim], __nv_bfloat16* base, int rows,
+                                           RowOf row_of) {
+  for (int idx = threadIdx.x; idx < rows * 16; idx += 128) {
+    const int i = idx >> 4, piece = idx & 15;
+    *reinterpret_cast<uint4*>(base + static_cast<int64_t>(row_of(i)) * kHeadDim + piece * 8) =
+        *reinterpret_cast<const uint4*>(&tile[i][piece * 8]);
+  }
+}
+
 // ------------------------------------------------------------------------------ streams 0 and 1
 template <int BITS>
 __global__ void __launch_bounds__(128) encode_dense_kernel(const EncodeParams p) {
@@ -113,32 +135,36 @@ __global__ void __launch_bounds__(128) encode_dense_kernel(const EncodeParams p)
   if (t0 >= quant) return;  // the tail stays bfloat16
   const int64_t in_row0 = (static_cast<int64_t>(head_in) * p.tokens + t0) * kHeadDim;
   const int tid = threadIdx.x;
+  auto consecutive = [](int i) { return i; };
 
   if (blockIdx.y == 0) {
     // ---------------- K: per channel over the block's 64 tokens; thread c owns channel c
-    __shared__ __nv_bfloat16 s_recon[kGroup][kHeadDim];
+    __shared__ __align__(16) __nv_bfloat16 s_in[kGroup][kHeadDim];
+    __shared__ __align__(16) __nv_bfloat16 s_recon[kGroup][kHeadDim];
     __shared__ uint8_t s_tile[kGroup][kHeadDim + 4];
     const int c = tid;
 #pragma unroll 1
     for (int s = 0; s < 2; ++s) {
-      const __nv_bfloat16* src = p.keys[s] + in_row0 + c;
+      load_rows(s_in, p.keys[s] + in_row0, kGroup, consecutive);
+      __syncthreads();
       float mn = INFINITY, mx = -INFINITY;
       for (int i = 0; i < kGroup; ++i) {
-        float x = __bfloat162float(src[i * kHeadDim]);
+        float x = __bfloat162float(s_in[i][c]);
         if (s > 0) x = bf16_round(x - __bfloat162float(s_recon[i][c]));
         mn = fminf(mn, x);
         mx = fmaxf(mx, x);
       }
       const float sc = quant_scale(mn, mx, kLevels);
+      const float inv = quant_inverse(sc);
       const __half mn16 = __float2half_rn(mn), sc16 = __float2half_rn(sc);
       const int64_t group = p.L.group_base[s][bh] + blk;
       p.k_min[s][group * kHeadDim + c] = mn16;
       p.k_scale[s][group * kHeadDim + c] = sc16;
       for (int i = 0; i < kGroup; ++i) {
-        float x = __bfloat162float(src[i * kHeadDim]);
+        float x = __bfloat162float(s_in[i][c]);
         const float base = s > 0 ? __bfloat162float(s_recon[i][c]) : 0.f;
         if (s > 0) x = bf16_round(x - base);
-        const uint32_t code = quant_code(x, mn, sc, kLevels);
+        const uint32_t code = quant_code(x, mn, sc, inv, kLevels);
         s_tile[i][c] = static_cast<uint8_t>(code);
         const float dec = bf16_round(dequant_f32(code, sc16, mn16));
         s_recon[i][c] = __float2bfloat16_rn(s > 0 ? base + dec : dec);
@@ -147,23 +173,31 @@ __global__ void __launch_bounds__(128) encode_dense_kernel(const EncodeParams p)
       store_code_rows<BITS>(s_tile, kGroup, p.k_codes[s] + (p.L.row_base[s][bh] + t0) * kRowBytes);
       __syncthreads();
     }
-    __nv_bfloat16* recon = p.recon_k + in_row0 + c;
-    for (int i = 0; i < kGroup; ++i) recon[i * kHeadDim] = s_recon[i][c];
+    store_rows(s_recon, p.recon_k + in_row0, kGroup, consecutive);
   } else {
-    // ---------------- V: per token over 64-channel groups; a warp per token, 4 channels per lane
+    // ---------------- V: per token over 64-channel groups; a warp per token, 4 channels per lane,
+    // four tokens at a time so that their loads are in flight together
     const int lane = tid & 31, warp = tid >> 5;
-    for (int i = warp; i < kGroup; i += 4) {
-      const int64_t in = in_row0 + static_cast<int64_t>(i) * kHeadDim + 4 * lane;
-      float x[4], recon[4], dec[4];
-      load4(p.values[0] + in, x);
-      encode_v_row<BITS>(x, p.v_rows[0] + (p.L.row_base[0][bh] + t0 + i) * (kRowBytes + 16), lane, recon);
-      load4(p.values[1] + in, x);
+    for (int i0 = warp * 4; i0 < kGroup; i0 += 16) {
+      float x0[4][4], x1[4][4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) x[k] = bf16_round(x[k] - recon[k]);
-      encode_v_row<BITS>(x, p.v_rows[1] + (p.L.row_base[1][bh] + t0 + i) * (kRowBytes + 16), lane, dec);
+      for (int j = 0; j < 4; ++j) {
+        const int64_t in = in_row0 + static_cast<int64_t>(i0 + j) * kHeadDim + 4 * lane;
+        load4(p.values[0] + in, x0[j]);
+        load4(p.values[1] + in, x1[j]);
+      }
 #pragma unroll
-      for (int k = 0; k < 4; ++k) recon[k] = bf16_round(recon[k] + dec[k]);
-      store4(p.recon_v + in, recon);
+      for (int j = 0; j < 4; ++j) {
+        const int i = i0 + j;
+        float recon[4], dec[4];
+        encode_v_row<BITS>(x0[j], p.v_rows[0] + (p.L.row_base[0][bh] + t0 + i) * (kRowBytes + 16), lane, recon);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) x1[j][k] = bf16_round(x1[j][k] - recon[k]);
+        encode_v_row<BITS>(x1[j], p.v_rows[1] + (p.L.row_base[1][bh] + t0 + i) * (kRowBytes + 16), lane, dec);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) recon[k] = bf16_round(recon[k] + dec[k]);
+        store4(p.recon_v + in_row0 + static_cast<int64_t>(i) * kHeadDim + 4 * lane, recon);
+      }
     }
   }
 }
@@ -202,48 +236,62 @@ __global__ void __launch_bounds__(128) encode_compact_kernel(const EncodeParams 
   const int rows = s_rows;
   if (rows == 0) return;
   const int64_t in_head = static_cast<int64_t>(head_in) * p.tokens * kHeadDim;
+  auto retained = [&](int i) { return s_pos[i]; };
 
   if (blockIdx.y == 0) {
+    __shared__ __align__(16) __nv_bfloat16 s_in[kGroup][kHeadDim];
+    __shared__ __align__(16) __nv_bfloat16 s_recon[kGroup][kHeadDim];
     __shared__ uint8_t s_tile[kGroup][kHeadDim + 4];
     const int c = tid;
-    const __nv_bfloat16* src = p.keys[s] + in_head + c;
-    __nv_bfloat16* recon = p.recon_k + in_head + c;
+    load_rows(s_in, p.keys[s] + in_head, rows, retained);
+    load_rows(s_recon, p.recon_k + in_head, rows, retained);
+    __syncthreads();
     float mn = INFINITY, mx = -INFINITY;
     for (int i = 0; i < rows; ++i) {
-      const int64_t at = static_cast<int64_t>(s_pos[i]) * kHeadDim;
-      const float x = bf16_round(__bfloat162float(src[at]) - __bfloat162float(recon[at]));
+      const float x = bf16_round(__bfloat162float(s_in[i][c]) - __bfloat162float(s_recon[i][c]));
       mn = fminf(mn, x);
       mx = fmaxf(mx, x);
     }
     const float sc = quant_scale(mn, mx, kLevels);
+    const float inv = quant_inverse(sc);
     const __half mn16 = __float2half_rn(mn), sc16 = __float2half_rn(sc);
     const int64_t group = p.L.group_base[s][bh] + grp;
     p.k_min[s][group * kHeadDim + c] = mn16;
     p.k_scale[s][group * kHeadDim + c] = sc16;
     for (int i = 0; i < rows; ++i) {
-      const int64_t at = static_cast<int64_t>(s_pos[i]) * kHeadDim;
-      const float base = __bfloat162float(recon[at]);
-      const float x = bf16_round(__bfloat162float(src[at]) - base);
-      const uint32_t code = quant_code(x, mn, sc, kLevels);
+      const float base = __bfloat162float(s_recon[i][c]);
+      const float x = bf16_round(__bfloat162float(s_in[i][c]) - base);
+      const uint32_t code = quant_code(x, mn, sc, inv, kLevels);
       s_tile[i][c] = static_cast<uint8_t>(code);
-      if (s == 2) recon[at] = __float2bfloat16_rn(base + bf16_round(dequant_f32(code, sc16, mn16)));
+      if (s == 2) s_recon[i][c] = __float2bfloat16_rn(base + bf16_round(dequant_f32(code, sc16, mn16)));
     }
     __syncthreads();
     store_code_rows<BITS>(s_tile, rows, p.k_codes[s] + (p.L.row_base[s][bh] + j0) * kRowBytes);
+    if (s == 2) store_rows(s_recon, p.recon_k + in_head, rows, retained);
   } else {
     const int lane = tid & 31, warp = tid >> 5;
-    for (int i = warp; i < rows; i += 4) {
-      const int64_t in = in_head + static_cast<int64_t>(s_pos[i]) * kHeadDim + 4 * lane;
-      float x[4], recon[4], dec[4];
-      load4(p.values[s] + in, x);
-      load4(p.recon_v + in, recon);
+    for (int i0 = warp * 4; i0 < rows; i0 += 16) {
+      float x[4][4], recon[4][4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) x[k] = bf16_round(x[k] - recon[k]);
-      encode_v_row<BITS>(x, p.v_rows[s] + (p.L.row_base[s][bh] + j0 + i) * (kRowBytes + 16), lane, dec);
-      if (s == 2) {
+      for (int j = 0; j < 4; ++j) {
+        const int i = min(i0 + j, rows - 1);
+        const int64_t in = in_head + static_cast<int64_t>(s_pos[i]) * kHeadDim + 4 * lane;
+        load4(p.values[s] + in, x[j]);
+        load4(p.recon_v + in, recon[j]);
+      }
 #pragma unroll
-        for (int k = 0; k < 4; ++k) recon[k] = bf16_round(recon[k] + dec[k]);
-        store4(p.recon_v + in, recon);
+      for (int j = 0; j < 4; ++j) {
+        const int i = i0 + j;
+        if (i >= rows) break;
+        float dec[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) x[j][k] = bf16_round(x[j][k] - recon[j][k]);
+        encode_v_row<BITS>(x[j], p.v_rows[s] + (p.L.row_base[s][bh] + j0 + i) * (kRowBytes + 16), lane, dec);
+        if (s == 2) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) recon[j][k] = bf16_round(recon[j][k] + dec[k]);
+          store4(p.recon_v + in_head + static_cast<int64_t>(s_pos[i]) * kHeadDim + 4 * lane, recon[j]);
+        }
       }
     }
   }
@@ -271,8 +319,7 @@ extern "C" int fl_encode_prefill(const fl_layer* layer, int32_t sequence_begin, 
   p.L = make_view(*layer);
   for (int s = 0; s < 4; ++s) {
     FL_REQUIRE(keys[s] && values[s], "%s: loop %d K/V pointer is null", who, s);
-    FL_REQUIRE((reinterpret_cast<uintptr_t>(keys[s]) & 7u) == 0 && (reinterpret_cast<uintptr_t>(values[s]) & 7u) == 0,
-               "%s: K/V must be 8-byte aligned", who);
+    FL_REQUIRE(aligned16(keys[s]) && aligned16(values[s]), "%s: K/V must be 16-byte aligned", who);
     p.k_codes[s] = static_cast<uint8_t*>(layer->k_codes[s]);
     p.k_min[s] = static_cast<__half*>(layer->k_min[s]);
     p.k_scale[s] = static_cast<__half*>(layer->k_scale[s]);
@@ -280,6 +327,7 @@ extern "C" int fl_encode_prefill(const fl_layer* layer, int32_t sequence_begin, 
     p.keys[s] = static_cast<const __nv_bfloat16*>(keys[s]);
     p.values[s] = static_cast<const __nv_bfloat16*>(values[s]);
   }
+  FL_REQUIRE(aligned16(recon_k) && aligned16(recon_v), "%s: scratch must be 16-byte aligned", who);
   p.recon_k = static_cast<__nv_bfloat16*>(recon_k);
   p.recon_v = static_cast<__nv_bfloat16*>(recon_v);
   p.positions[0] = positions3;

@@ -23,7 +23,24 @@ pack_k_kernel(const T* __restrict__ values, int64_t tokens, void* __restrict__ o
   const int64_t t0 = g * kGroup;
   const int cnt = (tokens - t0) < kGroup ? static_cast<int>(tokens - t0) : kGroup;
   const int64_t groups = (tokens + kGroup - 1) / kGroup;
-  const T* src = values + (bh * tokens + t0) * kHeadDim + c;
+  // The group's rows are staged in shared memory with 16-byte loads (one read of the input),
+  // then every thread walks its own channel.
+  __shared__ __align__(16) T tile_in[kGroup][kHeadDim];
+  {
+    const T* block = values + (bh * tokens + t0) * kHeadDim;
+    constexpr int kPer16 = 16 / sizeof(T);               // elements per 16-byte piece
+    constexpr int kRowPieces = kHeadDim / kPer16;
+    if ((reinterpret_cast<uintptr_t>(block) & 15u) == 0) {
+      for (int idx = c; idx < cnt * kRowPieces; idx += 128) {
+        const uint4 v = ldg128(block + static_cast<int64_t>(idx) * kPer16);
+        *reinterpret_cast<uint4*>(&tile_in[0][0] + static_cast<int64_t>(idx) * kPer16) = v;
+      }
+    } else {
+      for (int i = 0; i < cnt; ++i) tile_in[i][c] = block[static_cast<int64_t>(i) * kHeadDim + c];
+    }
+  }
+  __syncthreads();
+  const T* src = &tile_in[0][c];
 
   float mn = INFINITY, mx = -INFINITY;
   for (int i = 0; i < cnt; ++i) {
@@ -32,6 +49,7 @@ pack_k_kernel(const T* __restrict__ values, int64_t tokens, void* __restrict__ o
     mx = fmaxf(mx, x);
   }
   const float sc = quant_scale(mn, mx, kLevels);
+  const float inv = quant_inverse(sc);
   minimum[(bh * groups + g) * kHeadDim + c] = __float2half_rn(mn);
   scale[(bh * groups + g) * kHeadDim + c] = __float2half_rn(sc);
 
@@ -46,7 +64,7 @@ pack_k_kernel(const T* __restrict__ values, int64_t tokens, void* __restrict__ o
         const int i = w * 8 + j;
         if (i < cnt) {
           const float x = load_as_float(src + static_cast<int64_t>(i) * kHeadDim);
-          word |= quant_code(x, mn, sc, kLevels) << (4 * j);
+          word |= quant_code(x, mn, sc, inv, kLevels) << (4 * j);
         }
       }
       payload[(bh * word_rows + t0 / 8 + w) * kHeadDim + c] = static_cast<int32_t>(word);
@@ -55,7 +73,7 @@ pack_k_kernel(const T* __restrict__ values, int64_t tokens, void* __restrict__ o
     __shared__ uint8_t tile[kGroup][kHeadDim + 4];
     for (int i = 0; i < cnt; ++i) {
       const float x = load_as_float(src + static_cast<int64_t>(i) * kHeadDim);
-      tile[i][c] = static_cast<uint8_t>(quant_code(x, mn, sc, kLevels));
+      tile[i][c] = static_cast<uint8_t>(quant_code(x, mn, sc, inv, kLevels));
     }
     __syncthreads();
     constexpr int kRowWords = kRowBytes / 4;
@@ -74,8 +92,23 @@ pack_k_kernel(const T* __restrict__ values, int64_t tokens, void* __restrict__ o
 }
 
 // ------------------------------------------------------------------------------- V: per token
-// One warp per token; lane l owns channels 4l .. 4l+3; the two 64-channel groups are the two
-// 16-lane halves of the warp.
+// A warp per token, four tokens per warp with their loads issued together; lane l owns channels
+// 4l .. 4l+3; the two 64-channel groups are the two 16-lane halves of the warp.
+constexpr int kVTokensPerWarp = 4;
+
+template <typename T>
+__device__ __forceinline__ void load_four(const T* src, float (&x)[4]) {
+  if constexpr (sizeof(T) == 2) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);  // 8-byte aligned: 4 channels of 2 bytes
+    const T* h = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) x[k] = load_as_float(h + k);
+  } else {
+    const float4 raw = *reinterpret_cast<const float4*>(src);
+    x[0] = raw.x; x[1] = raw.y; x[2] = raw.z; x[3] = raw.w;
+  }
+}
+
 template <typename T, int BITS, bool KIVI>
 __global__ void __launch_bounds__(128)
 pack_v_kernel(const T* __restrict__ values, int64_t tokens, int64_t total_tokens,
@@ -84,47 +117,63 @@ pack_v_kernel(const T* __restrict__ values, int64_t tokens, int64_t total_tokens
   constexpr float kLevels = float((1 << BITS) - 1);
   constexpr int kRowBytes = 16 * BITS;
   const int lane = threadIdx.x & 31;
-  const int64_t wg = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
-  if (wg >= total_tokens) return;
-  const int64_t bh = wg / tokens;
-  const int64_t t = wg % tokens;
-  const T* src = values + wg * kHeadDim + 4 * lane;
-  float x[4];
+  const int64_t first = (static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5)) * kVTokensPerWarp;
+  if (first >= total_tokens) return;
+  const bool vector_ok = (reinterpret_cast<uintptr_t>(values) & 15u) == 0;
+  float xs[kVTokensPerWarp][4];
 #pragma unroll
-  for (int k = 0; k < 4; ++k) x[k] = load_as_float(src + k);
-  float mn = fminf(fminf(x[0], x[1]), fminf(x[2], x[3]));
-  float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
-#pragma unroll
-  for (int o = 8; o > 0; o >>= 1) {
-    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  }
-  const float sc = quant_scale(mn, mx, kLevels);
-  uint32_t packed = 0;
-#pragma unroll
-  for (int k = 0; k < 4; ++k) packed |= quant_code(x[k], mn, sc, kLevels) << (BITS * k);
-  const int g = lane >> 4;
-  if constexpr (KIVI) {
-    static_assert(BITS == 4, "the KIVI word layout is 4-bit");
-    const uint32_t other = __shfl_down_sync(0xffffffffu, packed, 1);
-    if ((lane & 1) == 0) {
-      static_cast<int32_t*>(out_codes)[(bh * 16 + (lane >> 1)) * tokens + t] =
-          static_cast<int32_t>(packed | (other << 16));
-    }
-    if ((lane & 15) == 0) {
-      minimum[(bh * 2 + g) * tokens + t] = __float2half_rn(mn);
-      scale[(bh * 2 + g) * tokens + t] = __float2half_rn(sc);
-    }
-  } else {
-    uint8_t* row = static_cast<uint8_t*>(out_codes) + wg * kRowBytes;
-    if constexpr (BITS == 4) {
-      reinterpret_cast<uint16_t*>(row)[lane] = static_cast<uint16_t>(packed);
+  for (int j = 0; j < kVTokensPerWarp; ++j) {
+    const int64_t wg = first + j < total_tokens ? first + j : total_tokens - 1;
+    const T* src = values + wg * kHeadDim + 4 * lane;
+    if (vector_ok) {
+      load_four(src, xs[j]);
     } else {
-      row[lane] = static_cast<uint8_t>(packed);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) xs[j][k] = load_as_float(src + k);
     }
-    if ((lane & 15) == 0) {
-      minimum[wg * meta_stride + g] = __float2half_rn(mn);
-      scale[wg * meta_stride + g] = __float2half_rn(sc);
+  }
+#pragma unroll
+  for (int j = 0; j < kVTokensPerWarp; ++j) {
+    const int64_t wg = first + j;
+    if (wg >= total_tokens) break;
+    const int64_t bh = wg / tokens;
+    const int64_t t = wg % tokens;
+    const float (&x)[4] = xs[j];
+    float mn = fminf(fminf(x[0], x[1]), fminf(x[2], x[3]));
+    float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) {
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    const float sc = quant_scale(mn, mx, kLevels);
+    const float inv = quant_inverse(sc);
+    uint32_t packed = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) packed |= quant_code(x[k], mn, sc, inv, kLevels) << (BITS * k);
+    const int g = lane >> 4;
+    if constexpr (KIVI) {
+      static_assert(BITS == 4, "the KIVI word layout is 4-bit");
+      const uint32_t other = __shfl_down_sync(0xffffffffu, packed, 1);
+      if ((lane & 1) == 0) {
+        static_cast<int32_t*>(out_codes)[(bh * 16 + (lane >> 1)) * tokens + t] =
+            static_cast<int32_t>(packed | (other << 16));
+      }
+      if ((lane & 15) == 0) {
+        minimum[(bh * 2 + g) * tokens + t] = __float2half_rn(mn);
+        scale[(bh * 2 + g) * tokens + t] = __float2half_rn(sc);
+      }
+    } else {
+      uint8_t* row = static_cast<uint8_t*>(out_codes) + wg * kRowBytes;
+      if constexpr (BITS == 4) {
+        reinterpret_cast<uint16_t*>(row)[lane] = static_cast<uint16_t>(packed);
+      } else {
+        row[lane] = static_cast<uint8_t>(packed);
+      }
+      if ((lane & 15) == 0) {
+        minimum[wg * meta_stride + g] = __float2half_rn(mn);
+        scale[wg * meta_stride + g] = __float2half_rn(sc);
+      }
     }
   }
 }
@@ -227,7 +276,8 @@ template <int BITS, bool KIVI>
 int launch_pack_v(const void* values, int32_t dtype, int64_t bh, int64_t tokens, void* codes,
                   void* minimum, void* scale, int64_t meta_stride, cudaStream_t stream) {
   const int64_t total = bh * tokens;
-  const unsigned grid = static_cast<unsigned>((total + 3) / 4);
+  const int64_t per_cta = 4 * kVTokensPerWarp;
+  const unsigned grid = static_cast<unsigned>((total + per_cta - 1) / per_cta);
   __half* mn = static_cast<__half*>(minimum);
   __half* sc = static_cast<__half*>(scale);
   switch (dtype) {
