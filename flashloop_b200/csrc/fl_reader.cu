@@ -44,9 +44,6 @@ struct ReaderParams {
   float* partial;
   int* tickets;
   int* status;
-  int* queue;  // [0]: next work item, [1]: CTAs that have left
-  int grid_chunks;
-  int chunk_tokens;
   int max_chunks;
   // selected readers
   const int32_t* indices;
@@ -415,53 +412,110 @@ __device__ __forceinline__ Span block_span(const LayerView& L, int s, int b, int
   return sp;
 }
 
-// A work item: one chunk of one (b,h) head (chunk < nchunks - 1) or its BF16 tail plus the
-// current token (chunk == nchunks - 1).
+// Work is counted in units: a head has one unit per 64-token block of its packed prefix plus
+// kTailUnits for its BF16 tail and the current token (about what the tail costs a CTA).  The units
+// of all heads form one sequence, head after head, and CTA c owns the contiguous range
+// [c*U/G, (c+1)*U/G) of it, so every CTA gets the same amount of work whatever the context
+// lengths are.  A work item is the part of one head inside that range: some blocks, the tail, or
+// both.  A CTA therefore meets a head once, keeps its online-softmax state in registers across all
+// of the head's blocks it owns, and merges and publishes once per item: one to three times in all.
+constexpr int kTailUnits = 8;
+
 struct ItemDesc {
-  int id;  // -1: the queue is empty
-  int bh, b, chunk, nchunks, quant, tail_len, tail_start, blk_begin, blk_end;
-  int64_t row_base[4];    // first row / first K metadata group of this (b,h) in every stream
+  int id;  // -1: past the end of this CTA's range
+  int bh, b, quant, tail_len, tail_start;
+  int blk_begin, blk_end;  // blocks of the head in this item (may be empty)
+  int has_tail;            // the item includes the head's tail and current token
+  int part, nparts;        // position of this CTA among the CTAs that share the head, and their number
+  int first_cta;           // the first of those CTAs
+  int rot;                 // block i of the item goes to warp (i + rot) % 8: the round robin over the
+                           // warps runs on across the CTA's items
+  int64_t row_base[4];     // first row / first K metadata group of this (b,h) in every stream
   int64_t group_base[4];
 };
 
-// Take the next valid item from the global queue (one thread per CTA calls this).
-__device__ __forceinline__ void draw_item(const ReaderParams& p, ItemDesc* d) {
+__device__ __forceinline__ int units_per_head(const LayerView& L, int b) {
+  return L.seq_state[b * FL_STATE_WORDS + FL_STATE_QUANT_TOKENS] / kGroup + kTailUnits;
+}
+__device__ __forceinline__ int64_t total_units(const LayerView& L) {
+  int64_t total = 0;
+  for (int b = 0; b < L.batch; ++b) total += static_cast<int64_t>(L.heads) * units_per_head(L, b);
+  return total;
+}
+
+// Walks the items of one CTA in order.  Held by the one thread that describes them.
+struct ItemCursor {
+  int64_t at, end;     // next unit, end of the CTA's range
+  int64_t head_first;  // first unit of the head that contains `at`
+  int b, h, each;      // that head, and the units per head of its sequence
+  int count;           // items described so far
+  int blocks_done;     // blocks in those items
+};
+
+__device__ __forceinline__ void cursor_start(const LayerView& L, int64_t lo, int64_t hi, ItemCursor* c) {
+  c->at = lo;
+  c->end = hi;
+  c->count = 0;
+  c->blocks_done = 0;
+  c->b = 0;
+  c->each = units_per_head(L, 0);
+  int64_t first = 0;
+  while (c->b + 1 < L.batch && lo >= first + static_cast<int64_t>(L.heads) * c->each) {
+    first += static_cast<int64_t>(L.heads) * c->each;
+    ++c->b;
+    c->each = units_per_head(L, c->b);
+  }
+  c->h = static_cast<int>((lo - first) / c->each);
+  if (c->h >= L.heads) c->h = L.heads - 1;  // only when the range is empty
+  c->head_first = first + static_cast<int64_t>(c->h) * c->each;
+}
+
+__device__ __forceinline__ void describe_next(const ReaderParams& p, int64_t all_units, ItemCursor* c, ItemDesc* d) {
   const LayerView& L = p.L;
-  const int batch_heads = L.batch * L.heads;
-  const int total = batch_heads * p.grid_chunks;
-  for (;;) {
-    const int id = atomicAdd(p.queue, 1);
-    if (id >= total) {
-      d->id = -1;
-      return;
-    }
-    const int chunk = id / batch_heads;  // chunk-major: the long heads' extra chunks come last
-    const int bh = id - chunk * batch_heads;
-    const int b = bh / L.heads;
-    const int32_t* st = L.seq_state + b * FL_STATE_WORDS;
-    const int quant = st[FL_STATE_QUANT_TOKENS];
-    const int nq_chunks = (quant + p.chunk_tokens - 1) / p.chunk_tokens;
-    if (chunk > nq_chunks) continue;
-    d->bh = bh;
-    d->b = b;
-    d->chunk = chunk;
-    d->nchunks = nq_chunks + 1;
-    d->quant = quant;
-    d->tail_len = st[FL_STATE_TAIL_LEN];
-    d->tail_start = st[FL_STATE_TAIL_START];
-    d->blk_begin = chunk * (p.chunk_tokens / kGroup);
-    d->blk_end = chunk == nq_chunks ? d->blk_begin
-                                    : min(d->blk_begin + p.chunk_tokens / kGroup, quant / kGroup);
-    for (int s = 0; s <= p.loop; ++s) {
-      d->row_base[s] = L.row_base[s][bh];
-      d->group_base[s] = L.group_base[s][bh];
-    }
-    d->id = id;
+  if (c->at >= c->end) {
+    d->id = -1;
     return;
+  }
+  const int64_t head_end = c->head_first + c->each;
+  const int64_t seg_end = head_end < c->end ? head_end : c->end;
+  const int blocks = c->each - kTailUnits;
+  const int u0 = static_cast<int>(c->at - c->head_first), u1 = static_cast<int>(seg_end - c->head_first);
+  const int bh = c->b * L.heads + c->h;
+  const int32_t* st = L.seq_state + c->b * FL_STATE_WORDS;
+  d->bh = bh;
+  d->b = c->b;
+  d->quant = st[FL_STATE_QUANT_TOKENS];
+  d->tail_len = st[FL_STATE_TAIL_LEN];
+  d->tail_start = st[FL_STATE_TAIL_START];
+  d->blk_begin = u0 < blocks ? u0 : blocks;
+  d->blk_end = u1 < blocks ? u1 : blocks;
+  d->has_tail = u0 <= blocks && blocks < u1;
+  // CTA that owns unit u: the largest c with c*U/G <= u
+  const int64_t grid = gridDim.x;
+  const int64_t first_owner = ((c->head_first + 1) * grid - 1) / all_units;
+  const int64_t last_owner = (head_end * grid - 1) / all_units;
+  d->part = static_cast<int>(static_cast<int64_t>(blockIdx.x) - first_owner);
+  d->nparts = static_cast<int>(last_owner - first_owner + 1);
+  d->first_cta = static_cast<int>(first_owner);
+  d->rot = c->blocks_done % kDenseWarps;
+  c->blocks_done += d->blk_end - d->blk_begin;
+  for (int s = 0; s <= p.loop; ++s) {
+    d->row_base[s] = L.row_base[s][bh];
+    d->group_base[s] = L.group_base[s][bh];
+  }
+  d->id = c->count++;
+  c->at = seg_end;
+  if (seg_end == head_end) {  // on to the next head
+    c->head_first = head_end;
+    if (++c->h == L.heads) {
+      c->h = 0;
+      if (c->b + 1 < L.batch) c->each = units_per_head(L, ++c->b);
+    }
   }
 }
 
-// Blocks of an item that belong to `warp` (blocks warp, warp + 8, ... of the chunk).
+// Blocks of an item that belong to the warp in position `warp` of the item's round robin
+// (blocks warp, warp + 8, ... of the item).
 __device__ __forceinline__ int blocks_of_warp(int blk_begin, int blk_end, int warp) {
   const int n = blk_end - blk_begin - warp;
   return n > 0 ? (n + kDenseWarps - 1) / kDenseWarps : 0;
@@ -497,9 +551,13 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (tid == 0) {
-    draw_item(p, &s_item[0]);
-    draw_item(p, &s_item[1]);
+  // this CTA's contiguous range of units; the thread that describes the items walks it
+  const int64_t all_units = total_units(L);
+  ItemCursor cursor;
+  cursor_start(L, all_units * blockIdx.x / gridDim.x, all_units * (blockIdx.x + 1) / gridDim.x, &cursor);
+  if (tid == kHeadDim) {
+    describe_next(p, all_units, &cursor, &s_item[0]);
+    describe_next(p, all_units, &cursor, &s_item[1]);
   }
   __syncthreads();
   if (s_item[0].id >= 0 && tid < kHeadDim) {
@@ -514,17 +572,20 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   int iss_item = 0, iss_blk = 0, iss_j = 0;
   bool timed_out = false;
 
+  OnlineState S;
+  state_init(S);
+
   for (int k = 0;; ++k) {
     const ItemDesc* curp = &s_item[k % 3];
     if (curp->id < 0) break;
     struct {
-      int bh, b, chunk, nchunks, quant, tail_len, tail_start, blk_begin, blk_end;
-    } cur = {curp->bh, curp->b, curp->chunk, curp->nchunks, curp->quant, curp->tail_len,
-             curp->tail_start, curp->blk_begin, curp->blk_end};
-    // Look ahead: one thread of the upper half of the CTA (the warps that sit out the merge) draws
-    // item k+2, the upper half fetches the query of item k+1.  Both become visible to the other
-    // warps at this item's merge barrier.
-    if (tid == kHeadDim) draw_item(p, &s_item[(k + 2) % 3]);
+      int bh, b, quant, tail_len, tail_start, blk_begin, blk_end, has_tail, part, nparts, first_cta, rot;
+    } cur = {curp->bh, curp->b, curp->quant, curp->tail_len, curp->tail_start, curp->blk_begin,
+             curp->blk_end, curp->has_tail, curp->part, curp->nparts, curp->first_cta, curp->rot};
+    // Look ahead: one thread of the upper half of the CTA (the warps that sit out the merge)
+    // describes item k+2, the upper half fetches the query of item k+1.  Both become visible to the
+    // other warps at this item's closing barrier.
+    if (tid == kHeadDim) describe_next(p, all_units, &cursor, &s_item[(k + 2) % 3]);
     if (tid >= kHeadDim) {
       const int next_id = s_item[(k + 1) % 3].id;
       if (next_id >= 0) {
@@ -537,16 +598,14 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
     const float* qf = s_qf[k & 1];
     float* logits_row = p.logits ? p.logits + bh * p.logits_stride : nullptr;
 
-    OnlineState S;
-    state_init(S);
-
-    if (cur.chunk < cur.nchunks - 1) {
-      const int my_blocks = blocks_of_warp(cur.blk_begin, cur.blk_end, warp);
+    if (cur.blk_end > cur.blk_begin) {
+      const int my_first = cur.blk_begin + ((warp - cur.rot) & (kDenseWarps - 1));
+      const int my_blocks = blocks_of_warp(cur.blk_begin, cur.blk_end, my_first - cur.blk_begin);
       float lg[8];
       __half2 hacc[16];
       __half2 hbias = __floats2half2_rn(0.f, 0.f);  // sum of p * (v_min + centre * v_scale) of one block
       for (int cb = 0; cb < my_blocks; ++cb) {
-        const int blk = cur.blk_begin + warp + cb * kDenseWarps;
+        const int blk = my_first + cb * kDenseWarps;
         const int t0 = blk * kGroup;
         for (int j = 0; j < units_per_block; ++j) {
           // ---- keep the ring full: issue units of this item, then of the next one
@@ -554,15 +613,15 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
             if (iss_item > k + 1) break;
             const ItemDesc* it = &s_item[iss_item % 3];
             if (it->id < 0) break;
-            const int it_blocks =
-                it->chunk < it->nchunks - 1 ? blocks_of_warp(it->blk_begin, it->blk_end, warp) : 0;
+            const int it_pos = (warp - it->rot) & (kDenseWarps - 1);
+            const int it_blocks = blocks_of_warp(it->blk_begin, it->blk_end, it_pos);
             if (iss_blk >= it_blocks) {
               ++iss_item;
               iss_blk = 0;
               iss_j = 0;
               continue;
             }
-            const int iblk = it->blk_begin + warp + iss_blk * kDenseWarps;
+            const int iblk = it->blk_begin + it_pos + iss_blk * kDenseWarps;
             const bool iv = iss_j >= streams;
             const int is = iv ? iss_j - streams : iss_j;
             const Span sp = block_span(L, is, it->b, iblk * kGroup, lane);
@@ -761,7 +820,7 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
       iss_blk = 0;
       iss_j = 0;
     }
-    if (cur.chunk == cur.nchunks - 1 && warp < 4) {
+    if (cur.has_tail && warp < 4) {
       // ---- the BF16 tail and the current token: entries 0..tail_len (the last is the current)
       const int entries = cur.tail_len + 1;
       const __nv_bfloat16* tk = L.tail_k[p.loop] + bh * L.tail_capacity * kHeadDim;
@@ -784,9 +843,11 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
       }
     }
 
-    // ---- merge the eight warps' states, publish the item's partial, finish the head if last
+    // ---- merge the eight warps' states, publish this CTA's partial of the head, finish the head
+    // if every CTA that shares it has published
     const int buf = k & 1;
     state_store<BITS>(S, lane, s_merge[buf][warp]);
+    state_init(S);
     __syncthreads();
     if (warp < 4) {
       const int c = tid;
@@ -801,10 +862,12 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
         a += s_merge[buf][w][c] * r;
         l += s_merge[buf][w][129] * r;
       }
-      if (cur.nchunks == 1) {
+      if (cur.nparts == 1) {
         p.out[bh * kHeadDim + c] = a / l;
       } else {
-        float* mine = p.partial + (bh * p.max_chunks + cur.chunk) * kPartialStride;
+        // Two partial slots per CTA: only a CTA's first item can continue a head from the CTA
+        // before (slot 0) and only its last item can leave a head to the CTA after (slot 1).
+        float* mine = p.partial + (2 * blockIdx.x + (cur.part > 0 ? 0 : 1)) * kPartialStride;
         mine[c] = a;
         if (c == 0) {
           mine[128] = mmax;
@@ -814,22 +877,24 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (c == 0) {
           const int t = atomicAdd(p.tickets + bh, 1);
-          s_last[buf] = (t == cur.nchunks - 1);
-          if (t == cur.nchunks - 1) p.tickets[bh] = 0;  // ready for the next launch
+          s_last[buf] = (t == cur.nparts - 1);
+          if (t == cur.nparts - 1) p.tickets[bh] = 0;  // ready for the next launch
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (s_last[buf]) {
           __threadfence();
-          const float* base = p.partial + bh * p.max_chunks * kPartialStride;
+          const float* base = p.partial + (2 * cur.first_cta + 1) * kPartialStride;
+          const auto part_of = [&](int jj) { return base + (jj > 0 ? (2 * jj - 1) * kPartialStride : 0); };
           float gm = -INFINITY;
-          for (int jj = 0; jj < cur.nchunks; ++jj) gm = fmaxf(gm, __ldcg(base + jj * kPartialStride + 128));
+          for (int jj = 0; jj < cur.nparts; ++jj) gm = fmaxf(gm, __ldcg(part_of(jj) + 128));
           a = 0.f;
           l = 0.f;
-          for (int jj = 0; jj < cur.nchunks; ++jj) {
-            const float mj = __ldcg(base + jj * kPartialStride + 128);
+          for (int jj = 0; jj < cur.nparts; ++jj) {
+            const float* pj = part_of(jj);
+            const float mj = __ldcg(pj + 128);
             const float r = (mj == -INFINITY) ? 0.f : exp2f(mj - gm);
-            a += __ldcg(base + jj * kPartialStride + c) * r;
-            l += __ldcg(base + jj * kPartialStride + 129) * r;
+            a += __ldcg(pj + c) * r;
+            l += __ldcg(pj + 129) * r;
           }
           p.out[bh * kHeadDim + c] = a / l;
         }
@@ -838,14 +903,6 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   }
 
   if (timed_out && lane == 0) atomicExch(p.status, 1);
-  if (tid == 0) {
-    // the last CTA to leave rewinds the queue for the next launch
-    const int d = atomicAdd(p.queue + 1, 1);
-    if (d == static_cast<int>(gridDim.x) - 1) {
-      p.queue[0] = 0;
-      p.queue[1] = 0;
-    }
-  }
 }
 
 // ------------------------------------------------------------------------------ selected readers
@@ -1297,14 +1354,18 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
 
 // ------------------------------------------------------------------------------ host side
 
-int choose_chunk_tokens(int64_t batch_heads, int64_t max_context_tokens) {
-  // Work items of the persistent dense reader: one 64-token block per warp (512 tokens) unless
-  // that gives every CTA more than ~32 items, then two or four blocks per warp.
-  const int64_t ctas = 148 * 2;
-  int chunk = kGroup * kDenseWarps;
-  while (chunk < 2048 && batch_heads * ((max_context_tokens + chunk - 1) / chunk) > 6 * ctas) chunk *= 2;
-  if (const char* env = getenv("FL_CHUNK")) chunk = atoi(env);
-  return chunk;
+// Grid of the persistent dense reader: two CTAs per SM, but never more CTAs than there are tail
+// units, so that every CTA's share of the units is non-empty whatever the context lengths are.
+unsigned dense_grid(int64_t batch_heads) {
+  static const int sm_count = [] {
+    int dev = 0, n = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n > 0 ? n : 148;
+  }();
+  const int64_t ctas = 2 * static_cast<int64_t>(sm_count < 148 ? sm_count : 148);
+  const int64_t cap = batch_heads * kTailUnits;
+  return static_cast<unsigned>(cap < ctas ? cap : ctas);
 }
 
 int choose_slots_per_cta(int64_t batch_heads, int64_t capacity) {
@@ -1318,13 +1379,14 @@ int choose_slots_per_cta(int64_t batch_heads, int64_t capacity) {
   return static_cast<int>(slots);
 }
 
-// tickets[batch_heads], one status word and the two words of the work queue, padded to 256 bytes
+// tickets[batch_heads] and one status word, padded to 256 bytes
 size_t tickets_bytes(int64_t batch_heads) { return (((batch_heads + 3) * sizeof(int) + 255) / 256) * 256; }
 
-int max_partials(int64_t batch_heads, int64_t max_context_tokens) {
-  const int chunk = choose_chunk_tokens(batch_heads, max_context_tokens);
-  const int64_t dense = (max_context_tokens + chunk - 1) / chunk + 1;
-  return static_cast<int>(dense > kMaxSplits ? dense : kMaxSplits);
+// Partial slots per (b,h).  The selected readers split a head over at most kMaxSplits CTAs; the
+// dense reader needs two slots per CTA, at most 2 * 8 * batch_heads in all.
+int max_partials() {
+  static_assert(kMaxSplits >= 2 * kTailUnits, "the dense reader's partials must fit the workspace");
+  return kMaxSplits;
 }
 
 }  // namespace
@@ -1362,7 +1424,7 @@ using namespace fl;
 extern "C" size_t fl_reader_workspace_bytes(int64_t batch_heads, int64_t max_context_tokens) {
   if (batch_heads <= 0 || max_context_tokens < 0) return 0;
   return tickets_bytes(batch_heads) +
-         static_cast<size_t>(batch_heads) * max_partials(batch_heads, max_context_tokens) * kPartialStride *
+         static_cast<size_t>(batch_heads) * max_partials() * kPartialStride *
              sizeof(float);
 }
 
@@ -1404,9 +1466,8 @@ int fill_common(ReaderParams& p, const fl_layer* layer, int loop, void* workspac
   p.loop = loop;
   p.tickets = static_cast<int*>(workspace);
   p.status = p.tickets + bh;
-  p.queue = p.tickets + bh + 1;
   p.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + tickets_bytes(bh));
-  p.max_chunks = max_partials(bh, max_context_tokens);
+  p.max_chunks = max_partials();
   return FL_OK;
 }
 
@@ -1438,17 +1499,7 @@ extern "C" int fl_dense_source_attention(const fl_layer* layer, int32_t loop, co
   p.out = output;
   p.logits = logits;
   p.logits_stride = logits_stride;
-  p.chunk_tokens = choose_chunk_tokens(bh, max_context_tokens);
-  p.grid_chunks = static_cast<int>((max_context_tokens + p.chunk_tokens - 1) / p.chunk_tokens) + 1;
-  // persistent CTAs, two per SM, fed from the work queue in the workspace
-  static const int sm_count = [] {
-    int dev = 0, n = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    return n > 0 ? n : 148;
-  }();
-  const int64_t items = bh * p.grid_chunks;
-  const unsigned grid = static_cast<unsigned>(items < 2 * sm_count ? items : 2 * sm_count);
+  const unsigned grid = dense_grid(bh);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (layer->bits == 4) {
     constexpr int kSmem = kDenseWarps * kStages * Stage<4>::kBytes;
@@ -1576,7 +1627,7 @@ extern "C" int fl_selected_qk(const fl_layer* layer, int32_t loop, const void* q
 // scratch buffer because they cannot allocate device memory at the point of the call -- code
 // running inside a stream capture, a plugin loaded into a server whose memory is owned by a
 // fixed pool it has no handle to, a host language binding without a device allocator.  The
-// scratch (tickets, status word, work queue, split partials) lives in the file-scope device
+// scratch (tickets, status word, split partials) lives in the file-scope device
 // array below, which every GPU that loads this library holds until the process exits.
 
 namespace fl {
@@ -1584,11 +1635,11 @@ namespace {
 
 constexpr int64_t kStaticMaxBatchHeads = 128;
 constexpr int64_t kStaticMaxContext = 16384;
-// partial slots per (b,h): one per 512-token chunk plus the tail item
-constexpr int kStaticSlots = static_cast<int>(kStaticMaxContext / (kGroup * kDenseWarps)) + 1;
+// partial slots: two per CTA of the largest grid
+constexpr int kStaticSlots = 2 * 2 * 148;
 constexpr size_t kStaticHeaderBytes = ((kStaticMaxBatchHeads + 3) * sizeof(int) + 255) / 256 * 256;
 constexpr size_t kStaticBytes =
-    kStaticHeaderBytes + static_cast<size_t>(kStaticMaxBatchHeads) * kStaticSlots * kPartialStride * sizeof(float);
+    kStaticHeaderBytes + static_cast<size_t>(kStaticSlots) * kPartialStride * sizeof(float);
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
 
@@ -1655,7 +1706,6 @@ extern "C" int fl_dense_source_attention_static(const fl_layer* layer, int32_t l
   p.loop = loop;
   p.tickets = static_cast<int*>(scratch);
   p.status = p.tickets + kStaticMaxBatchHeads;
-  p.queue = p.tickets + kStaticMaxBatchHeads + 1;
   p.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + kStaticHeaderBytes);
   p.max_chunks = kStaticSlots;
   p.q = static_cast<const __nv_bfloat16*>(query);
@@ -1666,14 +1716,7 @@ extern "C" int fl_dense_source_attention_static(const fl_layer* layer, int32_t l
   p.out = output;
   p.logits = logits;
   p.logits_stride = logits_stride;
-  p.chunk_tokens = kGroup * kDenseWarps;
-  p.grid_chunks = static_cast<int>((max_context_tokens + p.chunk_tokens - 1) / p.chunk_tokens) + 1;
-  int device = 0, sm_count = 0;
-  cudaGetDevice(&device);
-  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-  if (sm_count <= 0) sm_count = 148;
-  const int64_t items = bh * p.grid_chunks;
-  const unsigned grid = static_cast<unsigned>(items < 2 * sm_count ? items : 2 * sm_count);
+  const unsigned grid = dense_grid(bh);
   if (layer->bits == 4) {
     constexpr int kSmem = kDenseWarps * kStages * Stage<4>::kBytes;
     const cudaError_t attr =

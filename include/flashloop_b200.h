@@ -177,7 +177,7 @@ int fl_dense_source_attention(const fl_layer* layer, int32_t loop, const void* q
  * reference.  It is for callers that cannot allocate device memory where they call the reader:
  * code inside a stream capture, a plugin inside a server whose device memory belongs to a
  * fixed pool, a language binding with no device allocator at hand.  The scratch is a static
- * device array of about 2.2 MB that every GPU loading this library keeps until exit; nothing
+ * device array of about 0.3 MB that every GPU loading this library keeps until exit; nothing
  * is allocated or freed by the call.  Limits: batch*heads <= 128 and max_context_tokens <=
  * 16384 (FL_ERR_UNSUPPORTED beyond them).  The first call on each device looks up the array's
  * device address and clears its header, so make that call outside any stream capture.  All
