@@ -532,7 +532,9 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   __shared__ __align__(16) __half s_wtab[kDenseWarps][2][kHeadDim];
   __shared__ __align__(16) float s_merge[2][kDenseWarps][kPartialStride];
   __shared__ __align__(8) uint64_t s_bar[kDenseWarps][kStages];
-  __shared__ ItemDesc s_item[3];
+  __shared__ ItemDesc s_item[4];  // current, next, the one being described, and the one still being merged
+  __shared__ ItemCursor s_cursor;
+  __shared__ int64_t s_all_units;
   __shared__ int s_last[2];
 
   const LayerView& L = p.L;
@@ -551,13 +553,14 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  // this CTA's contiguous range of units; the thread that describes the items walks it
-  const int64_t all_units = total_units(L);
-  ItemCursor cursor;
-  cursor_start(L, all_units * blockIdx.x / gridDim.x, all_units * (blockIdx.x + 1) / gridDim.x, &cursor);
+  // this CTA's contiguous range of units; the one thread that describes the items walks it with a
+  // cursor kept in shared memory (registers are allocated for every thread)
   if (tid == kHeadDim) {
-    describe_next(p, all_units, &cursor, &s_item[0]);
-    describe_next(p, all_units, &cursor, &s_item[1]);
+    const int64_t all_units = total_units(L);
+    s_all_units = all_units;
+    cursor_start(L, all_units * blockIdx.x / gridDim.x, all_units * (blockIdx.x + 1) / gridDim.x, &s_cursor);
+    describe_next(p, all_units, &s_cursor, &s_item[0]);
+    describe_next(p, all_units, &s_cursor, &s_item[1]);
   }
   __syncthreads();
   if (s_item[0].id >= 0 && tid < kHeadDim) {
@@ -576,21 +579,22 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   state_init(S);
 
   for (int k = 0;; ++k) {
-    const ItemDesc* curp = &s_item[k % 3];
+    const ItemDesc* curp = &s_item[k % 4];
     if (curp->id < 0) break;
     struct {
-      int bh, b, quant, tail_len, tail_start, blk_begin, blk_end, has_tail, part, nparts, first_cta, rot;
-    } cur = {curp->bh, curp->b, curp->quant, curp->tail_len, curp->tail_start, curp->blk_begin,
-             curp->blk_end, curp->has_tail, curp->part, curp->nparts, curp->first_cta, curp->rot};
+      int bh, b, blk_begin, blk_end, has_tail, rot;
+    } cur = {curp->bh, curp->b, curp->blk_begin, curp->blk_end, curp->has_tail, curp->rot};
+    // (the fields that only the tail and the merge need are read from curp there: its slot is not
+    // rewritten before the merge of the item after this one has begun)
     // Look ahead: one thread of the upper half of the CTA (the warps that sit out the merge)
     // describes item k+2, the upper half fetches the query of item k+1.  Both become visible to the
     // other warps at this item's closing barrier.
-    if (tid == kHeadDim) describe_next(p, all_units, &cursor, &s_item[(k + 2) % 3]);
+    if (tid == kHeadDim) describe_next(p, s_all_units, &s_cursor, &s_item[(k + 2) % 4]);
     if (tid >= kHeadDim) {
-      const int next_id = s_item[(k + 1) % 3].id;
+      const int next_id = s_item[(k + 1) % 4].id;
       if (next_id >= 0) {
         s_qf[(k + 1) & 1][tid - kHeadDim] = __bfloat162float(
-            p.q[static_cast<int64_t>(s_item[(k + 1) % 3].bh) * kHeadDim + tid - kHeadDim]);
+            p.q[static_cast<int64_t>(s_item[(k + 1) % 4].bh) * kHeadDim + tid - kHeadDim]);
       }
     }
     const int64_t bh = cur.bh;
@@ -611,7 +615,7 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
           // ---- keep the ring full: issue units of this item, then of the next one
           while (issued - consumed < static_cast<uint32_t>(kStages)) {
             if (iss_item > k + 1) break;
-            const ItemDesc* it = &s_item[iss_item % 3];
+            const ItemDesc* it = &s_item[iss_item % 4];
             if (it->id < 0) break;
             const int it_pos = (warp - it->rot) & (kDenseWarps - 1);
             const int it_blocks = blocks_of_warp(it->blk_begin, it->blk_end, it_pos);
@@ -822,19 +826,19 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
     }
     if (cur.has_tail && warp < 4) {
       // ---- the BF16 tail and the current token: entries 0..tail_len (the last is the current)
-      const int entries = cur.tail_len + 1;
+      const int entries = curp->tail_len + 1;
       const __nv_bfloat16* tk = L.tail_k[p.loop] + bh * L.tail_capacity * kHeadDim;
       const __nv_bfloat16* tv = L.tail_v[p.loop] + bh * L.tail_capacity * kHeadDim;
       for (int e0 = warp * 8; e0 < entries; e0 += 4 * 8) {
         const int e = e0 + quad;
         const bool ok = e < entries;
-        const int slot = (cur.tail_start + e) % L.tail_capacity;
-        const __nv_bfloat16* krow = (e == cur.tail_len) ? p.kcur + bh * kHeadDim : tk + slot * kHeadDim;
-        const __nv_bfloat16* vrow = (e == cur.tail_len) ? p.vcur + bh * kHeadDim : tv + slot * kHeadDim;
+        const int slot = (curp->tail_start + e) % L.tail_capacity;
+        const __nv_bfloat16* krow = (e == curp->tail_len) ? p.kcur + bh * kHeadDim : tk + slot * kHeadDim;
+        const __nv_bfloat16* vrow = (e == curp->tail_len) ? p.vcur + bh * kHeadDim : tv + slot * kHeadDim;
         float dot = 0.f;
         if (ok) dot = bf16_row_dot<BITS>(krow, sub, qf);
         dot = quad_sum(dot);
-        if (ok && logits_row && sub == 0) logits_row[cur.quant + e] = dot * p.scaling;
+        if (ok && logits_row && sub == 0) logits_row[curp->quant + e] = dot * p.scaling;
         const float x = ok ? dot * p.scaling_log2 : -INFINITY;
         state_raise(S, across_quads_max(x));
         const float pr = ok ? exp2f(x - S.m) : 0.f;
@@ -862,12 +866,13 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
         a += s_merge[buf][w][c] * r;
         l += s_merge[buf][w][129] * r;
       }
-      if (cur.nparts == 1) {
+      const int nparts = curp->nparts;
+      if (nparts == 1) {
         p.out[bh * kHeadDim + c] = a / l;
       } else {
         // Two partial slots per CTA: only a CTA's first item can continue a head from the CTA
         // before (slot 0) and only its last item can leave a head to the CTA after (slot 1).
-        float* mine = p.partial + (2 * blockIdx.x + (cur.part > 0 ? 0 : 1)) * kPartialStride;
+        float* mine = p.partial + (2 * blockIdx.x + (curp->part > 0 ? 0 : 1)) * kPartialStride;
         mine[c] = a;
         if (c == 0) {
           mine[128] = mmax;
@@ -877,19 +882,19 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (c == 0) {
           const int t = atomicAdd(p.tickets + bh, 1);
-          s_last[buf] = (t == cur.nparts - 1);
-          if (t == cur.nparts - 1) p.tickets[bh] = 0;  // ready for the next launch
+          s_last[buf] = (t == nparts - 1);
+          if (t == nparts - 1) p.tickets[bh] = 0;  // ready for the next launch
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (s_last[buf]) {
           __threadfence();
-          const float* base = p.partial + (2 * cur.first_cta + 1) * kPartialStride;
+          const float* base = p.partial + (2 * curp->first_cta + 1) * kPartialStride;
           const auto part_of = [&](int jj) { return base + (jj > 0 ? (2 * jj - 1) * kPartialStride : 0); };
           float gm = -INFINITY;
-          for (int jj = 0; jj < cur.nparts; ++jj) gm = fmaxf(gm, __ldcg(part_of(jj) + 128));
+          for (int jj = 0; jj < nparts; ++jj) gm = fmaxf(gm, __ldcg(part_of(jj) + 128));
           a = 0.f;
           l = 0.f;
-          for (int jj = 0; jj < cur.nparts; ++jj) {
+          for (int jj = 0; jj < nparts; ++jj) {
             const float* pj = part_of(jj);
             const float mj = __ldcg(pj + 128);
             const float r = (mj == -INFINITY) ? 0.f : exp2f(mj - gm);
