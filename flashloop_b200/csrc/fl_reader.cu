@@ -25,8 +25,6 @@
 namespace fl {
 namespace {
 
-constexpr int kThreads = 128;
-constexpr int kWarps = kThreads / kWarp;
 constexpr int kPartialStride = 132;  // acc[128], running max (log2 domain), denominator, pad
 constexpr int kMaxSplits = 64;
 
@@ -305,10 +303,7 @@ __device__ __forceinline__ bool merge_and_publish(const ReaderParams& p, float (
 }
 
 // One BF16 row (tail or current token) for every quad of the warp: logits, online softmax, PV.
-template <int BITS>
-__device__ __forceinline__ float bf16_row_dot(const __nv_bfloat16* row, int sub, const float* s_qf) {
-  uint32_t w[16];
-  load_bf16_row(row, sub, w);
+__device__ __forceinline__ float bf16_words_dot(const uint32_t (&w)[16], int sub, const float* s_qf) {
   float dot = 0.f;
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
@@ -318,15 +313,25 @@ __device__ __forceinline__ float bf16_row_dot(const __nv_bfloat16* row, int sub,
   return dot;
 }
 template <int BITS>
-__device__ __forceinline__ void bf16_row_accumulate(const __nv_bfloat16* row, int sub, float pr,
-                                                    float (&acc)[32]) {
-  uint32_t w[16];
-  load_bf16_row(row, sub, w);
+__device__ __forceinline__ void bf16_words_accumulate(const uint32_t (&w)[16], float pr, float (&acc)[32]) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     acc[channel_slot<BITS>(2 * i)] = fmaf(pr, bf16_lo(w[i]), acc[channel_slot<BITS>(2 * i)]);
     acc[channel_slot<BITS>(2 * i + 1)] = fmaf(pr, bf16_hi(w[i]), acc[channel_slot<BITS>(2 * i + 1)]);
   }
+}
+template <int BITS>
+__device__ __forceinline__ float bf16_row_dot(const __nv_bfloat16* row, int sub, const float* s_qf) {
+  uint32_t w[16];
+  load_bf16_row(row, sub, w);
+  return bf16_words_dot(w, sub, s_qf);
+}
+template <int BITS>
+__device__ __forceinline__ void bf16_row_accumulate(const __nv_bfloat16* row, int sub, float pr,
+                                                    float (&acc)[32]) {
+  uint32_t w[16];
+  load_bf16_row(row, sub, w);
+  bf16_words_accumulate<BITS>(w, pr, acc);
 }
 
 // ------------------------------------------------------------------------------ dense reader
@@ -434,12 +439,18 @@ struct ItemDesc {
   int64_t group_base[4];
 };
 
+constexpr int kEachCached = 256;  // sequences whose unit counts the CTA keeps in shared memory
+
 __device__ __forceinline__ int units_per_head(const LayerView& L, int b) {
   return L.seq_state[b * FL_STATE_WORDS + FL_STATE_QUANT_TOKENS] / kGroup + kTailUnits;
 }
-__device__ __forceinline__ int64_t total_units(const LayerView& L) {
+// `each`: the CTA's shared copy of units_per_head for the first kEachCached sequences
+__device__ __forceinline__ int units_per_head(const LayerView& L, const int* each, int b) {
+  return b < kEachCached ? each[b] : units_per_head(L, b);
+}
+__device__ __forceinline__ int64_t total_units(const LayerView& L, const int* each) {
   int64_t total = 0;
-  for (int b = 0; b < L.batch; ++b) total += static_cast<int64_t>(L.heads) * units_per_head(L, b);
+  for (int b = 0; b < L.batch; ++b) total += static_cast<int64_t>(L.heads) * units_per_head(L, each, b);
   return total;
 }
 
@@ -452,25 +463,27 @@ struct ItemCursor {
   int blocks_done;     // blocks in those items
 };
 
-__device__ __forceinline__ void cursor_start(const LayerView& L, int64_t lo, int64_t hi, ItemCursor* c) {
+__device__ __forceinline__ void cursor_start(const LayerView& L, const int* each, int64_t lo, int64_t hi,
+                                             ItemCursor* c) {
   c->at = lo;
   c->end = hi;
   c->count = 0;
   c->blocks_done = 0;
   c->b = 0;
-  c->each = units_per_head(L, 0);
+  c->each = units_per_head(L, each, 0);
   int64_t first = 0;
   while (c->b + 1 < L.batch && lo >= first + static_cast<int64_t>(L.heads) * c->each) {
     first += static_cast<int64_t>(L.heads) * c->each;
     ++c->b;
-    c->each = units_per_head(L, c->b);
+    c->each = units_per_head(L, each, c->b);
   }
   c->h = static_cast<int>((lo - first) / c->each);
   if (c->h >= L.heads) c->h = L.heads - 1;  // only when the range is empty
   c->head_first = first + static_cast<int64_t>(c->h) * c->each;
 }
 
-__device__ __forceinline__ void describe_next(const ReaderParams& p, int64_t all_units, ItemCursor* c, ItemDesc* d) {
+__device__ __forceinline__ void describe_next(const ReaderParams& p, const int* each, int64_t all_units,
+                                              ItemCursor* c, ItemDesc* d) {
   const LayerView& L = p.L;
   if (c->at >= c->end) {
     d->id = -1;
@@ -509,7 +522,10 @@ __device__ __forceinline__ void describe_next(const ReaderParams& p, int64_t all
     c->head_first = head_end;
     if (++c->h == L.heads) {
       c->h = 0;
-      if (c->b + 1 < L.batch) c->each = units_per_head(L, ++c->b);
+      if (c->b + 1 < L.batch) {
+        ++c->b;
+        c->each = units_per_head(L, each, c->b);
+      }
     }
   }
 }
@@ -534,6 +550,7 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   __shared__ __align__(8) uint64_t s_bar[kDenseWarps][kStages];
   __shared__ ItemDesc s_item[4];  // current, next, the one being described, and the one still being merged
   __shared__ ItemCursor s_cursor;
+  __shared__ int s_each[kEachCached];
   __shared__ int64_t s_all_units;
   __shared__ int s_last[2];
 
@@ -555,12 +572,15 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   }
   // this CTA's contiguous range of units; the one thread that describes the items walks it with a
   // cursor kept in shared memory (registers are allocated for every thread)
+  for (int bb = tid; bb < L.batch && bb < kEachCached; bb += kDenseThreads) s_each[bb] = units_per_head(L, bb);
+  __syncthreads();
   if (tid == kHeadDim) {
-    const int64_t all_units = total_units(L);
+    const int64_t all_units = total_units(L, s_each);
     s_all_units = all_units;
-    cursor_start(L, all_units * blockIdx.x / gridDim.x, all_units * (blockIdx.x + 1) / gridDim.x, &s_cursor);
-    describe_next(p, all_units, &s_cursor, &s_item[0]);
-    describe_next(p, all_units, &s_cursor, &s_item[1]);
+    cursor_start(L, s_each, all_units * blockIdx.x / gridDim.x, all_units * (blockIdx.x + 1) / gridDim.x,
+                 &s_cursor);
+    describe_next(p, s_each, all_units, &s_cursor, &s_item[0]);
+    describe_next(p, s_each, all_units, &s_cursor, &s_item[1]);
   }
   __syncthreads();
   if (s_item[0].id >= 0 && tid < kHeadDim) {
@@ -589,7 +609,7 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
     // Look ahead: one thread of the upper half of the CTA (the warps that sit out the merge)
     // describes item k+2, the upper half fetches the query of item k+1.  Both become visible to the
     // other warps at this item's closing barrier.
-    if (tid == kHeadDim) describe_next(p, s_all_units, &s_cursor, &s_item[(k + 2) % 4]);
+    if (tid == kHeadDim) describe_next(p, s_each, s_all_units, &s_cursor, &s_item[(k + 2) % 4]);
     if (tid >= kHeadDim) {
       const int next_id = s_item[(k + 1) % 4].id;
       if (next_id >= 0) {
@@ -824,26 +844,32 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
       iss_blk = 0;
       iss_j = 0;
     }
-    if (cur.has_tail && warp < 4) {
-      // ---- the BF16 tail and the current token: entries 0..tail_len (the last is the current)
+    if (cur.has_tail) {
+      // ---- the BF16 tail and the current token: entries 0..tail_len (the last is the current),
+      // one per lane quad; the V row is fetched together with the K row
       const int entries = curp->tail_len + 1;
       const __nv_bfloat16* tk = L.tail_k[p.loop] + bh * L.tail_capacity * kHeadDim;
       const __nv_bfloat16* tv = L.tail_v[p.loop] + bh * L.tail_capacity * kHeadDim;
-      for (int e0 = warp * 8; e0 < entries; e0 += 4 * 8) {
+      for (int e0 = warp * 8; e0 < entries; e0 += kDenseWarps * 8) {
         const int e = e0 + quad;
         const bool ok = e < entries;
         const int slot = (curp->tail_start + e) % L.tail_capacity;
         const __nv_bfloat16* krow = (e == curp->tail_len) ? p.kcur + bh * kHeadDim : tk + slot * kHeadDim;
         const __nv_bfloat16* vrow = (e == curp->tail_len) ? p.vcur + bh * kHeadDim : tv + slot * kHeadDim;
+        uint32_t kw[16], vw[16];
+        if (ok) {
+          load_bf16_row(krow, sub, kw);
+          load_bf16_row(vrow, sub, vw);
+        }
         float dot = 0.f;
-        if (ok) dot = bf16_row_dot<BITS>(krow, sub, qf);
+        if (ok) dot = bf16_words_dot(kw, sub, qf);
         dot = quad_sum(dot);
         if (ok && logits_row && sub == 0) logits_row[curp->quant + e] = dot * p.scaling;
         const float x = ok ? dot * p.scaling_log2 : -INFINITY;
         state_raise(S, across_quads_max(x));
         const float pr = ok ? exp2f(x - S.m) : 0.f;
         S.l += pr;
-        if (ok) bf16_row_accumulate<BITS>(vrow, sub, pr, S.acc);
+        if (ok) bf16_words_accumulate<BITS>(vw, pr, S.acc);
       }
     }
 
@@ -912,24 +938,42 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
 
 // ------------------------------------------------------------------------------ selected readers
 //
-// Block-major gather with a per-warp asynchronous prefetch.  The selected indices arrive sorted,
-// so the slots that fall into one 64-token block are consecutive: a "run".  A warp takes whole
-// runs and walks them in passes of eight tokens, one per lane quad.  While it computes pass i
-// from shared memory, the rows of pass i+1 (K row and V record of every stream, and the K
-// metadata of a new run) are already on their way there as 16-byte cp.async copies that each
-// lane issues for the pieces it will read itself, so no registers are tied up by loads in flight
-// and a warp meets memory latency once per pipeline fill instead of once per pass.
+// Stream-major gather.  A selected token owns a row in streams 0 and 1 and, where the token was
+// retained, in the compact streams 2 and 3, so a token-major walk would run every stream for all
+// eight tokens of a pass whenever one of them holds a compact row.  Here every stream is packed
+// by itself instead.  A CTA stages a batch of slots (one per thread), builds per stream the list
+// of the slots that hold a row there, and cuts the work into passes of at most eight rows of ONE
+// stream:
 //
-// For a run the warp builds the block's query-folded K tables exactly as the dense reader does
-// (w_c = q_c * scale_c in float16, bias in float32; a second table where the compact rows of a
-// block straddle a metadata group), so K metadata is read once per run and stream and the
-// per-token arithmetic is the dense reader's fast path.
+//   K pass: up to eight rows of one stream that share a K metadata group (for the compact
+//           streams that is a group of 64 compact rows, about 256 tokens wide, so their passes
+//           are as full as those of streams 0 and 1).  The warp builds the group's query-folded
+//           table (w_c = q_c * scale_c in float16, bias in float32) as the dense reader does and
+//           writes one partial logit per row to shared memory.
+//   softmax: after a CTA barrier every thread sums the partial logits of its slot over the
+//           streams in a fixed order; the batch maximum raises the CTA's running maximum (online
+//           softmax at batch granularity) and the probability goes to shared memory.
+//   V pass: any eight records of one stream: p * v_scale * (code - centre) into the warp's
+//           float16-pair accumulators, widened every sixteen passes.
 //
-// Indices need not be sorted for correctness (an unsorted list only makes more, shorter runs).
+// The passes of a warp are independent of each other, so each warp runs them through a private
+// ring of kDepth shared-memory stages filled by 16-byte cp.async copies that every lane issues
+// for the pieces it will read itself; the V passes of a batch are already on their way while the
+// CTA is still in the softmax barrier.  Tail tokens and the current token (BF16 rows) are passes
+// of their own that read global memory directly.
+//
+// Indices need not be sorted for correctness (an unsorted list only makes more, shorter K passes).
 
 enum { kModeDelta = 0, kModePV = 1, kModeQK = 2 };
-constexpr int kSlotBatch = kThreads;  // slots staged per round: one per thread
-constexpr int kTailKey = INT_MAX;
+constexpr int kGatherWarps = 8;
+constexpr int kGatherThreads = kGatherWarps * kWarp;
+constexpr int kSlotBatch = kGatherThreads;  // slots staged per round: one per thread
+constexpr int kDepth = 4;                   // passes in flight per warp
+constexpr int kPassBytes = 1024;            // K: 8 rows (<= 512 B) + one metadata group (512 B); V: 8 records (<= 640 B)
+constexpr int kTailClass = 4;               // list of the slots that are tail tokens or the current token
+constexpr int kGatherCtasPerSm = 2;
+static_assert(kGatherWarps * kDepth * kPassBytes >= kGatherWarps * kPartialStride * 4,
+              "the merge buffer reuses the rings");
 
 template <int BYTES>
 __device__ __forceinline__ void cp_async(uint32_t dst_shared, const void* src_global) {
@@ -944,38 +988,58 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// Per-warp shared memory of the gather: two row buffers (8 tokens x 4 streams) and one K
-// metadata buffer (scale[128], min[128] of one group per stream).
-template <int BITS, int MODE>
-struct GatherSmem {
-  static constexpr int kRowBytes = 16 * BITS;
-  static constexpr int kRecord = kRowBytes + 16;
-  static constexpr int kKBytes = MODE == kModePV ? 0 : kRowBytes;
-  static constexpr int kVBytes = MODE == kModeQK ? 0 : kRecord;
-  static constexpr int kToken = kKBytes + kVBytes;  // one token of one stream
-  static constexpr int kRows = 8 * 4 * kToken;
-  static constexpr int kMeta = MODE == kModePV ? 0 : 4 * 512;
-  static constexpr int kWarp = 2 * kRows + kMeta;
-  static_assert(kWarps * kWarp >= kWarps * kPartialStride * 4, "the merge buffer reuses this memory");
-};
+// Pass descriptor (16 bits): stream or class in bits 12..14, first list entry in bits 4..11, rows
+// (1..8) in bits 0..3; 0 = no pass.  K passes of a batch sit at s_desc[0..), V passes at
+// s_desc[kVDescBase..).
+constexpr int kVDescBase = 4 * kSlotBatch + kSlotBatch / 8;
+constexpr int kDescCount = kVDescBase + 5 * (kSlotBatch / 8);
+
+// The K table of one metadata group, this lane's four channels 4*lane .. 4*lane+3: w_c = q_c *
+// scale_c as float16 in the pair order of unpack_centred (the products are exact in float32, so
+// rounding them once in float16 arithmetic gives the same table), stored with one 8-byte write
+// per lane after the lanes that hold the two halves of a pair have swapped one register.
+template <int BITS>
+__device__ __forceinline__ void table_store(__half* table, int lane, __half2 q01, __half2 q23, uint2 scale) {
+  constexpr int kPartner = BITS == 4 ? 1 : 2;  // pairs are (c, c + 4) or (c, c + 8)
+  const __half2 a = __hmul2(q01, as_half2(scale.x));
+  const __half2 b = __hmul2(q23, as_half2(scale.y));
+  const bool first = (lane & kPartner) == 0;
+  const uint32_t mine_a = as_u32(a), mine_b = as_u32(b);
+  const uint32_t got = __shfl_xor_sync(0xffffffffu, first ? mine_b : mine_a, kPartner);
+  const uint32_t lo = first ? mine_a : got, hi = first ? got : mine_b;
+  uint2 out;
+  out.x = __byte_perm(lo, hi, 0x5410);  // (lo.low, hi.low)
+  out.y = __byte_perm(lo, hi, 0x7632);  // (lo.high, hi.high)
+  int at;  // in halves
+  if constexpr (BITS == 4) {
+    at = 4 * lane;
+  } else {
+    at = 16 * (lane >> 2) + 8 * (lane & 1) + 4 * ((lane >> 1) & 1);
+  }
+  *reinterpret_cast<uint2*>(table + at) = out;
+}
 
 template <int BITS, int MODE>
-__global__ void __launch_bounds__(kThreads, 4)
+__global__ void __launch_bounds__(kGatherThreads, kGatherCtasPerSm)
 selected_reader_kernel(const __grid_constant__ ReaderParams p) {
-  using G = GatherSmem<BITS, MODE>;
-  constexpr int kRowBytes = G::kRowBytes;
+  constexpr int kRowBytes = 16 * BITS;
+  constexpr int kRecord = kRowBytes + 16;
   constexpr int kLaneBytes = kRowBytes / 4;
   constexpr uint32_t kFull = 0xffffffffu;
-  extern __shared__ __align__(128) uint8_t s_gather[];  // [warp][row buffer 0 | row buffer 1 | K metadata]
+  extern __shared__ __align__(128) uint8_t s_ring[];  // [warp][stage][kPassBytes]
   __shared__ __align__(16) float s_qf[kHeadDim];
-  __shared__ __align__(16) __half s_wtab[kWarps][4][kHeadDim];  // the current run's K table of every stream
-  __shared__ float s_kbias[kWarps][4];
-  __shared__ int s_g0[kWarps][4];         // first K metadata group of the run whose metadata is in the buffer
-  __shared__ int s_idx[kSlotBatch];       // logical index, or -1
-  __shared__ int s_grow[4][kSlotBatch];   // row of the slot in every stream, counted from the head's first row, or -1
-  __shared__ int s_key[kSlotBatch];       // 64-token block of the slot, kTailKey, or -1 (nothing to read)
-  __shared__ int s_run[kSlotBatch + 1];   // first slot of every run, then the end
-  __shared__ int s_warp_runs[kWarps];
+  __shared__ __align__(16) __half s_wtab[kGatherWarps][kHeadDim];  // the current K pass's table
+  __shared__ int s_crow[5][kSlotBatch];        // per stream: the rows to read, in slot order (tail class: ring slot, -1 = current token)
+  __shared__ uint8_t s_list[5][kSlotBatch];    // ... and the slots they belong to
+  __shared__ float s_dot[4][kSlotBatch];       // partial logit of the slot from every stream (tail rows: stream 0)
+  __shared__ float s_prob[kSlotBatch];         // probability (or the caller's weight) of the slot
+  __shared__ uint16_t s_desc[kDescCount];
+  __shared__ int s_wcount[5][kGatherWarps], s_woff[5][kGatherWarps];
+  __shared__ int s_whead[4][kGatherWarps], s_wfirst[4][kGatherWarps];
+  __shared__ int s_count[5];
+  __shared__ int s_nk_packed;
+  __shared__ int s_base[8];                    // row_base[0..3], group_base[0..3] of this (b,h)
+  __shared__ float s_red[kGatherWarps];
   __shared__ int s_last;
 
   const LayerView& L = p.L;
@@ -997,26 +1061,31 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   const int warp = tid >> 5;
   const int quad = lane >> 2;
   const int sub = lane & 3;
-  uint8_t* const my_gather = s_gather + warp * G::kWarp;
-  const uint32_t my_gather_u32 = smem_u32(my_gather);
-  const uint8_t* const my_meta = my_gather + 2 * G::kRows;
-  float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);  // query channels 4*lane .. 4*lane+3
+  const uint32_t lanes_below = (1u << lane) - 1u;
+  uint8_t* const my_ring = s_ring + warp * kDepth * kPassBytes;
+  const uint32_t my_ring_u32 = smem_u32(my_ring);
+  const int codes_at = quad * kRowBytes + sub * kLaneBytes;  // this lane's codes within a stage
+  float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);                // query channels 4*lane .. 4*lane+3
+  __half2 q01 = __floats2half2_rn(0.f, 0.f), q23 = q01;
   if constexpr (MODE != kModePV) {
-    s_qf[tid] = __bfloat162float(p.q[bh * kHeadDim + tid]);
+    if (tid < kHeadDim) s_qf[tid] = __bfloat162float(p.q[bh * kHeadDim + tid]);
     const uint2 raw = ldg64(p.q + bh * kHeadDim + 4 * lane);
     q4 = make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
+    q01 = __floats2half2_rn(q4.x, q4.y);
+    q23 = __floats2half2_rn(q4.z, q4.w);
   }
   // rows / K metadata groups of this (b,h) start here in every stream (the counts fit 31 bits)
-  int row_base[4], group_base[4];
-#pragma unroll
-  for (int s = 0; s < 4; ++s) {
-    row_base[s] = s < streams ? static_cast<int>(L.row_base[s][bh]) : 0;
-    group_base[s] = s < streams ? static_cast<int>(L.group_base[s][bh]) : 0;
+  if (tid < 8) {
+    const int s = tid & 3;
+    int v = 0;
+    if (s < streams) v = static_cast<int>(tid < 4 ? L.row_base[s][bh] : L.group_base[s][bh]);
+    s_base[tid] = v;
   }
 
   OnlineState S;
   state_init(S);
-  if constexpr (MODE == kModePV) S.m = 0.f;
+  float m_run = MODE == kModePV ? 0.f : -INFINITY;  // the CTA's running maximum (uniform)
+  float l_mine = 0.f;                                // sum of the probabilities of this thread's slots
   const int32_t* idx_row = p.indices + bh * p.capacity;
   const uint8_t* valid_row = p.valid ? p.valid + bh * p.capacity : nullptr;
   const __nv_bfloat16* tk = L.tail_k[p.loop] + bh * L.tail_capacity * kHeadDim;
@@ -1024,335 +1093,342 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   __half2 hacc[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) hacc[i] = __floats2half2_rn(0.f, 0.f);
-  int passes = 0;
-
-  // The K table of stream s for one metadata group: w_c = q_c * scale_c in pair order and
-  // bias = sum_c q_c * (min_c + centre * scale_c), from this lane's four channels.
-  auto build_table = [&](int s, uint2 sc, uint2 mn) {
-    const float2 sc01 = __half22float2(as_half2(sc.x)), sc23 = __half22float2(as_half2(sc.y));
-    const float2 mn01 = __half22float2(as_half2(mn.x)), mn23 = __half22float2(as_half2(mn.y));
-    const float kcn = float(kCentre<BITS>);
-    float bias = q4.x * fmaf(kcn, sc01.x, mn01.x);
-    bias = fmaf(q4.y, fmaf(kcn, sc01.y, mn01.y), bias);
-    bias = fmaf(q4.z, fmaf(kcn, sc23.x, mn23.x), bias);
-    bias = fmaf(q4.w, fmaf(kcn, sc23.y, mn23.y), bias);
-    __half* tab = &s_wtab[warp][s][(4 * lane) & ~31];
-    const int cc = (4 * lane) & 31;
-    tab[channel_slot<BITS>(cc + 0)] = __float2half_rn(q4.x * sc01.x);
-    tab[channel_slot<BITS>(cc + 1)] = __float2half_rn(q4.y * sc01.y);
-    tab[channel_slot<BITS>(cc + 2)] = __float2half_rn(q4.z * sc23.x);
-    tab[channel_slot<BITS>(cc + 3)] = __float2half_rn(q4.w * sc23.y);
-    bias = 0.25f * warp_sum(bias);  // added in each of the four lanes of a quad
-    if (lane == 0) s_kbias[warp][s] = bias;
-  };
+  int v_passes = 0;
 
   for (int batch_begin = slot_begin; batch_begin < slot_end; batch_begin += kSlotBatch) {
     const int batch_n = min(kSlotBatch, slot_end - batch_begin);
-    __syncthreads();  // the previous round's lists are no longer read
-    // ---- stage this round's slots: index, the row in every stream, run key
-    {
-      int idx = -1, key = -1;
-      int rows[4] = {-1, -1, -1, -1};
-      if (tid < batch_n) {
-        const int j = batch_begin + tid;
-        if (!valid_row || valid_row[j]) idx = idx_row[j];
-        if (idx >= 0 && idx < quant) {
-          // K tables belong to a 64-token block; without K (weighted PV) any eight slots make a pass
-          key = MODE == kModePV ? (tid >> 3) : (idx >> 6);
-          rows[0] = idx;
-          if (streams >= 2) rows[1] = idx;
-          if (streams >= 3) rows[2] = L.rank[0][L.rank_base[b] + idx];
-          if (streams >= 4) rows[3] = L.rank[1][L.rank_base[b] + idx];
-        } else if (idx >= quant) {
-          const bool has_current = (MODE == kModePV) ? p.vcur != nullptr : p.kcur != nullptr;
-          if (idx - quant < tail_len || (idx == cur_pos && has_current)) key = kTailKey;
-        }
-        if constexpr (MODE == kModeQK) {
-          if (key < 0) p.logits[bh * p.capacity + j] = 0.f;
+    __syncthreads();  // the previous round's lists and rings are no longer read (and s_base is written)
+    // ---- stage this round's slots: index, the row in every stream, class
+    int idx = -1;
+    bool live = false;    // the slot has something to read
+    uint32_t member = 0;  // bit c: the slot is on list c
+    int rows[5] = {-1, -1, -1, -1, -1};
+    if (tid < batch_n) {
+      const int j = batch_begin + tid;
+      if constexpr (MODE == kModePV) s_prob[tid] = p.weights[bh * p.capacity + j];
+      if (!valid_row || valid_row[j]) idx = idx_row[j];
+      if (idx >= 0 && idx < quant) {
+        live = true;
+        rows[0] = idx;
+        if (streams >= 2) rows[1] = idx;
+        if (streams >= 3) rows[2] = L.rank[0][L.rank_base[b] + idx];
+        if (streams >= 4) rows[3] = L.rank[1][L.rank_base[b] + idx];
+      } else if (idx >= quant) {
+        const bool has_current = (MODE == kModePV) ? p.vcur != nullptr : p.kcur != nullptr;
+        if (idx - quant < tail_len) {
+          live = true;
+          member = 1u << kTailClass;
+          rows[4] = (tail_start + idx - quant) % L.tail_capacity;
+        } else if (idx == cur_pos && has_current) {
+          live = true;
+          member = 1u << kTailClass;
         }
       }
-      s_idx[tid] = idx;
-#pragma unroll
-      for (int s = 0; s < 4; ++s) s_grow[s][tid] = rows[s];
-      s_key[tid] = key;
-    }
-    __syncthreads();
-    // ---- runs: maximal ranges of consecutive slots with the same key
-    const bool head = tid < batch_n && (tid == 0 || s_key[tid - 1] != s_key[tid]);
-    const uint32_t heads = __ballot_sync(kFull, head);
-    if (lane == 0) s_warp_runs[warp] = __popc(heads);
-    __syncthreads();
-    int run_base = 0, nruns = 0;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
-      if (w < warp) run_base += s_warp_runs[w];
-      nruns += s_warp_runs[w];
-    }
-    if (head) s_run[run_base + __popc(heads & ((1u << lane) - 1u))] = tid;
-    if (tid == 0) s_run[nruns] = batch_n;
-    __syncthreads();
-
-    // ---- the warp's passes: (run, first slot) pairs, walked with one pass of look-ahead
-    struct Pass {
-      int r, t0, run_a, run_e, key;  // r >= nruns: no more passes
-    };
-    auto next_run = [&](Pass& ps) {
-      for (ps.r += kWarps; ps.r < nruns; ps.r += kWarps) {
-        ps.run_a = s_run[ps.r];
-        ps.run_e = s_run[ps.r + 1];
-        ps.key = s_key[ps.run_a];
-        ps.t0 = ps.run_a;
-        if (ps.key >= 0) return;
+      if constexpr (MODE == kModeQK) {
+        if (!live) p.logits[bh * p.capacity + j] = 0.f;
       }
-    };
-    auto advance = [&](Pass& ps) {
-      ps.t0 += 8;
-      if (ps.t0 >= ps.run_e) next_run(ps);
-    };
-    // Issue the asynchronous copies of a packed pass into row buffer `buf` (one commit group).
-    // The first pass of a run also brings the run's K metadata (first group of every stream) into
-    // the metadata buffer, which the previous run has finished with by then.
-    auto issue = [&](const Pass& ps, int buf) {
-      const int t = min(ps.t0 + quad, ps.run_e - 1);  // idle quads repeat the run's last token
-      const uint32_t token = my_gather_u32 + buf * G::kRows + quad * 4 * G::kToken + sub * kLaneBytes;
+    }
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      s_dot[s][tid] = 0.f;
+      member |= rows[s] >= 0 ? 1u << s : 0u;
+    }
+    // ---- per class: the list of its slots and rows, in slot order
+    int rank_in_warp[5];
+#pragma unroll
+    for (int c = 0; c < 5; ++c) {
+      const uint32_t mask = __ballot_sync(kFull, (member >> c) & 1u);
+      rank_in_warp[c] = __popc(mask & lanes_below);
+      if (lane == 0) s_wcount[c][warp] = __popc(mask);
+    }
+    __syncthreads();
+    if (tid < 5 * kGatherWarps) {
+      const int c = tid >> 3, w = tid & 7;
+      int off = 0;
+      for (int k = 0; k < w; ++k) off += s_wcount[c][k];
+      s_woff[c][w] = off;
+      if (w == kGatherWarps - 1) s_count[c] = off + s_wcount[c][w];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < 5; ++c) {
+      if ((member >> c) & 1u) {
+        const int at = s_woff[c][warp] + rank_in_warp[c];
+        s_list[c][at] = static_cast<uint8_t>(tid);
+        s_crow[c][at] = c < 4 ? s_base[c] + rows[c] : rows[4];
+      }
+    }
+    __syncthreads();
+    const int tail_passes = (s_count[kTailClass] + 7) >> 3;
+    // ---- K passes of streams 0..3: list entry i opens a pass where the metadata group changes
+    // and every eight entries after that
+    if constexpr (MODE != kModePV) {
+      uint32_t run_heads[4];
+      bool entry_on[4], run_head[4];
 #pragma unroll
       for (int s = 0; s < 4; ++s) {
-        if (s < streams) {
-          const int local = s_grow[s][t];
-          if (local >= 0) {
-            const int row = row_base[s] + local;
-            if constexpr (MODE != kModePV) {
-              cp_async<kLaneBytes>(token + s * G::kToken,
-                                   L.k_codes[s] + static_cast<int64_t>(row) * kRowBytes + sub * kLaneBytes);
-            }
-            if constexpr (MODE != kModeQK) {
-              const uint8_t* record = L.v_rows[s] + static_cast<int64_t>(row) * G::kRecord + sub * kLaneBytes;
-              cp_async<kLaneBytes>(token + s * G::kToken + G::kKBytes, record);
-              if (sub == 0) cp_async<16>(token + s * G::kToken + G::kKBytes + kRowBytes, record + kRowBytes);
+        entry_on[s] = s < streams && tid < s_count[s];
+        const int base = s_base[s];
+        const int group = entry_on[s] ? (s_crow[s][tid] - base) >> 6 : -1;
+        const int before = entry_on[s] && tid > 0 ? (s_crow[s][tid - 1] - base) >> 6 : -1;
+        run_head[s] = entry_on[s] && (tid == 0 || group != before);
+        run_heads[s] = __ballot_sync(kFull, run_head[s]);
+        if (lane == 0) s_whead[s][warp] = run_heads[s] ? warp * 32 + 31 - __clz(run_heads[s]) : -1;
+      }
+      __syncthreads();
+      bool pass_head[4];
+      uint32_t pass_heads[4];
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        int run_start = 0;
+        const uint32_t upto = run_heads[s] & (lanes_below | (1u << lane));
+        if (upto) {
+          run_start = warp * 32 + 31 - __clz(upto);
+        } else {
+          for (int w = warp - 1; w >= 0; --w) {
+            const int h = s_whead[s][w];
+            if (h >= 0) {
+              run_start = h;
+              break;
             }
           }
         }
+        pass_head[s] = entry_on[s] && (run_head[s] || ((tid - run_start) & 7) == 0);
+        pass_heads[s] = __ballot_sync(kFull, pass_head[s]);
+        rank_in_warp[s] = __popc(pass_heads[s] & lanes_below);
+        if (lane == 0) {
+          s_wcount[s][warp] = __popc(pass_heads[s]);
+          s_wfirst[s][warp] = pass_heads[s] ? warp * 32 + __ffs(pass_heads[s]) - 1 : -1;
+        }
       }
-      if constexpr (MODE != kModePV) {
-        if (ps.t0 == ps.run_a) {
-          const uint32_t meta = my_gather_u32 + 2 * G::kRows + lane * 8;
+      __syncthreads();
+      if (warp == 0) {  // running pass counts over (stream, warp)
+        const int mine = s_wcount[lane >> 3][lane & 7];
+        int incl = mine;
 #pragma unroll
-          for (int s = 0; s < 4; ++s) {
-            if (s < streams) {
-              int g0;
-              if (s < 2) {
-                g0 = s_grow[s][ps.run_a] >> 6;
-              } else {
-                // rows of the run in a compact stream ascend with the slots: the first present one
-                int lo = INT_MAX;
-                for (int u = ps.run_a + lane; u < ps.run_e; u += 32) {
-                  const int rr = s_grow[s][u];
-                  if (rr >= 0) lo = min(lo, rr);
-                }
-                lo = warp_min_int(lo);
-                g0 = lo == INT_MAX ? -1 : lo >> 6;
+        for (int d = 1; d < 32; d <<= 1) {
+          const int up = __shfl_up_sync(kFull, incl, d);
+          if (lane >= d) incl += up;
+        }
+        s_woff[lane >> 3][lane & 7] = incl - mine;
+        if (lane == 31) s_nk_packed = incl;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        if (pass_head[s]) {
+          int next = s_count[s];
+          const uint32_t above = pass_heads[s] & ~(lanes_below | (1u << lane));
+          if (above) {
+            next = warp * 32 + __ffs(above) - 1;
+          } else {
+            for (int w = warp + 1; w < kGatherWarps; ++w) {
+              const int h = s_wfirst[s][w];
+              if (h >= 0) {
+                next = h;
+                break;
               }
-              if (g0 >= 0) {
-                const int64_t g = group_base[s] + g0;
-                cp_async<8>(meta + s * 512, L.k_scale[s] + g * kHeadDim + 4 * lane);
-                cp_async<8>(meta + s * 512 + 256, L.k_min[s] + g * kHeadDim + 4 * lane);
-              }
-              if (lane == 0) s_g0[warp][s] = g0;
             }
           }
+          s_desc[s_woff[s][warp] + rank_in_warp[s]] = static_cast<uint16_t>((s << 12) | (tid << 4) | (next - tid));
+        }
+      }
+      if (tid < tail_passes) {
+        s_desc[s_nk_packed + tid] =
+            static_cast<uint16_t>((kTailClass << 12) | ((8 * tid) << 4) | min(8, s_count[kTailClass] - 8 * tid));
+      }
+    }
+    int nv_all = 0;
+    if constexpr (MODE != kModeQK) {
+      int mine_c = -1, mine_k = 0;
+#pragma unroll
+      for (int c = 0; c < 5; ++c) {
+        const int n = (s_count[c] + 7) >> 3;
+        if (tid >= nv_all && tid < nv_all + n) {
+          mine_c = c;
+          mine_k = tid - nv_all;
+        }
+        nv_all += n;
+      }
+      if (mine_c >= 0) {
+        s_desc[kVDescBase + tid] = static_cast<uint16_t>((mine_c << 12) | ((8 * mine_k) << 4) |
+                                                         min(8, s_count[mine_c] - 8 * mine_k));
+      }
+    }
+    __syncthreads();
+
+    // ---- this warp's passes: K passes warp, warp + 8, ..., then V passes warp, warp + 8, ...
+    const int nk_all = MODE == kModePV ? 0 : s_nk_packed + tail_passes;
+    const int nk_mine = nk_all > warp ? (nk_all - warp + kGatherWarps - 1) / kGatherWarps : 0;
+    const int nv_mine = nv_all > warp ? (nv_all - warp + kGatherWarps - 1) / kGatherWarps : 0;
+    const int n_mine = nk_mine + nv_mine;
+    // bit 15 is set for a V pass; 0 = past the end
+    auto desc_of = [&](int q) -> uint32_t {
+      if (q >= n_mine) return 0u;
+      const bool is_v = q >= nk_mine;
+      const int at = is_v ? kVDescBase - kGatherWarps * nk_mine + warp + kGatherWarps * q : warp + kGatherWarps * q;
+      return s_desc[at] | (is_v ? 0x8000u : 0u);
+    };
+    // Copies of pass q into its stage (one commit group, empty for tail passes and past the end):
+    // codes of row i at i * kRowBytes; K metadata (scale[128], min[128]) or the V records' 16
+    // metadata bytes (record i at 512 + 16 i) behind them.
+    auto issue = [&](int q) {
+      const uint32_t d = desc_of(q);
+      const int s = (d >> 12) & 7;
+      if (d != 0u && s != kTailClass) {
+        const uint32_t stage = my_ring_u32 + (q % kDepth) * kPassBytes;
+        const int start = (d >> 4) & 0xff;
+        const bool is_v = d & 0x8000u;
+        const int first_row = s_crow[s][start];
+        if (quad < static_cast<int>(d & 0xfu)) {
+          const int row = s_crow[s][start + quad];
+          const uint8_t* src = is_v ? L.v_rows[s] + static_cast<int64_t>(row) * kRecord
+                                    : L.k_codes[s] + static_cast<int64_t>(row) * kRowBytes;
+          cp_async<kLaneBytes>(stage + codes_at, src + sub * kLaneBytes);
+          if (is_v && sub == 0) cp_async<16>(stage + 512 + quad * 16, src + kRowBytes);
+        }
+        if (!is_v) {
+          const int64_t g = s_base[4 + s] + ((first_row - s_base[s]) >> 6);
+          const __half* meta = (lane < 16 ? L.k_scale[s] : L.k_min[s]) + g * kHeadDim + (lane & 15) * 8;
+          cp_async<16>(stage + 512 + lane * 16, meta);
         }
       }
       cp_async_commit();
     };
-
-    Pass cur{warp - kWarps, 0, 0, 0, -1};
-    next_run(cur);
-    int buf = 0;               // the row buffer that holds (or will hold) the current packed pass
-    int run_g[2] = {-1, -1};   // K metadata group the tables of streams 2 and 3 were built for
-    if (cur.r < nruns && cur.key != kTailKey) issue(cur, buf);
-    while (cur.r < nruns) {
-      Pass nxt = cur;
-      advance(nxt);
-      const bool prefetch = nxt.r < nruns && nxt.key != kTailKey;
-      const bool packed_pass = cur.key != kTailKey;
-      if (packed_pass) {
-        cp_async_wait<0>();  // only the current pass is in flight here
-        __syncwarp();        // a quad shares the V metadata piece that its first lane copied
+    auto compute = [&](int q) {
+      const uint32_t d = desc_of(q);
+      const int s = (d >> 12) & 7;
+      const int start = (d >> 4) & 0xff;
+      const bool on = quad < static_cast<int>(d & 0xfu);
+      const int entry = start + (on ? quad : 0);
+      const int slot = s_list[s][entry];
+      const uint8_t* stage = my_ring + (q % kDepth) * kPassBytes;
+      if (!(d & 0x8000u)) {
         if constexpr (MODE != kModePV) {
-          if (cur.t0 == cur.run_a) {
-            // ---- the run's K tables, before the next run's metadata may overwrite the buffer
+          float dot;
+          if (s != kTailClass) {
+            // the group's table and bias = sum_c q_c * (min_c + centre * scale_c)
+            const uint2 sc = *reinterpret_cast<const uint2*>(stage + 512 + lane * 8);
+            const uint2 mn = *reinterpret_cast<const uint2*>(stage + 512 + 256 + lane * 8);
+            table_store<BITS>(s_wtab[warp], lane, q01, q23, sc);
+            const float2 sc01 = __half22float2(as_half2(sc.x)), sc23 = __half22float2(as_half2(sc.y));
+            const float2 mn01 = __half22float2(as_half2(mn.x)), mn23 = __half22float2(as_half2(mn.y));
+            const float kcn = float(kCentre<BITS>);
+            float bias = q4.x * fmaf(kcn, sc01.x, mn01.x);
+            bias = fmaf(q4.y, fmaf(kcn, sc01.y, mn01.y), bias);
+            bias = fmaf(q4.z, fmaf(kcn, sc23.x, mn23.x), bias);
+            bias = fmaf(q4.w, fmaf(kcn, sc23.y, mn23.y), bias);
+            const Codes<BITS> kc = load_codes_shared<BITS>(stage + codes_at);
+            bias = warp_sum(bias);
+            __syncwarp();
+            __half2 mult[16];
+            const uint4* tab4 = reinterpret_cast<const uint4*>(&s_wtab[warp][sub * 32]);
 #pragma unroll
-            for (int s = 0; s < 4; ++s) {
-              if (s < streams && s_g0[warp][s] >= 0) {
-                build_table(s, *reinterpret_cast<const uint2*>(my_meta + s * 512 + lane * 8),
-                            *reinterpret_cast<const uint2*>(my_meta + s * 512 + 256 + lane * 8));
-              }
+            for (int v = 0; v < 4; ++v) {
+              const uint4 x = tab4[v];
+              mult[4 * v + 0] = as_half2(x.x); mult[4 * v + 1] = as_half2(x.y);
+              mult[4 * v + 2] = as_half2(x.z); mult[4 * v + 3] = as_half2(x.w);
             }
-            run_g[0] = s_g0[warp][2];
-            run_g[1] = s_g0[warp][3];
-          }
-        }
-      }
-      __syncwarp();  // tables written; every lane is done with the row buffer the next pass is copied into
-      if (prefetch) issue(nxt, packed_pass ? buf ^ 1 : buf);
-
-      if (!packed_pass) {
-        // ---- BF16 rows: tail tokens and the current token (read directly)
-        const int t = cur.t0 + quad;
-        const bool on = t < cur.run_e;
-        const int idx = on ? s_idx[t] : -1;
-        const bool is_cur = idx == cur_pos;
-        const int slot = on && !is_cur ? (tail_start + idx - quant) % L.tail_capacity : 0;
-        float pr = 0.f;
-        bool skip_v = false;
-        if constexpr (MODE != kModePV) {
-          const __nv_bfloat16* krow = is_cur ? p.kcur + bh * kHeadDim : tk + slot * kHeadDim;
-          float dot = on ? bf16_row_dot<BITS>(krow, sub, s_qf) : 0.f;
-          dot = quad_sum(dot);
-          if constexpr (MODE == kModeQK) {
-            if (on && sub == 0) p.logits[bh * p.capacity + batch_begin + t] = dot;
-            skip_v = true;
+            dot = quad_sum(k_dot_fast<BITS>(kc, mult)) + bias;
           } else {
-            if (on && is_cur && p.cur_logits && sub == 0) p.cur_logits[bh] = dot * p.scaling;
-            const float x = on ? dot * p.scaling_log2 : -INFINITY;
-            const float mx = across_quads_max(x);
-            if (mx > S.m) {
-              flush_pairs(hacc, S.acc);  // the float16 partial sums belong to the old maximum
-              state_raise(S, mx);
-            }
-            pr = on ? exp2f(x - S.m) : 0.f;
-            S.l += pr;
+            const int ring_slot = s_crow[kTailClass][entry];
+            const __nv_bfloat16* krow = ring_slot < 0 ? p.kcur + bh * kHeadDim : tk + ring_slot * kHeadDim;
+            dot = quad_sum(on ? bf16_row_dot<BITS>(krow, sub, s_qf) : 0.f);
           }
-        } else {
-          pr = on ? p.weights[bh * p.capacity + batch_begin + t] : 0.f;
-        }
-        if constexpr (MODE != kModeQK) {
-          const __nv_bfloat16* vrow = is_cur ? p.vcur + bh * kHeadDim : tv + slot * kHeadDim;
-          if (on && !skip_v) bf16_row_accumulate<BITS>(vrow, sub, pr, S.acc);
+          if (on && sub == 0) s_dot[s & 3][slot] = dot;  // the tail class writes stream 0
         }
       } else {
-        // ---- a pass inside one packed 64-token block, from shared memory
-        const uint8_t* token = my_gather + buf * G::kRows + quad * 4 * G::kToken;
-        const bool on = cur.t0 + quad < cur.run_e;
-        const int t = min(cur.t0 + quad, cur.run_e - 1);
-        // which streams hold this token (idle quads: none); `any` is the same for the whole warp
-        uint32_t mine = 0, any = 0;
-        int group23[2] = {-1, -1};
-#pragma unroll
-        for (int s = 0; s < 4; ++s) {
-          if (s < streams) {
-            const int row = s_grow[s][t];
-            const bool have = on && row >= 0;
-            if (s >= 2) group23[s - 2] = have ? row >> 6 : -1;
-            mine |= have ? 1u << s : 0u;
-            any |= __any_sync(kFull, have) ? 1u << s : 0u;
-          }
-        }
-
-        float pr = 0.f;
-        if constexpr (MODE != kModePV) {
-          // Every lane runs every stream some lane needs; a lane without the row computes on
-          // whatever its buffer holds and drops the result (unpacked codes are always finite).
-          float dot = 0.f;
-#pragma unroll
-          for (int s = 0; s < 4; ++s) {
-            if (any & (1u << s)) {
-              const Codes<BITS> kc = load_codes_shared<BITS>(token + s * G::kToken + sub * kLaneBytes);
-              bool take = mine & (1u << s);
-              // The compact rows of one block may straddle two metadata groups: tokens of the
-              // first group use the table as built, then the table moves on to the second.
-              for (int round = 0; round < 2; ++round) {
-                bool now = take;
-                if (s >= 2) {
-                  const int g = group23[s >= 2 ? s - 2 : 0];
-                  now = take && g == run_g[s >= 2 ? s - 2 : 0];
-                  if (round == 1) {
-                    const bool later = take && g > run_g[s >= 2 ? s - 2 : 0];
-                    if (!__any_sync(kFull, later)) break;
-                    __syncwarp();
-                    const int next = run_g[s >= 2 ? s - 2 : 0] + 1;
-                    const int64_t gg = group_base[s] + next;
-                    build_table(s, ldg64(L.k_scale[s] + gg * kHeadDim + 4 * lane),
-                                ldg64(L.k_min[s] + gg * kHeadDim + 4 * lane));
-                    run_g[s >= 2 ? s - 2 : 0] = next;
-                    __syncwarp();
-                    now = later;
-                  }
-                } else if (round == 1) {
-                  break;
-                }
-                __half2 mult[16];
-                const uint4* tab = reinterpret_cast<const uint4*>(&s_wtab[warp][s][sub * 32]);
-#pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                  const uint4 x = tab[v];
-                  mult[4 * v + 0] = as_half2(x.x); mult[4 * v + 1] = as_half2(x.y);
-                  mult[4 * v + 2] = as_half2(x.z); mult[4 * v + 3] = as_half2(x.w);
-                }
-                const float kd = k_dot_fast<BITS>(kc, mult) + s_kbias[warp][s];
-                dot += now ? kd : 0.f;
-              }
-            }
-          }
-          dot = quad_sum(dot);
-          if constexpr (MODE == kModeQK) {
-            if (on && sub == 0) p.logits[bh * p.capacity + batch_begin + t] = dot;
-          } else {
-            const float x = on ? dot * p.scaling_log2 : -INFINITY;
-            const float mx = across_quads_max(x);
-            if (mx > S.m) {
-              flush_pairs(hacc, S.acc);
-              state_raise(S, mx);
-            }
-            pr = on ? exp2f(x - S.m) : 0.f;
-            S.l += pr;
-          }
-        } else {
-          pr = on ? p.weights[bh * p.capacity + batch_begin + t] : 0.f;
-        }
-
         if constexpr (MODE != kModeQK) {
-          const uint32_t pick = (sub < 2) ? 0x1010u : 0x3232u;
-          const __half2 centre2 = __floats2half2_rn(float(kCentre<BITS>), float(kCentre<BITS>));
-          const __half2 p2 = __float2half2_rn(pr);
-          __half2 hb = __floats2half2_rn(0.f, 0.f);
-#pragma unroll
-          for (int s = 0; s < 4; ++s) {
-            if (any & (1u << s)) {
-              const bool have = mine & (1u << s);
-              const uint8_t* record = token + s * G::kToken + G::kKBytes;
-              const Codes<BITS> vc = load_codes_shared<BITS>(record + sub * kLaneBytes);
-              const uint2 vmeta = *reinterpret_cast<const uint2*>(record + kRowBytes);
-              const __half2 vm2 = as_half2(have ? __byte_perm(vmeta.x, 0u, pick) : 0u);
-              const __half2 vs2 = as_half2(have ? __byte_perm(vmeta.y, 0u, pick) : 0u);
-              hb = __hfma2(centre2, vs2, __hadd2(vm2, hb));
-              v_accumulate<BITS>(vc, __hmul2(p2, vs2), hacc);
-            }
+          const float pr = on ? s_prob[slot] : 0.f;
+          if (s != kTailClass) {
+            const uint32_t pick = (sub < 2) ? 0x1010u : 0x3232u;
+            const __half2 centre2 = __floats2half2_rn(float(kCentre<BITS>), float(kCentre<BITS>));
+            const __half2 p2 = __float2half2_rn(pr);
+            const Codes<BITS> vc = load_codes_shared<BITS>(stage + codes_at);
+            const uint2 vmeta = *reinterpret_cast<const uint2*>(stage + 512 + quad * 16);
+            const __half2 vm2 = as_half2(on ? __byte_perm(vmeta.x, 0u, pick) : 0u);
+            const __half2 vs2 = as_half2(on ? __byte_perm(vmeta.y, 0u, pick) : 0u);
+            const __half2 hb = __hfma2(centre2, vs2, vm2);
+            v_accumulate<BITS>(vc, __hmul2(p2, vs2), hacc);
+            S.vbias = fmaf(pr, __low2float(hb), S.vbias);
+            // at most 16 float16 terms per accumulator before widening
+            if ((++v_passes & 15) == 0) flush_pairs(hacc, S.acc);
+          } else {
+            const int ring_slot = s_crow[kTailClass][entry];
+            const __nv_bfloat16* vrow = ring_slot < 0 ? p.vcur + bh * kHeadDim : tv + ring_slot * kHeadDim;
+            if (on) bf16_row_accumulate<BITS>(vrow, sub, pr, S.acc);
           }
-          S.vbias = fmaf(pr, __low2float(hb), S.vbias);
-          // at most 4 streams x 4 passes = 16 float16 terms per accumulator before widening
-          if ((++passes & 3) == 0) flush_pairs(hacc, S.acc);
         }
-        buf ^= 1;
       }
-      cur = nxt;
+    };
+    auto step = [&](int q) {
+      cp_async_wait<kDepth - 2>();  // pass q has landed
+      __syncwarp();                 // ... for every lane, and every lane is done with pass q - 1
+      issue(q + kDepth - 1);        // into the stage of pass q - 1
+      compute(q);
+    };
+
+#pragma unroll
+    for (int q = 0; q < kDepth - 1; ++q) issue(q);
+    for (int q = 0; q < nk_mine; ++q) step(q);
+
+    if constexpr (MODE != kModePV) {
+      __syncthreads();  // every K pass of the batch has written its partial logits
+      float logit = 0.f;
+      if (live) {
+#pragma unroll
+        for (int s = 0; s < 4; ++s) logit += s < streams ? s_dot[s][tid] : 0.f;
+      }
+      if constexpr (MODE == kModeQK) {
+        if (live) p.logits[bh * p.capacity + batch_begin + tid] = logit;
+      } else {
+        if (live && idx == cur_pos && p.cur_logits) p.cur_logits[bh] = logit * p.scaling;
+        const float x = live ? logit * p.scaling_log2 : -INFINITY;
+        const float wmax = warp_max(x);
+        if (lane == 0) s_red[warp] = wmax;
+        __syncthreads();
+        float bmax = s_red[0];
+#pragma unroll
+        for (int w = 1; w < kGatherWarps; ++w) bmax = fmaxf(bmax, s_red[w]);
+        if (bmax > m_run) {
+          const float r = exp2f(m_run - bmax);  // exp2f(-inf) == 0 on the first raise
+          flush_pairs(hacc, S.acc);             // the float16 partial sums belong to the old maximum
+          v_passes = 0;
+          l_mine *= r;
+          S.vbias *= r;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) S.acc[i] *= r;
+          m_run = bmax;
+        }
+        const float pr = live ? exp2f(x - m_run) : 0.f;
+        s_prob[tid] = pr;
+        l_mine += pr;
+        __syncthreads();
+      }
     }
+
+    for (int q = nk_mine; q < n_mine; ++q) step(q);
     cp_async_wait<0>();
   }
   if constexpr (MODE == kModeQK) return;
   flush_pairs(hacc, S.acc);
+  S.m = m_run;
 
-  __syncthreads();  // every warp has left its gather buffers: they become the merge buffer
-  float (*s_merge)[kPartialStride] = reinterpret_cast<float (*)[kPartialStride]>(s_gather);
+  __syncthreads();  // every warp has left its ring: the rings become the merge buffer
+  float (*s_merge)[kPartialStride] = reinterpret_cast<float (*)[kPartialStride]>(s_ring);
   state_store<BITS>(S, lane, s_merge[warp]);
+  const float l_warp = warp_sum(l_mine);
+  if (lane == 0) s_merge[warp][129] = l_warp;
   float total, denom;
-  if (merge_and_publish<kWarps>(p, s_merge, &s_last, bh, split, nsplits, total, denom)) {
+  if (merge_and_publish<kGatherWarps>(p, s_merge, &s_last, bh, split, nsplits, total, denom)) {
     const int c = threadIdx.x;
-    if constexpr (MODE == kModeDelta) {
-      const float target = denom > 0.f ? total / denom : 0.f;
-      p.out[bh * kHeadDim + c] = p.mass[bh] * (target - p.source_out[bh * kHeadDim + c]);
-    } else {
-      p.out[bh * kHeadDim + c] = total;
+    if (c < kHeadDim) {
+      if constexpr (MODE == kModeDelta) {
+        const float target = denom > 0.f ? total / denom : 0.f;
+        p.out[bh * kHeadDim + c] = p.mass[bh] * (target - p.source_out[bh * kHeadDim + c]);
+      } else {
+        p.out[bh * kHeadDim + c] = total;
+      }
     }
   }
 }
@@ -1374,9 +1450,9 @@ unsigned dense_grid(int64_t batch_heads) {
 }
 
 int choose_slots_per_cta(int64_t batch_heads, int64_t capacity) {
-  // One wave: four CTAs of the gather kernel are resident per SM, so the grid is kept within
-  // 148 * 4 CTAs where the capacity allows it (a second, partial wave would cost a whole round).
-  const int64_t budget = 148 * 4;
+  // One wave: the grid is kept within the CTAs of the gather kernel that are resident at once
+  // where the capacity allows it (a second, partial wave would cost a whole round).
+  const int64_t budget = 148 * kGatherCtasPerSm;
   int64_t slots = 32;
   while ((batch_heads * ((capacity + slots - 1) / slots) > budget || (capacity + slots - 1) / slots > kMaxSplits) &&
          slots < capacity)
@@ -1527,11 +1603,11 @@ namespace {
 
 template <int BITS, int MODE>
 void launch_selected_bits(const dim3 grid, const ReaderParams& p, cudaStream_t s) {
-  constexpr int kSmem = GatherSmem<BITS, MODE>::kWarp * kWarps;
+  constexpr int kSmem = kGatherWarps * kDepth * kPassBytes;
   static const cudaError_t attr = cudaFuncSetAttribute(
       selected_reader_kernel<BITS, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
   (void)attr;
-  selected_reader_kernel<BITS, MODE><<<grid, kThreads, kSmem, s>>>(p);
+  selected_reader_kernel<BITS, MODE><<<grid, kGatherThreads, kSmem, s>>>(p);
 }
 
 template <int MODE>
