@@ -988,12 +988,6 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// Pass descriptor (16 bits): stream or class in bits 12..14, first list entry in bits 4..11, rows
-// (1..8) in bits 0..3; 0 = no pass.  K passes of a batch sit at s_desc[0..), V passes at
-// s_desc[kVDescBase..).
-constexpr int kVDescBase = 4 * kSlotBatch + kSlotBatch / 8;
-constexpr int kDescCount = kVDescBase + 5 * (kSlotBatch / 8);
-
 // The K table of one metadata group, this lane's four channels 4*lane .. 4*lane+3: w_c = q_c *
 // scale_c as float16 in the pair order of unpack_centred (the products are exact in float32, so
 // rounding them once in float16 arithmetic gives the same table), stored with one 8-byte write
@@ -1014,10 +1008,16 @@ __device__ __forceinline__ void table_store(__half* table, int lane, __half2 q01
   if constexpr (BITS == 4) {
     at = 4 * lane;
   } else {
-    at = 16 * (lane >> 2) + 8 * (lane & 1) + 4 * ((lane >> 1) & 1);
+    at = 16 * (lane >> 2) + 8 * ((lane >> 1) & 1) + 4 * (lane & 1);
   }
   *reinterpret_cast<uint2*>(table + at) = out;
 }
+
+// The rows to read form one list per batch: the entries of stream 0 in slot order, then those of
+// stream 1, 2 and 3.  An entry is (stream << 30) | row, so a stream holds fewer than 2^30 rows
+// over all (b,h) pairs.  A V pass is any eight consecutive entries; a K pass is described by 16
+// bits: first entry in bits 0..9, rows - 1 in bits 10..12.
+constexpr int kMaxEntries = 4 * kSlotBatch;
 
 template <int BITS, int MODE>
 __global__ void __launch_bounds__(kGatherThreads, kGatherCtasPerSm)
@@ -1029,16 +1029,19 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   extern __shared__ __align__(128) uint8_t s_ring[];  // [warp][stage][kPassBytes]
   __shared__ __align__(16) float s_qf[kHeadDim];
   __shared__ __align__(16) __half s_wtab[kGatherWarps][kHeadDim];  // the current K pass's table
-  __shared__ int s_crow[5][kSlotBatch];        // per stream: the rows to read, in slot order (tail class: ring slot, -1 = current token)
-  __shared__ uint8_t s_list[5][kSlotBatch];    // ... and the slots they belong to
-  __shared__ float s_dot[4][kSlotBatch];       // partial logit of the slot from every stream (tail rows: stream 0)
-  __shared__ float s_prob[kSlotBatch];         // probability (or the caller's weight) of the slot
-  __shared__ uint16_t s_desc[kDescCount];
+  __shared__ uint32_t s_entry[kMaxEntries];
+  __shared__ float s_eval[kMaxEntries];     // per entry: its partial logit, then its probability (or weight)
+  __shared__ uint16_t s_kdesc[kMaxEntries];
+  __shared__ int s_kgroup[kMaxEntries];     // per K pass: its metadata group, counted over all (b,h)
+  __shared__ int s_tail[kSlotBatch];        // tail class: ring slot of the entry, -1 = the current token
+  __shared__ float s_tval[kSlotBatch];      // ... and its logit, then probability
   __shared__ int s_wcount[5][kGatherWarps], s_woff[5][kGatherWarps];
   __shared__ int s_whead[4][kGatherWarps], s_wfirst[4][kGatherWarps];
-  __shared__ int s_count[5];
+  __shared__ int s_count[5], s_ebase[5];    // entries per class; first entry of every stream, then the total
   __shared__ int s_nk_packed;
-  __shared__ int s_base[8];                    // row_base[0..3], group_base[0..3] of this (b,h)
+  __shared__ int s_rbase[4], s_gbase[4];    // first row / first K metadata group of this (b,h) in every stream
+  __shared__ const uint8_t* s_kptr[4];
+  __shared__ const uint8_t* s_vptr[4];
   __shared__ float s_red[kGatherWarps];
   __shared__ int s_last;
 
@@ -1074,12 +1077,12 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
     q01 = __floats2half2_rn(q4.x, q4.y);
     q23 = __floats2half2_rn(q4.z, q4.w);
   }
-  // rows / K metadata groups of this (b,h) start here in every stream (the counts fit 31 bits)
-  if (tid < 8) {
-    const int s = tid & 3;
-    int v = 0;
-    if (s < streams) v = static_cast<int>(tid < 4 ? L.row_base[s][bh] : L.group_base[s][bh]);
-    s_base[tid] = v;
+  if (tid < 4) {
+    const bool have = tid < streams;
+    s_rbase[tid] = have ? static_cast<int>(L.row_base[tid][bh]) : 0;
+    s_gbase[tid] = have ? static_cast<int>(L.group_base[tid][bh]) : 0;
+    s_kptr[tid] = have ? L.k_codes[tid] : nullptr;
+    s_vptr[tid] = have ? L.v_rows[tid] : nullptr;
   }
 
   OnlineState S;
@@ -1097,15 +1100,16 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
 
   for (int batch_begin = slot_begin; batch_begin < slot_end; batch_begin += kSlotBatch) {
     const int batch_n = min(kSlotBatch, slot_end - batch_begin);
-    __syncthreads();  // the previous round's lists and rings are no longer read (and s_base is written)
+    __syncthreads();  // the previous round's lists and rings are no longer read (and the bases are written)
     // ---- stage this round's slots: index, the row in every stream, class
     int idx = -1;
     bool live = false;    // the slot has something to read
     uint32_t member = 0;  // bit c: the slot is on list c
     int rows[5] = {-1, -1, -1, -1, -1};
+    float weight = 0.f;
     if (tid < batch_n) {
       const int j = batch_begin + tid;
-      if constexpr (MODE == kModePV) s_prob[tid] = p.weights[bh * p.capacity + j];
+      if constexpr (MODE == kModePV) weight = p.weights[bh * p.capacity + j];
       if (!valid_row || valid_row[j]) idx = idx_row[j];
       if (idx >= 0 && idx < quant) {
         live = true;
@@ -1129,55 +1133,74 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
       }
     }
 #pragma unroll
-    for (int s = 0; s < 4; ++s) {
-      s_dot[s][tid] = 0.f;
-      member |= rows[s] >= 0 ? 1u << s : 0u;
-    }
-    // ---- per class: the list of its slots and rows, in slot order
-    int rank_in_warp[5];
+    for (int s = 0; s < 4; ++s) member |= rows[s] >= 0 ? 1u << s : 0u;
+    // ---- the entry lists: every class in slot order, streams 0..3 back to back
+    int at[5];  // my entry in every class I am a member of
 #pragma unroll
     for (int c = 0; c < 5; ++c) {
       const uint32_t mask = __ballot_sync(kFull, (member >> c) & 1u);
-      rank_in_warp[c] = __popc(mask & lanes_below);
+      at[c] = __popc(mask & lanes_below);
       if (lane == 0) s_wcount[c][warp] = __popc(mask);
     }
     __syncthreads();
-    if (tid < 5 * kGatherWarps) {
-      const int c = tid >> 3, w = tid & 7;
+    if (warp == 0) {  // running entry counts over (stream, warp)
+      const int mine = s_wcount[lane >> 3][lane & 7];
+      int incl = mine;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int up = __shfl_up_sync(kFull, incl, d);
+        if (lane >= d) incl += up;
+      }
+      const int stream_first = __shfl_sync(kFull, incl - mine, lane & ~7);
+      s_woff[lane >> 3][lane & 7] = incl - mine;
+      if ((lane & 7) == 0) s_ebase[lane >> 3] = stream_first;
+      if ((lane & 7) == 7) s_count[lane >> 3] = incl - stream_first;
+      if (lane == 31) s_ebase[4] = incl;
+    } else if (warp == 1 && lane < kGatherWarps) {
       int off = 0;
-      for (int k = 0; k < w; ++k) off += s_wcount[c][k];
-      s_woff[c][w] = off;
-      if (w == kGatherWarps - 1) s_count[c] = off + s_wcount[c][w];
+      for (int k = 0; k < lane; ++k) off += s_wcount[kTailClass][k];
+      s_woff[kTailClass][lane] = off;
+      if (lane == kGatherWarps - 1) s_count[kTailClass] = off + s_wcount[kTailClass][lane];
     }
     __syncthreads();
 #pragma unroll
     for (int c = 0; c < 5; ++c) {
+      at[c] += s_woff[c][warp];
       if ((member >> c) & 1u) {
-        const int at = s_woff[c][warp] + rank_in_warp[c];
-        s_list[c][at] = static_cast<uint8_t>(tid);
-        s_crow[c][at] = c < 4 ? s_base[c] + rows[c] : rows[4];
+        if (c < 4) {
+          s_entry[at[c]] = (static_cast<uint32_t>(c) << 30) | static_cast<uint32_t>(s_rbase[c] + rows[c]);
+          s_eval[at[c]] = weight;  // the weighted-PV reader's probabilities are the caller's
+        } else {
+          s_tail[at[c]] = rows[4];
+          s_tval[at[c]] = weight;
+        }
       }
     }
     __syncthreads();
-    const int tail_passes = (s_count[kTailClass] + 7) >> 3;
-    // ---- K passes of streams 0..3: list entry i opens a pass where the metadata group changes
-    // and every eight entries after that
+    const int n_entries = s_ebase[4];
+    const int n_tail = s_count[kTailClass];
+    // ---- K passes: entry i of a stream opens a pass where the metadata group changes and every
+    // eight entries after that
     if constexpr (MODE != kModePV) {
       uint32_t run_heads[4];
       bool entry_on[4], run_head[4];
+      int group_of[4];
 #pragma unroll
       for (int s = 0; s < 4; ++s) {
         entry_on[s] = s < streams && tid < s_count[s];
-        const int base = s_base[s];
-        const int group = entry_on[s] ? (s_crow[s][tid] - base) >> 6 : -1;
-        const int before = entry_on[s] && tid > 0 ? (s_crow[s][tid - 1] - base) >> 6 : -1;
-        run_head[s] = entry_on[s] && (tid == 0 || group != before);
+        const int first = s_ebase[s];
+        const int base = s_rbase[s];
+        group_of[s] = entry_on[s] ? (static_cast<int>(s_entry[first + tid] & 0x3fffffffu) - base) >> 6 : -1;
+        const int before =
+            entry_on[s] && tid > 0 ? (static_cast<int>(s_entry[first + tid - 1] & 0x3fffffffu) - base) >> 6 : -1;
+        run_head[s] = entry_on[s] && (tid == 0 || group_of[s] != before);
         run_heads[s] = __ballot_sync(kFull, run_head[s]);
         if (lane == 0) s_whead[s][warp] = run_heads[s] ? warp * 32 + 31 - __clz(run_heads[s]) : -1;
       }
       __syncthreads();
       bool pass_head[4];
       uint32_t pass_heads[4];
+      int rank[4];
 #pragma unroll
       for (int s = 0; s < 4; ++s) {
         int run_start = 0;
@@ -1195,7 +1218,7 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
         }
         pass_head[s] = entry_on[s] && (run_head[s] || ((tid - run_start) & 7) == 0);
         pass_heads[s] = __ballot_sync(kFull, pass_head[s]);
-        rank_in_warp[s] = __popc(pass_heads[s] & lanes_below);
+        rank[s] = __popc(pass_heads[s] & lanes_below);
         if (lane == 0) {
           s_wcount[s][warp] = __popc(pass_heads[s]);
           s_wfirst[s][warp] = pass_heads[s] ? warp * 32 + __ffs(pass_heads[s]) - 1 : -1;
@@ -1230,155 +1253,105 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
               }
             }
           }
-          s_desc[s_woff[s][warp] + rank_in_warp[s]] = static_cast<uint16_t>((s << 12) | (tid << 4) | (next - tid));
+          const int k = s_woff[s][warp] + rank[s];
+          s_kdesc[k] = static_cast<uint16_t>((s_ebase[s] + tid) | ((next - tid - 1) << 10));
+          s_kgroup[k] = s_gbase[s] + group_of[s];
         }
       }
-      if (tid < tail_passes) {
-        s_desc[s_nk_packed + tid] =
-            static_cast<uint16_t>((kTailClass << 12) | ((8 * tid) << 4) | min(8, s_count[kTailClass] - 8 * tid));
-      }
+      __syncthreads();
     }
-    int nv_all = 0;
-    if constexpr (MODE != kModeQK) {
-      int mine_c = -1, mine_k = 0;
-#pragma unroll
-      for (int c = 0; c < 5; ++c) {
-        const int n = (s_count[c] + 7) >> 3;
-        if (tid >= nv_all && tid < nv_all + n) {
-          mine_c = c;
-          mine_k = tid - nv_all;
-        }
-        nv_all += n;
-      }
-      if (mine_c >= 0) {
-        s_desc[kVDescBase + tid] = static_cast<uint16_t>((mine_c << 12) | ((8 * mine_k) << 4) |
-                                                         min(8, s_count[mine_c] - 8 * mine_k));
-      }
-    }
-    __syncthreads();
 
     // ---- this warp's passes: K passes warp, warp + 8, ..., then V passes warp, warp + 8, ...
-    const int nk_all = MODE == kModePV ? 0 : s_nk_packed + tail_passes;
+    const int nk_all = MODE == kModePV ? 0 : s_nk_packed;
+    const int nv_all = MODE == kModeQK ? 0 : (n_entries + 7) >> 3;
     const int nk_mine = nk_all > warp ? (nk_all - warp + kGatherWarps - 1) / kGatherWarps : 0;
     const int nv_mine = nv_all > warp ? (nv_all - warp + kGatherWarps - 1) / kGatherWarps : 0;
     const int n_mine = nk_mine + nv_mine;
-    // bit 15 is set for a V pass; 0 = past the end
-    auto desc_of = [&](int q) -> uint32_t {
-      if (q >= n_mine) return 0u;
-      const bool is_v = q >= nk_mine;
-      const int at = is_v ? kVDescBase - kGatherWarps * nk_mine + warp + kGatherWarps * q : warp + kGatherWarps * q;
-      return s_desc[at] | (is_v ? 0x8000u : 0u);
-    };
-    // Copies of pass q into its stage (one commit group, empty for tail passes and past the end):
-    // codes of row i at i * kRowBytes; K metadata (scale[128], min[128]) or the V records' 16
-    // metadata bytes (record i at 512 + 16 i) behind them.
+    // Copies of pass q into its stage (one commit group, empty past the end): codes of row i at
+    // i * kRowBytes; behind them the K metadata group (scale[128], min[128]) or the V records' 16
+    // metadata bytes (record i at 512 + 16 i).
     auto issue = [&](int q) {
-      const uint32_t d = desc_of(q);
-      const int s = (d >> 12) & 7;
-      if (d != 0u && s != kTailClass) {
-        const uint32_t stage = my_ring_u32 + (q % kDepth) * kPassBytes;
-        const int start = (d >> 4) & 0xff;
-        const bool is_v = d & 0x8000u;
-        const int first_row = s_crow[s][start];
-        if (quad < static_cast<int>(d & 0xfu)) {
-          const int row = s_crow[s][start + quad];
-          const uint8_t* src = is_v ? L.v_rows[s] + static_cast<int64_t>(row) * kRecord
-                                    : L.k_codes[s] + static_cast<int64_t>(row) * kRowBytes;
-          cp_async<kLaneBytes>(stage + codes_at, src + sub * kLaneBytes);
-          if (is_v && sub == 0) cp_async<16>(stage + 512 + quad * 16, src + kRowBytes);
-        }
-        if (!is_v) {
-          const int64_t g = s_base[4 + s] + ((first_row - s_base[s]) >> 6);
-          const __half* meta = (lane < 16 ? L.k_scale[s] : L.k_min[s]) + g * kHeadDim + (lane & 15) * 8;
+      const uint32_t stage = my_ring_u32 + (q & (kDepth - 1)) * kPassBytes;
+      if (q < nk_mine) {
+        if constexpr (MODE != kModePV) {
+          const int k = warp + kGatherWarps * q;
+          const uint32_t d = s_kdesc[k];
+          const int s = s_entry[d & 1023u] >> 30;
+          if (quad <= static_cast<int>(d >> 10)) {
+            const uint32_t row = s_entry[(d & 1023u) + quad] & 0x3fffffffu;
+            cp_async<kLaneBytes>(stage + codes_at, s_kptr[s] + static_cast<uint64_t>(row) * kRowBytes + sub * kLaneBytes);
+          }
+          const __half* meta = (lane < 16 ? L.k_scale[s] : L.k_min[s]) +
+                               static_cast<int64_t>(s_kgroup[k]) * kHeadDim + (lane & 15) * 8;
           cp_async<16>(stage + 512 + lane * 16, meta);
+        }
+      } else if (q < n_mine) {
+        if constexpr (MODE != kModeQK) {
+          const int i = 8 * (warp + kGatherWarps * (q - nk_mine)) + quad;
+          if (i < n_entries) {
+            const uint32_t e = s_entry[i];
+            const uint8_t* record = s_vptr[e >> 30] + static_cast<uint64_t>(e & 0x3fffffffu) * kRecord;
+            cp_async<kLaneBytes>(stage + codes_at, record + sub * kLaneBytes);
+            if (sub == 0) cp_async<16>(stage + 512 + quad * 16, record + kRowBytes);
+          }
         }
       }
       cp_async_commit();
     };
-    auto compute = [&](int q) {
-      const uint32_t d = desc_of(q);
-      const int s = (d >> 12) & 7;
-      const int start = (d >> 4) & 0xff;
-      const bool on = quad < static_cast<int>(d & 0xfu);
-      const int entry = start + (on ? quad : 0);
-      const int slot = s_list[s][entry];
-      const uint8_t* stage = my_ring + (q % kDepth) * kPassBytes;
-      if (!(d & 0x8000u)) {
-        if constexpr (MODE != kModePV) {
-          float dot;
-          if (s != kTailClass) {
-            // the group's table and bias = sum_c q_c * (min_c + centre * scale_c)
-            const uint2 sc = *reinterpret_cast<const uint2*>(stage + 512 + lane * 8);
-            const uint2 mn = *reinterpret_cast<const uint2*>(stage + 512 + 256 + lane * 8);
-            table_store<BITS>(s_wtab[warp], lane, q01, q23, sc);
-            const float2 sc01 = __half22float2(as_half2(sc.x)), sc23 = __half22float2(as_half2(sc.y));
-            const float2 mn01 = __half22float2(as_half2(mn.x)), mn23 = __half22float2(as_half2(mn.y));
-            const float kcn = float(kCentre<BITS>);
-            float bias = q4.x * fmaf(kcn, sc01.x, mn01.x);
-            bias = fmaf(q4.y, fmaf(kcn, sc01.y, mn01.y), bias);
-            bias = fmaf(q4.z, fmaf(kcn, sc23.x, mn23.x), bias);
-            bias = fmaf(q4.w, fmaf(kcn, sc23.y, mn23.y), bias);
-            const Codes<BITS> kc = load_codes_shared<BITS>(stage + codes_at);
-            bias = warp_sum(bias);
-            __syncwarp();
-            __half2 mult[16];
-            const uint4* tab4 = reinterpret_cast<const uint4*>(&s_wtab[warp][sub * 32]);
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              const uint4 x = tab4[v];
-              mult[4 * v + 0] = as_half2(x.x); mult[4 * v + 1] = as_half2(x.y);
-              mult[4 * v + 2] = as_half2(x.z); mult[4 * v + 3] = as_half2(x.w);
-            }
-            dot = quad_sum(k_dot_fast<BITS>(kc, mult)) + bias;
-          } else {
-            const int ring_slot = s_crow[kTailClass][entry];
-            const __nv_bfloat16* krow = ring_slot < 0 ? p.kcur + bh * kHeadDim : tk + ring_slot * kHeadDim;
-            dot = quad_sum(on ? bf16_row_dot<BITS>(krow, sub, s_qf) : 0.f);
-          }
-          if (on && sub == 0) s_dot[s & 3][slot] = dot;  // the tail class writes stream 0
-        }
-      } else {
-        if constexpr (MODE != kModeQK) {
-          const float pr = on ? s_prob[slot] : 0.f;
-          if (s != kTailClass) {
-            const uint32_t pick = (sub < 2) ? 0x1010u : 0x3232u;
-            const __half2 centre2 = __floats2half2_rn(float(kCentre<BITS>), float(kCentre<BITS>));
-            const __half2 p2 = __float2half2_rn(pr);
-            const Codes<BITS> vc = load_codes_shared<BITS>(stage + codes_at);
-            const uint2 vmeta = *reinterpret_cast<const uint2*>(stage + 512 + quad * 16);
-            const __half2 vm2 = as_half2(on ? __byte_perm(vmeta.x, 0u, pick) : 0u);
-            const __half2 vs2 = as_half2(on ? __byte_perm(vmeta.y, 0u, pick) : 0u);
-            const __half2 hb = __hfma2(centre2, vs2, vm2);
-            v_accumulate<BITS>(vc, __hmul2(p2, vs2), hacc);
-            S.vbias = fmaf(pr, __low2float(hb), S.vbias);
-            // at most 16 float16 terms per accumulator before widening
-            if ((++v_passes & 15) == 0) flush_pairs(hacc, S.acc);
-          } else {
-            const int ring_slot = s_crow[kTailClass][entry];
-            const __nv_bfloat16* vrow = ring_slot < 0 ? p.vcur + bh * kHeadDim : tv + ring_slot * kHeadDim;
-            if (on) bf16_row_accumulate<BITS>(vrow, sub, pr, S.acc);
-          }
-        }
-      }
-    };
-    auto step = [&](int q) {
+    auto advance = [&](int q) {
       cp_async_wait<kDepth - 2>();  // pass q has landed
       __syncwarp();                 // ... for every lane, and every lane is done with pass q - 1
       issue(q + kDepth - 1);        // into the stage of pass q - 1
-      compute(q);
     };
 
 #pragma unroll
     for (int q = 0; q < kDepth - 1; ++q) issue(q);
-    for (int q = 0; q < nk_mine; ++q) step(q);
 
     if constexpr (MODE != kModePV) {
+      for (int q = 0; q < nk_mine; ++q) {
+        advance(q);
+        const uint8_t* stage = my_ring + (q & (kDepth - 1)) * kPassBytes;
+        const uint32_t d = s_kdesc[warp + kGatherWarps * q];
+        // the group's table and bias = sum_c q_c * (min_c + centre * scale_c)
+        const uint2 sc = *reinterpret_cast<const uint2*>(stage + 512 + lane * 8);
+        const uint2 mn = *reinterpret_cast<const uint2*>(stage + 512 + 256 + lane * 8);
+        table_store<BITS>(s_wtab[warp], lane, q01, q23, sc);
+        const float2 sc01 = __half22float2(as_half2(sc.x)), sc23 = __half22float2(as_half2(sc.y));
+        const float2 mn01 = __half22float2(as_half2(mn.x)), mn23 = __half22float2(as_half2(mn.y));
+        const float kcn = float(kCentre<BITS>);
+        float bias = q4.x * fmaf(kcn, sc01.x, mn01.x);
+        bias = fmaf(q4.y, fmaf(kcn, sc01.y, mn01.y), bias);
+        bias = fmaf(q4.z, fmaf(kcn, sc23.x, mn23.x), bias);
+        bias = fmaf(q4.w, fmaf(kcn, sc23.y, mn23.y), bias);
+        const Codes<BITS> kc = load_codes_shared<BITS>(stage + codes_at);
+        bias = warp_sum(bias);
+        __syncwarp();
+        __half2 mult[16];
+        const uint4* tab4 = reinterpret_cast<const uint4*>(&s_wtab[warp][sub * 32]);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const uint4 x = tab4[v];
+          mult[4 * v + 0] = as_half2(x.x); mult[4 * v + 1] = as_half2(x.y);
+          mult[4 * v + 2] = as_half2(x.z); mult[4 * v + 3] = as_half2(x.w);
+        }
+        const float dot = quad_sum(k_dot_fast<BITS>(kc, mult)) + bias;
+        if (quad <= static_cast<int>(d >> 10) && sub == 0) s_eval[(d & 1023u) + quad] = dot;
+      }
+      // tail tokens and the current token: BF16 rows, read directly
+      for (int i0 = 8 * warp; i0 < n_tail; i0 += 8 * kGatherWarps) {
+        const int i = i0 + quad;
+        const bool on = i < n_tail;
+        const int ring_slot = on ? s_tail[i] : 0;
+        const __nv_bfloat16* krow = ring_slot < 0 ? p.kcur + bh * kHeadDim : tk + ring_slot * kHeadDim;
+        const float dot = quad_sum(on ? bf16_row_dot<BITS>(krow, sub, s_qf) : 0.f);
+        if (on && sub == 0) s_tval[i] = dot;
+      }
+
       __syncthreads();  // every K pass of the batch has written its partial logits
       float logit = 0.f;
-      if (live) {
 #pragma unroll
-        for (int s = 0; s < 4; ++s) logit += s < streams ? s_dot[s][tid] : 0.f;
-      }
+      for (int s = 0; s < 4; ++s) logit += (member >> s) & 1u ? s_eval[at[s]] : 0.f;
+      if ((member >> kTailClass) & 1u) logit = s_tval[at[kTailClass]];
       if constexpr (MODE == kModeQK) {
         if (live) p.logits[bh * p.capacity + batch_begin + tid] = logit;
       } else {
@@ -1401,13 +1374,45 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
           m_run = bmax;
         }
         const float pr = live ? exp2f(x - m_run) : 0.f;
-        s_prob[tid] = pr;
         l_mine += pr;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          if ((member >> s) & 1u) s_eval[at[s]] = pr;
+        }
+        if ((member >> kTailClass) & 1u) s_tval[at[kTailClass]] = pr;
         __syncthreads();
       }
     }
 
-    for (int q = nk_mine; q < n_mine; ++q) step(q);
+    if constexpr (MODE != kModeQK) {
+      const uint32_t pick = (sub < 2) ? 0x1010u : 0x3232u;
+      const __half2 centre2 = __floats2half2_rn(float(kCentre<BITS>), float(kCentre<BITS>));
+      for (int q = nk_mine; q < n_mine; ++q) {
+        advance(q);
+        const uint8_t* stage = my_ring + (q & (kDepth - 1)) * kPassBytes;
+        const int i = 8 * (warp + kGatherWarps * (q - nk_mine)) + quad;
+        const bool on = i < n_entries;
+        const float pr = on ? s_eval[i] : 0.f;
+        const __half2 p2 = __float2half2_rn(pr);
+        const Codes<BITS> vc = load_codes_shared<BITS>(stage + codes_at);
+        const uint2 vmeta = *reinterpret_cast<const uint2*>(stage + 512 + quad * 16);
+        const __half2 vm2 = as_half2(on ? __byte_perm(vmeta.x, 0u, pick) : 0u);
+        const __half2 vs2 = as_half2(on ? __byte_perm(vmeta.y, 0u, pick) : 0u);
+        const __half2 hb = __hfma2(centre2, vs2, vm2);
+        v_accumulate<BITS>(vc, __hmul2(p2, vs2), hacc);
+        S.vbias = fmaf(pr, __low2float(hb), S.vbias);
+        // at most 16 float16 terms per accumulator before widening
+        if ((++v_passes & 15) == 0) flush_pairs(hacc, S.acc);
+      }
+      for (int i0 = 8 * warp; i0 < n_tail; i0 += 8 * kGatherWarps) {
+        const int i = i0 + quad;
+        if (i < n_tail) {
+          const int ring_slot = s_tail[i];
+          const __nv_bfloat16* vrow = ring_slot < 0 ? p.vcur + bh * kHeadDim : tv + ring_slot * kHeadDim;
+          bf16_row_accumulate<BITS>(vrow, sub, s_tval[i], S.acc);
+        }
+      }
+    }
     cp_async_wait<0>();
   }
   if constexpr (MODE == kModeQK) return;
