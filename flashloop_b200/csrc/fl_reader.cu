@@ -1098,8 +1098,11 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   for (int i = 0; i < 16; ++i) hacc[i] = __floats2half2_rn(0.f, 0.f);
   int v_passes = 0;
 
-  for (int batch_begin = slot_begin; batch_begin < slot_end; batch_begin += kSlotBatch) {
-    const int batch_n = min(kSlotBatch, slot_end - batch_begin);
+  // equal batches: 410 slots are staged as 205 + 205, not 256 + 154
+  const int n_batches = (slot_end - slot_begin + kSlotBatch - 1) / kSlotBatch;
+  const int batch_size = n_batches > 0 ? (slot_end - slot_begin + n_batches - 1) / n_batches : kSlotBatch;
+  for (int batch_begin = slot_begin; batch_begin < slot_end; batch_begin += batch_size) {
+    const int batch_n = min(batch_size, slot_end - batch_begin);
     __syncthreads();  // the previous round's lists and rings are no longer read (and the bases are written)
     // ---- stage this round's slots: index, the row in every stream, class
     int idx = -1;
