@@ -35,9 +35,9 @@ KEY_FRACTION = 0.10
 SCALING = HEAD_DIM ** -0.5
 METRIC = "decode tok/s (Ouro-1.4B-shape R4)"
 # DRAM bytes per token and stream of the dense reader, from one ncu capture of a smaller case
-# (dram__bytes_read.sum + dram__bytes_write.sum = 165.7 MB for 64 (b,h) x 8128 tokens x 2 streams);
+# (dram__bytes_read.sum + dram__bytes_write.sum = 165.9 MB for 64 (b,h) x 8128 tokens x 2 streams);
 # every packed byte is read once, so traffic grows in proportion to the tokens a launch covers.
-DENSE_TRAFFIC_PER_TOKEN_STREAM = {4: 165.7e6 / (64 * 8128 * 2)}
+DENSE_TRAFFIC_PER_TOKEN_STREAM = {4: 165.9e6 / (64 * 8128 * 2)}
 
 
 def parse_args():
