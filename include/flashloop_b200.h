@@ -196,7 +196,9 @@ int fl_dense_source_attention_static(const fl_layer* layer, int32_t loop, const 
  * tail rows, or the current token at index quant+tail) compute the subset softmax target and
  * return global_mass * (target - source_output).  indices int32 / valid uint8 [bh][capacity];
  * source_output float32 [bh][128]; global_mass float32 [bh]; output float32 [bh][128];
- * current_logits (nullable) float32 [bh] receives the scaled logit of the current token. */
+ * current_logits (nullable) float32 [bh] receives the scaled logit of the current token.
+ * The selected readers (this entry, fl_selected_pv, fl_selected_qk) address a row by 30 bits:
+ * a stream may hold at most 2^30 - 1 rows over all (b,h) pairs. */
 int fl_sparse_attention_delta(const fl_layer* layer, int32_t loop, const void* query,
                               const void* current_key, const void* current_value,
                               const int32_t* indices, const uint8_t* valid, int64_t capacity,
