@@ -552,6 +552,73 @@ def test_full_size_properties(fl):
     assert layer.reader_status() == 0 and layer2.reader_status() == 0
 
 
+def test_sparse_equals_dense_with_retention_and_any_slot_order(fl):
+    """Compact streams at a size where one gather CTA stages several batches: with every key
+    selected the sparse reader must reproduce the dense reader of loops 3 and 4 (25 % / 10 % of the
+    tokens hold a row in streams 2 / 3), and the order of the slots must not matter."""
+
+    from flashloop_b200.cache import CrossLoopKVLayer
+    from flashloop_b200.synthetic import make_loop_kv
+
+    batch, heads, tokens = 4, 16, 4096
+    keys = [[] for _ in range(4)]
+    values = [[] for _ in range(4)]
+    for b in range(batch):
+        k, v = make_loop_kv(heads, tokens, seed=40 + b, device="cuda")
+        for r in range(4):
+            keys[r].append(k[r])
+            values[r].append(v[r])
+    keys = [torch.cat(k) for k in keys]
+    values = [torch.cat(v) for v in values]
+    g = torch.Generator(device="cuda").manual_seed(5)
+    m3 = torch.rand(batch, tokens, generator=g, device="cuda") < 0.25
+    m4 = m3 & (torch.rand(batch, tokens, generator=g, device="cuda") < 0.4)
+    layer = CrossLoopKVLayer.from_prefill(keys, values, mask_loop3=m3, mask_loop4=m4)
+    q = torch.randn(batch, heads, 1, 128, generator=g, device="cuda").to(torch.bfloat16)
+    ck = torch.randn(batch, heads, 1, 128, generator=g, device="cuda").to(torch.bfloat16)
+    cv = torch.randn(batch, heads, 1, 128, generator=g, device="cuda").to(torch.bfloat16)
+    _, logits = layer.dense_source_attention(1, query=q, current_key=ck, current_value=cv, scaling=SCALING,
+                                             return_logits=True)
+    full = layer.select_decode_keys(logits, fraction=1.0)
+    some = layer.select_decode_keys(logits, fraction=0.10)
+    zero = torch.zeros(batch, heads, 1, 128, device="cuda")
+    one = torch.ones(batch, heads, 1, 1, device="cuda")
+    for loop in (2, 3):
+        dense, _ = layer.dense_source_attention(loop, query=q, current_key=ck, current_value=cv, scaling=SCALING,
+                                                return_logits=False)
+        sparse = layer.cached_mass_sparse_attention_delta(loop, query=q, current_key=ck, current_value=cv,
+                                                          indices=full.indices, valid=full.valid,
+                                                          source_selected_output=zero, global_mass=one,
+                                                          scaling=SCALING)
+        assert float((dense - sparse).abs().max()) < 5e-3, (loop, float((dense - sparse).abs().max()))
+        # a permutation of the slots (padding slots included) gives the same sums
+        for sel in (full, some):
+            perm = torch.randperm(sel.indices.shape[-1], generator=g, device="cuda")
+            base = layer.cached_mass_sparse_attention_delta(loop, query=q, current_key=ck, current_value=cv,
+                                                            indices=sel.indices, valid=sel.valid,
+                                                            source_selected_output=zero, global_mass=one,
+                                                            scaling=SCALING)
+            mixed = layer.cached_mass_sparse_attention_delta(loop, query=q, current_key=ck, current_value=cv,
+                                                             indices=sel.indices[..., perm].contiguous(),
+                                                             valid=sel.valid[..., perm].contiguous(),
+                                                             source_selected_output=zero, global_mass=one,
+                                                             scaling=SCALING)
+            assert float((base - mixed).abs().max()) < 2e-3, (loop, float((base - mixed).abs().max()))
+    perm = torch.randperm(some.indices.shape[-1], generator=g, device="cuda")
+    for loop in (1, 3):
+        base = layer.pv(loop, some.selected_weights, some.indices, current_value=cv, valid=some.valid,
+                        validate_indices=False)
+        mixed = layer.pv(loop, some.selected_weights[..., perm].contiguous(), some.indices[..., perm].contiguous(),
+                         current_value=cv, valid=some.valid[..., perm].contiguous(), validate_indices=False)
+        assert float((base - mixed).abs().max()) < 2e-3, (loop, float((base - mixed).abs().max()))
+        qk = layer.qk(loop, q, some.indices, validate_indices=False, current_key=ck)
+        qk_mixed = layer.qk(loop, q, some.indices[..., perm].contiguous(), validate_indices=False, current_key=ck)
+        # unselected padding slots carry index 0 with valid unknown to qk: compare the valid ones
+        keep = some.valid[:, :, None, :]
+        assert float(((qk[..., perm] - qk_mixed) * keep[..., perm]).abs().max()) < 2e-2
+    assert layer.reader_status() == 0
+
+
 def layer_decode(layer, s, kind, tokens):
     """float32 dequantisation of stream ``s`` of every sequence with torch ops."""
     from flashloop_b200.packing import Packed4Bit
