@@ -1,10 +1,11 @@
 // Decode-attention readers over the packed anchor + delta streams (row layout).
 //
 //   dense_reader_kernel     one launch: QK^T over streams 0..loop + BF16 tail + current token,
-//                           online softmax, PV, split over token chunks, partials merged by the
-//                           last-arriving CTA of each (b,h) (an atomic ticket, no waiting).
-//   selected_reader_kernel  the same over a gathered list of selected logical indices:
-//                           cached-mass sparse delta, weighted PV, or plain QK.
+//                           online softmax, PV; persistent CTAs that each own a contiguous,
+//                           equally large range of 64-token blocks over all (b,h); partials of a
+//                           (b,h) merged by its last-arriving CTA (an atomic ticket, no waiting).
+//   selected_reader_kernel  the same over a gathered list of selected logical indices, stream by
+//                           stream: cached-mass sparse delta, weighted PV, or plain QK.
 //
 // Work decomposition: a warp handles eight tokens per step, one per lane quad; lane `sub` of a
 // quad owns channels 32*sub .. 32*sub+31 of the token's K row and V row, i.e. one 16-byte
@@ -336,14 +337,14 @@ __device__ __forceinline__ void bf16_row_accumulate(const __nv_bfloat16* row, in
 
 // ------------------------------------------------------------------------------ dense reader
 //
-// Eight warps per CTA; each warp owns whole 64-token blocks of the chunk and runs its own
-// two-stage shared-memory ring.  A "unit" is one (block, stream, K|V) piece: for K the 64 packed
+// Eight warps per CTA; each warp owns whole 64-token blocks of the CTA's work items and runs its
+// own two-stage shared-memory ring.  A "unit" is one (block, stream, K|V) piece: for K the 64 packed
 // rows (4 KiB at 4 bits) plus the scale/min rows of the one or two 64-row groups they live in,
 // for V the 64 records (codes and metadata together, one copy).  Lane 0 of the warp arms the stage's
 // mbarrier with the byte count and issues the TMA bulk copies (cp.async.bulk, global ->
 // shared); the warp then waits on the barrier's phase, computes from shared memory, and
 // re-issues the unit two places ahead into the stage it has just drained.  No CTA-wide
-// synchronisation happens until the final merge, and waits are bounded: a wait that runs out
+// synchronisation happens until the merge that closes a work item, and waits are bounded: a wait that runs out
 // raises the status word in the workspace and the kernel runs to its end.
 
 constexpr int kDenseWarps = 8;
