@@ -513,9 +513,18 @@ __device__ __forceinline__ void describe_next(const ReaderParams& p, const int* 
   d->first_cta = static_cast<int>(first_owner);
   d->rot = c->blocks_done % kDenseWarps;
   c->blocks_done += d->blk_end - d->blk_begin;
-  for (int s = 0; s <= p.loop; ++s) {
-    d->row_base[s] = L.row_base[s][bh];
-    d->group_base[s] = L.group_base[s][bh];
+  // all loads first, then the stores: one memory latency instead of one per stream
+  int64_t rows_at[4], groups_at[4];
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    const bool on = s <= p.loop;
+    rows_at[s] = on ? L.row_base[s][bh] : 0;
+    groups_at[s] = on ? L.group_base[s][bh] : 0;
+  }
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    d->row_base[s] = rows_at[s];
+    d->group_base[s] = groups_at[s];
   }
   d->id = c->count++;
   c->at = seg_end;
@@ -575,17 +584,21 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   // cursor kept in shared memory (registers are allocated for every thread)
   for (int bb = tid; bb < L.batch && bb < kEachCached; bb += kDenseThreads) s_each[bb] = units_per_head(L, bb);
   __syncthreads();
-  if (tid == kHeadDim) {
+  {
+    // Every thread finds the CTA's range and the head it starts in (shared-memory reads only), so
+    // that the first query is fetched while one thread describes the first two items.
     const int64_t all_units = total_units(L, s_each);
-    s_all_units = all_units;
-    cursor_start(L, s_each, all_units * blockIdx.x / gridDim.x, all_units * (blockIdx.x + 1) / gridDim.x,
-                 &s_cursor);
-    describe_next(p, s_each, all_units, &s_cursor, &s_item[0]);
-    describe_next(p, s_each, all_units, &s_cursor, &s_item[1]);
-  }
-  __syncthreads();
-  if (s_item[0].id >= 0 && tid < kHeadDim) {
-    s_qf[0][tid] = __bfloat162float(p.q[static_cast<int64_t>(s_item[0].bh) * kHeadDim + tid]);
+    ItemCursor cursor;
+    cursor_start(L, s_each, all_units * blockIdx.x / gridDim.x, all_units * (blockIdx.x + 1) / gridDim.x, &cursor);
+    if (tid == kHeadDim) {
+      s_all_units = all_units;
+      s_cursor = cursor;
+      describe_next(p, s_each, all_units, &s_cursor, &s_item[0]);
+      describe_next(p, s_each, all_units, &s_cursor, &s_item[1]);
+    } else if (tid < kHeadDim && cursor.at < cursor.end) {
+      const int64_t first_bh = static_cast<int64_t>(cursor.b) * L.heads + cursor.h;
+      s_qf[0][tid] = __bfloat162float(p.q[first_bh * kHeadDim + tid]);
+    }
   }
   __syncthreads();
 
