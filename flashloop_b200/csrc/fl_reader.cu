@@ -547,7 +547,7 @@ __device__ __forceinline__ int blocks_of_warp(int blk_begin, int blk_end, int wa
   return n > 0 ? (n + kDenseWarps - 1) / kDenseWarps : 0;
 }
 
-template <int BITS>
+template <int BITS, int LOOP>
 __global__ void __launch_bounds__(kDenseThreads, 2)
 dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   using St = Stage<BITS>;
@@ -570,8 +570,11 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   const int warp = tid >> 5;
   const int quad = lane >> 2;
   const int sub = lane & 3;
-  const int streams = p.loop + 1;
-  const int units_per_block = 2 * streams;
+  // the loop is a template parameter: loops 1 and 2 read streams 0 and 1 only, where every token
+  // holds a row, so the paths for compact streams drop out of their kernels
+  constexpr int streams = LOOP + 1;
+  constexpr int units_per_block = 2 * streams;
+  constexpr bool kAllRows = LOOP <= 1;
   uint8_t* ring = s_ring + static_cast<size_t>(warp) * kStages * St::kBytes;
 
   if (lane == 0) {
@@ -662,7 +665,7 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
             const int iblk = it->blk_begin + it_pos + iss_blk * kDenseWarps;
             const bool iv = iss_j >= streams;
             const int is = iv ? iss_j - streams : iss_j;
-            const Span sp = block_span(L, is, it->b, iblk * kGroup, lane);
+            const Span sp = kAllRows ? Span{iblk * kGroup, kGroup} : block_span(L, is, it->b, iblk * kGroup, lane);
             if (lane == 0) {
               const uint32_t stage_index = issued % kStages;
               const uint32_t bar = smem_u32(&s_bar[warp][stage_index]);
@@ -703,13 +706,13 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
           const uint32_t stage_index = consumed % kStages;
           const uint8_t* stage = ring + stage_index * St::kBytes;
           if (!mbar_wait(smem_u32(&s_bar[warp][stage_index]), (consumed / kStages) & 1u)) timed_out = true;
-          const Span sp = block_span(L, s, b, t0, lane);
+          const Span sp = kAllRows ? Span{t0, kGroup} : block_span(L, s, b, t0, lane);
           const int32_t* rank = s >= 2 ? L.rank[s - 2] + L.rank_base[b] + t0 : nullptr;
         const int g0 = sp.r0 >> 6;
-        const int ng = sp.m > 0 ? ((sp.r0 + sp.m - 1) >> 6) - g0 + 1 : 0;
+        const int ng = kAllRows ? 1 : (sp.m > 0 ? ((sp.r0 + sp.m - 1) >> 6) - g0 + 1 : 0);
         // A block whose 64 tokens are all present in one metadata group (always true for streams
         // 0 and 1) takes the branch-free path: row i of the stage is token i.
-        const bool full = sp.m == kGroup && ng == 1;
+        const bool full = kAllRows || (sp.m == kGroup && ng == 1);
         if (!is_v) {
           if (s == 0) {
   #pragma unroll
@@ -776,7 +779,7 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
               }
             }
           }
-          if (s == p.loop) {
+          if (s == LOOP) {
             // all streams summed: logits -> probabilities of my eight tokens
             float mx = -INFINITY;
   #pragma unroll
@@ -840,7 +843,7 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
               }
             }
           }
-          if (s == p.loop) {
+          if (s == LOOP) {
             flush_pairs(hacc, S.acc);
             S.vbias += __low2float(hbias);
             hbias = __floats2half2_rn(0.f, 0.f);
@@ -862,8 +865,8 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
       // ---- the BF16 tail and the current token: entries 0..tail_len (the last is the current),
       // one per lane quad; the V row is fetched together with the K row
       const int entries = curp->tail_len + 1;
-      const __nv_bfloat16* tk = L.tail_k[p.loop] + bh * L.tail_capacity * kHeadDim;
-      const __nv_bfloat16* tv = L.tail_v[p.loop] + bh * L.tail_capacity * kHeadDim;
+      const __nv_bfloat16* tk = L.tail_k[LOOP] + bh * L.tail_capacity * kHeadDim;
+      const __nv_bfloat16* tv = L.tail_v[LOOP] + bh * L.tail_capacity * kHeadDim;
       for (int e0 = warp * 8; e0 < entries; e0 += kDenseWarps * 8) {
         const int e = e0 + quad;
         const bool ok = e < entries;
@@ -1576,6 +1579,36 @@ int fill_common(ReaderParams& p, const fl_layer* layer, int loop, void* workspac
 
 }  // namespace
 
+namespace fl {
+namespace {
+
+template <int BITS, int LOOP>
+cudaError_t launch_dense_as(unsigned grid, cudaStream_t s, const ReaderParams& p) {
+  constexpr int kSmem = kDenseWarps * kStages * Stage<BITS>::kBytes;
+  static const cudaError_t attr = cudaFuncSetAttribute(dense_reader_kernel<BITS, LOOP>,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  if (attr != cudaSuccess) return attr;
+  dense_reader_kernel<BITS, LOOP><<<grid, kDenseThreads, kSmem, s>>>(p);
+  return cudaSuccess;
+}
+
+template <int BITS>
+cudaError_t launch_dense_bits(int loop, unsigned grid, cudaStream_t s, const ReaderParams& p) {
+  switch (loop) {
+    case 0: return launch_dense_as<BITS, 0>(grid, s, p);
+    case 1: return launch_dense_as<BITS, 1>(grid, s, p);
+    case 2: return launch_dense_as<BITS, 2>(grid, s, p);
+    default: return launch_dense_as<BITS, 3>(grid, s, p);
+  }
+}
+
+cudaError_t launch_dense(int bits, int loop, unsigned grid, cudaStream_t s, const ReaderParams& p) {
+  return bits == 4 ? launch_dense_bits<4>(loop, grid, s, p) : launch_dense_bits<2>(loop, grid, s, p);
+}
+
+}  // namespace
+}  // namespace fl
+
 extern "C" int fl_dense_source_attention(const fl_layer* layer, int32_t loop, const void* query,
                                          const void* current_key, const void* current_value,
                                          float scaling, float* output, float* logits,
@@ -1604,18 +1637,9 @@ extern "C" int fl_dense_source_attention(const fl_layer* layer, int32_t loop, co
   p.logits_stride = logits_stride;
   const unsigned grid = dense_grid(bh);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (layer->bits == 4) {
-    constexpr int kSmem = kDenseWarps * kStages * Stage<4>::kBytes;
-    static const cudaError_t attr = cudaFuncSetAttribute(
-        dense_reader_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-    (void)attr;
-    dense_reader_kernel<4><<<grid, kDenseThreads, kSmem, s>>>(p);
-  } else {
-    constexpr int kSmem = kDenseWarps * kStages * Stage<2>::kBytes;
-    static const cudaError_t attr = cudaFuncSetAttribute(
-        dense_reader_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-    (void)attr;
-    dense_reader_kernel<2><<<grid, kDenseThreads, kSmem, s>>>(p);
+  if (cudaError_t err = launch_dense(layer->bits, loop, grid, s, p); err != cudaSuccess) {
+    set_error("fl_dense_source_attention: %s", cudaGetErrorString(err));
+    return FL_ERR_CUDA;
   }
   FL_CHECK_LAUNCH("fl_dense_source_attention");
   return FL_OK;
@@ -1820,24 +1844,9 @@ extern "C" int fl_dense_source_attention_static(const fl_layer* layer, int32_t l
   p.logits = logits;
   p.logits_stride = logits_stride;
   const unsigned grid = dense_grid(bh);
-  if (layer->bits == 4) {
-    constexpr int kSmem = kDenseWarps * kStages * Stage<4>::kBytes;
-    const cudaError_t attr =
-        cudaFuncSetAttribute(dense_reader_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-    if (attr != cudaSuccess) {
-      set_error("%s: %s", who, cudaGetErrorString(attr));
-      return FL_ERR_CUDA;
-    }
-    dense_reader_kernel<4><<<grid, kDenseThreads, kSmem, s>>>(p);
-  } else {
-    constexpr int kSmem = kDenseWarps * kStages * Stage<2>::kBytes;
-    const cudaError_t attr =
-        cudaFuncSetAttribute(dense_reader_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-    if (attr != cudaSuccess) {
-      set_error("%s: %s", who, cudaGetErrorString(attr));
-      return FL_ERR_CUDA;
-    }
-    dense_reader_kernel<2><<<grid, kDenseThreads, kSmem, s>>>(p);
+  if (cudaError_t err = launch_dense(layer->bits, loop, grid, s, p); err != cudaSuccess) {
+    set_error("%s: %s", who, cudaGetErrorString(err));
+    return FL_ERR_CUDA;
   }
   FL_CHECK_LAUNCH(who);
   return FL_OK;
