@@ -1036,7 +1036,9 @@ __device__ __forceinline__ void table_store(__half* table, int lane, __half2 q01
 // bits: first entry in bits 0..9, rows - 1 in bits 10..12.
 constexpr int kMaxEntries = 4 * kSlotBatch;
 
-template <int BITS, int MODE>
+// STREAMS = loop + 1 is a template parameter, so that the staging of a batch touches only the
+// streams the loop reads.
+template <int BITS, int MODE, int STREAMS>
 __global__ void __launch_bounds__(kGatherThreads, kGatherCtasPerSm)
 selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   constexpr int kRowBytes = 16 * BITS;
@@ -1074,7 +1076,7 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   const int split = blockIdx.x;
   const int slot_begin = split * p.slots_per_cta;
   const int slot_end = min(p.capacity, slot_begin + p.slots_per_cta);
-  const int streams = p.loop + 1;
+  constexpr int streams = STREAMS;
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -1153,18 +1155,19 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
       }
     }
 #pragma unroll
-    for (int s = 0; s < 4; ++s) member |= rows[s] >= 0 ? 1u << s : 0u;
+    for (int s = 0; s < STREAMS; ++s) member |= rows[s] >= 0 ? 1u << s : 0u;
     // ---- the entry lists: every class in slot order, streams 0..3 back to back
     int at[5];  // my entry in every class I am a member of
 #pragma unroll
     for (int c = 0; c < 5; ++c) {
+      if (c >= STREAMS && c != kTailClass) continue;
       const uint32_t mask = __ballot_sync(kFull, (member >> c) & 1u);
       at[c] = __popc(mask & lanes_below);
       if (lane == 0) s_wcount[c][warp] = __popc(mask);
     }
     __syncthreads();
     if (warp == 0) {  // running entry counts over (stream, warp)
-      const int mine = s_wcount[lane >> 3][lane & 7];
+      const int mine = (lane >> 3) < STREAMS ? s_wcount[lane >> 3][lane & 7] : 0;
       int incl = mine;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
@@ -1185,6 +1188,7 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
     __syncthreads();
 #pragma unroll
     for (int c = 0; c < 5; ++c) {
+      if (c >= STREAMS && c != kTailClass) continue;
       at[c] += s_woff[c][warp];
       if ((member >> c) & 1u) {
         if (c < 4) {
@@ -1206,8 +1210,8 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
       bool entry_on[4], run_head[4];
       int group_of[4];
 #pragma unroll
-      for (int s = 0; s < 4; ++s) {
-        entry_on[s] = s < streams && tid < s_count[s];
+      for (int s = 0; s < STREAMS; ++s) {
+        entry_on[s] = tid < s_count[s];
         const int first = s_ebase[s];
         const int base = s_rbase[s];
         group_of[s] = entry_on[s] ? (static_cast<int>(s_entry[first + tid] & 0x3fffffffu) - base) >> 6 : -1;
@@ -1222,7 +1226,7 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
       uint32_t pass_heads[4];
       int rank[4];
 #pragma unroll
-      for (int s = 0; s < 4; ++s) {
+      for (int s = 0; s < STREAMS; ++s) {
         int run_start = 0;
         const uint32_t upto = run_heads[s] & (lanes_below | (1u << lane));
         if (upto) {
@@ -1246,7 +1250,7 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
       }
       __syncthreads();
       if (warp == 0) {  // running pass counts over (stream, warp)
-        const int mine = s_wcount[lane >> 3][lane & 7];
+        const int mine = (lane >> 3) < STREAMS ? s_wcount[lane >> 3][lane & 7] : 0;
         int incl = mine;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
@@ -1258,7 +1262,7 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
       }
       __syncthreads();
 #pragma unroll
-      for (int s = 0; s < 4; ++s) {
+      for (int s = 0; s < STREAMS; ++s) {
         if (pass_head[s]) {
           int next = s_count[s];
           const uint32_t above = pass_heads[s] & ~(lanes_below | (1u << lane));
@@ -1370,7 +1374,7 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
       __syncthreads();  // every K pass of the batch has written its partial logits
       float logit = 0.f;
 #pragma unroll
-      for (int s = 0; s < 4; ++s) logit += (member >> s) & 1u ? s_eval[at[s]] : 0.f;
+      for (int s = 0; s < STREAMS; ++s) logit += (member >> s) & 1u ? s_eval[at[s]] : 0.f;
       if ((member >> kTailClass) & 1u) logit = s_tval[at[kTailClass]];
       if constexpr (MODE == kModeQK) {
         if (live) p.logits[bh * p.capacity + batch_begin + tid] = logit;
@@ -1396,7 +1400,7 @@ selected_reader_kernel(const __grid_constant__ ReaderParams p) {
         const float pr = live ? exp2f(x - m_run) : 0.f;
         l_mine += pr;
 #pragma unroll
-        for (int s = 0; s < 4; ++s) {
+        for (int s = 0; s < STREAMS; ++s) {
           if ((member >> s) & 1u) s_eval[at[s]] = pr;
         }
         if ((member >> kTailClass) & 1u) s_tval[at[kTailClass]] = pr;
@@ -1647,13 +1651,23 @@ extern "C" int fl_dense_source_attention(const fl_layer* layer, int32_t loop, co
 
 namespace {
 
-template <int BITS, int MODE>
-void launch_selected_bits(const dim3 grid, const ReaderParams& p, cudaStream_t s) {
+template <int BITS, int MODE, int STREAMS>
+void launch_selected_as(const dim3 grid, const ReaderParams& p, cudaStream_t s) {
   constexpr int kSmem = kGatherWarps * kDepth * kPassBytes;
   static const cudaError_t attr = cudaFuncSetAttribute(
-      selected_reader_kernel<BITS, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+      selected_reader_kernel<BITS, MODE, STREAMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
   (void)attr;
-  selected_reader_kernel<BITS, MODE><<<grid, kGatherThreads, kSmem, s>>>(p);
+  selected_reader_kernel<BITS, MODE, STREAMS><<<grid, kGatherThreads, kSmem, s>>>(p);
+}
+
+template <int BITS, int MODE>
+void launch_selected_bits(const dim3 grid, const ReaderParams& p, cudaStream_t s) {
+  switch (p.loop) {
+    case 0: launch_selected_as<BITS, MODE, 1>(grid, p, s); break;
+    case 1: launch_selected_as<BITS, MODE, 2>(grid, p, s); break;
+    case 2: launch_selected_as<BITS, MODE, 3>(grid, p, s); break;
+    default: launch_selected_as<BITS, MODE, 4>(grid, p, s); break;
+  }
 }
 
 template <int MODE>
