@@ -1,17 +1,22 @@
 #!/usr/bin/env python3
-"""Decode-path benchmark: tokens/s of the int4 KV-residual attention hot path.
+"""Decode benchmark: tokens/s of the four-loop decoder over the int4 KV-residual cache.
 
-Workload (BASELINE configs[1], "sparse late-loop decode"): per GPU a batch of 8 sequences,
-16 heads x 128, context 8192, four loops, 4-bit K/V in groups of 64 with a 64-token BF16 tail,
-held for the 24 layers of an Ouro-1.4B-shaped decoder.  One step decodes one token per
-sequence through the KV-attention path of every layer: dense reader loop 1, dense reader
-loop 2 (+ logits), top-10 % key selection, selected-value aggregate, cached-mass sparse reader
-loops 3 and 4, then the append of the token's four K/V rows to the tail (with the 64-token
-rollover when the tail reaches 128).  Queries and current K/V are synthetic (there is no
-model in front of the path); the cache is synthetic K/V of the named shape.
+Default workload (BASELINE configs[3], the configuration the metric is quoted on): the
+Ouro-1.4B-shaped random-init bf16 model (24 layers x 4 loops, hidden 2048, 16 heads x 128,
+SwiGLU 5632, vocab 49152) decoding through ``FlashLoopEngine`` at batch 16 per GPU after
+2048-token random prompts: loops 1-2 dense, 25 % / 10 % token retention, 10 % key retention,
+4-bit K/V in groups of 64 with a 64-token BF16 tail.  One step = one decoded token per sequence
+(embed, 4 x 24 layers of norm / QKV / RoPE / reader / o_proj / MLP, append, lm_head).
 
-Prints ONE JSON line (rank 0).  ``--impl reference`` times the CPU oracle port of the same
-step on the host cores instead.
+``--workload hotpath`` is the reader-only step of BASELINE configs[1] (batch 8, context 8192,
+the KV-attention kernels of 24 layers on synthetic vectors), ``ragged`` configs[2], ``kernels`` a
+per-kernel table.  Every line carries ``roofline`` (the dominant kernel of the timed step) and
+``roofline_dense`` / ``roofline_sparse``: the dense loop-2 reader and the loop-4 sparse reader at
+the configs[1] shapes (batch 8 x 16 heads x 8192, 820 selected keys), the shapes the 70 %
+HBM target is quoted on.
+
+Prints ONE JSON line (rank 0).  ``--impl reference`` times the CPU port of the same step on the
+host cores instead.
 """
 
 from __future__ import annotations
@@ -34,10 +39,26 @@ HEADS, HEAD_DIM, CONTEXT, LAYERS, BATCH = 16, 128, 8192, 24, 8
 KEY_FRACTION = 0.10
 SCALING = HEAD_DIM ** -0.5
 METRIC = "decode tok/s (Ouro-1.4B-shape R4)"
-# DRAM bytes per token and stream of the dense reader, from one ncu capture of a smaller case
-# (dram__bytes_read.sum + dram__bytes_write.sum = 165.9 MB for 64 (b,h) x 8128 tokens x 2 streams);
-# every packed byte is read once, so traffic grows in proportion to the tokens a launch covers.
-DENSE_TRAFFIC_PER_TOKEN_STREAM = {4: 165.9e6 / (64 * 8128 * 2)}
+METRIC_HOTPATH = "decode tok/s of the KV-attention path alone (configs[1] reader step, no model)"
+# Measured DRAM traffic of the readers: written by `python bench.py --update-traffic <ncu raw csv>`
+# from an ncu capture of a small case, with the commit it was captured at.
+TRAFFIC_FILE = ROOT / "profiles" / "reader_traffic.json"
+
+
+def measured_traffic(kernel: str, algorithmic_bytes: float):
+    """DRAM bytes per launch of ``kernel`` ("dense_reader" / "selected_reader"): the ncu capture's
+    traffic-to-algorithmic ratio (every packed byte is read once, so traffic grows in proportion
+    to the algorithmic bytes) times this launch's algorithmic bytes; (None, why) without a
+    capture."""
+
+    if not TRAFFIC_FILE.exists():
+        return None, "no ncu capture recorded in profiles/reader_traffic.json"
+    entry = json.loads(TRAFFIC_FILE.read_text()).get(kernel)
+    if not entry:
+        return None, f"no ncu capture of {kernel} recorded"
+    ratio = entry["dram_bytes_per_launch"] / entry["algorithmic_bytes_per_launch"]
+    return ratio * algorithmic_bytes, (f"ncu dram__bytes_read+write of the capture at commit {entry['commit']} "
+                                       f"({entry['case']}): {ratio:.3f} x algorithmic, scaled to this launch")
 
 
 def parse_args():
@@ -46,10 +67,10 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="hotpath", choices=["hotpath", "ragged", "e2e", "e2e-2.6b", "kernels"],
-                    help="hotpath: configs[1], the KV-attention path of every layer on synthetic vectors; "
+    ap.add_argument("--workload", default="e2e", choices=["hotpath", "ragged", "e2e", "e2e-2.6b", "kernels"],
+                    help="e2e (default): configs[3], the Ouro-1.4B-shaped model decoding through the engine; "
+                         "hotpath: configs[1], the KV-attention path of every layer on synthetic vectors; "
                          "ragged: configs[2], the same path over 32 sequences of 1024..32768 tokens (one layer); "
-                         "e2e: configs[3], the Ouro-1.4B-shaped model decoding through the engine; "
                          "kernels: every kernel of the path alone at the configs[1] shapes, with its bytes and fraction of peak; "
                          "e2e-2.6b: one GPU's share of configs[4] (48 layers, 8 of the 64 sequences, 8192-token prompts)")
     ap.add_argument("--layers", type=int, default=None, help="physical layers (default 24; 1 for ragged)")
@@ -61,6 +82,11 @@ def parse_args():
                     help="e2e workload: shard heads and FFN columns over the ranks (NCCL all-reduce after o_proj "
                          "and the MLP) instead of running one replica per rank")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-probes", action="store_true",
+                    help="skip the configs[1]-shaped reader probes behind roofline_dense / roofline_sparse")
+    ap.add_argument("--update-traffic", metavar="CSV", nargs="+", default=None,
+                    help="read `ncu -i <rep> --page raw --csv` exports of reader captures and record their DRAM "
+                         "traffic in profiles/reader_traffic.json (no GPU needed)")
     args = ap.parse_args()
     args.config_index = 3
     if args.workload == "e2e-2.6b":
@@ -92,6 +118,23 @@ def workload_name(args) -> str:
     return (f"configs[1] sparse late-loop decode: batch {args.batch}/GPU, {HEADS} heads x {HEAD_DIM}, "
             f"context {args.context}, 4 loops, {args.bits}-bit K/V group 64, 64-token BF16 tail, "
             f"top-10% keys in loops 3-4, {args.layers} layers")
+
+
+def bench_config(args) -> dict:
+    """The ``config`` object of the JSON line; both arms print the same one for the same flags."""
+
+    world = max(1, int(args.gpus))
+    tp = bool(getattr(args, "tp", False)) and world > 1
+    if args.workload == "e2e":
+        l2 = "inputs larger than L2: each step streams the layer weights four times and the packed cache"
+        parallelism = (f"tensor parallel x{world}: heads and FFN columns sharded, all-reduce after o_proj and the MLP"
+                       if tp else f"batch-data-parallel replicas x{world}, no data-path collective")
+    else:
+        l2 = "inputs larger than L2: each step streams the packed cache of every layer"
+        parallelism = f"batch-sharded x{world}, no data-path collective"
+    return {"workload": workload_name(args), "global_batch": args.batch if tp else args.batch * world, "l2": l2,
+            "parallelism": parallelism,
+            "launch": "eager" if args.no_graph else "one CUDA graph replay per step"}
 
 
 # ----------------------------------------------------------------------------- algorithmic bytes
@@ -162,6 +205,106 @@ class ClockSampler:
         return out
 
 
+# ----------------------------------------------------------------------------- reader probes
+
+
+def load_peak():
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    peaks = json.loads(peaks_path.read_text()) if peaks_path.exists() else {}
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    return peak, ("measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback 6650 GB/s")
+
+
+def roofline_object(kernel: str, traffic_key: str, algorithmic_bytes: float, launch_ms: list, peak: float,
+                    peak_kind: str, timing: str) -> dict:
+    avg_ms = statistics.mean(launch_ms) if launch_ms else float("nan")
+    achieved = algorithmic_bytes / (avg_ms * 1e-3) / 1e9
+    traffic, source = measured_traffic(traffic_key, algorithmic_bytes)
+    return {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "frac_of_nominal_8000": achieved / 8000.0, "peak_source": peak_kind,
+            "algorithmic_bytes_per_launch": algorithmic_bytes, "avg_launch_ms": avg_ms,
+            "launches_timed": len(launch_ms), "timing": timing, "traffic": traffic, "traffic_source": source}
+
+
+def probe_configs1_readers(device, bits: int, layers_n: int = 4) -> dict:
+    """The two readers at the shapes the HBM target is quoted on (BASELINE configs[1]: batch 8,
+    16 heads x 128, context 8192, residuals on every token, 820 selected keys): the dense loop-2
+    reader and the loop-4 cached-mass sparse reader, each timed with CUDA events around a graph of
+    twelve launches that cycle over ``layers_n`` layers, so that no launch finds its input in L2.
+    Returns {"roofline_dense": ..., "roofline_sparse": ...}."""
+
+    import torch
+
+    from flashloop_b200.cache import CrossLoopKVLayer
+    from flashloop_b200.synthetic import make_loop_kv
+
+    B, H, T = BATCH, HEADS, CONTEXT
+    peak, peak_kind = load_peak()
+    ones = torch.ones(B, T, dtype=torch.bool, device=device)
+    layers = []
+    for li in range(layers_n):
+        keys, values = [[] for _ in range(4)], [[] for _ in range(4)]
+        for b in range(B):
+            k, v = make_loop_kv(H, T, seed=7000 + li * 100 + b, device=device)
+            for r in range(4):
+                keys[r].append(k[r])
+                values[r].append(v[r])
+        layers.append(CrossLoopKVLayer.from_prefill([torch.cat(k) for k in keys], [torch.cat(v) for v in values],
+                                                    mask_loop3=ones, mask_loop4=ones, bits=bits))
+        del keys, values
+    quant, tail = layers[0].quantized_tokens, layers[0].tail_tokens
+    gen = torch.Generator(device=device).manual_seed(1)
+    q, ck, cv = (torch.randn(B, H, 1, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16) for _ in range(3))
+    out = torch.empty(B, H, 1, HEAD_DIM, device=device)
+    logits = [layer.dense_source_attention(1, query=q, current_key=ck, current_value=cv, scaling=SCALING,
+                                           return_logits=True)[1].clone() for layer in layers]
+    sels = [layer.select_decode_keys(lg, fraction=KEY_FRACTION) for layer, lg in zip(layers, logits)]
+    srcs = [layer.pv(1, sel.selected_weights, sel.indices, current_value=cv, valid=sel.valid, validate_indices=False)
+            for layer, sel in zip(layers, sels)]
+    keys_n = math.ceil((quant + tail + 1) * KEY_FRACTION)
+
+    def timeit(fn, reps: int = 12, rounds: int = 5) -> list:
+        for i in range(layers_n):
+            fn(i)
+        torch.cuda.synchronize(device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(reps):
+                fn(i)
+        graph.replay()
+        torch.cuda.synchronize(device)
+        ms = []
+        for _ in range(rounds):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize(device)
+            ms.append(e0.elapsed_time(e1) / reps)
+        return ms
+
+    lg_out = torch.empty_like(logits[0])
+    dense_ms = timeit(lambda i: layers[i % layers_n].dense_source_attention(
+        1, query=q, current_key=ck, current_value=cv, scaling=SCALING, return_logits=True, out=out, logits_out=lg_out))
+    sparse_ms = timeit(lambda i: layers[i % layers_n].cached_mass_sparse_attention_delta(
+        3, query=q, current_key=ck, current_value=cv, indices=sels[i % layers_n].indices,
+        valid=sels[i % layers_n].valid, source_selected_output=srcs[i % layers_n],
+        global_mass=sels[i % layers_n].global_mass, scaling=SCALING, out=out))
+    status = max(layer.reader_status() for layer in layers)
+    timing = (f"CUDA events around a graph of 12 launches cycling over {layers_n} layers of batch {B} x {H} heads x "
+              f"context {T} (inputs larger than L2), 5 replays")
+    return {
+        "roofline_dense": roofline_object(
+            f"dense_reader_kernel<{bits},1> (loop 2: anchor + delta-2 streams) at configs[1] shapes", "dense_reader",
+            dense_bytes(B * H, 1, quant, tail, bits), dense_ms, peak, peak_kind, timing),
+        "roofline_sparse": roofline_object(
+            f"selected_reader_kernel<{bits},delta,4> (loop 4: cached-mass sparse reader, {keys_n} keys of {quant + tail + 1}) "
+            "at configs[1] shapes", "selected_reader", sparse_bytes(B * H, 3, keys_n, quant, bits), sparse_ms, peak,
+            peak_kind, timing),
+        "probe_reader_status": status,
+    }
+
+
 # ----------------------------------------------------------------------------- the CPU oracle leg
 
 
@@ -198,19 +341,32 @@ def _oracle_head_step(seed: int, context: int, bits: int) -> float:
     return time.perf_counter() - start
 
 
-def cpu_oracle_tokens_per_second(args, tasks_per_core: int = 3) -> dict:
-    """Time the oracle on every host core at once (one head-step task per core per round) and
-    scale to whole decode tokens: one token = HEADS heads x layers."""
+def cpu_pool():
+    """One worker process per host core (at most 32).  spawn, not fork: the parent may hold a CUDA
+    context and OpenMP threads."""
 
     import multiprocessing
     from concurrent.futures import ProcessPoolExecutor
 
     cores = min(os.cpu_count() or 1, 32)
+    return ProcessPoolExecutor(max_workers=cores, mp_context=multiprocessing.get_context("spawn")), cores
+
+
+def cpu_oracle_tokens_per_second(args, tasks_per_core: int = 3, pool=None) -> dict:
+    """Time the oracle on every host core at once (one head-step task per core per round) and
+    scale to whole decode tokens: one token = HEADS heads x layers."""
+
+    own = pool is None
+    if own:
+        pool = cpu_pool()
+    executor, cores = pool
     tasks = cores * tasks_per_core
     start = time.perf_counter()
-    # spawn, not fork: the parent may hold a CUDA context and OpenMP threads
-    with ProcessPoolExecutor(max_workers=cores, mp_context=multiprocessing.get_context("spawn")) as pool:
-        seconds = list(pool.map(_oracle_head_step, range(tasks), [args.context] * tasks, [args.bits] * tasks))
+    try:
+        seconds = list(executor.map(_oracle_head_step, range(tasks), [args.context] * tasks, [args.bits] * tasks))
+    finally:
+        if own:
+            executor.shutdown()
     wall = time.perf_counter() - start
     # all workers run at once: aggregate rate = workers / mean seconds per head-step
     head_steps_per_s = cores / (sum(seconds) / len(seconds))
@@ -226,21 +382,39 @@ def cpu_oracle_tokens_per_second(args, tasks_per_core: int = 3) -> dict:
 
 
 def run_reference(args) -> None:
+    """The CPU arm: the port of the reference's path on the host cores.  One step is one bounded
+    sample of the workload (one head-step of the KV-attention path per core, plus, for the
+    end-to-end workload, the projections and MLP of two layers in float32 Torch); ``warmup``
+    samples are discarded, ``steps`` samples are timed.  ``steps`` and ``ms_per_step`` describe
+    the samples that really ran; ``value`` extrapolates them to whole decode steps (the line says
+    so: "extrapolated")."""
+
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    rounds = max(1, min(args.steps, 4))
-    measure = cpu_e2e_tokens_per_second if args.workload == "e2e" else cpu_oracle_tokens_per_second
-    for _ in range(min(args.warmup, 1)):
-        measure(args)
-    results = [measure(args) for _ in range(rounds)]
-    best = max(results, key=lambda r: r["value"])
+    e2e = args.workload == "e2e"
+    measure = cpu_e2e_tokens_per_second if e2e else cpu_oracle_tokens_per_second
+    pool = cpu_pool()
+    for _ in range(args.warmup):
+        measure(args, tasks_per_core=1, pool=pool)
+    results, walls = [], []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        results.append(measure(args, tasks_per_core=1, pool=pool))
+        walls.append(time.perf_counter() - t0)
+    pool[0].shutdown()
+    value = statistics.mean(r["value"] for r in results)
+    best = dict(results[0])
+    best["value"] = value
+    best["sample"] = f"{args.steps} timed samples after {args.warmup} warm-up samples, each: " + results[0]["sample"]
     line = {
-        "impl": "reference", "metric": METRIC, "value": best["value"], "unit": "tok/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / best["value"], "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(args)}, "cpu_baseline": best,
-        "e2e": {"value": best["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": METRIC if e2e else METRIC_HOTPATH, "value": value, "unit": "tok/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * statistics.mean(walls), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "extrapolated": True,
+        "ms_per_full_step_extrapolated": 1e3 / value,
+        "config": bench_config(args), "cpu_baseline": best,
+        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
@@ -297,7 +471,6 @@ def run_b200(args) -> None:
     bound = max(lengths) + steps_total + 64
     for layer in layers:
         layer.context_bound = bound  # fixed launch geometry: the step can be replayed as a CUDA graph
-    kernels_per_layer = 9  # 2 dense + select + selected PV + 2 sparse + 3 append/rollover/state
 
     def step(inputs, advance_host: bool = True) -> None:
         q_all, k_all, v_all = inputs[0], inputs[1], inputs[2]
@@ -330,9 +503,15 @@ def run_b200(args) -> None:
         barrier()
         return sharding.max_over_ranks(e0.elapsed_time(e1), device)
 
-    # ---- warm-up (eager), then record one step as a CUDA graph over static input buffers
-    for _ in range(args.warmup):
+    # ---- warm-up (eager; the launches of one step are counted), then record one step as a CUDA
+    # graph over static input buffers
+    for i in range(max(1, args.warmup)):
+        if i == 0:
+            _native.count_launches(True)
         step(dev_inputs)
+        if i == 0:
+            launch_counts = _native.count_launches(False)
+    launches_per_step = sum(launch_counts.values())
     graph = None
     if not args.no_graph:
         torch.cuda.synchronize()
@@ -357,7 +536,7 @@ def run_b200(args) -> None:
     ms_total = timed(run_step, args.steps)
     torch.cuda.profiler.stop()
     clocks = sampler.stop() if sampler else {}
-    timed_launches = kernels_per_layer * NL * args.steps
+    timed_launches = launches_per_step * args.steps
     # every rank decodes its own B sequences: tokens of all ranks over the slowest rank's time
     value = sharding.sum_over_ranks(B * args.steps, device) / (ms_total * 1e-3)
 
@@ -391,49 +570,60 @@ def run_b200(args) -> None:
     e2e_value = sharding.sum_over_ranks(B * e2e_steps, device) / (e2e_ms * 1e-3)
     status = max(layer.reader_status() for layer in layers)
 
+    # ---- the loop-4 sparse reader of every layer, same arguments as in the step
+    sparse_probe = []
+    q3, k3, v3 = dev_inputs[0][:, 3], dev_inputs[1][:, 3], dev_inputs[2][:, 3]
+    for rep in range(3):
+        for li, layer in enumerate(layers):
+            _, lg = layer.dense_source_attention(1, query=q1[li], current_key=k1[li], current_value=v1[li],
+                                                 scaling=SCALING, return_logits=True, out=out[li, 1])
+            sel = layer.select_decode_keys(lg, fraction=KEY_FRACTION)
+            src = layer.pv(1, sel.selected_weights, sel.indices, current_value=v1[li], valid=sel.valid,
+                           validate_indices=False)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            layer.cached_mass_sparse_attention_delta(3, query=q3[li], current_key=k3[li], current_value=v3[li],
+                                                     indices=sel.indices, valid=sel.valid, source_selected_output=src,
+                                                     global_mass=sel.global_mass, scaling=SCALING, out=out[li, 3])
+            e1.record()
+            if rep:
+                sparse_probe.append((e0, e1))
+    torch.cuda.synchronize()
+    sparse_ms = [a.elapsed_time(b) for a, b in sparse_probe]
+    status = max(status, max(layer.reader_status() for layer in layers))
+
     if rank == 0:
-        peaks = {}
-        peaks_path = ROOT / "MEASURED_PEAKS.json"
-        if peaks_path.exists():
-            peaks = json.loads(peaks_path.read_text())
-        peak = float(peaks.get("hbm_gbs", 6650.0))
-        peak_kind = "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback 6650 GB/s"
-        bh = B * H
+        peak, peak_kind = load_peak()
         algo = sum(dense_bytes(H, 1, q_, t_, args.bits) for q_, t_ in zip(quants, tails))
-        avg_ms = statistics.mean(probe_ms) if probe_ms else float("nan")
-        achieved = algo / (avg_ms * 1e-3) / 1e9
+        sparse_algo = sum(sparse_bytes(H, 3, math.ceil((q_ + t_ + 1) * KEY_FRACTION), q_, args.bits)
+                          for q_, t_ in zip(quants, tails))
         step_bytes = 0
         for q_, t_ in zip(quants, tails):
             keys = math.ceil((q_ + t_ + 1) * KEY_FRACTION)
             step_bytes += NL * (dense_bytes(H, 0, q_, t_, args.bits) + dense_bytes(H, 1, q_, t_, args.bits)
                                 + sparse_bytes(H, 1, keys, q_, args.bits) - H * 1280  # selected PV, loop 2
                                 + sparse_bytes(H, 2, keys, q_, args.bits) + sparse_bytes(H, 3, keys, q_, args.bits))
+        in_step = "CUDA events around single launches with the step's own arguments, right after the timed region"
         line = {
-            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "metric": METRIC_HOTPATH, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16" if True else "", "data": "synthetic",
-            "config": {"workload": workload_name(args), "global_batch": B * world,
-                       "l2": "inputs larger than L2: each step streams ~%.1f GB of packed cache per GPU" %
-                             (step_bytes / 1e9),
-                       "parallelism": f"batch-sharded x{world}, no data-path collective",
-                       "launch": "eager" if graph is None else "one CUDA graph replay per step"},
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": bench_config(args),
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": int(host_inputs.numel() * 2),
                     "d2h_bytes_per_step": int(host_out.numel() * 4), "steps": e2e_steps},
             "gpu_launches": timed_launches,
-            "roofline": {"bound": "hbm", "kernel": "dense_reader_kernel<4> (loop 2: anchor + delta-2 streams)",
-                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "frac_of_nominal_8000": achieved / 8000.0, "peak_source": peak_kind,
-                         "algorithmic_bytes_per_launch": algo, "avg_launch_ms": avg_ms,
-                         "launches_timed": len(probe_ms),
-                         "traffic": DENSE_TRAFFIC_PER_TOKEN_STREAM[args.bits] * H * sum(quants) * 2
-                         if args.bits in DENSE_TRAFFIC_PER_TOKEN_STREAM else None,
-                         "traffic_source": "ncu dram__bytes_read+write of the batch-4 capture in profiles/"
-                                           "dense_reader_loop2_batch4_ctx8192.md, scaled by (b,h) pairs x tokens",
-                         "step_algorithmic_GBps": step_bytes / (ms_total / args.steps * 1e-3) / 1e9},
+            "gpu_launches_source": f"{launches_per_step} launches of this library's kernels counted in one step "
+                                   f"({launch_counts}) x {args.steps} timed steps",
+            "roofline": roofline_object(f"dense_reader_kernel<{args.bits},1> (loop 2: anchor + delta-2 streams)",
+                                        "dense_reader", algo, probe_ms, peak, peak_kind, in_step),
+            "roofline_sparse": roofline_object(
+                f"selected_reader_kernel<{args.bits},delta,4> (loop 4: cached-mass sparse reader)", "selected_reader",
+                sparse_algo, sparse_ms, peak, peak_kind, in_step),
+            "step_algorithmic_GBps": step_bytes / (ms_total / args.steps * 1e-3) / 1e9,
             "reader_status": status,
         }
-        line["dtype"] = "f16"  # codes are dequantised and multiplied in float16 pairs, accumulated in float32
+        # codes are dequantised and multiplied in float16 pairs, accumulated in float32
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_oracle_tokens_per_second(args)
         print(json.dumps(line))
@@ -618,7 +808,7 @@ def run_kernel_table(args) -> None:
 # ----------------------------------------------------------------------------- the end-to-end workload
 
 
-def cpu_e2e_tokens_per_second(args) -> dict:
+def cpu_e2e_tokens_per_second(args, tasks_per_core: int = 3, pool=None) -> dict:
     """CPU stand-in for one decode token of the model: the oracle's KV-attention step (per head,
     scaled) plus the projection / MLP GEMVs of two Ouro-shaped layers in torch on the host cores
     (scaled to ``layers`` x 4 loops)."""
@@ -628,7 +818,7 @@ def cpu_e2e_tokens_per_second(args) -> dict:
     from flashloop_b200.ouro_shape import OuroShapedConfig, OuroShapedForCausalLM
     from flashloop_b200.weights import fused_mlp, project_qkv
 
-    kv = cpu_oracle_tokens_per_second(args)
+    kv = cpu_oracle_tokens_per_second(args, tasks_per_core=tasks_per_core, pool=pool)
     torch.set_num_threads(os.cpu_count() or 1)
     model = OuroShapedForCausalLM(OuroShapedConfig(num_hidden_layers=2, vocab_size=1024), dtype=torch.float32)
     x = torch.randn(1, 1, 2048)
@@ -670,7 +860,7 @@ def run_e2e(args) -> None:
         dist.init_process_group("nccl", device_id=device)
     B, T, NL = args.batch, args.context, args.layers
     e2e_steps = max(2, min(args.steps, 16))
-    budget = args.warmup + args.steps + e2e_steps + 8
+    budget = max(2, args.warmup) + args.steps + e2e_steps + 8
     cfg = OuroShapedConfig(num_hidden_layers=NL)
     model = OuroShapedForCausalLM(cfg, seed=0, device=device)
     tp = args.tp and world > 1
@@ -701,7 +891,13 @@ def run_e2e(args) -> None:
         sharding.barrier(device)
         return sharding.max_over_ranks(e0.elapsed_time(e1), device)
 
-    for _ in range(args.warmup):
+    # the engine runs its first decode eagerly (the launches of that step are counted), records the
+    # second as a CUDA graph and replays it from then on
+    _native.count_launches(True)
+    run_step()
+    launch_counts = _native.count_launches(False)
+    launches_per_step = sum(launch_counts.values())
+    for _ in range(max(2, args.warmup) - 1):
         run_step()
     sampler = ClockSampler(local) if rank == 0 else None
     torch.cuda.profiler.start()
@@ -743,37 +939,40 @@ def run_e2e(args) -> None:
     status = max(layer.reader_status() for layer in layers)
     quant, tail = layers[0].quantized_tokens, layers[0].tail_tokens
 
+    # ---- the two readers at the shapes the HBM target is quoted on (rank 0 only: a probe, not part
+    # of the job's throughput)
+    probes = {}
+    if rank == 0 and not args.no_probes:
+        probes = probe_configs1_readers(device, args.bits)
+    if world > 1:
+        dist.barrier()
+
     if rank == 0:
-        peaks_path = ROOT / "MEASURED_PEAKS.json"
-        peaks = json.loads(peaks_path.read_text()) if peaks_path.exists() else {}
-        peak = float(peaks.get("hbm_gbs", 6650.0))
+        peak, peak_kind = load_peak()
         algo = dense_bytes(B * H, 1, quant, tail, args.bits)
-        avg_ms = statistics.mean(probe_ms)
-        achieved = algo / (avg_ms * 1e-3) / 1e9
         weights = sum(p.numel() for n, p in model.named_parameters() if "embed" not in n) * 2
         line = {
             "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
             "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": workload_name(args), "global_batch": B if tp else B * world,
-                       "l2": "inputs larger than L2: each step streams the layer weights four times "
-                             "(%.1f GB) and the packed cache" % (4 * weights / 1e9),
-                       "parallelism": (f"tensor parallel x{world}: heads and FFN columns sharded, NCCL all-reduce "
-                                       f"after o_proj and the MLP" if tp else
-                                       f"batch-data-parallel replicas x{world}, no collective"),
-                       "launch": "eager" if (args.no_graph or tp) else "one CUDA graph replay per step",
-                       "prefill_seconds": prefill_s, "context_at_end": quant + tail},
+            "config": bench_config(args),
+            "details": {"prefill_seconds": prefill_s, "context_at_end": quant + tail,
+                        "weight_bytes_streamed_per_step": 4 * weights},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": int(host_token.numel() * 8),
                     "d2h_bytes_per_step": int(host_token.numel() * 8), "steps": e2e_steps},
-            "gpu_launches": 9 * NL * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "dense_reader_kernel<%d> (loop 2: anchor + delta-2 streams)" % args.bits,
-                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback 6650 GB/s",
-                         "algorithmic_bytes_per_launch": algo, "avg_launch_ms": avg_ms,
-                         "launches_timed": len(probe_ms), "traffic": None},
+            "gpu_launches": launches_per_step * args.steps,
+            "gpu_launches_source": f"{launches_per_step} launches of this library's kernels counted in one eager "
+                                   f"decode step ({launch_counts}) x {args.steps} timed steps; the step's library "
+                                   f"GEMMs (cuBLAS) are not counted",
+            "roofline": roofline_object(
+                f"dense_reader_kernel<{args.bits},1> (loop 2: anchor + delta-2 streams), the dominant kernel of "
+                f"this library in the step, at the step's shapes ({B * H} heads x {quant + tail} tokens)",
+                "dense_reader", algo, probe_ms, peak, peak_kind,
+                "CUDA events around single launches on the engine's cache layers, right after the timed region"),
             "reader_status": status,
         }
+        line.update(probes)
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_e2e_tokens_per_second(args)
         print(json.dumps(line))
@@ -782,9 +981,53 @@ def run_e2e(args) -> None:
         dist.destroy_process_group()
 
 
+def update_traffic(args) -> None:
+    """Record the measured DRAM traffic of the readers from `ncu -i <report> --page raw --csv`
+    exports (no GPU needed).  The captures are of the hotpath workload at ``--batch`` x 16 heads x
+    ``--context`` (all-token residuals, top 10 % keys); per kernel the launches found are averaged.
+    Writes profiles/reader_traffic.json with the commit the files were captured at."""
+
+    import csv
+
+    scale = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
+    B, H, T, bits = args.batch, HEADS, args.context, args.bits
+    quant = ((T - 64) // 64) * 64
+    tail = T - quant
+    keys_n = math.ceil((T + 1) * KEY_FRACTION)
+    wanted = {
+        "dense_reader": (f"dense_reader_kernel<{bits}, 1>", dense_bytes(B * H, 1, quant, tail, bits)),
+        "selected_reader": (f"selected_reader_kernel<{bits}, 0, 4>", sparse_bytes(B * H, 3, keys_n, quant, bits)),
+    }
+    found = {k: [] for k in wanted}
+    for path in args.update_traffic:
+        rows = list(csv.reader(open(path)))
+        start = next(i for i, row in enumerate(rows) if "Kernel Name" in row)
+        header, units = rows[start], rows[start + 1]
+        name_at = header.index("Kernel Name")
+        cols = [header.index(m) for m in ("dram__bytes_read.sum", "dram__bytes_write.sum")]
+        for row in rows[start + 2:]:
+            if len(row) <= max(cols):
+                continue
+            for key, (pattern, _) in wanted.items():
+                if pattern.replace(" ", "") in row[name_at].replace(" ", ""):
+                    found[key].append(sum(float(row[c].replace(",", "")) * scale[units[c]] for c in cols))
+    commit = subprocess.run(["git", "rev-parse", "--short", "HEAD"], cwd=ROOT, capture_output=True, text=True).stdout.strip()
+    record = json.loads(TRAFFIC_FILE.read_text()) if TRAFFIC_FILE.exists() else {}
+    for key, values in found.items():
+        if values:
+            record[key] = {"kernel": wanted[key][0], "dram_bytes_per_launch": statistics.mean(values),
+                           "algorithmic_bytes_per_launch": wanted[key][1], "launches": len(values),
+                           "case": f"batch {B} x {H} heads x context {T}, {bits}-bit, {keys_n} selected keys",
+                           "commit": commit, "files": [Path(f).name for f in args.update_traffic]}
+    TRAFFIC_FILE.write_text(json.dumps(record, indent=1) + "\n")
+    print(json.dumps(record, indent=1))
+
+
 def main() -> None:
     args = parse_args()
-    if args.impl == "reference":
+    if args.update_traffic:
+        update_traffic(args)
+    elif args.impl == "reference":
         run_reference(args)
     elif args.workload == "e2e":
         run_e2e(args)

@@ -54,6 +54,7 @@ SIGNATURES = {
                                             _i64, _i64, _vp, _sz, _vp]),
     "fl_dense_source_attention_static": (C.c_int, [C.POINTER(FlLayer), _i32, _vp, _vp, _vp, _f32, _vp, _vp,
                                                    _i64, _i64, _vp]),
+    "fl_static_status": (C.c_int, [C.POINTER(_i32), _vp]),
     "fl_sparse_attention_delta": (C.c_int, [C.POINTER(FlLayer), _i32, _vp, _vp, _vp, _vp, _vp, _i64,
                                             _vp, _vp, _f32, _vp, _vp, _vp, _sz, _vp]),
     "fl_selected_pv": (C.c_int, [C.POINTER(FlLayer), _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
@@ -71,13 +72,58 @@ SIGNATURES = {
     "fl_swiglu": (C.c_int, [_vp, _i64, _i32, _vp, _vp]),
 }
 
+# kernels launched by one call of an entry point (entry points that launch nothing are absent)
+LAUNCHES_PER_CALL = {
+    "fl_pack_k_rows": 1, "fl_pack_v_rows": 1, "fl_pack_kivi_k": 1, "fl_pack_kivi_v": 1, "fl_decode_rows": 1,
+    "fl_kivi_to_rows_k": 1, "fl_kivi_to_rows_v": 1, "fl_dense_source_attention": 1,
+    "fl_dense_source_attention_static": 1, "fl_sparse_attention_delta": 1, "fl_selected_pv": 1, "fl_selected_qk": 1,
+    "fl_append_decode_token": 3, "fl_select_decode_keys": 1, "fl_hidden_delta_score": 1,
+    "fl_select_prefill_tokens": 1, "fl_gather_rows": 1, "fl_scatter_rows": 1, "fl_encode_prefill": 3,
+    "fl_rmsnorm": 1, "fl_rope_split": 1, "fl_swiglu": 1,
+}
+
 _LIB = None
+_COUNTER = None
 
 
-def load() -> C.CDLL:
+class _CountingLibrary:
+    """The library with every kernel-launching entry point wrapped so that its launches are
+    counted (``count_launches``); used by the benchmark to report how many of this library's
+    kernels one step launches."""
+
+    def __init__(self, lib: C.CDLL) -> None:
+        self._lib = lib
+        self.counts: dict[str, int] = {}
+
+    def __getattr__(self, name: str):
+        fn = getattr(self._lib, name)
+        per_call = LAUNCHES_PER_CALL.get(name, 0)
+        if not per_call:
+            return fn
+
+        def counted(*args):
+            self.counts[name] = self.counts.get(name, 0) + per_call
+            return fn(*args)
+
+        return counted
+
+
+def count_launches(enable: bool) -> dict[str, int]:
+    """Start (True) or stop (False) counting kernel launches per entry point; returns the counts
+    gathered so far."""
+
+    global _COUNTER
+    counts = dict(_COUNTER.counts) if _COUNTER is not None else {}
+    _COUNTER = _CountingLibrary(load()) if enable else None
+    return counts
+
+
+def load():
     """Load the CUDA library once; raise if it has not been built."""
 
     global _LIB
+    if _COUNTER is not None:
+        return _COUNTER
     if _LIB is None:
         if not LIBRARY_PATH.exists():
             raise RuntimeError(

@@ -36,15 +36,18 @@ _WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
 
 
 def reader_workspace(device: torch.device, batch_heads: int, max_context_tokens: int) -> torch.Tensor:
-    """Zero-initialised scratch shared by every reader call on ``device`` (the kernels
-    leave it zeroed again).  Calls that share it must run on one stream."""
+    """Zero-initialised reader scratch on ``device`` for ``batch_heads`` pairs (the kernels leave
+    it zeroed again).  Layers of equal batch*heads on one device share one tensor, which is never
+    replaced: a layer keeps a reference to the tensor it was given, so an address recorded in a
+    CUDA graph stays valid for as long as that layer lives, whatever other layers or engines the
+    process creates.  Calls that share a workspace must run on one stream."""
 
     lib = _native.load()
     need = int(lib.fl_reader_workspace_bytes(batch_heads, max_context_tokens))
-    key = (device.index if device.index is not None else torch.cuda.current_device(), 0)
+    key = (device.index if device.index is not None else torch.cuda.current_device(), int(batch_heads))
     current = _WORKSPACES.get(key)
     if current is None or current.numel() < need:
-        current = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+        current = torch.zeros(need, dtype=torch.uint8, device=device)
         _WORKSPACES[key] = current
     return current
 
@@ -138,6 +141,8 @@ class CrossLoopKVLayer:
         self._tail_active_host: list[list[list[bool]]] = [[[], []] for _ in range(self.batch)]
         self.context_bound: int | None = None
         self._native = self._make_native()
+        # this layer's reader scratch: held here so that nothing can free it under a recorded graph
+        self._ws = reader_workspace(self._device, self.batch * self.heads, max(caps[0]) + TAIL_CAPACITY)
 
     # ------------------------------------------------------------------ native descriptor
 
@@ -488,8 +493,7 @@ class CrossLoopKVLayer:
         _native.require_cuda(*vectors)
 
     def _workspace(self) -> torch.Tensor:
-        return reader_workspace(self._device, self.batch * self.heads,
-                                max(self._caps[0]) + TAIL_CAPACITY)
+        return self._ws
 
     def reader_status(self) -> int:
         """Synchronise and return the readers' status word: 0, or 1 when a reader gave up
@@ -552,12 +556,15 @@ class CrossLoopKVLayer:
                                            indices: torch.Tensor, valid: torch.Tensor,
                                            source_selected_output: torch.Tensor, global_mass: torch.Tensor,
                                            scaling: float, current_position: int | None = None,
-                                           out: torch.Tensor | None = None) -> torch.Tensor:
+                                           out: torch.Tensor | None = None,
+                                           current_logits_out: torch.Tensor | None = None) -> torch.Tensor:
         """The cached-mass late-loop attention correction
         (flashloop/cache.py:1517-1642): ``global_mass * (subset-softmax target -
         source_selected_output)`` over the valid selected indices.  The current token
         is index quant + tail of each sequence; ``current_position`` is accepted for
-        interface compatibility and checked against it for a batch of one."""
+        interface compatibility and checked against it for a batch of one.
+        ``current_logits_out`` (float32 [batch*heads]) receives the scaled logit of the current
+        token of the heads that selected it (kivi_outer_gemv_cuda.cu:1826-1835)."""
 
         loop = int(loop)
         if loop not in (2, 3):
@@ -588,7 +595,7 @@ class CrossLoopKVLayer:
             C.byref(self._native), loop, _native.ptr(query.contiguous()),
             _native.ptr(current_key.contiguous()), _native.ptr(current_value.contiguous()),
             _native.ptr(idx), _native.ptr(val), int(idx.shape[-1]), _native.ptr(src), _native.ptr(mass),
-            float(scaling), _native.ptr(out), None, _native.ptr(ws), ws.numel(),
+            float(scaling), _native.ptr(out), _native.ptr(current_logits_out), _native.ptr(ws), ws.numel(),
             _native.current_stream(self._device)), "fl_sparse_attention_delta")
         return out
 

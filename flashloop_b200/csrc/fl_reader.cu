@@ -1,11 +1,11 @@
-// Decode-attention readers over the packed anchor + delta streams (row layout).
+// Dense decode-attention reader over the packed anchor + delta streams (row layout).
 //
 //   dense_reader_kernel     one launch: QK^T over streams 0..loop + BF16 tail + current token,
 //                           online softmax, PV; persistent CTAs that each own a contiguous,
 //                           equally large range of 64-token blocks over all (b,h); partials of a
 //                           (b,h) merged by its last-arriving CTA (an atomic ticket, no waiting).
-//   selected_reader_kernel  the same over a gathered list of selected logical indices, stream by
-//                           stream: cached-mass sparse delta, weighted PV, or plain QK.
+//
+// The gathered readers (cached-mass sparse delta, weighted PV, selected QK) live in fl_selected.cu.
 //
 // Work decomposition: a warp handles eight tokens per step, one per lane quad; lane `sub` of a
 // quad owns channels 32*sub .. 32*sub+31 of the token's K row and V row, i.e. one 16-byte
@@ -18,322 +18,10 @@
 // centre * s_c)), the per-token V scale into the probability (W = p * s).  Products accumulate
 // in float16 pairs over at most eight terms (K) or one group (V) and are then widened to
 // float32.
-#include <climits>
-#include <cstdlib>
-
-#include "fl_common.cuh"
+#include "fl_reader_common.cuh"
 
 namespace fl {
 namespace {
-
-constexpr int kPartialStride = 132;  // acc[128], running max (log2 domain), denominator, pad
-constexpr int kMaxSplits = 64;
-
-struct ReaderParams {
-  LayerView L;
-  int loop;
-  const __nv_bfloat16* q;
-  const __nv_bfloat16* kcur;
-  const __nv_bfloat16* vcur;
-  float scaling;
-  float scaling_log2;
-  float* out;
-  float* logits;
-  int64_t logits_stride;
-  float* partial;
-  int* tickets;
-  int* status;
-  int max_chunks;
-  // selected readers
-  const int32_t* indices;
-  const uint8_t* valid;
-  int capacity;
-  int slots_per_cta;
-  const float* weights;
-  const float* source_out;
-  const float* mass;
-  float* cur_logits;
-};
-
-// ------------------------------------------------------------------------------ code handling
-
-template <int BITS>
-struct Codes;
-template <>
-struct Codes<4> {
-  uint32_t w[4];
-};
-template <>
-struct Codes<2> {
-  uint32_t w[2];
-};
-
-template <int BITS>
-__device__ __forceinline__ Codes<BITS> load_codes_shared(const uint8_t* piece) {
-  Codes<BITS> c;
-  if constexpr (BITS == 4) {
-    const uint4 v = *reinterpret_cast<const uint4*>(piece);
-    c.w[0] = v.x; c.w[1] = v.y; c.w[2] = v.z; c.w[3] = v.w;
-  } else {
-    const uint2 v = *reinterpret_cast<const uint2*>(piece);
-    c.w[0] = v.x; c.w[1] = v.y;
-  }
-  return c;
-}
-
-template <int BITS>
-constexpr int kCentre = 1 << (BITS - 1);
-
-// Channel (0..31 within the lane) held by half `hi` of pair `p` after unpack_centred.
-template <int BITS>
-__host__ __device__ constexpr int pair_channel(int p, int hi) {
-  return BITS == 4 ? (p / 4) * 8 + (p % 4) + 4 * hi : (p / 8) * 16 + (p % 8) + 8 * hi;
-}
-// Inverse: accumulator slot 2*p + hi of the lane's channel cc.
-template <int BITS>
-__host__ __device__ constexpr int channel_slot(int cc) {
-  return BITS == 4 ? 2 * ((cc / 8) * 4 + (cc % 8) % 4) + (cc % 8) / 4
-                   : 2 * ((cc / 16) * 8 + (cc % 16) % 8) + (cc % 16) / 8;
-}
-
-// The lane's 32 codes as 16 half2 of exact integers (code - centre), in pair order.
-template <int BITS>
-__device__ __forceinline__ void unpack_centred(const Codes<BITS>& c, __half2 (&h)[16]) {
-  const uint32_t kMagic = 0x64006400u;
-  if constexpr (BITS == 4) {
-    const __half2 kOff = __floats2half2_rn(1032.f, 1032.f);
-    const __half2 k16th = __floats2half2_rn(0.0625f, 0.0625f);
-    const __half2 kOff16 = __floats2half2_rn(-72.f, -72.f);
-#pragma unroll
-    for (int wd = 0; wd < 4; ++wd) {
-      const uint32_t w = c.w[wd];
-      const uint32_t w8 = w >> 8;
-      h[4 * wd + 0] = __hsub2(as_half2(and_or(w, 0x000F000Fu, kMagic)), kOff);
-      h[4 * wd + 1] = __hfma2(as_half2(and_or(w, 0x00F000F0u, kMagic)), k16th, kOff16);
-      h[4 * wd + 2] = __hsub2(as_half2(and_or(w8, 0x000F000Fu, kMagic)), kOff);
-      h[4 * wd + 3] = __hfma2(as_half2(and_or(w8, 0x00F000F0u, kMagic)), k16th, kOff16);
-    }
-  } else {
-    const __half2 kOff = __floats2half2_rn(1026.f, 1026.f);
-    const __half2 k4th = __floats2half2_rn(0.25f, 0.25f);
-    const __half2 kOff4 = __floats2half2_rn(-258.f, -258.f);
-    const __half2 k16th = __floats2half2_rn(0.0625f, 0.0625f);
-    const __half2 kOff16 = __floats2half2_rn(-66.f, -66.f);
-    const __half2 k64th = __floats2half2_rn(0.015625f, 0.015625f);
-    const __half2 kOff64 = __floats2half2_rn(-18.f, -18.f);
-#pragma unroll
-    for (int wd = 0; wd < 2; ++wd) {
-      const uint32_t w = c.w[wd];
-      const uint32_t w8 = w >> 8;
-      h[8 * wd + 0] = __hsub2(as_half2(and_or(w, 0x00030003u, kMagic)), kOff);
-      h[8 * wd + 1] = __hfma2(as_half2(and_or(w, 0x000C000Cu, kMagic)), k4th, kOff4);
-      h[8 * wd + 2] = __hfma2(as_half2(and_or(w, 0x00300030u, kMagic)), k16th, kOff16);
-      h[8 * wd + 3] = __hfma2(as_half2(and_or(w, 0x00C000C0u, kMagic)), k64th, kOff64);
-      h[8 * wd + 4] = __hsub2(as_half2(and_or(w8, 0x00030003u, kMagic)), kOff);
-      h[8 * wd + 5] = __hfma2(as_half2(and_or(w8, 0x000C000Cu, kMagic)), k4th, kOff4);
-      h[8 * wd + 6] = __hfma2(as_half2(and_or(w8, 0x00300030u, kMagic)), k16th, kOff16);
-      h[8 * wd + 7] = __hfma2(as_half2(and_or(w8, 0x00C000C0u, kMagic)), k64th, kOff64);
-    }
-  }
-}
-
-// K, fast path: sum over the lane's 32 channels of w_c * (code_c - centre).
-template <int BITS>
-__device__ __forceinline__ float k_dot_fast(const Codes<BITS>& c, const __half2 (&mult)[16]) {
-  __half2 h[16];
-  unpack_centred<BITS>(c, h);
-  __half2 a0 = __hmul2(h[0], mult[0]);
-  __half2 a1 = __hmul2(h[1], mult[1]);
-#pragma unroll
-  for (int p = 2; p < 16; p += 2) {
-    a0 = __hfma2(h[p], mult[p], a0);
-    a1 = __hfma2(h[p + 1], mult[p + 1], a1);
-  }
-  const float2 f0 = __half22float2(a0);
-  const float2 f1 = __half22float2(a1);
-  return (f0.x + f0.y) + (f1.x + f1.y);
-}
-
-template <int BITS>
-__device__ __forceinline__ void v_accumulate(const Codes<BITS>& c, __half2 w, __half2 (&hacc)[16]) {
-  __half2 h[16];
-  unpack_centred<BITS>(c, h);
-#pragma unroll
-  for (int p = 0; p < 16; ++p) hacc[p] = __hfma2(h[p], w, hacc[p]);
-}
-
-__device__ __forceinline__ void flush_pairs(__half2 (&hacc)[16], float (&acc)[32]) {
-#pragma unroll
-  for (int p = 0; p < 16; ++p) {
-    const float2 f = __half22float2(hacc[p]);
-    acc[2 * p] += f.x;
-    acc[2 * p + 1] += f.y;
-    hacc[p] = __floats2half2_rn(0.f, 0.f);
-  }
-}
-
-__device__ __forceinline__ float quad_sum(float v) {
-  v += __shfl_xor_sync(0xffffffffu, v, 1);
-  v += __shfl_xor_sync(0xffffffffu, v, 2);
-  return v;
-}
-__device__ __forceinline__ float across_quads_max(float v) {
-  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
-  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
-  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
-  return v;
-}
-__device__ __forceinline__ float across_quads_sum(float v) {
-  v += __shfl_xor_sync(0xffffffffu, v, 4);
-  v += __shfl_xor_sync(0xffffffffu, v, 8);
-  v += __shfl_xor_sync(0xffffffffu, v, 16);
-  return v;
-}
-
-// The lane's 32 bf16 channels of a BF16 row (tail or current token): dot with q / weighted add.
-__device__ __forceinline__ void load_bf16_row(const __nv_bfloat16* row, int sub, uint32_t (&w)[16]) {
-#pragma unroll
-  for (int v = 0; v < 4; ++v) {
-    const uint4 x = ldg128(row + sub * 32 + v * 8);
-    w[4 * v + 0] = x.x; w[4 * v + 1] = x.y; w[4 * v + 2] = x.z; w[4 * v + 3] = x.w;
-  }
-}
-
-struct OnlineState {
-  float m;        // running maximum of the scaled logits, log2 domain
-  float l;        // sum of probabilities of this lane's tokens (equal in the 4 lanes of a quad)
-  float vbias;    // sum of p * (v_min + centre * v_scale) of the lane's channel group
-  float acc[32];  // sum of p * v_scale * (code - centre), pair order
-};
-
-__device__ __forceinline__ void state_init(OnlineState& s) {
-  s.m = -INFINITY;
-  s.l = 0.f;
-  s.vbias = 0.f;
-#pragma unroll
-  for (int i = 0; i < 32; ++i) s.acc[i] = 0.f;
-}
-
-// Raise the running maximum to at least `mx` (warp-uniform) and rescale the sums.
-__device__ __forceinline__ void state_raise(OnlineState& s, float mx) {
-  if (mx > s.m) {
-    const float r = exp2f(s.m - mx);  // exp2f(-inf) == 0 on the first raise
-    s.l *= r;
-    s.vbias *= r;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) s.acc[i] *= r;
-    s.m = mx;
-  }
-}
-
-// Reduce the warp's state over its eight quads and park it in shared memory as
-// acc[128] (natural channel order), m, l.
-template <int BITS>
-__device__ __forceinline__ void state_store(OnlineState& s, int lane, float* dst) {
-  const int sub = lane & 3;
-#pragma unroll
-  for (int i = 0; i < 32; ++i) s.acc[i] = across_quads_sum(s.acc[i]);
-  const float vb = across_quads_sum(s.vbias);
-  const float l = across_quads_sum(s.l);
-  if (lane < 4) {
-#pragma unroll
-    for (int cc = 0; cc < 32; ++cc) dst[sub * 32 + cc] = s.acc[channel_slot<BITS>(cc)] + vb;
-    if (lane == 0) {
-      dst[128] = s.m;
-      dst[129] = l;
-    }
-  }
-}
-
-// CTA-level merge of the warps' states, publication of the partial and, in the last CTA of
-// this (b,h), the merge over all partials.  Returns true in the CTA that holds the final
-// result: `total` (this thread's channel, un-normalised) and `denom`.
-template <int NWARPS>
-__device__ __forceinline__ bool merge_and_publish(const ReaderParams& p, float (*s_merge)[kPartialStride],
-                                                  int* s_last, int64_t bh, int slot, int nslots,
-                                                  float& total, float& denom) {
-  const int c = threadIdx.x & (kHeadDim - 1);
-  const bool worker = threadIdx.x < kHeadDim;
-  __syncthreads();
-  float mmax = -INFINITY;
-#pragma unroll
-  for (int w = 0; w < NWARPS; ++w) mmax = fmaxf(mmax, s_merge[w][128]);
-  float a = 0.f, l = 0.f;
-#pragma unroll
-  for (int w = 0; w < NWARPS; ++w) {
-    const float mw = s_merge[w][128];
-    const float r = (mw == -INFINITY) ? 0.f : exp2f(mw - mmax);
-    a += s_merge[w][c] * r;
-    l += s_merge[w][129] * r;
-  }
-  if (nslots == 1) {
-    total = a;
-    denom = l;
-    return true;
-  }
-  float* mine = p.partial + (bh * p.max_chunks + slot) * kPartialStride;
-  if (worker) mine[c] = a;
-  if (threadIdx.x == 0) {
-    mine[128] = mmax;
-    mine[129] = l;
-  }
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const int t = atomicAdd(p.tickets + bh, 1);
-    *s_last = (t == nslots - 1);
-    if (t == nslots - 1) p.tickets[bh] = 0;  // ready for the next launch
-  }
-  __syncthreads();
-  if (!*s_last) return false;
-  __threadfence();
-  const float* base = p.partial + bh * p.max_chunks * kPartialStride;
-  float gm = -INFINITY;
-  for (int j = 0; j < nslots; ++j) gm = fmaxf(gm, __ldcg(base + j * kPartialStride + 128));
-  a = 0.f;
-  l = 0.f;
-  for (int j = 0; j < nslots; ++j) {
-    const float mj = __ldcg(base + j * kPartialStride + 128);
-    const float r = (mj == -INFINITY) ? 0.f : exp2f(mj - gm);
-    a += __ldcg(base + j * kPartialStride + c) * r;
-    l += __ldcg(base + j * kPartialStride + 129) * r;
-  }
-  total = a;
-  denom = l;
-  return true;
-}
-
-// One BF16 row (tail or current token) for every quad of the warp: logits, online softmax, PV.
-__device__ __forceinline__ float bf16_words_dot(const uint32_t (&w)[16], int sub, const float* s_qf) {
-  float dot = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    dot = fmaf(bf16_lo(w[i]), s_qf[sub * 32 + 2 * i], dot);
-    dot = fmaf(bf16_hi(w[i]), s_qf[sub * 32 + 2 * i + 1], dot);
-  }
-  return dot;
-}
-template <int BITS>
-__device__ __forceinline__ void bf16_words_accumulate(const uint32_t (&w)[16], float pr, float (&acc)[32]) {
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    acc[channel_slot<BITS>(2 * i)] = fmaf(pr, bf16_lo(w[i]), acc[channel_slot<BITS>(2 * i)]);
-    acc[channel_slot<BITS>(2 * i + 1)] = fmaf(pr, bf16_hi(w[i]), acc[channel_slot<BITS>(2 * i + 1)]);
-  }
-}
-template <int BITS>
-__device__ __forceinline__ float bf16_row_dot(const __nv_bfloat16* row, int sub, const float* s_qf) {
-  uint32_t w[16];
-  load_bf16_row(row, sub, w);
-  return bf16_words_dot(w, sub, s_qf);
-}
-template <int BITS>
-__device__ __forceinline__ void bf16_row_accumulate(const __nv_bfloat16* row, int sub, float pr,
-                                                    float (&acc)[32]) {
-  uint32_t w[16];
-  load_bf16_row(row, sub, w);
-  bf16_words_accumulate<BITS>(w, pr, acc);
-}
 
 // ------------------------------------------------------------------------------ dense reader
 //
@@ -363,9 +51,6 @@ struct Stage {
   static_assert(kGroup * kRecord <= kBytes, "a V unit must fit the stage");
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* ptr) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(ptr));
-}
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -953,550 +638,15 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   if (timed_out && lane == 0) atomicExch(p.status, 1);
 }
 
-// ------------------------------------------------------------------------------ selected readers
-//
-// Stream-major gather.  A selected token owns a row in streams 0 and 1 and, where the token was
-// retained, in the compact streams 2 and 3, so a token-major walk would run every stream for all
-// eight tokens of a pass whenever one of them holds a compact row.  Here every stream is packed
-// by itself instead.  A CTA stages a batch of slots (one per thread), builds per stream the list
-// of the slots that hold a row there, and cuts the work into passes of at most eight rows of ONE
-// stream:
-//
-//   K pass: up to eight rows of one stream that share a K metadata group (for the compact
-//           streams that is a group of 64 compact rows, about 256 tokens wide, so their passes
-//           are as full as those of streams 0 and 1).  The warp builds the group's query-folded
-//           table (w_c = q_c * scale_c in float16, bias in float32) as the dense reader does and
-//           writes one partial logit per row to shared memory.
-//   softmax: after a CTA barrier every thread sums the partial logits of its slot over the
-//           streams in a fixed order; the batch maximum raises the CTA's running maximum (online
-//           softmax at batch granularity) and the probability goes to shared memory.
-//   V pass: any eight records of one stream: p * v_scale * (code - centre) into the warp's
-//           float16-pair accumulators, widened every sixteen passes.
-//
-// The passes of a warp are independent of each other, so each warp runs them through a private
-// ring of kDepth shared-memory stages filled by 16-byte cp.async copies that every lane issues
-// for the pieces it will read itself; the V passes of a batch are already on their way while the
-// CTA is still in the softmax barrier.  Tail tokens and the current token (BF16 rows) are passes
-// of their own that read global memory directly.
-//
-// Indices need not be sorted for correctness (an unsorted list only makes more, shorter K passes).
-
-enum { kModeDelta = 0, kModePV = 1, kModeQK = 2 };
-constexpr int kGatherWarps = 8;
-constexpr int kGatherThreads = kGatherWarps * kWarp;
-constexpr int kSlotBatch = kGatherThreads;  // slots staged per round: one per thread
-constexpr int kDepth = 4;                   // passes in flight per warp
-constexpr int kPassBytes = 1024;            // K: 8 rows (<= 512 B) + one metadata group (512 B); V: 8 records (<= 640 B)
-constexpr int kTailClass = 4;               // list of the slots that are tail tokens or the current token
-constexpr int kGatherCtasPerSm = 2;
-static_assert(kGatherWarps * kDepth * kPassBytes >= kGatherWarps * kPartialStride * 4,
-              "the merge buffer reuses the rings");
-
-template <int BYTES>
-__device__ __forceinline__ void cp_async(uint32_t dst_shared, const void* src_global) {
-  if constexpr (BYTES == 16) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_shared), "l"(src_global) : "memory");
-  } else {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(dst_shared), "l"(src_global), "n"(BYTES)
-                 : "memory");
-  }
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-// The K table of one metadata group, this lane's four channels 4*lane .. 4*lane+3: w_c = q_c *
-// scale_c as float16 in the pair order of unpack_centred (the products are exact in float32, so
-// rounding them once in float16 arithmetic gives the same table), stored with one 8-byte write
-// per lane after the lanes that hold the two halves of a pair have swapped one register.
-template <int BITS>
-__device__ __forceinline__ void table_store(__half* table, int lane, __half2 q01, __half2 q23, uint2 scale) {
-  constexpr int kPartner = BITS == 4 ? 1 : 2;  // pairs are (c, c + 4) or (c, c + 8)
-  const __half2 a = __hmul2(q01, as_half2(scale.x));
-  const __half2 b = __hmul2(q23, as_half2(scale.y));
-  const bool first = (lane & kPartner) == 0;
-  const uint32_t mine_a = as_u32(a), mine_b = as_u32(b);
-  const uint32_t got = __shfl_xor_sync(0xffffffffu, first ? mine_b : mine_a, kPartner);
-  const uint32_t lo = first ? mine_a : got, hi = first ? got : mine_b;
-  uint2 out;
-  out.x = __byte_perm(lo, hi, 0x5410);  // (lo.low, hi.low)
-  out.y = __byte_perm(lo, hi, 0x7632);  // (lo.high, hi.high)
-  int at;  // in halves
-  if constexpr (BITS == 4) {
-    at = 4 * lane;
-  } else {
-    at = 16 * (lane >> 2) + 8 * ((lane >> 1) & 1) + 4 * (lane & 1);
-  }
-  *reinterpret_cast<uint2*>(table + at) = out;
-}
-
-// The rows to read form one list per batch: the entries of stream 0 in slot order, then those of
-// stream 1, 2 and 3.  An entry is (stream << 30) | row, so a stream holds fewer than 2^30 rows
-// over all (b,h) pairs.  A V pass is any eight consecutive entries; a K pass is described by 16
-// bits: first entry in bits 0..9, rows - 1 in bits 10..12.
-constexpr int kMaxEntries = 4 * kSlotBatch;
-
-// STREAMS = loop + 1 is a template parameter, so that the staging of a batch touches only the
-// streams the loop reads.
-template <int BITS, int MODE, int STREAMS>
-__global__ void __launch_bounds__(kGatherThreads, kGatherCtasPerSm)
-selected_reader_kernel(const __grid_constant__ ReaderParams p) {
-  constexpr int kRowBytes = 16 * BITS;
-  constexpr int kRecord = kRowBytes + 16;
-  constexpr int kLaneBytes = kRowBytes / 4;
-  constexpr uint32_t kFull = 0xffffffffu;
-  extern __shared__ __align__(128) uint8_t s_ring[];  // [warp][stage][kPassBytes]
-  __shared__ __align__(16) float s_qf[kHeadDim];
-  __shared__ __align__(16) __half s_wtab[kGatherWarps][kHeadDim];  // the current K pass's table
-  __shared__ uint32_t s_entry[kMaxEntries];
-  __shared__ float s_eval[kMaxEntries];     // per entry: its partial logit, then its probability (or weight)
-  __shared__ uint16_t s_kdesc[kMaxEntries];
-  __shared__ int s_kgroup[kMaxEntries];     // per K pass: its metadata group, counted over all (b,h)
-  __shared__ int s_tail[kSlotBatch];        // tail class: ring slot of the entry, -1 = the current token
-  __shared__ float s_tval[kSlotBatch];      // ... and its logit, then probability
-  __shared__ int s_wcount[5][kGatherWarps], s_woff[5][kGatherWarps];
-  __shared__ int s_whead[4][kGatherWarps], s_wfirst[4][kGatherWarps];
-  __shared__ int s_count[5], s_ebase[5];    // entries per class; first entry of every stream, then the total
-  __shared__ int s_nk_packed;
-  __shared__ int s_rbase[4], s_gbase[4];    // first row / first K metadata group of this (b,h) in every stream
-  __shared__ const uint8_t* s_kptr[4];
-  __shared__ const uint8_t* s_vptr[4];
-  __shared__ float s_red[kGatherWarps];
-  __shared__ int s_last;
-
-  const LayerView& L = p.L;
-  const int64_t bh = blockIdx.y;
-  const int b = static_cast<int>(bh / L.heads);
-  const int32_t* st = L.seq_state + b * FL_STATE_WORDS;
-  const int quant = st[FL_STATE_QUANT_TOKENS];
-  const int tail_len = st[FL_STATE_TAIL_LEN];
-  const int tail_start = st[FL_STATE_TAIL_START];
-  const int cur_pos = quant + tail_len;
-  const int nsplits = (p.capacity + p.slots_per_cta - 1) / p.slots_per_cta;
-  const int split = blockIdx.x;
-  const int slot_begin = split * p.slots_per_cta;
-  const int slot_end = min(p.capacity, slot_begin + p.slots_per_cta);
-  constexpr int streams = STREAMS;
-
-  const int tid = threadIdx.x;
-  const int lane = tid & 31;
-  const int warp = tid >> 5;
-  const int quad = lane >> 2;
-  const int sub = lane & 3;
-  const uint32_t lanes_below = (1u << lane) - 1u;
-  uint8_t* const my_ring = s_ring + warp * kDepth * kPassBytes;
-  const uint32_t my_ring_u32 = smem_u32(my_ring);
-  const int codes_at = quad * kRowBytes + sub * kLaneBytes;  // this lane's codes within a stage
-  float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);                // query channels 4*lane .. 4*lane+3
-  __half2 q01 = __floats2half2_rn(0.f, 0.f), q23 = q01;
-  if constexpr (MODE != kModePV) {
-    if (tid < kHeadDim) s_qf[tid] = __bfloat162float(p.q[bh * kHeadDim + tid]);
-    const uint2 raw = ldg64(p.q + bh * kHeadDim + 4 * lane);
-    q4 = make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
-    q01 = __floats2half2_rn(q4.x, q4.y);
-    q23 = __floats2half2_rn(q4.z, q4.w);
-  }
-  if (tid < 4) {
-    const bool have = tid < streams;
-    s_rbase[tid] = have ? static_cast<int>(L.row_base[tid][bh]) : 0;
-    s_gbase[tid] = have ? static_cast<int>(L.group_base[tid][bh]) : 0;
-    s_kptr[tid] = have ? L.k_codes[tid] : nullptr;
-    s_vptr[tid] = have ? L.v_rows[tid] : nullptr;
-  }
-
-  OnlineState S;
-  state_init(S);
-  float m_run = MODE == kModePV ? 0.f : -INFINITY;  // the CTA's running maximum (uniform)
-  float l_mine = 0.f;                                // sum of the probabilities of this thread's slots
-  const int32_t* idx_row = p.indices + bh * p.capacity;
-  const uint8_t* valid_row = p.valid ? p.valid + bh * p.capacity : nullptr;
-  const __nv_bfloat16* tk = L.tail_k[p.loop] + bh * L.tail_capacity * kHeadDim;
-  const __nv_bfloat16* tv = L.tail_v[p.loop] + bh * L.tail_capacity * kHeadDim;
-  __half2 hacc[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) hacc[i] = __floats2half2_rn(0.f, 0.f);
-  int v_passes = 0;
-
-  // equal batches: 410 slots are staged as 205 + 205, not 256 + 154
-  const int n_batches = (slot_end - slot_begin + kSlotBatch - 1) / kSlotBatch;
-  const int batch_size = n_batches > 0 ? (slot_end - slot_begin + n_batches - 1) / n_batches : kSlotBatch;
-  for (int batch_begin = slot_begin; batch_begin < slot_end; batch_begin += batch_size) {
-    const int batch_n = min(batch_size, slot_end - batch_begin);
-    __syncthreads();  // the previous round's lists and rings are no longer read (and the bases are written)
-    // ---- stage this round's slots: index, the row in every stream, class
-    int idx = -1;
-    bool live = false;    // the slot has something to read
-    uint32_t member = 0;  // bit c: the slot is on list c
-    int rows[5] = {-1, -1, -1, -1, -1};
-    float weight = 0.f;
-    if (tid < batch_n) {
-      const int j = batch_begin + tid;
-      if constexpr (MODE == kModePV) weight = p.weights[bh * p.capacity + j];
-      if (!valid_row || valid_row[j]) idx = idx_row[j];
-      if (idx >= 0 && idx < quant) {
-        live = true;
-        rows[0] = idx;
-        if (streams >= 2) rows[1] = idx;
-        if (streams >= 3) rows[2] = L.rank[0][L.rank_base[b] + idx];
-        if (streams >= 4) rows[3] = L.rank[1][L.rank_base[b] + idx];
-      } else if (idx >= quant) {
-        const bool has_current = (MODE == kModePV) ? p.vcur != nullptr : p.kcur != nullptr;
-        if (idx - quant < tail_len) {
-          live = true;
-          member = 1u << kTailClass;
-          rows[4] = (tail_start + idx - quant) % L.tail_capacity;
-        } else if (idx == cur_pos && has_current) {
-          live = true;
-          member = 1u << kTailClass;
-        }
-      }
-      if constexpr (MODE == kModeQK) {
-        if (!live) p.logits[bh * p.capacity + j] = 0.f;
-      }
-    }
-#pragma unroll
-    for (int s = 0; s < STREAMS; ++s) member |= rows[s] >= 0 ? 1u << s : 0u;
-    // ---- the entry lists: every class in slot order, streams 0..3 back to back
-    int at[5];  // my entry in every class I am a member of
-#pragma unroll
-    for (int c = 0; c < 5; ++c) {
-      if (c >= STREAMS && c != kTailClass) continue;
-      const uint32_t mask = __ballot_sync(kFull, (member >> c) & 1u);
-      at[c] = __popc(mask & lanes_below);
-      if (lane == 0) s_wcount[c][warp] = __popc(mask);
-    }
-    __syncthreads();
-    if (warp == 0) {  // running entry counts over (stream, warp)
-      const int mine = (lane >> 3) < STREAMS ? s_wcount[lane >> 3][lane & 7] : 0;
-      int incl = mine;
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const int up = __shfl_up_sync(kFull, incl, d);
-        if (lane >= d) incl += up;
-      }
-      const int stream_first = __shfl_sync(kFull, incl - mine, lane & ~7);
-      s_woff[lane >> 3][lane & 7] = incl - mine;
-      if ((lane & 7) == 0) s_ebase[lane >> 3] = stream_first;
-      if ((lane & 7) == 7) s_count[lane >> 3] = incl - stream_first;
-      if (lane == 31) s_ebase[4] = incl;
-    } else if (warp == 1 && lane < kGatherWarps) {
-      int off = 0;
-      for (int k = 0; k < lane; ++k) off += s_wcount[kTailClass][k];
-      s_woff[kTailClass][lane] = off;
-      if (lane == kGatherWarps - 1) s_count[kTailClass] = off + s_wcount[kTailClass][lane];
-    }
-    __syncthreads();
-#pragma unroll
-    for (int c = 0; c < 5; ++c) {
-      if (c >= STREAMS && c != kTailClass) continue;
-      at[c] += s_woff[c][warp];
-      if ((member >> c) & 1u) {
-        if (c < 4) {
-          s_entry[at[c]] = (static_cast<uint32_t>(c) << 30) | static_cast<uint32_t>(s_rbase[c] + rows[c]);
-          s_eval[at[c]] = weight;  // the weighted-PV reader's probabilities are the caller's
-        } else {
-          s_tail[at[c]] = rows[4];
-          s_tval[at[c]] = weight;
-        }
-      }
-    }
-    __syncthreads();
-    const int n_entries = s_ebase[4];
-    const int n_tail = s_count[kTailClass];
-    // ---- K passes: entry i of a stream opens a pass where the metadata group changes and every
-    // eight entries after that
-    if constexpr (MODE != kModePV) {
-      uint32_t run_heads[4];
-      bool entry_on[4], run_head[4];
-      int group_of[4];
-#pragma unroll
-      for (int s = 0; s < STREAMS; ++s) {
-        entry_on[s] = tid < s_count[s];
-        const int first = s_ebase[s];
-        const int base = s_rbase[s];
-        group_of[s] = entry_on[s] ? (static_cast<int>(s_entry[first + tid] & 0x3fffffffu) - base) >> 6 : -1;
-        const int before =
-            entry_on[s] && tid > 0 ? (static_cast<int>(s_entry[first + tid - 1] & 0x3fffffffu) - base) >> 6 : -1;
-        run_head[s] = entry_on[s] && (tid == 0 || group_of[s] != before);
-        run_heads[s] = __ballot_sync(kFull, run_head[s]);
-        if (lane == 0) s_whead[s][warp] = run_heads[s] ? warp * 32 + 31 - __clz(run_heads[s]) : -1;
-      }
-      __syncthreads();
-      bool pass_head[4];
-      uint32_t pass_heads[4];
-      int rank[4];
-#pragma unroll
-      for (int s = 0; s < STREAMS; ++s) {
-        int run_start = 0;
-        const uint32_t upto = run_heads[s] & (lanes_below | (1u << lane));
-        if (upto) {
-          run_start = warp * 32 + 31 - __clz(upto);
-        } else {
-          for (int w = warp - 1; w >= 0; --w) {
-            const int h = s_whead[s][w];
-            if (h >= 0) {
-              run_start = h;
-              break;
-            }
-          }
-        }
-        pass_head[s] = entry_on[s] && (run_head[s] || ((tid - run_start) & 7) == 0);
-        pass_heads[s] = __ballot_sync(kFull, pass_head[s]);
-        rank[s] = __popc(pass_heads[s] & lanes_below);
-        if (lane == 0) {
-          s_wcount[s][warp] = __popc(pass_heads[s]);
-          s_wfirst[s][warp] = pass_heads[s] ? warp * 32 + __ffs(pass_heads[s]) - 1 : -1;
-        }
-      }
-      __syncthreads();
-      if (warp == 0) {  // running pass counts over (stream, warp)
-        const int mine = (lane >> 3) < STREAMS ? s_wcount[lane >> 3][lane & 7] : 0;
-        int incl = mine;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-          const int up = __shfl_up_sync(kFull, incl, d);
-          if (lane >= d) incl += up;
-        }
-        s_woff[lane >> 3][lane & 7] = incl - mine;
-        if (lane == 31) s_nk_packed = incl;
-      }
-      __syncthreads();
-#pragma unroll
-      for (int s = 0; s < STREAMS; ++s) {
-        if (pass_head[s]) {
-          int next = s_count[s];
-          const uint32_t above = pass_heads[s] & ~(lanes_below | (1u << lane));
-          if (above) {
-            next = warp * 32 + __ffs(above) - 1;
-          } else {
-            for (int w = warp + 1; w < kGatherWarps; ++w) {
-              const int h = s_wfirst[s][w];
-              if (h >= 0) {
-                next = h;
-                break;
-              }
-            }
-          }
-          const int k = s_woff[s][warp] + rank[s];
-          s_kdesc[k] = static_cast<uint16_t>((s_ebase[s] + tid) | ((next - tid - 1) << 10));
-          s_kgroup[k] = s_gbase[s] + group_of[s];
-        }
-      }
-      __syncthreads();
-    }
-
-    // ---- this warp's passes: K passes warp, warp + 8, ..., then V passes warp, warp + 8, ...
-    const int nk_all = MODE == kModePV ? 0 : s_nk_packed;
-    const int nv_all = MODE == kModeQK ? 0 : (n_entries + 7) >> 3;
-    const int nk_mine = nk_all > warp ? (nk_all - warp + kGatherWarps - 1) / kGatherWarps : 0;
-    const int nv_mine = nv_all > warp ? (nv_all - warp + kGatherWarps - 1) / kGatherWarps : 0;
-    const int n_mine = nk_mine + nv_mine;
-    // Copies of pass q into its stage (one commit group, empty past the end): codes of row i at
-    // i * kRowBytes; behind them the K metadata group (scale[128], min[128]) or the V records' 16
-    // metadata bytes (record i at 512 + 16 i).
-    auto issue = [&](int q) {
-      const uint32_t stage = my_ring_u32 + (q & (kDepth - 1)) * kPassBytes;
-      if (q < nk_mine) {
-        if constexpr (MODE != kModePV) {
-          const int k = warp + kGatherWarps * q;
-          const uint32_t d = s_kdesc[k];
-          const int s = s_entry[d & 1023u] >> 30;
-          if (quad <= static_cast<int>(d >> 10)) {
-            const uint32_t row = s_entry[(d & 1023u) + quad] & 0x3fffffffu;
-            cp_async<kLaneBytes>(stage + codes_at, s_kptr[s] + static_cast<uint64_t>(row) * kRowBytes + sub * kLaneBytes);
-          }
-          const __half* meta = (lane < 16 ? L.k_scale[s] : L.k_min[s]) +
-                               static_cast<int64_t>(s_kgroup[k]) * kHeadDim + (lane & 15) * 8;
-          cp_async<16>(stage + 512 + lane * 16, meta);
-        }
-      } else if (q < n_mine) {
-        if constexpr (MODE != kModeQK) {
-          const int i = 8 * (warp + kGatherWarps * (q - nk_mine)) + quad;
-          if (i < n_entries) {
-            const uint32_t e = s_entry[i];
-            const uint8_t* record = s_vptr[e >> 30] + static_cast<uint64_t>(e & 0x3fffffffu) * kRecord;
-            cp_async<kLaneBytes>(stage + codes_at, record + sub * kLaneBytes);
-            if (sub == 0) cp_async<16>(stage + 512 + quad * 16, record + kRowBytes);
-          }
-        }
-      }
-      cp_async_commit();
-    };
-    auto advance = [&](int q) {
-      cp_async_wait<kDepth - 2>();  // pass q has landed
-      __syncwarp();                 // ... for every lane, and every lane is done with pass q - 1
-      issue(q + kDepth - 1);        // into the stage of pass q - 1
-    };
-
-#pragma unroll
-    for (int q = 0; q < kDepth - 1; ++q) issue(q);
-
-    if constexpr (MODE != kModePV) {
-      for (int q = 0; q < nk_mine; ++q) {
-        advance(q);
-        const uint8_t* stage = my_ring + (q & (kDepth - 1)) * kPassBytes;
-        const uint32_t d = s_kdesc[warp + kGatherWarps * q];
-        // the group's table and bias = sum_c q_c * (min_c + centre * scale_c)
-        const uint2 sc = *reinterpret_cast<const uint2*>(stage + 512 + lane * 8);
-        const uint2 mn = *reinterpret_cast<const uint2*>(stage + 512 + 256 + lane * 8);
-        table_store<BITS>(s_wtab[warp], lane, q01, q23, sc);
-        const float2 sc01 = __half22float2(as_half2(sc.x)), sc23 = __half22float2(as_half2(sc.y));
-        const float2 mn01 = __half22float2(as_half2(mn.x)), mn23 = __half22float2(as_half2(mn.y));
-        const float kcn = float(kCentre<BITS>);
-        float bias = q4.x * fmaf(kcn, sc01.x, mn01.x);
-        bias = fmaf(q4.y, fmaf(kcn, sc01.y, mn01.y), bias);
-        bias = fmaf(q4.z, fmaf(kcn, sc23.x, mn23.x), bias);
-        bias = fmaf(q4.w, fmaf(kcn, sc23.y, mn23.y), bias);
-        const Codes<BITS> kc = load_codes_shared<BITS>(stage + codes_at);
-        bias = warp_sum(bias);
-        __syncwarp();
-        __half2 mult[16];
-        const uint4* tab4 = reinterpret_cast<const uint4*>(&s_wtab[warp][sub * 32]);
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          const uint4 x = tab4[v];
-          mult[4 * v + 0] = as_half2(x.x); mult[4 * v + 1] = as_half2(x.y);
-          mult[4 * v + 2] = as_half2(x.z); mult[4 * v + 3] = as_half2(x.w);
-        }
-        const float dot = quad_sum(k_dot_fast<BITS>(kc, mult)) + bias;
-        if (quad <= static_cast<int>(d >> 10) && sub == 0) s_eval[(d & 1023u) + quad] = dot;
-      }
-      // tail tokens and the current token: BF16 rows, read directly
-      for (int i0 = 8 * warp; i0 < n_tail; i0 += 8 * kGatherWarps) {
-        const int i = i0 + quad;
-        const bool on = i < n_tail;
-        const int ring_slot = on ? s_tail[i] : 0;
-        const __nv_bfloat16* krow = ring_slot < 0 ? p.kcur + bh * kHeadDim : tk + ring_slot * kHeadDim;
-        const float dot = quad_sum(on ? bf16_row_dot<BITS>(krow, sub, s_qf) : 0.f);
-        if (on && sub == 0) s_tval[i] = dot;
-      }
-
-      __syncthreads();  // every K pass of the batch has written its partial logits
-      float logit = 0.f;
-#pragma unroll
-      for (int s = 0; s < STREAMS; ++s) logit += (member >> s) & 1u ? s_eval[at[s]] : 0.f;
-      if ((member >> kTailClass) & 1u) logit = s_tval[at[kTailClass]];
-      if constexpr (MODE == kModeQK) {
-        if (live) p.logits[bh * p.capacity + batch_begin + tid] = logit;
-      } else {
-        if (live && idx == cur_pos && p.cur_logits) p.cur_logits[bh] = logit * p.scaling;
-        const float x = live ? logit * p.scaling_log2 : -INFINITY;
-        const float wmax = warp_max(x);
-        if (lane == 0) s_red[warp] = wmax;
-        __syncthreads();
-        float bmax = s_red[0];
-#pragma unroll
-        for (int w = 1; w < kGatherWarps; ++w) bmax = fmaxf(bmax, s_red[w]);
-        if (bmax > m_run) {
-          const float r = exp2f(m_run - bmax);  // exp2f(-inf) == 0 on the first raise
-          flush_pairs(hacc, S.acc);             // the float16 partial sums belong to the old maximum
-          v_passes = 0;
-          l_mine *= r;
-          S.vbias *= r;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) S.acc[i] *= r;
-          m_run = bmax;
-        }
-        const float pr = live ? exp2f(x - m_run) : 0.f;
-        l_mine += pr;
-#pragma unroll
-        for (int s = 0; s < STREAMS; ++s) {
-          if ((member >> s) & 1u) s_eval[at[s]] = pr;
-        }
-        if ((member >> kTailClass) & 1u) s_tval[at[kTailClass]] = pr;
-        __syncthreads();
-      }
-    }
-
-    if constexpr (MODE != kModeQK) {
-      const uint32_t pick = (sub < 2) ? 0x1010u : 0x3232u;
-      const __half2 centre2 = __floats2half2_rn(float(kCentre<BITS>), float(kCentre<BITS>));
-      for (int q = nk_mine; q < n_mine; ++q) {
-        advance(q);
-        const uint8_t* stage = my_ring + (q & (kDepth - 1)) * kPassBytes;
-        const int i = 8 * (warp + kGatherWarps * (q - nk_mine)) + quad;
-        const bool on = i < n_entries;
-        const float pr = on ? s_eval[i] : 0.f;
-        const __half2 p2 = __float2half2_rn(pr);
-        const Codes<BITS> vc = load_codes_shared<BITS>(stage + codes_at);
-        const uint2 vmeta = *reinterpret_cast<const uint2*>(stage + 512 + quad * 16);
-        const __half2 vm2 = as_half2(on ? __byte_perm(vmeta.x, 0u, pick) : 0u);
-        const __half2 vs2 = as_half2(on ? __byte_perm(vmeta.y, 0u, pick) : 0u);
-        const __half2 hb = __hfma2(centre2, vs2, vm2);
-        v_accumulate<BITS>(vc, __hmul2(p2, vs2), hacc);
-        S.vbias = fmaf(pr, __low2float(hb), S.vbias);
-        // at most 16 float16 terms per accumulator before widening
-        if ((++v_passes & 15) == 0) flush_pairs(hacc, S.acc);
-      }
-      for (int i0 = 8 * warp; i0 < n_tail; i0 += 8 * kGatherWarps) {
-        const int i = i0 + quad;
-        if (i < n_tail) {
-          const int ring_slot = s_tail[i];
-          const __nv_bfloat16* vrow = ring_slot < 0 ? p.vcur + bh * kHeadDim : tv + ring_slot * kHeadDim;
-          bf16_row_accumulate<BITS>(vrow, sub, s_tval[i], S.acc);
-        }
-      }
-    }
-    cp_async_wait<0>();
-  }
-  if constexpr (MODE == kModeQK) return;
-  flush_pairs(hacc, S.acc);
-  S.m = m_run;
-
-  __syncthreads();  // every warp has left its ring: the rings become the merge buffer
-  float (*s_merge)[kPartialStride] = reinterpret_cast<float (*)[kPartialStride]>(s_ring);
-  state_store<BITS>(S, lane, s_merge[warp]);
-  const float l_warp = warp_sum(l_mine);
-  if (lane == 0) s_merge[warp][129] = l_warp;
-  float total, denom;
-  if (merge_and_publish<kGatherWarps>(p, s_merge, &s_last, bh, split, nsplits, total, denom)) {
-    const int c = threadIdx.x;
-    if (c < kHeadDim) {
-      if constexpr (MODE == kModeDelta) {
-        const float target = denom > 0.f ? total / denom : 0.f;
-        p.out[bh * kHeadDim + c] = p.mass[bh] * (target - p.source_out[bh * kHeadDim + c]);
-      } else {
-        p.out[bh * kHeadDim + c] = total;
-      }
-    }
-  }
-}
-
 // ------------------------------------------------------------------------------ host side
 
 // Grid of the persistent dense reader: two CTAs per SM, but never more CTAs than there are tail
 // units, so that every CTA's share of the units is non-empty whatever the context lengths are.
 unsigned dense_grid(int64_t batch_heads) {
-  static const int sm_count = [] {
-    int dev = 0, n = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    return n > 0 ? n : 148;
-  }();
+  const int sm_count = device_sm_count();
   const int64_t ctas = 2 * static_cast<int64_t>(sm_count < 148 ? sm_count : 148);
   const int64_t cap = batch_heads * kTailUnits;
   return static_cast<unsigned>(cap < ctas ? cap : ctas);
-}
-
-int choose_slots_per_cta(int64_t batch_heads, int64_t capacity) {
-  // One wave: the grid is kept within the CTAs of the gather kernel that are resident at once
-  // where the capacity allows it (a second, partial wave would cost a whole round).
-  const int64_t budget = 148 * kGatherCtasPerSm;
-  int64_t slots = 32;
-  while ((batch_heads * ((capacity + slots - 1) / slots) > budget || (capacity + slots - 1) / slots > kMaxSplits) &&
-         slots < capacity)
-    slots += 32;
-  return static_cast<int>(slots);
-}
-
-// tickets[batch_heads] and one status word, padded to 256 bytes
-size_t tickets_bytes(int64_t batch_heads) { return (((batch_heads + 3) * sizeof(int) + 255) / 256) * 256; }
-
-// Partial slots per (b,h).  The selected readers split a head over at most kMaxSplits CTAs; the
-// dense reader needs two slots per CTA, at most 2 * 8 * batch_heads in all.
-int max_partials() {
-  static_assert(kMaxSplits >= 2 * kTailUnits, "the dense reader's partials must fit the workspace");
-  return kMaxSplits;
 }
 
 }  // namespace
@@ -1533,17 +683,15 @@ using namespace fl;
 
 extern "C" size_t fl_reader_workspace_bytes(int64_t batch_heads, int64_t max_context_tokens) {
   if (batch_heads <= 0 || max_context_tokens < 0) return 0;
-  return tickets_bytes(batch_heads) +
-         static_cast<size_t>(batch_heads) * max_partials() * kPartialStride *
-             sizeof(float);
+  return workspace_bytes(batch_heads);
 }
 
 extern "C" int fl_workspace_status(const void* workspace, int64_t batch_heads, int32_t* status,
                                    fl_cuda_stream stream) {
   FL_REQUIRE(workspace != nullptr && status != nullptr && batch_heads > 0, "fl_workspace_status: bad argument");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  cudaError_t err = cudaMemcpyAsync(status, static_cast<const int*>(workspace) + batch_heads, sizeof(int32_t),
-                                    cudaMemcpyDeviceToHost, s);
+  // the status word is the first word of the workspace, whatever batch_heads is
+  cudaError_t err = cudaMemcpyAsync(status, workspace, sizeof(int32_t), cudaMemcpyDeviceToHost, s);
   if (err == cudaSuccess) err = cudaStreamSynchronize(s);
   if (err != cudaSuccess) {
     set_error("fl_workspace_status: %s", cudaGetErrorString(err));
@@ -1561,27 +709,6 @@ extern "C" int fl_workspace_init(void* workspace, size_t bytes, fl_cuda_stream s
   }
   return FL_OK;
 }
-
-namespace {
-
-int fill_common(ReaderParams& p, const fl_layer* layer, int loop, void* workspace, size_t workspace_bytes,
-                int64_t max_context_tokens, const char* who) {
-  const int64_t bh = static_cast<int64_t>(layer->batch) * layer->heads;
-  const size_t need = fl_reader_workspace_bytes(bh, max_context_tokens);
-  if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) {
-    set_error("%s: workspace of %zu bytes (16-byte aligned) required, got %zu", who, need, workspace_bytes);
-    return FL_ERR_WORKSPACE;
-  }
-  p.L = make_view(*layer);
-  p.loop = loop;
-  p.tickets = static_cast<int*>(workspace);
-  p.status = p.tickets + bh;
-  p.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + tickets_bytes(bh));
-  p.max_chunks = max_partials();
-  return FL_OK;
-}
-
-}  // namespace
 
 namespace fl {
 namespace {
@@ -1627,9 +754,7 @@ extern "C" int fl_dense_source_attention(const fl_layer* layer, int32_t loop, co
   FL_REQUIRE(!logits || logits_stride > max_context_tokens,
              "fl_dense_source_attention: logits_stride must exceed max_context_tokens");
   ReaderParams p{};
-  if (int rc = fill_common(p, layer, loop, workspace, workspace_bytes, max_context_tokens,
-                           "fl_dense_source_attention"))
-    return rc;
+  if (int rc = bind_workspace(p, layer, loop, workspace, workspace_bytes, "fl_dense_source_attention")) return rc;
   const int64_t bh = static_cast<int64_t>(layer->batch) * layer->heads;
   p.q = static_cast<const __nv_bfloat16*>(query);
   p.kcur = static_cast<const __nv_bfloat16*>(current_key);
@@ -1648,120 +773,6 @@ extern "C" int fl_dense_source_attention(const fl_layer* layer, int32_t loop, co
   FL_CHECK_LAUNCH("fl_dense_source_attention");
   return FL_OK;
 }
-
-namespace {
-
-template <int BITS, int MODE, int STREAMS>
-void launch_selected_as(const dim3 grid, const ReaderParams& p, cudaStream_t s) {
-  constexpr int kSmem = kGatherWarps * kDepth * kPassBytes;
-  static const cudaError_t attr = cudaFuncSetAttribute(
-      selected_reader_kernel<BITS, MODE, STREAMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-  (void)attr;
-  selected_reader_kernel<BITS, MODE, STREAMS><<<grid, kGatherThreads, kSmem, s>>>(p);
-}
-
-template <int BITS, int MODE>
-void launch_selected_bits(const dim3 grid, const ReaderParams& p, cudaStream_t s) {
-  switch (p.loop) {
-    case 0: launch_selected_as<BITS, MODE, 1>(grid, p, s); break;
-    case 1: launch_selected_as<BITS, MODE, 2>(grid, p, s); break;
-    case 2: launch_selected_as<BITS, MODE, 3>(grid, p, s); break;
-    default: launch_selected_as<BITS, MODE, 4>(grid, p, s); break;
-  }
-}
-
-template <int MODE>
-int launch_selected(const fl_layer* layer, ReaderParams& p, cudaStream_t s, const char* who) {
-  const int64_t bh = static_cast<int64_t>(layer->batch) * layer->heads;
-  p.slots_per_cta = choose_slots_per_cta(bh, p.capacity);
-  const int splits = (p.capacity + p.slots_per_cta - 1) / p.slots_per_cta;
-  const dim3 grid(splits, static_cast<unsigned>(bh));
-  if (layer->bits == 4) {
-    launch_selected_bits<4, MODE>(grid, p, s);
-  } else {
-    launch_selected_bits<2, MODE>(grid, p, s);
-  }
-  FL_CHECK_LAUNCH(who);
-  return FL_OK;
-}
-
-}  // namespace
-
-extern "C" int fl_sparse_attention_delta(const fl_layer* layer, int32_t loop, const void* query,
-                                         const void* current_key, const void* current_value,
-                                         const int32_t* indices, const uint8_t* valid,
-                                         int64_t capacity, const float* source_output,
-                                         const float* global_mass, float scaling, float* output,
-                                         float* current_logits, void* workspace,
-                                         size_t workspace_bytes, fl_cuda_stream stream) {
-  const char* who = "fl_sparse_attention_delta";
-  if (int rc = validate_layer(layer, loop, who)) return rc;
-  FL_REQUIRE(query && current_key && current_value && indices && valid && source_output && global_mass && output,
-             "%s: null argument", who);
-  FL_REQUIRE(aligned16(query) && aligned16(current_key) && aligned16(current_value),
-             "%s: vectors must be 16-byte aligned", who);
-  FL_REQUIRE(capacity > 0 && capacity < (1 << 24), "%s: capacity out of range", who);
-  ReaderParams p{};
-  if (int rc = fill_common(p, layer, loop, workspace, workspace_bytes, 0, who)) return rc;
-  p.q = static_cast<const __nv_bfloat16*>(query);
-  p.kcur = static_cast<const __nv_bfloat16*>(current_key);
-  p.vcur = static_cast<const __nv_bfloat16*>(current_value);
-  p.scaling = scaling;
-  p.scaling_log2 = scaling * 1.4426950408889634f;
-  p.out = output;
-  p.indices = indices;
-  p.valid = valid;
-  p.capacity = static_cast<int>(capacity);
-  p.source_out = source_output;
-  p.mass = global_mass;
-  p.cur_logits = current_logits;
-  return launch_selected<kModeDelta>(layer, p, static_cast<cudaStream_t>(stream), who);
-}
-
-extern "C" int fl_selected_pv(const fl_layer* layer, int32_t loop, const float* weights,
-                              const int32_t* indices, const uint8_t* valid, int64_t capacity,
-                              const void* current_value, float* output, void* workspace,
-                              size_t workspace_bytes, fl_cuda_stream stream) {
-  const char* who = "fl_selected_pv";
-  if (int rc = validate_layer(layer, loop, who)) return rc;
-  FL_REQUIRE(weights && indices && output, "%s: null argument", who);
-  FL_REQUIRE(!current_value || aligned16(current_value), "%s: current_value must be 16-byte aligned", who);
-  FL_REQUIRE(capacity > 0 && capacity < (1 << 24), "%s: capacity out of range", who);
-  ReaderParams p{};
-  if (int rc = fill_common(p, layer, loop, workspace, workspace_bytes, 0, who)) return rc;
-  p.vcur = static_cast<const __nv_bfloat16*>(current_value);
-  p.out = output;
-  p.indices = indices;
-  p.valid = valid;
-  p.capacity = static_cast<int>(capacity);
-  p.weights = weights;
-  return launch_selected<kModePV>(layer, p, static_cast<cudaStream_t>(stream), who);
-}
-
-extern "C" int fl_selected_qk(const fl_layer* layer, int32_t loop, const void* query,
-                              const int32_t* indices, const uint8_t* valid, int64_t capacity,
-                              const void* current_key, float* logits, fl_cuda_stream stream) {
-  const char* who = "fl_selected_qk";
-  if (int rc = validate_layer(layer, loop, who)) return rc;
-  FL_REQUIRE(query && indices && logits, "%s: null argument", who);
-  FL_REQUIRE(aligned16(query) && (!current_key || aligned16(current_key)),
-             "%s: vectors must be 16-byte aligned", who);
-  FL_REQUIRE(capacity > 0 && capacity < (1 << 24), "%s: capacity out of range", who);
-  ReaderParams p{};
-  p.L = make_view(*layer);
-  p.loop = loop;
-  p.q = static_cast<const __nv_bfloat16*>(query);
-  p.kcur = static_cast<const __nv_bfloat16*>(current_key);
-  p.scaling = 1.f;
-  p.scaling_log2 = 1.f;
-  p.logits = logits;
-  p.indices = indices;
-  p.valid = valid;
-  p.capacity = static_cast<int>(capacity);
-  p.max_chunks = kMaxSplits;
-  return launch_selected<kModeQK>(layer, p, static_cast<cudaStream_t>(stream), who);
-}
-
 // ------------------------------------------------------------------------------ scratch-free variant
 //
 // fl_dense_source_attention_static: the dense reader for callers that cannot hand over a
@@ -1778,7 +789,8 @@ constexpr int64_t kStaticMaxBatchHeads = 128;
 constexpr int64_t kStaticMaxContext = 16384;
 // partial slots: two per CTA of the largest grid
 constexpr int kStaticSlots = 2 * 2 * 148;
-constexpr size_t kStaticHeaderBytes = ((kStaticMaxBatchHeads + 3) * sizeof(int) + 255) / 256 * 256;
+// the same layout as a caller-provided workspace: status word first, then the tickets
+constexpr size_t kStaticHeaderBytes = kWorkspaceHeader + (kStaticMaxBatchHeads * sizeof(int) + 255) / 256 * 256;
 constexpr size_t kStaticBytes =
     kStaticHeaderBytes + static_cast<size_t>(kStaticSlots) * kPartialStride * sizeof(float);
 
@@ -1789,7 +801,11 @@ void* g_static_address[kMaxDevices] = {};
 
 // The array's name is only a host-side handle: the device address has to be asked for, once
 // per device, with that device current.  The header words are cleared here so that a first
-// call starts from zero whatever a previous, failed launch may have left behind.
+// call starts from zero whatever a previous, failed launch may have left behind.  The table of
+// addresses is filled without a lock: two host threads making the FIRST call on one device at
+// the same time may both run this set-up (harmless, both find the same address, but the second
+// memset can land after the first thread's launch), so the first call per device belongs to one
+// thread.
 int static_scratch_address(void** address, cudaStream_t stream) {
   int device = -1;
   cudaError_t err = cudaGetDevice(&device);
@@ -1845,8 +861,8 @@ extern "C" int fl_dense_source_attention_static(const fl_layer* layer, int32_t l
   ReaderParams p{};
   p.L = make_view(*layer);
   p.loop = loop;
-  p.tickets = static_cast<int*>(scratch);
-  p.status = p.tickets + kStaticMaxBatchHeads;
+  p.status = static_cast<int*>(scratch);
+  p.tickets = reinterpret_cast<int*>(static_cast<unsigned char*>(scratch) + kWorkspaceHeader);
   p.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + kStaticHeaderBytes);
   p.max_chunks = kStaticSlots;
   p.q = static_cast<const __nv_bfloat16*>(query);
@@ -1863,5 +879,19 @@ extern "C" int fl_dense_source_attention_static(const fl_layer* layer, int32_t l
     return FL_ERR_CUDA;
   }
   FL_CHECK_LAUNCH(who);
+  return FL_OK;
+}
+
+extern "C" int fl_static_status(int32_t* status, fl_cuda_stream stream) {
+  FL_REQUIRE(status != nullptr, "fl_static_status: null status");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  void* scratch = nullptr;
+  if (int rc = static_scratch_address(&scratch, s)) return rc;
+  cudaError_t err = cudaMemcpyAsync(status, scratch, sizeof(int32_t), cudaMemcpyDeviceToHost, s);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+  if (err != cudaSuccess) {
+    set_error("fl_static_status: %s", cudaGetErrorString(err));
+    return FL_ERR_CUDA;
+  }
   return FL_OK;
 }

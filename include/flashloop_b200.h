@@ -152,10 +152,10 @@ int fl_kivi_to_rows_v(const void* payload, const void* minimum, const void* scal
 size_t fl_reader_workspace_bytes(int64_t batch_heads, int64_t max_context_tokens);
 int fl_workspace_init(void* workspace, size_t bytes, fl_cuda_stream stream);
 
-/* Synchronises `stream` and copies the workspace's status word to *status (host memory):
- * 0, or 1 when a reader launched with this workspace for `batch_heads` pairs gave up waiting
- * for one of its own asynchronous copies (its output is then undefined).  The reference has
- * no counterpart: its kernels never wait on anything. */
+/* Synchronises `stream` and copies the workspace's status word (its first word, whatever
+ * batch_heads is) to *status (host memory): 0, or 1 when a reader launched with this workspace
+ * gave up waiting for one of its own asynchronous copies (its output is then undefined).  The
+ * reference has no counterpart: its kernels never wait on anything. */
 int fl_workspace_status(const void* workspace, int64_t batch_heads, int32_t* status,
                         fl_cuda_stream stream);
 
@@ -182,13 +182,19 @@ int fl_dense_source_attention(const fl_layer* layer, int32_t loop, const void* q
  * 16384 (FL_ERR_UNSUPPORTED beyond them).  The first call on each device looks up the array's
  * device address and clears its header, so make that call outside any stream capture.  All
  * calls on a device share the array: calls that may overlap on the GPU (different streams)
- * race and must be serialised by the caller.  Results are identical to
- * fl_dense_source_attention. */
+ * race and must be serialised by the caller.  The first call on a device is not thread-safe:
+ * make it from one host thread.  Results are identical to fl_dense_source_attention. */
 int fl_dense_source_attention_static(const fl_layer* layer, int32_t loop, const void* query,
                                      const void* current_key, const void* current_value,
                                      float scaling, float* output, float* logits,
                                      int64_t logits_stride, int64_t max_context_tokens,
                                      fl_cuda_stream stream);
+
+/* The status word of the built-in scratch of fl_dense_source_attention_static on the current
+ * device, read like fl_workspace_status reads a workspace's (synchronises `stream`): 0, or 1
+ * when a launch through that entry point gave up waiting for one of its own copies.  Allocates
+ * nothing.  No counterpart in the reference. */
+int fl_static_status(int32_t* status, fl_cuda_stream stream);
 
 /* CrossLoopKVLayer.cached_mass_sparse_attention_delta (flashloop/cache.py:1517-1642) ->
  * sparse_attention_delta_cuda (kivi_outer_gemv_cuda.cu:1711-1912, kernels :1015, :813, :1146)
@@ -197,8 +203,10 @@ int fl_dense_source_attention_static(const fl_layer* layer, int32_t loop, const 
  * return global_mass * (target - source_output).  indices int32 / valid uint8 [bh][capacity];
  * source_output float32 [bh][128]; global_mass float32 [bh]; output float32 [bh][128];
  * current_logits (nullable) float32 [bh] receives the scaled logit of the current token.
- * The selected readers (this entry, fl_selected_pv, fl_selected_qk) address a row by 30 bits:
- * a stream may hold at most 2^30 - 1 rows over all (b,h) pairs. */
+ * source_output and output must be 16-byte aligned.  The selected readers (this entry,
+ * fl_selected_pv, fl_selected_qk) hold a row's number within its (b,h) in 31 bits.  Indices
+ * may come in any order; an ascending list (what fl_select_decode_keys emits) is the fast
+ * case, because consecutive slots then share K metadata groups. */
 int fl_sparse_attention_delta(const fl_layer* layer, int32_t loop, const void* query,
                               const void* current_key, const void* current_value,
                               const int32_t* indices, const uint8_t* valid, int64_t capacity,

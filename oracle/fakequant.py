@@ -109,3 +109,78 @@ def fake_quant_attention(keys, values, *, loop, query, current_key, current_valu
     w /= w.sum(axis=-1, keepdims=True)
     out = np.einsum("bhqn,bhnd->bhqd", w, v_all.astype(np.float64))
     return out.astype(np.float32), logits.astype(np.float32)
+
+
+def _fake_quant_contexts(keys, values, *, loops, currents, active_masks, group_size, residual_length,
+                         codec_profile):
+    """K and V of every key the given loops attend: fake-quantised prefix, BF16 tail, current
+    token.  The temporal group is encoded once; ``currents[loop]`` = (current_key, current_value)."""
+
+    tokens = keys[0].shape[2]
+    last = max(loops)
+    packed = max(0, ((tokens - residual_length) // group_size) * group_size)
+    masks = None if active_masks is None else [np.asarray(m, bool).reshape(-1)[:packed]
+                                               for m in active_masks[:last]]
+    if packed:
+        rk, rv = encode_temporal_group([k[:, :, :packed] for k in keys[:last + 1]],
+                                       [v[:, :, :packed] for v in values[:last + 1]],
+                                       active_masks=masks, group_size=group_size, codec_profile=codec_profile)
+    out = {}
+    for loop in loops:
+        current_key, current_value = currents[loop]
+        if packed:
+            k_all = np.concatenate([rk[loop], keys[loop][:, :, packed:], current_key], axis=2)
+            v_all = np.concatenate([rv[loop], values[loop][:, :, packed:], current_value], axis=2)
+        else:
+            k_all = np.concatenate([keys[loop], current_key], axis=2)
+            v_all = np.concatenate([values[loop], current_value], axis=2)
+        out[loop] = (k_all.astype(np.float64), v_all.astype(np.float64))
+    return out
+
+
+def _subset_softmax(logits, mask):
+    """flashloop_torch/attention_utils.py:152-168 masked_subset_softmax."""
+
+    masked = np.where(mask, logits, -np.inf)
+    w = np.exp(masked - masked.max(axis=-1, keepdims=True))
+    w = np.where(mask, w, 0.0)
+    return w / w.sum(axis=-1, keepdims=True)
+
+
+def fake_quant_sparse_deltas(keys, values, *, loops, source_query, source_current_key, source_current_value,
+                             query, current_key, current_value, scaling, fraction=0.10, active_masks=None,
+                             group_size=64, residual_length=64, codec_profile="kivi4_channel"):
+    """The tolerance oracle for the sparse late-loop reader: the reference's
+    ``mass_scaled_sparse_output`` (flashloop_torch/attention_utils.py:216-248, both scales equal
+    to the selected mass, source_output zero) over the fake-quant reconstructions.  The source is
+    loop 2 (index 1) with its own query / current K,V; the keys are the top ``fraction`` of the
+    source's global softmax weights (attention_utils.py:139-148, 196-213); the targets are
+    ``loops`` (indices 2 and/or 3) with ``query`` / ``current_key`` / ``current_value``.
+
+    Returns a dict: ``delta[loop]`` float32 [1,H,1,D] = mass * (target_subset - source_subset),
+    ``mask`` bool [1,H,1,N+1], ``mass`` [1,H,1,1], ``source_subset`` [1,H,1,D]."""
+
+    currents = {1: (source_current_key, source_current_value)}
+    for loop in loops:
+        currents[loop] = (current_key, current_value)
+    ctx = _fake_quant_contexts(keys, values, loops=sorted(currents), currents=currents, active_masks=active_masks,
+                               group_size=group_size, residual_length=residual_length, codec_profile=codec_profile)
+    src_k, src_v = ctx[1]
+    src_logits = np.einsum("bhqd,bhnd->bhqn", source_query.astype(np.float64), src_k) * float(scaling)
+    weights = np.exp(src_logits - src_logits.max(axis=-1, keepdims=True))
+    weights /= weights.sum(axis=-1, keepdims=True)
+    n = weights.shape[-1]
+    budget = min(n, max(1, int(np.ceil(n * float(fraction)))))
+    order = np.argsort(-weights, axis=-1, kind="stable")[..., :budget]
+    mask = np.zeros(weights.shape, bool)
+    np.put_along_axis(mask, order, True, axis=-1)
+    mass = (weights * mask).sum(axis=-1, keepdims=True)
+    source_subset = np.einsum("bhqn,bhnd->bhqd", _subset_softmax(src_logits, mask), src_v)
+    deltas = {}
+    for loop in loops:
+        tgt_k, tgt_v = ctx[loop]
+        tgt_logits = np.einsum("bhqd,bhnd->bhqn", query.astype(np.float64), tgt_k) * float(scaling)
+        target_subset = np.einsum("bhqn,bhnd->bhqd", _subset_softmax(tgt_logits, mask), tgt_v)
+        deltas[loop] = (mass * (target_subset - source_subset)).astype(np.float32)
+    return {"delta": deltas, "mask": mask, "mass": mass.astype(np.float32),
+            "source_subset": source_subset.astype(np.float32)}

@@ -66,6 +66,22 @@ def pad_decode_indices(indices: np.ndarray, *, block_size: int = 64):
     return padded, valid
 
 
+def pad_selected(mask: np.ndarray, *, block_size: int = 64):
+    """A boolean key mask [B,H,1,N] with the same count in every row -> the engine's padded
+    ascending index list and validity mask (engine.py:84-109), [B,H,cap] each."""
+
+    batch, heads, _, keys = mask.shape
+    count = int(mask[0, 0, 0].sum())
+    indices = np.zeros((batch, heads, count), np.int32)
+    for b in range(batch):
+        for h in range(heads):
+            chosen = np.nonzero(mask[b, h, 0])[0]
+            if chosen.size != count:
+                raise ValueError("every row must select the same number of keys")
+            indices[b, h] = chosen
+    return pad_decode_indices(indices, block_size=block_size)
+
+
 def softmax_f32(logits: np.ndarray) -> np.ndarray:
     work = logits.astype(np.float32)
     shifted = work - work.max(axis=-1, keepdims=True)

@@ -231,6 +231,32 @@ for profile in ("kivi4_channel", "kivi2_channel"):
     for loop in (1, 3):
         put(f"fq.{profile}.k{loop}", res.reconstructed_keys[loop])
         put(f"fq.{profile}.v{loop}", res.reconstructed_values[loop])
+    if profile != "kivi4_channel":
+        continue
+    # --- J. the sparse late-loop output in the fake-quant domain: the reference's own
+    # mass_scaled_sparse_output on its own reconstructions (prefix), BF16 tail and current token.
+    # Source = loop 2 with the query / current K,V of section C; targets = loops 3, 4 with those
+    # of section F; selection = top 10 % of the source weights; both scales = the selected mass.
+    from flashloop_torch import attention_utils as ref_au  # noqa: E402
+
+    def full(rec, loop_tensors, current, loop):
+        return torch.cat([rec[loop].float(), loop_tensors[loop][:, :, Tq:].float(), current.float()], dim=2)
+
+    src_k = full(res.reconstructed_keys, keys, cur_k, 1)
+    src_v = full(res.reconstructed_values, values, cur_v, 1)
+    src_logits = torch.matmul(query.float(), src_k.transpose(-1, -2)) * scaling
+    fq_mask = ref_au.make_decode_topk_mask(torch.softmax(src_logits, dim=-1), 0.10)
+    fq_mass = ref_au.selected_attention_mass(src_logits, fq_mask)
+    put("fqsparse.mask", fq_mask)
+    put("fqsparse.mass", fq_mass)
+    put("fqsparse.source_subset", torch.matmul(ref_au.masked_subset_softmax(src_logits, fq_mask), src_v))
+    zero = torch.zeros(1, H, 1, D)
+    for loop in (2, 3):
+        tgt_k = full(res.reconstructed_keys, keys, k3, loop)
+        tgt_v = full(res.reconstructed_values, values, v3, loop)
+        tgt_logits = torch.matmul(q3.float(), tgt_k.transpose(-1, -2)) * scaling
+        put(f"fqsparse.loop{loop}.delta",
+            ref_au.mass_scaled_sparse_output(zero, src_logits, tgt_logits, src_v, tgt_v, fq_mask, fq_mass, fq_mass))
 
 # --- I. token retention -------------------------------------------------------------------
 g2 = torch.Generator().manual_seed(3)

@@ -197,6 +197,40 @@ def test_packed_cache_within_tolerance_of_fake_quant(golden, layer):
         np.testing.assert_allclose(out, ref, rtol=1e-2, atol=2e-2)
 
 
+def test_fake_quant_sparse_delta_matches_reference(golden):
+    """The oracle's fake-quant definition of the sparse late-loop output against the reference's
+    own mass_scaled_sparse_output (flashloop_torch/attention_utils.py:216-248)."""
+
+    keys, values, m3, m4, q, ck, cv = golden_inputs(golden)
+    q3, k3, v3 = bf(golden["sparse.query"]), bf(golden["sparse.cur_k"]), bf(golden["sparse.cur_v"])
+    got = fakequant.fake_quant_sparse_deltas(
+        keys, values, loops=(2, 3), source_query=q, source_current_key=ck, source_current_value=cv,
+        query=q3, current_key=k3, current_value=v3, scaling=SCALING, active_masks=[np.ones(200, bool), m3, m4])
+    np.testing.assert_array_equal(got["mask"], golden["fqsparse.mask"])
+    np.testing.assert_allclose(got["mass"], golden["fqsparse.mass"], rtol=1e-5)
+    np.testing.assert_allclose(got["source_subset"], golden["fqsparse.source_subset"], rtol=1e-4, atol=1e-5)
+    for loop in (2, 3):
+        np.testing.assert_allclose(got["delta"][loop], golden[f"fqsparse.loop{loop}.delta"], rtol=1e-4, atol=1e-5)
+
+
+def test_packed_sparse_delta_within_tolerance_of_fake_quant(golden, layer):
+    """The oracle's exact evaluation of the packed cache against the fake-quant sparse output, on
+    the keys, source aggregate and mass of the fake-quant path: the BF16 tolerance the sparse
+    reader is held to."""
+
+    keys, values, m3, m4, q, ck, cv = golden_inputs(golden)
+    q3, k3, v3 = bf(golden["sparse.query"]), bf(golden["sparse.cur_k"]), bf(golden["sparse.cur_v"])
+    ref = fakequant.fake_quant_sparse_deltas(
+        keys, values, loops=(2, 3), source_query=q, source_current_key=ck, source_current_value=cv,
+        query=q3, current_key=k3, current_value=v3, scaling=SCALING, active_masks=[np.ones(200, bool), m3, m4])
+    idx, valid = selection.pad_selected(ref["mask"])
+    for loop in (2, 3):
+        out = layer.cached_mass_sparse_attention_delta(
+            loop, query=q3, current_key=k3, current_value=v3, current_position=200, indices=idx, valid=valid,
+            source_selected_output=ref["source_subset"], global_mass=ref["mass"], scaling=SCALING)
+        np.testing.assert_allclose(out, ref["delta"][loop], rtol=1e-2, atol=2e-2)
+
+
 def test_token_retention_bit_exact(golden):
     h1, h2, h3 = bf(golden["retain.h1"]), bf(golden["retain.h2"]), bf(golden["retain.h3"])
     s3 = selection.hidden_delta_score(h2, h1)
