@@ -33,8 +33,7 @@ struct ReaderParams {
   const int32_t* indices;
   const uint8_t* valid;
   int capacity;
-  int passes_per_head;  // ceil(capacity / 8): a pass is eight slots, one per lane quad
-  int sel_warps;        // warps that own a share of the passes
+  int slots_per_cta;
   const float* weights;
   const float* source_out;
   const float* mass;

@@ -1,570 +1,599 @@
 // Gathered decode-attention readers over a list of selected logical indices: the cached-mass
 // sparse delta of loops 3 and 4, the probability-weighted V sum, and the plain selected QK.
 //
-// Decomposition.  A pass is eight slots of one (b,h), one slot per lane quad; lane `sub` of the
-// quad owns channels 32*sub .. 32*sub+31 of every row of its slot.  The passes of all (b,h) pairs
-// form one sequence and every warp of the grid owns a contiguous, equally long range of it, so
-// the machine is filled evenly whatever batch*heads is.  Warps are autonomous: no CTA barrier
-// anywhere.  A warp meets a head in at most two pieces (the end of one head, the start of the
-// next); each piece keeps its online-softmax state in registers and is published as a float32
-// partial that the last-arriving warp of the head merges (an atomic ticket, nobody waits).
-//
-// Per piece the warp stages 64 slots at a time: index, validity, the rank-map lookups of the
-// compact streams, and a class (rows in streams 0..3 / 0..2 / 0..1, BF16 tail row, nothing).  The
-// slots are reordered by class inside the stage, so that the eight slots of a pass hold rows in the
-// same streams and a pass runs exactly the streams it needs.  For a pass every lane then issues
-// all its loads at once, straight into registers: per stream 16 bytes of K codes, 16 bytes of V
-// codes and the V record's 8 metadata bytes.  While they are in flight the warp makes sure the K
-// tables of the metadata groups the pass touches are in its table ring: a table is one group's
-// scale and minimum rows (512 bytes, fetched with cp.async) folded with the query in place,
-// w_c = q_c * scale_c in float16 in the pair order of the unpacked codes plus the float32 bias
-// sum_c q_c * (min_c + centre * scale_c).  A ring of four tables per stream covers the groups
-// of consecutive passes of an ascending index list; any other order only costs rebuilds.  Then
-// K: unpack, float16-pair dot with the quad's table, widen; softmax update per pass; V: p * scale
-// folded, float16-pair accumulate, widened every sixteen terms.
+//   selected_reader_kernel  one launch over a gathered list of selected logical indices, stream by
+//                           stream; the CTAs that share a (b,h) publish float32 partials that the
+//                           last-arriving one merges (an atomic ticket, nobody waits).
 #include "fl_reader_common.cuh"
 
 namespace fl {
 namespace {
 
-enum { kModeDelta = 0, kModePV = 1, kModeQK = 2 };
-constexpr int kSelWarps = 8;
-constexpr int kSelThreads = kSelWarps * kWarp;
-constexpr int kStageSlots = 64;  // slots a warp stages at a time: two per lane
-constexpr int kRing = 4;         // K tables a warp keeps per stream
-constexpr int kTableBytes = 512;
-constexpr uint32_t kFull = 0xffffffffu;
-
-// Per-warp shared memory.
-template <int STREAMS, bool TABLES>
-struct alignas(16) WarpScratch {
-  int rows[STREAMS][kStageSlots];  // row of the slot in stream s, relative to the (b,h) row base; -1 = none
-  int tail[kStageSlots];           // tail-class entries: ring slot of the BF16 row, -1 = the current token
-  float val[kStageSlots];          // weighted PV: the slot's weight; QK: the slot's position (as int bits)
-  float tval[kStageSlots];         // the same for the tail-class entries
-  float qf[kHeadDim];              // the query in float32
-  float merge[kPartialStride];     // the piece's state: acc[128], running max, denominator
-  const uint8_t* kbase[STREAMS];   // first K row / V record of this (b,h) in every stream
-  const uint8_t* vbase[STREAMS];
-  const __half* scale_base[STREAMS];  // first K metadata group of this (b,h)
-  const __half* min_base[STREAMS];
-  alignas(16) uint8_t table[TABLES ? STREAMS : 1][kRing][kTableBytes];
-  alignas(16) uint8_t vstage[STREAMS][8][96];  // the V records of the current pass: codes, then 16 metadata bytes
-};
-
-
-template <int BITS>
-__device__ __forceinline__ Codes<BITS> zero_codes() {
-  Codes<BITS> c;
+// CTA-level merge of the warps' states, publication of the partial and, in the last CTA of
+// this (b,h), the merge over all partials.  Returns true in the CTA that holds the final
+// result: `total` (this thread's channel, un-normalised) and `denom`.
+template <int NWARPS>
+__device__ __forceinline__ bool merge_and_publish(const ReaderParams& p, float (*s_merge)[kPartialStride],
+                                                  int* s_last, int64_t bh, int slot, int nslots,
+                                                  float& total, float& denom) {
+  const int c = threadIdx.x & (kHeadDim - 1);
+  const bool worker = threadIdx.x < kHeadDim;
+  __syncthreads();
+  float mmax = -INFINITY;
 #pragma unroll
-  for (int i = 0; i < BITS; ++i) c.w[i] = 0u;
-  return c;
-}
-template <int BITS>
-__device__ __forceinline__ Codes<BITS> load_codes_global(const uint8_t* piece) {
-  Codes<BITS> c;
-  if constexpr (BITS == 4) {
-    const uint4 v = ldg128(piece);
-    c.w[0] = v.x; c.w[1] = v.y; c.w[2] = v.z; c.w[3] = v.w;
-  } else {
-    const uint2 v = ldg64(piece);
-    c.w[0] = v.x; c.w[1] = v.y;
+  for (int w = 0; w < NWARPS; ++w) mmax = fmaxf(mmax, s_merge[w][128]);
+  float a = 0.f, l = 0.f;
+#pragma unroll
+  for (int w = 0; w < NWARPS; ++w) {
+    const float mw = s_merge[w][128];
+    const float r = (mw == -INFINITY) ? 0.f : exp2f(mw - mmax);
+    a += s_merge[w][c] * r;
+    l += s_merge[w][129] * r;
   }
-  return c;
+  if (nslots == 1) {
+    total = a;
+    denom = l;
+    return true;
+  }
+  float* mine = p.partial + (bh * p.max_chunks + slot) * kPartialStride;
+  if (worker) mine[c] = a;
+  if (threadIdx.x == 0) {
+    mine[128] = mmax;
+    mine[129] = l;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int t = atomicAdd(p.tickets + bh, 1);
+    *s_last = (t == nslots - 1);
+    if (t == nslots - 1) p.tickets[bh] = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!*s_last) return false;
+  __threadfence();
+  const float* base = p.partial + bh * p.max_chunks * kPartialStride;
+  float gm = -INFINITY;
+  for (int j = 0; j < nslots; ++j) gm = fmaxf(gm, __ldcg(base + j * kPartialStride + 128));
+  a = 0.f;
+  l = 0.f;
+  for (int j = 0; j < nslots; ++j) {
+    const float mj = __ldcg(base + j * kPartialStride + 128);
+    const float r = (mj == -INFINITY) ? 0.f : exp2f(mj - gm);
+    a += __ldcg(base + j * kPartialStride + c) * r;
+    l += __ldcg(base + j * kPartialStride + 129) * r;
+  }
+  total = a;
+  denom = l;
+  return true;
 }
 
+// ------------------------------------------------------------------------------ selected readers
+//
+// Stream-major gather.  A selected token owns a row in streams 0 and 1 and, where the token was
+// retained, in the compact streams 2 and 3, so a token-major walk would run every stream for all
+// eight tokens of a pass whenever one of them holds a compact row.  Here every stream is packed
+// by itself instead.  A CTA stages a batch of slots (one per thread), builds per stream the list
+// of the slots that hold a row there, and cuts the work into passes of at most eight rows of ONE
+// stream:
+//
+//   K pass: up to eight rows of one stream that share a K metadata group (for the compact
+//           streams that is a group of 64 compact rows, about 256 tokens wide, so their passes
+//           are as full as those of streams 0 and 1).  The warp builds the group's query-folded
+//           table (w_c = q_c * scale_c in float16, bias in float32) as the dense reader does and
+//           writes one partial logit per row to shared memory.
+//   softmax: after a CTA barrier every thread sums the partial logits of its slot over the
+//           streams in a fixed order; the batch maximum raises the CTA's running maximum (online
+//           softmax at batch granularity) and the probability goes to shared memory.
+//   V pass: any eight records of one stream: p * v_scale * (code - centre) into the warp's
+//           float16-pair accumulators, widened every sixteen passes.
+//
+// The passes of a warp are independent of each other, so each warp runs them through a private
+// ring of kDepth shared-memory stages filled by 16-byte cp.async copies that every lane issues
+// for the pieces it will read itself; the V passes of a batch are already on their way while the
+// CTA is still in the softmax barrier.  Tail tokens and the current token (BF16 rows) are passes
+// of their own that read global memory directly.
+//
+// Indices need not be sorted for correctness (an unsorted list only makes more, shorter K passes).
+
+enum { kModeDelta = 0, kModePV = 1, kModeQK = 2 };
+constexpr int kGatherWarps = 8;
+constexpr int kGatherThreads = kGatherWarps * kWarp;
+constexpr int kSlotBatch = kGatherThreads;  // slots staged per round: one per thread
+constexpr int kDepth = 4;                   // passes in flight per warp
+constexpr int kPassBytes = 1024;            // K: 8 rows (<= 512 B) + one metadata group (512 B); V: 8 records (<= 640 B)
+constexpr int kTailClass = 4;               // list of the slots that are tail tokens or the current token
+constexpr int kGatherCtasPerSm = 2;
+static_assert(kGatherWarps * kDepth * kPassBytes >= kGatherWarps * kPartialStride * 4,
+              "the merge buffer reuses the rings");
+
+
+// The rows to read form one list per batch: the entries of stream 0 in slot order, then those of
+// stream 1, 2 and 3.  An entry is (stream << 30) | row, so a stream holds fewer than 2^30 rows
+// over all (b,h) pairs.  A V pass is any eight consecutive entries; a K pass is described by 16
+// bits: first entry in bits 0..9, rows - 1 in bits 10..12.
+constexpr int kMaxEntries = 4 * kSlotBatch;
+
+// STREAMS = loop + 1 is a template parameter, so that the staging of a batch touches only the
+// streams the loop reads.
 template <int BITS, int MODE, int STREAMS>
-__global__ void __launch_bounds__(kSelThreads, 2)
+__global__ void __launch_bounds__(kGatherThreads, kGatherCtasPerSm)
 selected_reader_kernel(const __grid_constant__ ReaderParams p) {
   constexpr int kRowBytes = 16 * BITS;
   constexpr int kRecord = kRowBytes + 16;
   constexpr int kLaneBytes = kRowBytes / 4;
-  constexpr bool kTables = MODE != kModePV;
-  using Scratch = WarpScratch<STREAMS, kTables>;
-  extern __shared__ __align__(128) uint8_t s_raw[];
+  constexpr uint32_t kFull = 0xffffffffu;
+  extern __shared__ __align__(128) uint8_t s_ring[];  // [warp][stage][kPassBytes]
+  __shared__ __align__(16) float s_qf[kHeadDim];
+  __shared__ __align__(16) __half s_wtab[kGatherWarps][kHeadDim];  // the current K pass's table
+  __shared__ uint32_t s_entry[kMaxEntries];
+  __shared__ float s_eval[kMaxEntries];     // per entry: its partial logit, then its probability (or weight)
+  __shared__ uint16_t s_kdesc[kMaxEntries];
+  __shared__ int s_kgroup[kMaxEntries];     // per K pass: its metadata group, counted over all (b,h)
+  __shared__ int s_tail[kSlotBatch];        // tail class: ring slot of the entry, -1 = the current token
+  __shared__ float s_tval[kSlotBatch];      // ... and its logit, then probability
+  __shared__ int s_wcount[5][kGatherWarps], s_woff[5][kGatherWarps];
+  __shared__ int s_whead[4][kGatherWarps], s_wfirst[4][kGatherWarps];
+  __shared__ int s_count[5], s_ebase[5];    // entries per class; first entry of every stream, then the total
+  __shared__ int s_nk_packed;
+  __shared__ int s_rbase[4], s_gbase[4];    // first row / first K metadata group of this (b,h) in every stream
+  __shared__ const uint8_t* s_kptr[4];
+  __shared__ const uint8_t* s_vptr[4];
+  __shared__ float s_red[kGatherWarps];
+  __shared__ int s_last;
 
   const LayerView& L = p.L;
-  const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
+  const int64_t bh = blockIdx.y;
+  const int b = static_cast<int>(bh / L.heads);
+  const int32_t* st = L.seq_state + b * FL_STATE_WORDS;
+  const int quant = st[FL_STATE_QUANT_TOKENS];
+  const int tail_len = st[FL_STATE_TAIL_LEN];
+  const int tail_start = st[FL_STATE_TAIL_START];
+  const int cur_pos = quant + tail_len;
+  const int nsplits = (p.capacity + p.slots_per_cta - 1) / p.slots_per_cta;
+  const int split = blockIdx.x;
+  const int slot_begin = split * p.slots_per_cta;
+  const int slot_end = min(p.capacity, slot_begin + p.slots_per_cta);
+  constexpr int streams = STREAMS;
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
   const int quad = lane >> 2;
   const int sub = lane & 3;
   const uint32_t lanes_below = (1u << lane) - 1u;
-  Scratch& sc = reinterpret_cast<Scratch*>(s_raw)[warp];
+  uint8_t* const my_ring = s_ring + warp * kDepth * kPassBytes;
+  const uint32_t my_ring_u32 = smem_u32(my_ring);
+  const int codes_at = quad * kRowBytes + sub * kLaneBytes;  // this lane's codes within a stage
+  float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);                // query channels 4*lane .. 4*lane+3
+  __half2 q01 = __floats2half2_rn(0.f, 0.f), q23 = q01;
+  if constexpr (MODE != kModePV) {
+    if (tid < kHeadDim) s_qf[tid] = __bfloat162float(p.q[bh * kHeadDim + tid]);
+    const uint2 raw = ldg64(p.q + bh * kHeadDim + 4 * lane);
+    q4 = make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
+    q01 = __floats2half2_rn(q4.x, q4.y);
+    q23 = __floats2half2_rn(q4.z, q4.w);
+  }
+  if (tid < 4) {
+    const bool have = tid < streams;
+    s_rbase[tid] = have ? static_cast<int>(L.row_base[tid][bh]) : 0;
+    s_gbase[tid] = have ? static_cast<int>(L.group_base[tid][bh]) : 0;
+    s_kptr[tid] = have ? L.k_codes[tid] : nullptr;
+    s_vptr[tid] = have ? L.v_rows[tid] : nullptr;
+  }
 
-  const int64_t gw = static_cast<int64_t>(blockIdx.x) * kSelWarps + warp;
-  const int64_t n_warps = p.sel_warps;
-  if (gw >= n_warps) return;
-  const int64_t PH = p.passes_per_head;
-  const int64_t all_passes = static_cast<int64_t>(L.batch) * L.heads * PH;
-  int64_t at = all_passes * gw / n_warps;
-  const int64_t range_end = all_passes * (gw + 1) / n_warps;
+  OnlineState S;
+  state_init(S);
+  float m_run = MODE == kModePV ? 0.f : -INFINITY;  // the CTA's running maximum (uniform)
+  float l_mine = 0.f;                                // sum of the probabilities of this thread's slots
+  const int32_t* idx_row = p.indices + bh * p.capacity;
+  const uint8_t* valid_row = p.valid ? p.valid + bh * p.capacity : nullptr;
+  const __nv_bfloat16* tk = L.tail_k[p.loop] + bh * L.tail_capacity * kHeadDim;
+  const __nv_bfloat16* tv = L.tail_v[p.loop] + bh * L.tail_capacity * kHeadDim;
+  __half2 hacc[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) hacc[i] = __floats2half2_rn(0.f, 0.f);
+  int v_passes = 0;
 
-  while (at < range_end) {
-    // ---- the piece: passes [p0, p1) of head bh
-    const int64_t bh = at / PH;
-    const int p0 = static_cast<int>(at - bh * PH);
-    const int p1 = static_cast<int>(range_end - bh * PH < PH ? range_end - bh * PH : PH);
-    const int64_t head_first = bh * PH, head_end = head_first + PH;
-    const int first_owner = static_cast<int>(((head_first + 1) * n_warps - 1) / all_passes);
-    const int last_owner = static_cast<int>((head_end * n_warps - 1) / all_passes);
-    const int nparts = last_owner - first_owner + 1;
-    const int part = static_cast<int>(gw) - first_owner;
-    at += p1 - p0;
-
-    const int b = static_cast<int>(bh / L.heads);
-    const int32_t* st = L.seq_state + b * FL_STATE_WORDS;
-    const int quant = st[FL_STATE_QUANT_TOKENS];
-    const int tail_len = st[FL_STATE_TAIL_LEN];
-    const int tail_start = st[FL_STATE_TAIL_START];
-    const int cur_pos = quant + tail_len;
-    const int slot_end = min(p.capacity, 8 * p1);
-    const int32_t* idx_row = p.indices + bh * p.capacity;
-    const uint8_t* valid_row = p.valid ? p.valid + bh * p.capacity : nullptr;
-    const __nv_bfloat16* tk = L.tail_k[p.loop] + bh * L.tail_capacity * kHeadDim;
-    const __nv_bfloat16* tv = L.tail_v[p.loop] + bh * L.tail_capacity * kHeadDim;
-
-    __syncwarp();  // the previous piece's scratch is no longer read
-    if (lane < STREAMS) {
-      const int64_t rb = L.row_base[lane][bh], gb = L.group_base[lane][bh];
-      sc.kbase[lane] = L.k_codes[lane] + rb * kRowBytes;
-      sc.vbase[lane] = L.v_rows[lane] + rb * kRecord;
-      sc.scale_base[lane] = L.k_scale[lane] + gb * kHeadDim;
-      sc.min_base[lane] = L.k_min[lane] + gb * kHeadDim;
+  // equal batches: 410 slots are staged as 205 + 205, not 256 + 154
+  const int n_batches = (slot_end - slot_begin + kSlotBatch - 1) / kSlotBatch;
+  const int batch_size = n_batches > 0 ? (slot_end - slot_begin + n_batches - 1) / n_batches : kSlotBatch;
+  for (int batch_begin = slot_begin; batch_begin < slot_end; batch_begin += batch_size) {
+    const int batch_n = min(batch_size, slot_end - batch_begin);
+    __syncthreads();  // the previous round's lists and rings are no longer read (and the bases are written)
+    // ---- stage this round's slots: index, the row in every stream, class
+    int idx = -1;
+    bool live = false;    // the slot has something to read
+    uint32_t member = 0;  // bit c: the slot is on list c
+    int rows[5] = {-1, -1, -1, -1, -1};
+    float weight = 0.f;
+    if (tid < batch_n) {
+      const int j = batch_begin + tid;
+      if constexpr (MODE == kModePV) weight = p.weights[bh * p.capacity + j];
+      if (!valid_row || valid_row[j]) idx = idx_row[j];
+      if (idx >= 0 && idx < quant) {
+        live = true;
+        rows[0] = idx;
+        if (streams >= 2) rows[1] = idx;
+        if (streams >= 3) rows[2] = L.rank[0][L.rank_base[b] + idx];
+        if (streams >= 4) rows[3] = L.rank[1][L.rank_base[b] + idx];
+      } else if (idx >= quant) {
+        const bool has_current = (MODE == kModePV) ? p.vcur != nullptr : p.kcur != nullptr;
+        if (idx - quant < tail_len) {
+          live = true;
+          member = 1u << kTailClass;
+          rows[4] = (tail_start + idx - quant) % L.tail_capacity;
+        } else if (idx == cur_pos && has_current) {
+          live = true;
+          member = 1u << kTailClass;
+        }
+      }
+      if constexpr (MODE == kModeQK) {
+        if (!live) p.logits[bh * p.capacity + j] = 0.f;
+      }
     }
-    __half2 q01 = __floats2half2_rn(0.f, 0.f), q23 = q01;  // query channels 4*lane .. 4*lane+3
-    float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    if constexpr (MODE != kModePV) {
-      const uint2 raw = ldg64(p.q + bh * kHeadDim + 4 * lane);
-      q4 = make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
-      *reinterpret_cast<float4*>(&sc.qf[4 * lane]) = q4;
-      q01 = __floats2half2_rn(q4.x, q4.y);
-      q23 = __floats2half2_rn(q4.z, q4.w);
+#pragma unroll
+    for (int s = 0; s < STREAMS; ++s) member |= rows[s] >= 0 ? 1u << s : 0u;
+    // ---- the entry lists: every class in slot order, streams 0..3 back to back
+    int at[5];  // my entry in every class I am a member of
+#pragma unroll
+    for (int c = 0; c < 5; ++c) {
+      if (c >= STREAMS && c != kTailClass) continue;
+      const uint32_t mask = __ballot_sync(kFull, (member >> c) & 1u);
+      at[c] = __popc(mask & lanes_below);
+      if (lane == 0) s_wcount[c][warp] = __popc(mask);
     }
-    // the tags of the table ring: lane s * kRing + r holds the group whose table sits in ring
-    // place r of stream s (-1: none)
-    int tag = -1;
-
-    OnlineState S;
-    state_init(S);
-    if constexpr (MODE == kModePV) S.m = 0.f;
-    __half2 hacc[16];
+    __syncthreads();
+    if (warp == 0) {  // running entry counts over (stream, warp)
+      const int mine = (lane >> 3) < STREAMS ? s_wcount[lane >> 3][lane & 7] : 0;
+      int incl = mine;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) hacc[i] = __floats2half2_rn(0.f, 0.f);
-    int terms = 0;  // float16 terms in hacc since the last widening
-
-    for (int stage_begin = 8 * p0; stage_begin < slot_end; stage_begin += kStageSlots) {
-      const int stage_n = min(kStageSlots, slot_end - stage_begin);
-      __syncwarp();  // the previous stage's lists are no longer read
-      // ---- stage: two slots per lane; class 0: rows in streams 0..3, 1: 0..2, 2: 0..1, 3: BF16
-      // tail row or the current token, 4: nothing to read
-      int cls[2], rows[2][4], tslot[2], where[2];
-      float value[2];
-#pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        const int local = lane + 32 * k;
-        const int j = stage_begin + local;
-        cls[k] = 4;
-        tslot[k] = -1;
-        value[k] = 0.f;
-#pragma unroll
-        for (int s = 0; s < 4; ++s) rows[k][s] = -1;
-        if (local < stage_n) {
-          int idx = -1;
-          if (!valid_row || valid_row[j]) idx = idx_row[j];
-          if constexpr (MODE == kModePV) value[k] = p.weights[bh * p.capacity + j];
-          if constexpr (MODE == kModeQK) value[k] = __int_as_float(j);
-          if (idx >= 0 && idx < quant) {
-            rows[k][0] = idx;
-            if (STREAMS >= 2) rows[k][1] = idx;
-            if (STREAMS >= 3) rows[k][2] = L.rank[0][L.rank_base[b] + idx];
-            if (STREAMS >= 4) rows[k][3] = L.rank[1][L.rank_base[b] + idx];
-            cls[k] = (STREAMS >= 4 && rows[k][3] >= 0) ? 0 : (STREAMS >= 3 && rows[k][2] >= 0) ? 1 : 2;
-          } else if (idx >= quant) {
-            const bool has_current = (MODE == kModePV) ? p.vcur != nullptr : p.kcur != nullptr;
-            if (idx - quant < tail_len) {
-              cls[k] = 3;
-              tslot[k] = (tail_start + idx - quant) % L.tail_capacity;
-            } else if (idx == cur_pos && has_current) {
-              cls[k] = 3;
-            }
-          }
-          if constexpr (MODE == kModeQK) {
-            if (cls[k] == 4) p.logits[bh * p.capacity + j] = 0.f;
-          }
-        }
+      for (int d = 1; d < 32; d <<= 1) {
+        const int up = __shfl_up_sync(kFull, incl, d);
+        if (lane >= d) incl += up;
       }
-      // ---- positions in class order
-      int base = 0, n_packed = 0;
+      const int stream_first = __shfl_sync(kFull, incl - mine, lane & ~7);
+      s_woff[lane >> 3][lane & 7] = incl - mine;
+      if ((lane & 7) == 0) s_ebase[lane >> 3] = stream_first;
+      if ((lane & 7) == 7) s_count[lane >> 3] = incl - stream_first;
+      if (lane == 31) s_ebase[4] = incl;
+    } else if (warp == 1 && lane < kGatherWarps) {
+      int off = 0;
+      for (int k = 0; k < lane; ++k) off += s_wcount[kTailClass][k];
+      s_woff[kTailClass][lane] = off;
+      if (lane == kGatherWarps - 1) s_count[kTailClass] = off + s_wcount[kTailClass][lane];
+    }
+    __syncthreads();
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        if (c == 0 && STREAMS < 4) continue;
-        if (c == 1 && STREAMS < 3) continue;
-        const uint32_t m0 = __ballot_sync(kFull, cls[0] == c);
-        const uint32_t m1 = __ballot_sync(kFull, cls[1] == c);
-        if (cls[0] == c) where[0] = base + __popc(m0 & lanes_below);
-        if (cls[1] == c) where[1] = base + __popc(m0) + __popc(m1 & lanes_below);
-        base += __popc(m0) + __popc(m1);
-        if (c == 2) n_packed = base;
-      }
-      const int n_tail = base - n_packed;
-#pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        if (cls[k] < 3) {
-#pragma unroll
-          for (int s = 0; s < STREAMS; ++s) sc.rows[s][where[k]] = rows[k][s];
-          sc.val[where[k]] = value[k];
-        } else if (cls[k] == 3) {
-          sc.tail[where[k] - n_packed] = tslot[k];
-          sc.tval[where[k] - n_packed] = value[k];
-        }
-      }
-      __syncwarp();
-
-      // ---- packed passes
-      for (int pass = 0; pass < n_packed; pass += 8) {
-        const int e = pass + quad;
-        const bool live = e < n_packed;
-        int r[STREAMS];
-#pragma unroll
-        for (int s = 0; s < STREAMS; ++s) r[s] = live ? sc.rows[s][e] : -1;
-        uint32_t on[STREAMS];  // quads of the pass that hold a row in stream s (as lane masks)
-#pragma unroll
-        for (int s = 0; s < STREAMS; ++s) on[s] = __ballot_sync(kFull, r[s] >= 0);
-
-        // K tables the pass needs and the ring does not hold: fetch their raw metadata
-        uint32_t fresh = 0;  // bit s * kRing + place: a table to fold once the copies have landed
-        if constexpr (kTables) {
-#pragma unroll
-          for (int s = 0; s < STREAMS; ++s) {
-            if (on[s] == 0) continue;
-            const int g = r[s] >= 0 ? r[s] >> 6 : -1;
-#pragma unroll
-            for (int place = 0; place < kRing; ++place) {
-              const uint32_t m = __ballot_sync(kFull, g >= 0 && (g & (kRing - 1)) == place);
-              if (m == 0) continue;
-              const int want = __shfl_sync(kFull, g, __ffs(m) - 1);
-              const int have = __shfl_sync(kFull, tag, s * kRing + place);
-              if (have == want) continue;
-              const __half* src = (lane < 16 ? sc.scale_base[s] : sc.min_base[s]) +
-                                  static_cast<int64_t>(want) * kHeadDim + (lane & 15) * 8;
-              cp_async<16>(smem_u32(sc.table[s][place]) + lane * 16, src);
-              if (lane == s * kRing + place) tag = want;
-              fresh |= 1u << (s * kRing + place);
-            }
-          }
-        }
-        // every load of the pass at once: the V records through cp.async into the warp's stage,
-        // the K codes straight into registers
-        if constexpr (MODE != kModeQK) {
-#pragma unroll
-          for (int s = 0; s < STREAMS; ++s) {
-            if (r[s] >= 0) {
-              const uint8_t* record = sc.vbase[s] + static_cast<int64_t>(r[s]) * kRecord;
-              const uint32_t dst = smem_u32(sc.vstage[s][quad]);
-              cp_async<kLaneBytes>(dst + sub * kLaneBytes, record + sub * kLaneBytes);
-              if (sub == 0) cp_async<16>(dst + kRowBytes, record + kRowBytes);
-            }
-          }
-        }
-        cp_async_commit();
-        Codes<BITS> kc[STREAMS];
-        if constexpr (MODE != kModePV) {
-#pragma unroll
-          for (int s = 0; s < STREAMS; ++s) {
-            kc[s] = zero_codes<BITS>();
-            if (r[s] >= 0)
-              kc[s] = load_codes_global<BITS>(sc.kbase[s] + static_cast<int64_t>(r[s]) * kRowBytes + sub * kLaneBytes);
-          }
-        }
-
-        float logit = 0.f;
-        cp_async_wait<0>();
-        __syncwarp();
-        if constexpr (kTables) {
-          // fold the fresh tables in place
-          while (fresh) {
-            const int which = __ffs(fresh) - 1;
-            fresh &= fresh - 1;
-            uint8_t* raw = sc.table[which / kRing][which % kRing];
-            const uint2 scl = *reinterpret_cast<const uint2*>(raw + lane * 8);
-            const uint2 mn = *reinterpret_cast<const uint2*>(raw + 256 + lane * 8);
-            const float2 sc01 = __half22float2(as_half2(scl.x)), sc23 = __half22float2(as_half2(scl.y));
-            const float2 mn01 = __half22float2(as_half2(mn.x)), mn23 = __half22float2(as_half2(mn.y));
-            const float kcn = float(kCentre<BITS>);
-            float bias = q4.x * fmaf(kcn, sc01.x, mn01.x);
-            bias = fmaf(q4.y, fmaf(kcn, sc01.y, mn01.y), bias);
-            bias = fmaf(q4.z, fmaf(kcn, sc23.x, mn23.x), bias);
-            bias = fmaf(q4.w, fmaf(kcn, sc23.y, mn23.y), bias);
-            bias = warp_sum(bias);
-            __syncwarp();  // every lane has read the raw rows
-            table_store<BITS>(reinterpret_cast<__half*>(raw), lane, q01, q23, scl);
-            if (lane == 0) *reinterpret_cast<float*>(raw + 256) = bias;
-          }
-          __syncwarp();
-          // K: every quad against the table of its row's group
-#pragma unroll
-          for (int s = 0; s < STREAMS; ++s) {
-            if (on[s] == 0) continue;
-            const int g = r[s] >= 0 ? r[s] >> 6 : -1;
-            const int place = g & (kRing - 1);
-            // (the shuffle runs in every lane: behind a short-circuit it would be skipped by the quads
-            // without a row while the others wait for them)
-            const int held = __shfl_sync(kFull, tag, s * kRing + place);
-            bool ready = g >= 0 && held == g;
-            if (__any_sync(kFull, ready)) {
-              const uint8_t* tab = sc.table[s][ready ? place : 0];
-              __half2 mult[16];
-              const uint4* tab4 = reinterpret_cast<const uint4*>(tab + sub * 64);
-#pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                const uint4 x = tab4[v];
-                mult[4 * v + 0] = as_half2(x.x); mult[4 * v + 1] = as_half2(x.y);
-                mult[4 * v + 2] = as_half2(x.z); mult[4 * v + 3] = as_half2(x.w);
-              }
-              const float dot = quad_sum(k_dot_fast<BITS>(kc[s], mult)) + *reinterpret_cast<const float*>(tab + 256);
-              if (ready) logit += dot;
-            }
-            // quads whose table lost its ring place to another group of this pass (only when one
-            // pass spans more than kRing groups): one group at a time through the same place
-            uint32_t pending = __ballot_sync(kFull, g >= 0 && !ready);
-            while (pending) {
-              const int want = __shfl_sync(kFull, g, __ffs(pending) - 1);
-              const int wplace = want & (kRing - 1);
-              uint8_t* raw = sc.table[s][wplace];
-              const __half* src = (lane < 16 ? sc.scale_base[s] : sc.min_base[s]) +
-                                  static_cast<int64_t>(want) * kHeadDim + (lane & 15) * 8;
-              __syncwarp();
-              cp_async<16>(smem_u32(raw) + lane * 16, src);
-              cp_async_commit();
-              cp_async_wait<0>();
-              __syncwarp();
-              const uint2 scl = *reinterpret_cast<const uint2*>(raw + lane * 8);
-              const uint2 mn = *reinterpret_cast<const uint2*>(raw + 256 + lane * 8);
-              const float2 sc01 = __half22float2(as_half2(scl.x)), sc23 = __half22float2(as_half2(scl.y));
-              const float2 mn01 = __half22float2(as_half2(mn.x)), mn23 = __half22float2(as_half2(mn.y));
-              const float kcn = float(kCentre<BITS>);
-              float bias = q4.x * fmaf(kcn, sc01.x, mn01.x);
-              bias = fmaf(q4.y, fmaf(kcn, sc01.y, mn01.y), bias);
-              bias = fmaf(q4.z, fmaf(kcn, sc23.x, mn23.x), bias);
-              bias = fmaf(q4.w, fmaf(kcn, sc23.y, mn23.y), bias);
-              bias = warp_sum(bias);
-              __syncwarp();
-              table_store<BITS>(reinterpret_cast<__half*>(raw), lane, q01, q23, scl);
-              if (lane == 0) *reinterpret_cast<float*>(raw + 256) = bias;  // later passes find the table in the ring
-              if (lane == s * kRing + wplace) tag = want;
-              __syncwarp();
-              __half2 mult[16];
-              const uint4* tab4 = reinterpret_cast<const uint4*>(raw + sub * 64);
-#pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                const uint4 x = tab4[v];
-                mult[4 * v + 0] = as_half2(x.x); mult[4 * v + 1] = as_half2(x.y);
-                mult[4 * v + 2] = as_half2(x.z); mult[4 * v + 3] = as_half2(x.w);
-              }
-              const float dot = quad_sum(k_dot_fast<BITS>(kc[s], mult)) + bias;
-              const bool mine = g == want && !ready;
-              if (mine) {
-                logit += dot;
-                ready = true;
-              }
-              pending &= ~__ballot_sync(kFull, mine);
-            }
-          }
-        }
-
-        if constexpr (MODE == kModeQK) {
-          if (live && sub == 0) p.logits[bh * p.capacity + __float_as_int(sc.val[e])] = logit;
-          continue;
-        }
-        float pr;
-        if constexpr (MODE == kModePV) {
-          pr = live ? sc.val[e] : 0.f;
+    for (int c = 0; c < 5; ++c) {
+      if (c >= STREAMS && c != kTailClass) continue;
+      at[c] += s_woff[c][warp];
+      if ((member >> c) & 1u) {
+        if (c < 4) {
+          s_entry[at[c]] = (static_cast<uint32_t>(c) << 30) | static_cast<uint32_t>(s_rbase[c] + rows[c]);
+          s_eval[at[c]] = weight;  // the weighted-PV reader's probabilities are the caller's
         } else {
-          const float x = live ? logit * p.scaling_log2 : -INFINITY;
-          const float pmax = across_quads_max(x);
-          if (pmax > S.m) {
-            flush_pairs(hacc, S.acc);  // the float16 partial sums belong to the old maximum
-            terms = 0;
-            state_raise(S, pmax);
+          s_tail[at[c]] = rows[4];
+          s_tval[at[c]] = weight;
+        }
+      }
+    }
+    __syncthreads();
+    const int n_entries = s_ebase[4];
+    const int n_tail = s_count[kTailClass];
+    // ---- K passes: entry i of a stream opens a pass where the metadata group changes and every
+    // eight entries after that
+    if constexpr (MODE != kModePV) {
+      uint32_t run_heads[4];
+      bool entry_on[4], run_head[4];
+      int group_of[4];
+#pragma unroll
+      for (int s = 0; s < STREAMS; ++s) {
+        entry_on[s] = tid < s_count[s];
+        const int first = s_ebase[s];
+        const int base = s_rbase[s];
+        group_of[s] = entry_on[s] ? (static_cast<int>(s_entry[first + tid] & 0x3fffffffu) - base) >> 6 : -1;
+        const int before =
+            entry_on[s] && tid > 0 ? (static_cast<int>(s_entry[first + tid - 1] & 0x3fffffffu) - base) >> 6 : -1;
+        run_head[s] = entry_on[s] && (tid == 0 || group_of[s] != before);
+        run_heads[s] = __ballot_sync(kFull, run_head[s]);
+        if (lane == 0) s_whead[s][warp] = run_heads[s] ? warp * 32 + 31 - __clz(run_heads[s]) : -1;
+      }
+      __syncthreads();
+      bool pass_head[4];
+      uint32_t pass_heads[4];
+      int rank[4];
+#pragma unroll
+      for (int s = 0; s < STREAMS; ++s) {
+        int run_start = 0;
+        const uint32_t upto = run_heads[s] & (lanes_below | (1u << lane));
+        if (upto) {
+          run_start = warp * 32 + 31 - __clz(upto);
+        } else {
+          for (int w = warp - 1; w >= 0; --w) {
+            const int h = s_whead[s][w];
+            if (h >= 0) {
+              run_start = h;
+              break;
+            }
           }
-          pr = live ? exp2f(x - S.m) : 0.f;
-          S.l += pr;
         }
-        // V
-        if (terms + STREAMS > 16) {
-          flush_pairs(hacc, S.acc);
-          terms = 0;
+        pass_head[s] = entry_on[s] && (run_head[s] || ((tid - run_start) & 7) == 0);
+        pass_heads[s] = __ballot_sync(kFull, pass_head[s]);
+        rank[s] = __popc(pass_heads[s] & lanes_below);
+        if (lane == 0) {
+          s_wcount[s][warp] = __popc(pass_heads[s]);
+          s_wfirst[s][warp] = pass_heads[s] ? warp * 32 + __ffs(pass_heads[s]) - 1 : -1;
         }
-        const uint32_t pick = (sub < 2) ? 0x1010u : 0x3232u;
-        const __half2 centre2 = __floats2half2_rn(float(kCentre<BITS>), float(kCentre<BITS>));
-        const __half2 p2 = __float2half2_rn(pr);
+      }
+      __syncthreads();
+      if (warp == 0) {  // running pass counts over (stream, warp)
+        const int mine = (lane >> 3) < STREAMS ? s_wcount[lane >> 3][lane & 7] : 0;
+        int incl = mine;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int up = __shfl_up_sync(kFull, incl, d);
+          if (lane >= d) incl += up;
+        }
+        s_woff[lane >> 3][lane & 7] = incl - mine;
+        if (lane == 31) s_nk_packed = incl;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int s = 0; s < STREAMS; ++s) {
+        if (pass_head[s]) {
+          int next = s_count[s];
+          const uint32_t above = pass_heads[s] & ~(lanes_below | (1u << lane));
+          if (above) {
+            next = warp * 32 + __ffs(above) - 1;
+          } else {
+            for (int w = warp + 1; w < kGatherWarps; ++w) {
+              const int h = s_wfirst[s][w];
+              if (h >= 0) {
+                next = h;
+                break;
+              }
+            }
+          }
+          const int k = s_woff[s][warp] + rank[s];
+          s_kdesc[k] = static_cast<uint16_t>((s_ebase[s] + tid) | ((next - tid - 1) << 10));
+          s_kgroup[k] = s_gbase[s] + group_of[s];
+        }
+      }
+      __syncthreads();
+    }
+
+    // ---- this warp's passes: K passes warp, warp + 8, ..., then V passes warp, warp + 8, ...
+    const int nk_all = MODE == kModePV ? 0 : s_nk_packed;
+    const int nv_all = MODE == kModeQK ? 0 : (n_entries + 7) >> 3;
+    const int nk_mine = nk_all > warp ? (nk_all - warp + kGatherWarps - 1) / kGatherWarps : 0;
+    const int nv_mine = nv_all > warp ? (nv_all - warp + kGatherWarps - 1) / kGatherWarps : 0;
+    const int n_mine = nk_mine + nv_mine;
+    // Copies of pass q into its stage (one commit group, empty past the end): codes of row i at
+    // i * kRowBytes; behind them the K metadata group (scale[128], min[128]) or the V records' 16
+    // metadata bytes (record i at 512 + 16 i).
+    auto issue = [&](int q) {
+      const uint32_t stage = my_ring_u32 + (q & (kDepth - 1)) * kPassBytes;
+      if (q < nk_mine) {
+        if constexpr (MODE != kModePV) {
+          const int k = warp + kGatherWarps * q;
+          const uint32_t d = s_kdesc[k];
+          const int s = s_entry[d & 1023u] >> 30;
+          if (quad <= static_cast<int>(d >> 10)) {
+            const uint32_t row = s_entry[(d & 1023u) + quad] & 0x3fffffffu;
+            cp_async<kLaneBytes>(stage + codes_at, s_kptr[s] + static_cast<uint64_t>(row) * kRowBytes + sub * kLaneBytes);
+          }
+          const __half* meta = (lane < 16 ? L.k_scale[s] : L.k_min[s]) +
+                               static_cast<int64_t>(s_kgroup[k]) * kHeadDim + (lane & 15) * 8;
+          cp_async<16>(stage + 512 + lane * 16, meta);
+        }
+      } else if (q < n_mine) {
+        if constexpr (MODE != kModeQK) {
+          const int i = 8 * (warp + kGatherWarps * (q - nk_mine)) + quad;
+          if (i < n_entries) {
+            const uint32_t e = s_entry[i];
+            const uint8_t* record = s_vptr[e >> 30] + static_cast<uint64_t>(e & 0x3fffffffu) * kRecord;
+            cp_async<kLaneBytes>(stage + codes_at, record + sub * kLaneBytes);
+            if (sub == 0) cp_async<16>(stage + 512 + quad * 16, record + kRowBytes);
+          }
+        }
+      }
+      cp_async_commit();
+    };
+    auto advance = [&](int q) {
+      cp_async_wait<kDepth - 2>();  // pass q has landed
+      __syncwarp();                 // ... for every lane, and every lane is done with pass q - 1
+      issue(q + kDepth - 1);        // into the stage of pass q - 1
+    };
+
+#pragma unroll
+    for (int q = 0; q < kDepth - 1; ++q) issue(q);
+
+    if constexpr (MODE != kModePV) {
+      for (int q = 0; q < nk_mine; ++q) {
+        advance(q);
+        const uint8_t* stage = my_ring + (q & (kDepth - 1)) * kPassBytes;
+        const uint32_t d = s_kdesc[warp + kGatherWarps * q];
+        // the group's table and bias = sum_c q_c * (min_c + centre * scale_c)
+        const uint2 sc = *reinterpret_cast<const uint2*>(stage + 512 + lane * 8);
+        const uint2 mn = *reinterpret_cast<const uint2*>(stage + 512 + 256 + lane * 8);
+        table_store<BITS>(s_wtab[warp], lane, q01, q23, sc);
+        const float2 sc01 = __half22float2(as_half2(sc.x)), sc23 = __half22float2(as_half2(sc.y));
+        const float2 mn01 = __half22float2(as_half2(mn.x)), mn23 = __half22float2(as_half2(mn.y));
+        const float kcn = float(kCentre<BITS>);
+        float bias = q4.x * fmaf(kcn, sc01.x, mn01.x);
+        bias = fmaf(q4.y, fmaf(kcn, sc01.y, mn01.y), bias);
+        bias = fmaf(q4.z, fmaf(kcn, sc23.x, mn23.x), bias);
+        bias = fmaf(q4.w, fmaf(kcn, sc23.y, mn23.y), bias);
+        const Codes<BITS> kc = load_codes_shared<BITS>(stage + codes_at);
+        bias = warp_sum(bias);
+        __syncwarp();
+        __half2 mult[16];
+        const uint4* tab4 = reinterpret_cast<const uint4*>(&s_wtab[warp][sub * 32]);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const uint4 x = tab4[v];
+          mult[4 * v + 0] = as_half2(x.x); mult[4 * v + 1] = as_half2(x.y);
+          mult[4 * v + 2] = as_half2(x.z); mult[4 * v + 3] = as_half2(x.w);
+        }
+        const float dot = quad_sum(k_dot_fast<BITS>(kc, mult)) + bias;
+        if (quad <= static_cast<int>(d >> 10) && sub == 0) s_eval[(d & 1023u) + quad] = dot;
+      }
+      // tail tokens and the current token: BF16 rows, read directly
+      for (int i0 = 8 * warp; i0 < n_tail; i0 += 8 * kGatherWarps) {
+        const int i = i0 + quad;
+        const bool on = i < n_tail;
+        const int ring_slot = on ? s_tail[i] : 0;
+        const __nv_bfloat16* krow = ring_slot < 0 ? p.kcur + bh * kHeadDim : tk + ring_slot * kHeadDim;
+        const float dot = quad_sum(on ? bf16_row_dot<BITS>(krow, sub, s_qf) : 0.f);
+        if (on && sub == 0) s_tval[i] = dot;
+      }
+
+      __syncthreads();  // every K pass of the batch has written its partial logits
+      float logit = 0.f;
+#pragma unroll
+      for (int s = 0; s < STREAMS; ++s) logit += (member >> s) & 1u ? s_eval[at[s]] : 0.f;
+      if ((member >> kTailClass) & 1u) logit = s_tval[at[kTailClass]];
+      if constexpr (MODE == kModeQK) {
+        if (live) p.logits[bh * p.capacity + batch_begin + tid] = logit;
+      } else {
+        if (live && idx == cur_pos && p.cur_logits) p.cur_logits[bh] = logit * p.scaling;
+        const float x = live ? logit * p.scaling_log2 : -INFINITY;
+        const float wmax = warp_max(x);
+        if (lane == 0) s_red[warp] = wmax;
+        __syncthreads();
+        float bmax = s_red[0];
+#pragma unroll
+        for (int w = 1; w < kGatherWarps; ++w) bmax = fmaxf(bmax, s_red[w]);
+        if (bmax > m_run) {
+          const float r = exp2f(m_run - bmax);  // exp2f(-inf) == 0 on the first raise
+          flush_pairs(hacc, S.acc);             // the float16 partial sums belong to the old maximum
+          v_passes = 0;
+          l_mine *= r;
+          S.vbias *= r;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) S.acc[i] *= r;
+          m_run = bmax;
+        }
+        const float pr = live ? exp2f(x - m_run) : 0.f;
+        l_mine += pr;
 #pragma unroll
         for (int s = 0; s < STREAMS; ++s) {
-          if (on[s] == 0) continue;
-          // quads without a row in this stream read what an earlier pass left in the stage: their
-          // metadata is forced to zero, so the (finite) codes contribute nothing
-          const uint8_t* record = sc.vstage[s][quad];
-          const Codes<BITS> vc = load_codes_shared<BITS>(record + sub * kLaneBytes);
-          const uint2 vmeta = *reinterpret_cast<const uint2*>(record + kRowBytes);
-          const bool has = r[s] >= 0;
-          const __half2 vm2 = as_half2(has ? __byte_perm(vmeta.x, 0u, pick) : 0u);
-          const __half2 vs2 = as_half2(has ? __byte_perm(vmeta.y, 0u, pick) : 0u);
-          const __half2 hb = __hfma2(centre2, vs2, vm2);
-          v_accumulate<BITS>(vc, __hmul2(p2, vs2), hacc);
-          S.vbias = fmaf(pr, __low2float(hb), S.vbias);
-          ++terms;
+          if ((member >> s) & 1u) s_eval[at[s]] = pr;
         }
+        if ((member >> kTailClass) & 1u) s_tval[at[kTailClass]] = pr;
+        __syncthreads();
       }
+    }
 
-      // ---- BF16 rows: tail tokens and the current token, read directly
-      for (int t0 = 0; t0 < n_tail; t0 += 8) {
-        const int e = t0 + quad;
-        const bool live = e < n_tail;
-        const int ring_slot = live ? sc.tail[e] : 0;
-        float logit = 0.f;
-        if constexpr (MODE != kModePV) {
-          const __nv_bfloat16* krow = ring_slot < 0 ? p.kcur + bh * kHeadDim : tk + ring_slot * kHeadDim;
-          logit = quad_sum(live ? bf16_row_dot<BITS>(krow, sub, sc.qf) : 0.f);
-        }
-        if constexpr (MODE == kModeQK) {
-          if (live && sub == 0) p.logits[bh * p.capacity + __float_as_int(sc.tval[e])] = logit;
-          continue;
-        }
-        float pr;
-        if constexpr (MODE == kModePV) {
-          pr = live ? sc.tval[e] : 0.f;
-        } else {
-          if (live && ring_slot < 0 && sub == 0 && p.cur_logits) p.cur_logits[bh] = logit * p.scaling;
-          const float x = live ? logit * p.scaling_log2 : -INFINITY;
-          const float pmax = across_quads_max(x);
-          if (pmax > S.m) {
-            flush_pairs(hacc, S.acc);
-            terms = 0;
-            state_raise(S, pmax);
-          }
-          pr = live ? exp2f(x - S.m) : 0.f;
-          S.l += pr;
-        }
-        if (live) {
+    if constexpr (MODE != kModeQK) {
+      const uint32_t pick = (sub < 2) ? 0x1010u : 0x3232u;
+      const __half2 centre2 = __floats2half2_rn(float(kCentre<BITS>), float(kCentre<BITS>));
+      for (int q = nk_mine; q < n_mine; ++q) {
+        advance(q);
+        const uint8_t* stage = my_ring + (q & (kDepth - 1)) * kPassBytes;
+        const int i = 8 * (warp + kGatherWarps * (q - nk_mine)) + quad;
+        const bool on = i < n_entries;
+        const float pr = on ? s_eval[i] : 0.f;
+        const __half2 p2 = __float2half2_rn(pr);
+        const Codes<BITS> vc = load_codes_shared<BITS>(stage + codes_at);
+        const uint2 vmeta = *reinterpret_cast<const uint2*>(stage + 512 + quad * 16);
+        const __half2 vm2 = as_half2(on ? __byte_perm(vmeta.x, 0u, pick) : 0u);
+        const __half2 vs2 = as_half2(on ? __byte_perm(vmeta.y, 0u, pick) : 0u);
+        const __half2 hb = __hfma2(centre2, vs2, vm2);
+        v_accumulate<BITS>(vc, __hmul2(p2, vs2), hacc);
+        S.vbias = fmaf(pr, __low2float(hb), S.vbias);
+        // at most 16 float16 terms per accumulator before widening
+        if ((++v_passes & 15) == 0) flush_pairs(hacc, S.acc);
+      }
+      for (int i0 = 8 * warp; i0 < n_tail; i0 += 8 * kGatherWarps) {
+        const int i = i0 + quad;
+        if (i < n_tail) {
+          const int ring_slot = s_tail[i];
           const __nv_bfloat16* vrow = ring_slot < 0 ? p.vcur + bh * kHeadDim : tv + ring_slot * kHeadDim;
-          bf16_row_accumulate<BITS>(vrow, sub, pr, S.acc);
+          bf16_row_accumulate<BITS>(vrow, sub, s_tval[i], S.acc);
         }
       }
     }
-    if constexpr (MODE == kModeQK) continue;
+    cp_async_wait<0>();
+  }
+  if constexpr (MODE == kModeQK) return;
+  flush_pairs(hacc, S.acc);
+  S.m = m_run;
 
-    // ---- close the piece: reduce the warp's state, publish it, merge the head when it is complete
-    flush_pairs(hacc, S.acc);
-    __syncwarp();
-    state_store<BITS>(S, lane, sc.merge);
-    __syncwarp();
-    float4 a = *reinterpret_cast<const float4*>(&sc.merge[4 * lane]);
-    float denom = sc.merge[129];
-    bool final_here = nparts == 1;
-    if (!final_here) {
-      // two partial slots per warp: only a warp's first piece can continue a head from the warp
-      // before (slot 0) and only its last piece can leave a head to the warp after (slot 1)
-      float* mine = p.partial + (2 * gw + (part > 0 ? 0 : 1)) * kPartialStride;
-      *reinterpret_cast<float4*>(&mine[4 * lane]) = a;
-      if (lane == 0) {
-        mine[128] = sc.merge[128];
-        mine[129] = denom;
-      }
-      __threadfence();
-      __syncwarp();
-      int last = 0;
-      if (lane == 0) {
-        const int t = atomicAdd(p.tickets + bh, 1);
-        last = t == nparts - 1;
-        if (last) p.tickets[bh] = 0;  // ready for the next launch
-      }
-      last = __shfl_sync(kFull, last, 0);
-      if (last) {
-        __threadfence();
-        const float* first = p.partial + (2 * static_cast<int64_t>(first_owner) + 1) * kPartialStride;
-        const auto part_of = [&](int jj) { return jj > 0 ? first + (2 * jj - 1) * kPartialStride : first; };
-        float gm = -INFINITY;
-        for (int jj = 0; jj < nparts; ++jj) gm = fmaxf(gm, __ldcg(part_of(jj) + 128));
-        a = make_float4(0.f, 0.f, 0.f, 0.f);
-        denom = 0.f;
-        for (int jj = 0; jj < nparts; ++jj) {
-          const float* pj = part_of(jj);
-          const float mj = __ldcg(pj + 128);
-          const float rr = (mj == -INFINITY) ? 0.f : exp2f(mj - gm);
-          const float4 x = __ldcg(reinterpret_cast<const float4*>(pj + 4 * lane));
-          a.x = fmaf(x.x, rr, a.x); a.y = fmaf(x.y, rr, a.y); a.z = fmaf(x.z, rr, a.z); a.w = fmaf(x.w, rr, a.w);
-          denom = fmaf(__ldcg(pj + 129), rr, denom);
-        }
-        final_here = true;
-      }
-    }
-    if (final_here) {
-      float4 o;
+  __syncthreads();  // every warp has left its ring: the rings become the merge buffer
+  float (*s_merge)[kPartialStride] = reinterpret_cast<float (*)[kPartialStride]>(s_ring);
+  state_store<BITS>(S, lane, s_merge[warp]);
+  const float l_warp = warp_sum(l_mine);
+  if (lane == 0) s_merge[warp][129] = l_warp;
+  float total, denom;
+  if (merge_and_publish<kGatherWarps>(p, s_merge, &s_last, bh, split, nsplits, total, denom)) {
+    const int c = threadIdx.x;
+    if (c < kHeadDim) {
       if constexpr (MODE == kModeDelta) {
-        const float inv = denom > 0.f ? 1.f / denom : 0.f;
-        const float mass = p.mass[bh];
-        const float4 src = *reinterpret_cast<const float4*>(p.source_out + bh * kHeadDim + 4 * lane);
-        o = make_float4(mass * (a.x * inv - src.x), mass * (a.y * inv - src.y), mass * (a.z * inv - src.z),
-                        mass * (a.w * inv - src.w));
+        const float target = denom > 0.f ? total / denom : 0.f;
+        p.out[bh * kHeadDim + c] = p.mass[bh] * (target - p.source_out[bh * kHeadDim + c]);
       } else {
-        o = a;
+        p.out[bh * kHeadDim + c] = total;
       }
-      *reinterpret_cast<float4*>(p.out + bh * kHeadDim + 4 * lane) = o;
     }
   }
 }
 
 // ------------------------------------------------------------------------------ host side
 
-template <int BITS, int MODE, int STREAMS>
-cudaError_t launch_selected_as(unsigned grid, const ReaderParams& p, cudaStream_t s) {
-  constexpr size_t kSmem = kSelWarps * sizeof(WarpScratch<STREAMS, MODE != kModePV>);
-  static const cudaError_t attr = cudaFuncSetAttribute(
-      selected_reader_kernel<BITS, MODE, STREAMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-  if (attr != cudaSuccess) return attr;
-  selected_reader_kernel<BITS, MODE, STREAMS><<<grid, kSelThreads, kSmem, s>>>(p);
-  return cudaSuccess;
-}
-
-template <int BITS, int MODE>
-cudaError_t launch_selected_bits(unsigned grid, const ReaderParams& p, cudaStream_t s) {
-  switch (p.loop) {
-    case 0: return launch_selected_as<BITS, MODE, 1>(grid, p, s);
-    case 1: return launch_selected_as<BITS, MODE, 2>(grid, p, s);
-    case 2: return launch_selected_as<BITS, MODE, 3>(grid, p, s);
-    default: return launch_selected_as<BITS, MODE, 4>(grid, p, s);
-  }
-}
-
-// The passes of all (b,h) pairs are dealt to the warps of the grid in equal contiguous ranges.
-// Warps: at most two CTAs per multiprocessor, at most 32 per (b,h) (two partial slots each in a
-// workspace of kMaxSplits slots per (b,h)), at least three passes each where there are that many.
-template <int MODE>
-int launch_selected(const fl_layer* layer, ReaderParams& p, cudaStream_t s, const char* who) {
-  const int64_t bh = static_cast<int64_t>(layer->batch) * layer->heads;
-  p.passes_per_head = (p.capacity + 7) / 8;
-  const int64_t passes = bh * p.passes_per_head;
-  int64_t warps = static_cast<int64_t>(2) * device_sm_count() * kSelWarps;
-  warps = warps < (kMaxSplits / 2) * bh ? warps : (kMaxSplits / 2) * bh;
-  const int64_t by_work = passes / 3 > kSelWarps ? passes / 3 : kSelWarps;
-  warps = warps < by_work ? warps : by_work;
-  warps = warps < passes ? warps : passes;
-  p.sel_warps = static_cast<int>(warps);
-  const unsigned grid = static_cast<unsigned>((warps + kSelWarps - 1) / kSelWarps);
-  const cudaError_t err = layer->bits == 4 ? launch_selected_bits<4, MODE>(grid, p, s)
-                                           : launch_selected_bits<2, MODE>(grid, p, s);
-  if (err != cudaSuccess) {
-    set_error("%s: %s", who, cudaGetErrorString(err));
-    return FL_ERR_CUDA;
-  }
-  FL_CHECK_LAUNCH(who);
-  return FL_OK;
+int choose_slots_per_cta(int64_t batch_heads, int64_t capacity) {
+  // One wave: the grid is kept within the CTAs of the gather kernel that are resident at once
+  // where the capacity allows it (a second, partial wave would cost a whole round).
+  const int64_t budget = 148 * kGatherCtasPerSm;
+  int64_t slots = 32;
+  while ((batch_heads * ((capacity + slots - 1) / slots) > budget || (capacity + slots - 1) / slots > kMaxSplits) &&
+         slots < capacity)
+    slots += 32;
+  return static_cast<int>(slots);
 }
 
 }  // namespace
 }  // namespace fl
 
 using namespace fl;
+
+namespace {
+
+template <int BITS, int MODE, int STREAMS>
+void launch_selected_as(const dim3 grid, const ReaderParams& p, cudaStream_t s) {
+  constexpr int kSmem = kGatherWarps * kDepth * kPassBytes;
+  static const cudaError_t attr = cudaFuncSetAttribute(
+      selected_reader_kernel<BITS, MODE, STREAMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  (void)attr;
+  selected_reader_kernel<BITS, MODE, STREAMS><<<grid, kGatherThreads, kSmem, s>>>(p);
+}
+
+template <int BITS, int MODE>
+void launch_selected_bits(const dim3 grid, const ReaderParams& p, cudaStream_t s) {
+  switch (p.loop) {
+    case 0: launch_selected_as<BITS, MODE, 1>(grid, p, s); break;
+    case 1: launch_selected_as<BITS, MODE, 2>(grid, p, s); break;
+    case 2: launch_selected_as<BITS, MODE, 3>(grid, p, s); break;
+    default: launch_selected_as<BITS, MODE, 4>(grid, p, s); break;
+  }
+}
+
+template <int MODE>
+int launch_selected(const fl_layer* layer, ReaderParams& p, cudaStream_t s, const char* who) {
+  const int64_t bh = static_cast<int64_t>(layer->batch) * layer->heads;
+  p.slots_per_cta = choose_slots_per_cta(bh, p.capacity);
+  const int splits = (p.capacity + p.slots_per_cta - 1) / p.slots_per_cta;
+  const dim3 grid(splits, static_cast<unsigned>(bh));
+  if (layer->bits == 4) {
+    launch_selected_bits<4, MODE>(grid, p, s);
+  } else {
+    launch_selected_bits<2, MODE>(grid, p, s);
+  }
+  FL_CHECK_LAUNCH(who);
+  return FL_OK;
+}
+
+}  // namespace
 
 extern "C" int fl_sparse_attention_delta(const fl_layer* layer, int32_t loop, const void* query,
                                          const void* current_key, const void* current_value,
@@ -579,7 +608,6 @@ extern "C" int fl_sparse_attention_delta(const fl_layer* layer, int32_t loop, co
              "%s: null argument", who);
   FL_REQUIRE(aligned16(query) && aligned16(current_key) && aligned16(current_value),
              "%s: vectors must be 16-byte aligned", who);
-  FL_REQUIRE(aligned16(source_output) && aligned16(output), "%s: source_output and output must be 16-byte aligned", who);
   FL_REQUIRE(capacity > 0 && capacity < (1 << 24), "%s: capacity out of range", who);
   ReaderParams p{};
   if (int rc = bind_workspace(p, layer, loop, workspace, workspace_bytes, who)) return rc;
@@ -606,7 +634,6 @@ extern "C" int fl_selected_pv(const fl_layer* layer, int32_t loop, const float* 
   if (int rc = validate_layer(layer, loop, who)) return rc;
   FL_REQUIRE(weights && indices && output, "%s: null argument", who);
   FL_REQUIRE(!current_value || aligned16(current_value), "%s: current_value must be 16-byte aligned", who);
-  FL_REQUIRE(aligned16(output), "%s: output must be 16-byte aligned", who);
   FL_REQUIRE(capacity > 0 && capacity < (1 << 24), "%s: capacity out of range", who);
   ReaderParams p{};
   if (int rc = bind_workspace(p, layer, loop, workspace, workspace_bytes, who)) return rc;
@@ -642,4 +669,3 @@ extern "C" int fl_selected_qk(const fl_layer* layer, int32_t loop, const void* q
   p.max_chunks = kMaxSplits;
   return launch_selected<kModeQK>(layer, p, static_cast<cudaStream_t>(stream), who);
 }
-
