@@ -872,10 +872,13 @@ def run_e2e(args) -> None:
     gen = torch.Generator().manual_seed(100 + (0 if tp else rank))
     prompts = torch.randint(0, cfg.vocab_size, (B, T), generator=gen).to(device)
     torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats(device)
+    before_prefill = torch.cuda.memory_allocated(device)
     t0 = time.perf_counter()
     logits = engine.prefill(prompts).logits
     torch.cuda.synchronize()
     prefill_s = time.perf_counter() - t0
+    prefill_peak = torch.cuda.max_memory_allocated(device) - before_prefill
     state = {"token": logits.argmax(-1, keepdim=True)}
 
     def run_step():
@@ -956,7 +959,8 @@ def run_e2e(args) -> None:
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
             "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": bench_config(args),
-            "details": {"prefill_seconds": prefill_s, "context_at_end": quant + tail,
+            "details": {"prefill_seconds": prefill_s, "prefill_peak_bytes_above_model": prefill_peak,
+                        "cache_storage_bytes": engine.state.cache.storage_bytes, "context_at_end": quant + tail,
                         "weight_bytes_streamed_per_step": 4 * weights},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": int(host_token.numel() * 8),

@@ -7,7 +7,7 @@ of the decode hot path it replaces (``packing``, ``kivi_backend``, ``selection``
 CPU fallback.
 """
 
-from .cache import CrossLoopKVCache, CrossLoopKVLayer
+from .cache import CrossLoopKVCache, CrossLoopKVLayer, CrossLoopKVLayerBuilder
 from .config import FlashLoopConfig
 from .engine import DecodeOutput, DecodeReceipt, EngineState, FlashLoopEngine, PrefillOutput
 from .kivi_backend import KiviPacked4Bit, pack_kivi_k_per_channel, pack_kivi_v_per_token
@@ -17,6 +17,7 @@ from .selection import DecodeSelection, select_decode_keys, select_prefill_token
 __all__ = [
     "CrossLoopKVCache",
     "CrossLoopKVLayer",
+    "CrossLoopKVLayerBuilder",
     "DecodeOutput",
     "DecodeReceipt",
     "DecodeSelection",

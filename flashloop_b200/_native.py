@@ -67,6 +67,7 @@ SIGNATURES = {
     "fl_gather_rows": (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _i32, _vp]),
     "fl_scatter_rows": (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _i32, _vp]),
     "fl_encode_prefill": (C.c_int, [_vp, _i32, _i32, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp]),
+    "fl_encode_prefill_stage": (C.c_int, [_vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp, _i64, _i32, _vp]),
     "fl_rmsnorm": (C.c_int, [_vp, _vp, _vp, _f32, _vp, _f32, _i64, _i32, _vp, _vp, _vp]),
     "fl_rope_split": (C.c_int, [_vp, _vp, _vp, _i64, _vp, _vp, _i64, _i32, _vp, _vp, _vp, _vp]),
     "fl_swiglu": (C.c_int, [_vp, _i64, _i32, _vp, _vp]),
@@ -78,7 +79,7 @@ LAUNCHES_PER_CALL = {
     "fl_kivi_to_rows_k": 1, "fl_kivi_to_rows_v": 1, "fl_dense_source_attention": 1,
     "fl_dense_source_attention_static": 1, "fl_sparse_attention_delta": 1, "fl_selected_pv": 1, "fl_selected_qk": 1,
     "fl_append_decode_token": 3, "fl_select_decode_keys": 1, "fl_hidden_delta_score": 1,
-    "fl_select_prefill_tokens": 1, "fl_gather_rows": 1, "fl_scatter_rows": 1, "fl_encode_prefill": 3,
+    "fl_select_prefill_tokens": 1, "fl_gather_rows": 1, "fl_scatter_rows": 1, "fl_encode_prefill": 3, "fl_encode_prefill_stage": 1,
     "fl_rmsnorm": 1, "fl_rope_split": 1, "fl_swiglu": 1,
 }
 

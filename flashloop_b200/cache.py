@@ -77,7 +77,7 @@ class CrossLoopKVLayer:
     """One physical layer's packed recurrent cache for a batch of sequences."""
 
     def __init__(self, *, batch: int, heads: int, token_capacities: Sequence[int],
-                 compact_capacities: Sequence[tuple[int, int]], bits: int = 4,
+                 compact_capacities: Sequence[tuple[int, int]] | None, bits: int = 4,
                  group_size: int = GROUP, residual_length: int = 64,
                  device: torch.device | str = "cuda", dtype: torch.dtype = torch.bfloat16) -> None:
         if group_size != GROUP or residual_length != 64:
@@ -96,33 +96,18 @@ class CrossLoopKVLayer:
         self._device = torch.device(device)
         self._dtype = dtype
         self._shape_prefix = (self.batch, self.heads, HEAD_DIM)
-        row_bytes = 16 * bits
-        caps = [[_round_up(c, GROUP) for c in token_capacities],
-                [_round_up(c, GROUP) for c in token_capacities],
-                [_round_up(c[0], GROUP) for c in compact_capacities],
-                [_round_up(c[1], GROUP) for c in compact_capacities]]
-        self._caps = caps
         dev = self._device
-        self._k_codes, self._k_min, self._k_scale, self._v_rows, self._v_codes, self._v_meta = [], [], [], [], [], []
-        self._row_base, self._group_base, self._row_base_host = [], [], []
-        for s in range(4):
-            bases, off = [], 0
-            for b in range(self.batch):
-                for h in range(self.heads):
-                    bases.append(off + h * caps[s][b])
-                off += self.heads * caps[s][b]
-            total = max(off, GROUP)
-            self._k_codes.append(torch.zeros((total, row_bytes), dtype=torch.uint8, device=dev))
-            # V records: codes, then float16 min0 min1 scale0 scale1, then 8 bytes of padding
-            records = torch.zeros((total, row_bytes + 16), dtype=torch.uint8, device=dev)
-            self._v_rows.append(records)
-            self._v_codes.append(records[:, :row_bytes])
-            self._v_meta.append(records[:, row_bytes:row_bytes + 8].view(torch.float16))
-            self._k_min.append(torch.zeros((total // GROUP, HEAD_DIM), dtype=torch.float16, device=dev))
-            self._k_scale.append(torch.zeros((total // GROUP, HEAD_DIM), dtype=torch.float16, device=dev))
-            self._row_base_host.append(bases)
-            self._row_base.append(torch.tensor(bases, dtype=torch.int64, device=dev))
-            self._group_base.append(torch.tensor([x // GROUP for x in bases], dtype=torch.int64, device=dev))
+        self._caps: list = [None] * 4
+        self._k_codes, self._k_min, self._k_scale = [None] * 4, [None] * 4, [None] * 4
+        self._v_rows, self._v_codes, self._v_meta = [None] * 4, [None] * 4, [None] * 4
+        self._row_base, self._group_base, self._row_base_host = [None] * 4, [None] * 4, [None] * 4
+        token_caps = [_round_up(c, GROUP) for c in token_capacities]
+        self._allocate_stream(0, token_caps)
+        self._allocate_stream(1, token_caps)
+        if compact_capacities is not None:
+            self._allocate_stream(2, [_round_up(c[0], GROUP) for c in compact_capacities])
+            self._allocate_stream(3, [_round_up(c[1], GROUP) for c in compact_capacities])
+        caps = self._caps
         rank_bases, off = [], 0
         for b in range(self.batch):
             rank_bases.append(off)
@@ -144,12 +129,47 @@ class CrossLoopKVLayer:
         # this layer's reader scratch: held here so that nothing can free it under a recorded graph
         self._ws = reader_workspace(self._device, self.batch * self.heads, max(caps[0]) + TAIL_CAPACITY)
 
+    def _allocate_stream(self, s: int, caps: Sequence[int]) -> None:
+        """Storage of stream ``s`` with ``caps[b]`` rows (multiples of 64) per head of sequence b."""
+
+        row_bytes = 16 * self.bits
+        dev = self._device
+        bases, off = [], 0
+        for b in range(self.batch):
+            for h in range(self.heads):
+                bases.append(off + h * caps[b])
+            off += self.heads * caps[b]
+        total = max(off, GROUP)
+        self._caps[s] = list(caps)
+        self._k_codes[s] = torch.zeros((total, row_bytes), dtype=torch.uint8, device=dev)
+        # V records: codes, then float16 min0 min1 scale0 scale1, then 8 bytes of padding
+        records = torch.zeros((total, row_bytes + 16), dtype=torch.uint8, device=dev)
+        self._v_rows[s] = records
+        self._v_codes[s] = records[:, :row_bytes]
+        self._v_meta[s] = records[:, row_bytes:row_bytes + 8].view(torch.float16)
+        self._k_min[s] = torch.zeros((total // GROUP, HEAD_DIM), dtype=torch.float16, device=dev)
+        self._k_scale[s] = torch.zeros((total // GROUP, HEAD_DIM), dtype=torch.float16, device=dev)
+        self._row_base_host[s] = bases
+        self._row_base[s] = torch.tensor(bases, dtype=torch.int64, device=dev)
+        self._group_base[s] = torch.tensor([x // GROUP for x in bases], dtype=torch.int64, device=dev)
+
+    def _allocate_compact(self, compact_capacities: Sequence[tuple[int, int]]) -> None:
+        """Streams 2 and 3, once the retained counts are known (staged construction)."""
+
+        self._allocate_stream(2, [_round_up(c[0], GROUP) for c in compact_capacities])
+        self._allocate_stream(3, [_round_up(c[1], GROUP) for c in compact_capacities])
+        self._native = self._make_native()
+
     # ------------------------------------------------------------------ native descriptor
 
     def _make_native(self) -> _native.FlLayer:
         n = _native.FlLayer()
         n.batch, n.heads, n.bits, n.tail_capacity = self.batch, self.heads, self.bits, TAIL_CAPACITY
         for s in range(4):
+            if self._k_codes[s] is None:  # compact streams of a layer still under construction
+                n.tail_k[s] = self._tail_k[s].data_ptr()
+                n.tail_v[s] = self._tail_v[s].data_ptr()
+                continue
             n.k_codes[s] = self._k_codes[s].data_ptr()
             n.k_min[s] = self._k_min[s].data_ptr()
             n.k_scale[s] = self._k_scale[s].data_ptr()
@@ -259,6 +279,26 @@ class CrossLoopKVLayer:
                                     [int(mask3[:packed].sum().item())], [int(mask4[:packed].sum().item())])
         layer._push_state()
         return layer
+
+    @classmethod
+    def from_prefill_updates(cls, *, loop1_key: torch.Tensor, loop1_value: torch.Tensor, loop2_key: torch.Tensor,
+                             loop2_value: torch.Tensor, loop3_positions: torch.Tensor, loop3_keys: torch.Tensor,
+                             loop3_values: torch.Tensor, loop4_positions: torch.Tensor, loop4_keys: torch.Tensor,
+                             loop4_values: torch.Tensor, group_size: int = 64, residual_length: int = 64,
+                             absolute_late_overrides: bool = False, absolute_override_dtype: str = "int4",
+                             reader_backend: str = "kivi_outer", bits: int = 4,
+                             max_new_tokens: int = 0) -> "CrossLoopKVLayer":
+        """Build the layer from the dense Loop-1/2 K/V and the compact Loop-3/4 rows without ever
+        forming full Loop-3/4 tensors (flashloop/cache.py:820-1006): the three builder stages in
+        one call."""
+
+        builder = CrossLoopKVLayerBuilder.from_loop1(
+            loop1_key, loop1_value, group_size=group_size, residual_length=residual_length,
+            absolute_late_overrides=absolute_late_overrides, absolute_override_dtype=absolute_override_dtype,
+            reader_backend=reader_backend, bits=bits, max_new_tokens=max_new_tokens)
+        builder.add_loop2(loop2_key, loop2_value)
+        return builder.finalize(loop3_positions=loop3_positions, loop3_keys=loop3_keys, loop3_values=loop3_values,
+                                loop4_positions=loop4_positions, loop4_keys=loop4_keys, loop4_values=loop4_values)
 
     @classmethod
     def from_streams(cls, key_streams, value_streams, rank_maps) -> "CrossLoopKVLayer":
@@ -480,6 +520,70 @@ class CrossLoopKVLayer:
         out["tail_active3"] = self._tail_active[0, b].index_select(0, slots).bool()
         out["tail_active4"] = self._tail_active[1, b].index_select(0, slots).bool()
         return out
+
+    def _decode_rows(self, s: int, b: int, rows: torch.Tensor, kind: str) -> torch.Tensor:
+        """bfloat16 [H, n, 128] = decode of rows ``rows`` of stream ``s`` of sequence ``b``
+        (code * scale + minimum in float32, rounded: flashloop/packing.py:108-132)."""
+
+        codes = self._rows(self._k_codes if kind == "k" else self._v_codes, s, b).index_select(1, rows)  # [H, n, 16 * bits]
+        per_byte = 8 // self.bits
+        shifts = torch.arange(per_byte, device=self._device, dtype=torch.uint8) * self.bits
+        values = ((codes.unsqueeze(-1) >> shifts) & ((1 << self.bits) - 1)).reshape(self.heads, -1, HEAD_DIM).float()
+        if kind == "k":
+            groups = rows // GROUP
+            minimum = self._rows(self._k_min, s, b, GROUP).index_select(1, groups).float()
+            scale = self._rows(self._k_scale, s, b, GROUP).index_select(1, groups).float()
+        else:
+            record = self._rows(self._v_meta, s, b).index_select(1, rows).float()  # [H, n, 4]: min0 min1 scale0 scale1
+            minimum = record[..., 0:2].repeat_interleave(GROUP, dim=-1)
+            scale = record[..., 2:4].repeat_interleave(GROUP, dim=-1)
+        return (values * scale + minimum).to(torch.bfloat16)
+
+    def gather(self, loop: int, indices: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """The reconstructed K and V rows of ``loop`` at one-dimensional logical ``indices``
+        (flashloop/cache.py:1114-1200): bfloat16 [B, H, n, 128].  An audit path in tensor ops
+        (every sum is rounded to bfloat16 as there); the readers never go through it."""
+
+        loop = int(loop)
+        if loop not in range(4):
+            raise ValueError("loop must be in [0, 3]")
+        if indices.ndim != 1:
+            raise ValueError("indices must be one-dimensional")
+        indices = indices.to(device=self._device, dtype=torch.long)
+        counts = self.token_counts()
+        if indices.numel() and (int(indices.min()) < 0 or int(indices.max()) >= min(counts)):
+            raise IndexError("cache index is outside the logical sequence")
+        out_k = torch.empty((self.batch, self.heads, int(indices.numel()), HEAD_DIM), dtype=torch.bfloat16,
+                            device=self._device)
+        out_v = torch.empty_like(out_k)
+        for b in range(self.batch):
+            quant, start = self.quantized_tokens_of(b), int(self._state_host[b, _native.STATE_TAIL_START])
+            inside = torch.nonzero(indices < quant).flatten()
+            if inside.numel():
+                rows = indices.index_select(0, inside)
+                k = self._decode_rows(0, b, rows, "k")
+                v = self._decode_rows(0, b, rows, "v")
+                for s in range(1, loop + 1):
+                    if s == 1:
+                        k = k + self._decode_rows(1, b, rows, "k")
+                        v = v + self._decode_rows(1, b, rows, "v")
+                        continue
+                    base = self._rank_base_host[b]
+                    ranks = self._rank[s - 2][base:base + quant].index_select(0, rows)
+                    held = torch.nonzero(ranks >= 0).flatten()
+                    if held.numel():
+                        compact = ranks.index_select(0, held).long()
+                        k.index_add_(1, held, self._decode_rows(s, b, compact, "k"))
+                        v.index_add_(1, held, self._decode_rows(s, b, compact, "v"))
+                out_k[b].index_copy_(1, inside, k)
+                out_v[b].index_copy_(1, inside, v)
+            outside = torch.nonzero(indices >= quant).flatten()
+            if outside.numel():
+                slots = (start + indices.index_select(0, outside) - quant) % TAIL_CAPACITY
+                sl = slice(b * self.heads, (b + 1) * self.heads)
+                out_k[b].index_copy_(1, outside, self._tail_k[loop, sl].index_select(1, slots))
+                out_v[b].index_copy_(1, outside, self._tail_v[loop, sl].index_select(1, slots))
+        return out_k, out_v
 
     # ------------------------------------------------------------------ readers
 
@@ -713,6 +817,195 @@ class CrossLoopKVLayer:
                 st[_native.STATE_ROWS3] += GROUP
                 st[_native.STATE_TAIL_LEN] -= GROUP
                 st[_native.STATE_TAIL_START] = (int(st[_native.STATE_TAIL_START]) + GROUP) % TAIL_CAPACITY
+
+
+class CrossLoopKVLayerBuilder:
+    """Build one physical cache layer loop by loop, so that a prefill can drop every loop's dense
+    K/V as soon as it is packed (flashloop/cache.py:315-625): ``from_loop1`` packs the anchor,
+    ``add_loop2`` the delta against its decode, ``finalize`` the compact Loop-3/4 deltas against
+    the reconstruction read back from the packed streams.  Batched: all tensors carry B sequences
+    of equal prompt length; compact tensors hold the retained rows in position order, positions
+    are int32 ``[B, rows]`` (ascending, padded with -1; one-dimensional for a batch of one).
+
+    One ``fl_encode_prefill_stage`` launch per stage; the codes are the same bits as the
+    reference's builder produces (and as :meth:`CrossLoopKVLayer.from_prefill`)."""
+
+    def __init__(self) -> None:
+        self.group_size = 0
+        self.residual_length = 0
+        self.packed_tokens = 0
+        self.reader_backend = "kivi_outer"
+        self.absolute_late_overrides = False
+        self._layer: CrossLoopKVLayer | None = None
+        self._tokens = 0
+        self._extra = 0
+        self._has_loop2 = False
+
+    @property
+    def retains_dense_loop1_prefix(self) -> bool:
+        """Audit flag (flashloop/cache.py:399-403): nothing dense is kept between the stages."""
+
+        return False
+
+    @classmethod
+    def from_loop1(cls, loop1_key: torch.Tensor, loop1_value: torch.Tensor, *, group_size: int = 64,
+                   residual_length: int = 64, absolute_late_overrides: bool = False,
+                   absolute_override_dtype: str = "int4", reader_backend: str = "kivi_outer", bits: int = 4,
+                   max_new_tokens: int = 0) -> "CrossLoopKVLayerBuilder":
+        shape = tuple(int(v) for v in loop1_key.shape)
+        if len(shape) != 4 or loop1_value.shape != loop1_key.shape:
+            raise ValueError("Loop-1 K/V must match [batch, heads, tokens, channels]")
+        if loop1_value.dtype != loop1_key.dtype or loop1_value.device != loop1_key.device:
+            raise ValueError("Loop-1 K/V must share dtype and device")
+        if int(group_size) <= 0 or int(residual_length) < 0:
+            raise ValueError("invalid group_size or residual_length")
+        if absolute_late_overrides or absolute_override_dtype != "int4":
+            raise ValueError("the CUDA cache supports additive cross-loop deltas only")
+        if reader_backend not in {"kivi_outer", "triton_row"}:
+            raise ValueError("unknown KV reader backend")
+        batch, heads, tokens, channels = shape
+        if channels != HEAD_DIM:
+            raise ValueError("the CUDA cache specializes head_dim=128")
+        _native.require_cuda(loop1_key, loop1_value)
+        self = cls()
+        self.group_size, self.residual_length = int(group_size), int(residual_length)
+        self.reader_backend = reader_backend
+        self._tokens = tokens
+        self.packed_tokens = packed = max(0, ((tokens - self.residual_length) // self.group_size) * self.group_size)
+        if tokens - packed > TAIL_CAPACITY:
+            raise RuntimeError("tail longer than the ring")
+        self._extra = _round_up(max_new_tokens, GROUP) + 2 * GROUP
+        layer = CrossLoopKVLayer(batch=batch, heads=heads, token_capacities=[packed + self._extra] * batch,
+                                 compact_capacities=None, bits=bits, group_size=group_size,
+                                 residual_length=residual_length, device=loop1_key.device, dtype=loop1_key.dtype)
+        st = layer._state_host
+        st[:, _native.STATE_QUANT_TOKENS] = packed
+        st[:, _native.STATE_TAIL_LEN] = tokens - packed
+        layer._push_state()
+        self._layer = layer
+        self._stage(0, loop1_key, loop1_value)
+        return self
+
+    def _stage(self, stage: int, keys: torch.Tensor, values: torch.Tensor, positions: torch.Tensor | None = None) -> None:
+        layer = self._layer
+        keys, values = keys.contiguous(), values.contiguous()
+        rows = int(keys.shape[2])
+        if stage < 2:
+            tail = self._tokens - self.packed_tokens
+            bh = layer.batch * layer.heads
+            layer._tail_k[stage, :, :tail].copy_(keys[:, :, self.packed_tokens:].reshape(bh, tail, HEAD_DIM))
+            layer._tail_v[stage, :, :tail].copy_(values[:, :, self.packed_tokens:].reshape(bh, tail, HEAD_DIM))
+            if not self.packed_tokens:
+                return
+        elif not self.packed_tokens or rows == 0:
+            return
+        _native.check(_native.load().fl_encode_prefill_stage(
+            C.byref(layer._native), 0, layer.batch, rows, stage, _native.ptr(keys), _native.ptr(values),
+            _native.ptr(positions), 0 if positions is None else int(positions.shape[1]), 0 if stage < 2 else 1,
+            _native.current_stream(layer._device)), "fl_encode_prefill_stage")
+
+    def _check_dense(self, key: torch.Tensor, value: torch.Tensor, label: str) -> None:
+        layer = self._layer
+        expected = (layer.batch, layer.heads, self._tokens, HEAD_DIM)
+        if tuple(key.shape) != expected or value.shape != key.shape:
+            raise ValueError(f"{label} K/V shape differs from Loop 1")
+        if key.dtype != layer._dtype or value.dtype != layer._dtype:
+            raise ValueError(f"{label} K/V dtype differs from Loop 1")
+        if key.device != layer._device or value.device != layer._device:
+            raise ValueError(f"{label} K/V device differs from Loop 1")
+
+    def add_loop2(self, loop2_key: torch.Tensor, loop2_value: torch.Tensor) -> None:
+        if self._has_loop2:
+            raise RuntimeError("Loop 2 is already installed")
+        self._check_dense(loop2_key, loop2_value, "Loop-2")
+        self._stage(1, loop2_key, loop2_value)
+        self._has_loop2 = True
+
+    def _check_updates(self, positions: torch.Tensor, key: torch.Tensor, value: torch.Tensor, label: str):
+        """Positions as int32 [B, rows] on the device, the number of retained rows per sequence."""
+
+        layer = self._layer
+        logical = positions.to(device=layer._device, dtype=torch.int32)
+        if logical.ndim == 1:
+            logical = logical[None].expand(layer.batch, -1) if layer.batch == 1 else None
+        if logical is None or logical.ndim != 2 or logical.shape[0] != layer.batch:
+            raise ValueError(f"{label} positions must have shape [batch, rows]")
+        logical = logical.contiguous()
+        held = logical >= 0
+        count = held.sum(1)
+        rows = int(logical.shape[1])
+        if rows:
+            ordered = (logical[:, 1:] > logical[:, :-1]) | ~held[:, 1:]
+            padded_last = held[:, :-1] | ~held[:, 1:]  # no position after a -1
+            if not bool(ordered.all()) or not bool(padded_last.all()):
+                raise ValueError(f"{label} positions must be strictly sorted")
+            if int(logical.max()) >= self._tokens:
+                raise IndexError(f"{label} update is outside the prompt")
+        expected = (layer.batch, layer.heads, rows, HEAD_DIM)
+        if tuple(key.shape) != expected or value.shape != key.shape:
+            raise ValueError(f"{label} compact K/V shape differs from its positions")
+        if key.dtype != layer._dtype or value.dtype != layer._dtype:
+            raise ValueError(f"{label} compact K/V dtype differs from Loop 1")
+        if key.device != layer._device or value.device != layer._device:
+            raise ValueError(f"{label} compact K/V device differs from Loop 1")
+        return logical, count
+
+    def finalize(self, *, loop3_positions: torch.Tensor, loop3_keys: torch.Tensor, loop3_values: torch.Tensor,
+                 loop4_positions: torch.Tensor, loop4_keys: torch.Tensor,
+                 loop4_values: torch.Tensor) -> CrossLoopKVLayer:
+        if not self._has_loop2:
+            raise RuntimeError("Loop 2 must be installed before finalization")
+        layer, packed, tokens = self._layer, self.packed_tokens, self._tokens
+        pos3, _ = self._check_updates(loop3_positions, loop3_keys, loop3_values, "Loop-3")
+        pos4, _ = self._check_updates(loop4_positions, loop4_keys, loop4_values, "Loop-4")
+        device = layer._device
+        member3 = torch.zeros((layer.batch, tokens + 1), dtype=torch.bool, device=device)
+        member3.scatter_(1, torch.where(pos3 >= 0, pos3, tokens).long(), True)
+        if pos4.numel() and not bool(member3.gather(1, torch.where(pos4 >= 0, pos4, tokens).long())[pos4 >= 0].all()):
+            raise ValueError("Loop-4 positions must be nested in Loop-3 positions")
+        inside = [((p >= 0) & (p < packed)) for p in (pos3, pos4)]
+        counts = [m.sum(1).tolist() for m in inside]
+        layer._allocate_compact([(_round_up(n3, GROUP) + self._extra, _round_up(n4, GROUP) + self._extra)
+                                 for n3, n4 in zip(*counts)])
+        # rank maps: logical prefix token -> its row in the compact stream (positions are ascending,
+        # so the i-th retained position inside the prefix is row i)
+        for i, (pos, mask) in enumerate(zip((pos3, pos4), inside)):
+            ranks = torch.cumsum(mask.to(torch.int32), 1, dtype=torch.int32) - 1
+            for b in range(layer.batch):
+                base = layer._rank_base_host[b]
+                view = layer._rank[i][base:base + packed]
+                view.fill_(-1)
+                view[pos[b][mask[b]].long()] = ranks[b][mask[b]]
+        for b in range(layer.batch):
+            st = layer._state_host[b]
+            st[_native.STATE_ROWS2] = _round_up(int(counts[0][b]), GROUP)
+            st[_native.STATE_ROWS3] = _round_up(int(counts[1][b]), GROUP)
+            layer._compact_counts[b] = [int(counts[0][b]), int(counts[1][b])]
+        layer._push_state()
+        self._stage(2, loop3_keys, loop3_values, pos3)
+        self._stage(3, loop4_keys, loop4_values, pos4)
+        # tails of loops 3 and 4: the tail before, with the retained tail tokens replaced
+        tail = tokens - packed
+        bh = layer.batch * layer.heads
+        for i, (pos, key, value) in enumerate(((pos3, loop3_keys, loop3_values), (pos4, loop4_keys, loop4_values))):
+            loop = 2 + i
+            layer._tail_k[loop, :, :tail].copy_(layer._tail_k[loop - 1, :, :tail])
+            layer._tail_v[loop, :, :tail].copy_(layer._tail_v[loop - 1, :, :tail])
+            flags = torch.zeros((layer.batch, TAIL_CAPACITY), dtype=torch.uint8, device=device)
+            for b in range(layer.batch):
+                late = torch.nonzero(pos[b] >= packed).flatten()
+                if late.numel():
+                    slots = pos[b][late].long() - packed
+                    sl = slice(b * layer.heads, (b + 1) * layer.heads)
+                    layer._tail_k[loop, sl].index_copy_(1, slots, key[b].index_select(1, late))
+                    layer._tail_v[loop, sl].index_copy_(1, slots, value[b].index_select(1, late))
+                    flags[b, slots] = 1
+            layer._tail_active[i].copy_(flags)
+            host = flags[:, :tail].bool().tolist()
+            for b in range(layer.batch):
+                layer._tail_active_host[b][i] = host[b]
+        self._layer = None
+        return layer
 
 
 class CrossLoopKVCache:

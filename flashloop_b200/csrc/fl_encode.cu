@@ -20,6 +20,8 @@
 namespace fl {
 namespace {
 
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
 struct EncodeParams {
   LayerView L;
   uint8_t* k_codes[4];
@@ -36,9 +38,68 @@ struct EncodeParams {
   int tokens;                      // tokens per input sequence
   int blocks;                      // grid: 64-token blocks (dense) or 64-row groups (compact) per head
   int stream;                      // compact kernel: 2 or 3
+  int first_stream, last_stream;   // dense kernel: the streams of this launch (0..1, 0..0 or 1..1)
+  int compact_input;               // compact kernel: input row i of a sequence is its i-th retained row
+                                   // (otherwise the row of its logical position)
 };
 
-__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+// The bfloat16 value a packed K row holds in channel c: code * scale + minimum in float32, rounded
+// (flashloop/packing.py:108-132), read back from stream s of the layer under construction.
+template <int BITS>
+__device__ __forceinline__ float decode_k(const EncodeParams& p, int s, int64_t bh, int row, int c) {
+  constexpr int kRowBytes = 16 * BITS;
+  constexpr int kPerByte = 8 / BITS;
+  const uint8_t byte = p.k_codes[s][(p.L.row_base[s][bh] + row) * kRowBytes + c / kPerByte];
+  const uint32_t code = (byte >> (BITS * (c % kPerByte))) & ((1u << BITS) - 1u);
+  const int64_t group = p.L.group_base[s][bh] + (row >> 6);
+  return bf16_round(dequant_f32(code, p.k_scale[s][group * kHeadDim + c], p.k_min[s][group * kHeadDim + c]));
+}
+// The same for the lane's four V channels 4*lane .. 4*lane+3 of a record.
+template <int BITS>
+__device__ __forceinline__ void decode_v4(const EncodeParams& p, int s, int64_t bh, int row, int lane, float (&dec)[4]) {
+  constexpr int kRowBytes = 16 * BITS;
+  const uint8_t* record = p.v_rows[s] + (p.L.row_base[s][bh] + row) * (kRowBytes + 16);
+  uint32_t packed;
+  if constexpr (BITS == 4) {
+    packed = reinterpret_cast<const uint16_t*>(record)[lane];
+  } else {
+    packed = record[lane];
+  }
+  const __half* meta = reinterpret_cast<const __half*>(record + kRowBytes);
+  const __half mn16 = meta[lane >> 4], sc16 = meta[2 + (lane >> 4)];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) dec[k] = bf16_round(dequant_f32((packed >> (BITS * k)) & ((1u << BITS) - 1u), sc16, mn16));
+}
+// The base a compact stream's residual is taken against at logical position `pos`: decode(anchor)
+// + decode(delta-2), and for stream 3 + decode(delta-3) of the position's loop-3 row, each sum
+// rounded to bfloat16 (flashloop/cache.py:488-504).
+template <int BITS>
+__device__ __forceinline__ float base_k(const EncodeParams& p, int s, int b, int64_t bh, int pos, int c) {
+  float base = bf16_round(decode_k<BITS>(p, 0, bh, pos, c) + decode_k<BITS>(p, 1, bh, pos, c));
+  if (s == 3) {
+    const int r3 = p.L.rank[0][p.L.rank_base[b] + pos];
+    if (r3 >= 0) base = bf16_round(base + decode_k<BITS>(p, 2, bh, r3, c));
+  }
+  return base;
+}
+template <int BITS>
+__device__ __forceinline__ void base_v4(const EncodeParams& p, int s, int b, int64_t bh, int pos, int lane,
+                                        float (&base)[4]) {
+  float d0[4], d1[4];
+  decode_v4<BITS>(p, 0, bh, pos, lane, d0);
+  decode_v4<BITS>(p, 1, bh, pos, lane, d1);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) base[k] = bf16_round(d0[k] + d1[k]);
+  if (s == 3) {
+    const int r3 = p.L.rank[0][p.L.rank_base[b] + pos];
+    if (r3 >= 0) {
+      decode_v4<BITS>(p, 2, bh, r3, lane, d0);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) base[k] = bf16_round(base[k] + d0[k]);
+    }
+  }
+}
+
 
 // Pack one byte-per-code tile of `rows` rows into code rows.
 template <int BITS>
@@ -143,8 +204,11 @@ __global__ void __launch_bounds__(128) encode_dense_kernel(const EncodeParams p)
     __shared__ __align__(16) __nv_bfloat16 s_recon[kGroup][kHeadDim];
     __shared__ uint8_t s_tile[kGroup][kHeadDim + 4];
     const int c = tid;
+    if (p.first_stream == 1) {  // delta-2 alone: its base is the anchor as it was packed
+      for (int i = 0; i < kGroup; ++i) s_recon[i][c] = __float2bfloat16_rn(decode_k<BITS>(p, 0, bh, t0 + i, c));
+    }
 #pragma unroll 1
-    for (int s = 0; s < 2; ++s) {
+    for (int s = p.first_stream; s <= p.last_stream; ++s) {
       load_rows(s_in, p.keys[s] + in_row0, kGroup, consecutive);
       __syncthreads();
       float mn = INFINITY, mx = -INFINITY;
@@ -173,7 +237,7 @@ __global__ void __launch_bounds__(128) encode_dense_kernel(const EncodeParams p)
       store_code_rows<BITS>(s_tile, kGroup, p.k_codes[s] + (p.L.row_base[s][bh] + t0) * kRowBytes);
       __syncthreads();
     }
-    store_rows(s_recon, p.recon_k + in_row0, kGroup, consecutive);
+    if (p.recon_k) store_rows(s_recon, p.recon_k + in_row0, kGroup, consecutive);
   } else {
     // ---------------- V: per token over 64-channel groups; a warp per token, 4 channels per lane,
     // four tokens at a time so that their loads are in flight together
@@ -183,20 +247,27 @@ __global__ void __launch_bounds__(128) encode_dense_kernel(const EncodeParams p)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int64_t in = in_row0 + static_cast<int64_t>(i0 + j) * kHeadDim + 4 * lane;
-        load4(p.values[0] + in, x0[j]);
-        load4(p.values[1] + in, x1[j]);
+        if (p.first_stream == 0) load4(p.values[0] + in, x0[j]);
+        if (p.last_stream == 1) load4(p.values[1] + in, x1[j]);
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int i = i0 + j;
         float recon[4], dec[4];
-        encode_v_row<BITS>(x0[j], p.v_rows[0] + (p.L.row_base[0][bh] + t0 + i) * (kRowBytes + 16), lane, recon);
+        if (p.first_stream == 0) {
+          encode_v_row<BITS>(x0[j], p.v_rows[0] + (p.L.row_base[0][bh] + t0 + i) * (kRowBytes + 16), lane, recon);
+        } else {
+          decode_v4<BITS>(p, 0, bh, t0 + i, lane, recon);
+        }
+        if (p.last_stream == 0) continue;
 #pragma unroll
         for (int k = 0; k < 4; ++k) x1[j][k] = bf16_round(x1[j][k] - recon[k]);
         encode_v_row<BITS>(x1[j], p.v_rows[1] + (p.L.row_base[1][bh] + t0 + i) * (kRowBytes + 16), lane, dec);
+        if (p.recon_v) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) recon[k] = bf16_round(recon[k] + dec[k]);
-        store4(p.recon_v + in_row0 + static_cast<int64_t>(i) * kHeadDim + 4 * lane, recon);
+          for (int k = 0; k < 4; ++k) recon[k] = bf16_round(recon[k] + dec[k]);
+          store4(p.recon_v + in_row0 + static_cast<int64_t>(i) * kHeadDim + 4 * lane, recon);
+        }
       }
     }
   }
@@ -237,14 +308,20 @@ __global__ void __launch_bounds__(128) encode_compact_kernel(const EncodeParams 
   if (rows == 0) return;
   const int64_t in_head = static_cast<int64_t>(head_in) * p.tokens * kHeadDim;
   auto retained = [&](int i) { return s_pos[i]; };
+  // where the group's rows sit in the input: at their logical positions, or packed in retained order
+  auto input_row = [&](int i) { return p.compact_input ? j0 + i : s_pos[i]; };
 
   if (blockIdx.y == 0) {
     __shared__ __align__(16) __nv_bfloat16 s_in[kGroup][kHeadDim];
     __shared__ __align__(16) __nv_bfloat16 s_recon[kGroup][kHeadDim];
     __shared__ uint8_t s_tile[kGroup][kHeadDim + 4];
     const int c = tid;
-    load_rows(s_in, p.keys[s] + in_head, rows, retained);
-    load_rows(s_recon, p.recon_k + in_head, rows, retained);
+    load_rows(s_in, p.keys[s] + in_head, rows, input_row);
+    if (p.recon_k) {
+      load_rows(s_recon, p.recon_k + in_head, rows, retained);
+    } else {
+      for (int i = 0; i < rows; ++i) s_recon[i][c] = __float2bfloat16_rn(base_k<BITS>(p, s, b, bh, s_pos[i], c));
+    }
     __syncthreads();
     float mn = INFINITY, mx = -INFINITY;
     for (int i = 0; i < rows; ++i) {
@@ -267,7 +344,7 @@ __global__ void __launch_bounds__(128) encode_compact_kernel(const EncodeParams 
     }
     __syncthreads();
     store_code_rows<BITS>(s_tile, rows, p.k_codes[s] + (p.L.row_base[s][bh] + j0) * kRowBytes);
-    if (s == 2) store_rows(s_recon, p.recon_k + in_head, rows, retained);
+    if (s == 2 && p.recon_k) store_rows(s_recon, p.recon_k + in_head, rows, retained);
   } else {
     const int lane = tid & 31, warp = tid >> 5;
     for (int i0 = warp * 4; i0 < rows; i0 += 16) {
@@ -275,9 +352,12 @@ __global__ void __launch_bounds__(128) encode_compact_kernel(const EncodeParams 
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int i = min(i0 + j, rows - 1);
-        const int64_t in = in_head + static_cast<int64_t>(s_pos[i]) * kHeadDim + 4 * lane;
-        load4(p.values[s] + in, x[j]);
-        load4(p.recon_v + in, recon[j]);
+        load4(p.values[s] + in_head + static_cast<int64_t>(input_row(i)) * kHeadDim + 4 * lane, x[j]);
+        if (p.recon_v) {
+          load4(p.recon_v + in_head + static_cast<int64_t>(s_pos[i]) * kHeadDim + 4 * lane, recon[j]);
+        } else {
+          base_v4<BITS>(p, s, b, bh, s_pos[i], lane, recon[j]);
+        }
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -287,7 +367,7 @@ __global__ void __launch_bounds__(128) encode_compact_kernel(const EncodeParams 
 #pragma unroll
         for (int k = 0; k < 4; ++k) x[j][k] = bf16_round(x[j][k] - recon[j][k]);
         encode_v_row<BITS>(x[j], p.v_rows[s] + (p.L.row_base[s][bh] + j0 + i) * (kRowBytes + 16), lane, dec);
-        if (s == 2) {
+        if (s == 2 && p.recon_v) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) recon[j][k] = bf16_round(recon[j][k] + dec[k]);
           store4(p.recon_v + in_head + static_cast<int64_t>(s_pos[i]) * kHeadDim + 4 * lane, recon[j]);
@@ -337,6 +417,9 @@ extern "C" int fl_encode_prefill(const fl_layer* layer, int32_t sequence_begin, 
   p.tokens = static_cast<int>(tokens);
   p.blocks = static_cast<int>(tokens / kGroup);
   p.stream = 0;
+  p.first_stream = 0;
+  p.last_stream = 1;
+  p.compact_input = 0;
   const int64_t heads_in = static_cast<int64_t>(sequence_count) * layer->heads;
   FL_REQUIRE(heads_in * (p.blocks + 1) < (int64_t(1) << 31), "%s: grid too large", who);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -352,5 +435,56 @@ extern "C" int fl_encode_prefill(const fl_layer* layer, int32_t sequence_begin, 
       }
     }
   }
+  return FL_OK;
+}
+
+extern "C" int fl_encode_prefill_stage(const fl_layer* layer, int32_t sequence_begin, int32_t sequence_count,
+                                       int64_t rows, int32_t stage, const void* keys, const void* values,
+                                       const int32_t* positions, int64_t positions_stride, int32_t compact_input,
+                                       fl_cuda_stream stream) {
+  const char* who = "fl_encode_prefill_stage";
+  FL_REQUIRE(stage >= 0 && stage < 4, "%s: stage must be in [0, 3], got %d", who, stage);
+  if (int rc = validate_layer(layer, stage, who)) return rc;
+  FL_REQUIRE(keys && values, "%s: null K/V", who);
+  FL_REQUIRE(aligned16(keys) && aligned16(values), "%s: K/V must be 16-byte aligned", who);
+  FL_REQUIRE(sequence_begin >= 0 && sequence_count > 0 && sequence_begin + sequence_count <= layer->batch,
+             "%s: sequences [%d, %d) outside the layer's batch of %d", who, sequence_begin,
+             sequence_begin + sequence_count, layer->batch);
+  FL_REQUIRE(rows > 0 && rows < (int64_t(1) << 30), "%s: bad row count", who);
+  FL_REQUIRE(stage < 2 || (positions && positions_stride > 0), "%s: stages 2 and 3 need the retained positions", who);
+  EncodeParams p{};
+  p.L = make_view(*layer);
+  for (int s = 0; s < 4; ++s) {
+    p.k_codes[s] = static_cast<uint8_t*>(layer->k_codes[s]);
+    p.k_min[s] = static_cast<__half*>(layer->k_min[s]);
+    p.k_scale[s] = static_cast<__half*>(layer->k_scale[s]);
+    p.v_rows[s] = static_cast<uint8_t*>(layer->v_rows[s]);
+  }
+  p.keys[stage] = static_cast<const __nv_bfloat16*>(keys);
+  p.values[stage] = static_cast<const __nv_bfloat16*>(values);
+  p.recon_k = nullptr;
+  p.recon_v = nullptr;
+  p.sequence_begin = sequence_begin;
+  p.tokens = static_cast<int>(rows);
+  p.stream = stage;
+  p.first_stream = p.last_stream = stage;
+  p.compact_input = compact_input ? 1 : 0;
+  const int64_t heads_in = static_cast<int64_t>(sequence_count) * layer->heads;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (stage < 2) {
+    p.blocks = static_cast<int>(rows / kGroup);
+    if (p.blocks == 0) return FL_OK;
+    FL_REQUIRE(heads_in * p.blocks < (int64_t(1) << 31), "%s: grid too large", who);
+    const dim3 grid(static_cast<unsigned>(heads_in * p.blocks), 2);
+    if (layer->bits == 4) encode_dense_kernel<4><<<grid, 128, 0, st>>>(p); else encode_dense_kernel<2><<<grid, 128, 0, st>>>(p);
+  } else {
+    p.positions[stage - 2] = positions;
+    p.positions_stride = positions_stride;
+    p.blocks = static_cast<int>((positions_stride + kGroup - 1) / kGroup);
+    FL_REQUIRE(heads_in * p.blocks < (int64_t(1) << 31), "%s: grid too large", who);
+    const dim3 grid(static_cast<unsigned>(heads_in * p.blocks), 2);
+    if (layer->bits == 4) encode_compact_kernel<4><<<grid, 128, 0, st>>>(p); else encode_compact_kernel<2><<<grid, 128, 0, st>>>(p);
+  }
+  FL_CHECK_LAUNCH(who);
   return FL_OK;
 }

@@ -20,7 +20,7 @@ from dataclasses import dataclass
 
 import torch
 
-from .cache import CrossLoopKVCache, CrossLoopKVLayer
+from .cache import CrossLoopKVCache, CrossLoopKVLayer, CrossLoopKVLayerBuilder
 from .compaction import RetainedTokens, hidden_delta_score, retain_tokens
 from .config import FlashLoopConfig, validate_ouro_model
 from .selection import decode_budget
@@ -141,15 +141,29 @@ class FlashLoopEngine:
         rope = self.backbone.rotary_emb(hidden, positions)
         norm = self.backbone.norm
 
+        # Every loop's dense K/V is packed as soon as the loop ends and dropped (engine.py:204-260):
+        # Loop 1 goes into the anchor streams before Loop 2 runs, Loop 2 into the delta-2 streams,
+        # and the late loops write their retained rows into the Loop-2 composite in place and hand
+        # the cache only those rows.  At most one full-size composite is alive at any time.
         loop1 = dense_prefill_loop(self.layers, hidden, position_embeddings=rope, final_norm=norm, loop=1,
                                    reduce=self._reduce)
+        builders = []
+        for index in range(len(self.layers)):
+            builders.append(CrossLoopKVLayerBuilder.from_loop1(
+                loop1.composite_cache.keys[index], loop1.composite_cache.values[index],
+                group_size=self.config.group_size, residual_length=self.config.residual_length,
+                bits=self.config.kv_bits, max_new_tokens=self.max_new_tokens))
+            loop1.composite_cache.keys[index] = None
+            loop1.composite_cache.values[index] = None
         loop2 = dense_prefill_loop(self.layers, loop1.hidden_states, position_embeddings=rope, final_norm=norm,
                                    loop=2, reduce=self._reduce)
+        for index, builder in enumerate(builders):
+            builder.add_loop2(loop2.composite_cache.keys[index], loop2.composite_cache.values[index])
         fraction3, fraction4 = self.config.effective_prefill_fractions
         keep3 = self._retain(3, hidden_delta_score(loop2.hidden_states, loop1.hidden_states), fraction3, None)
         loop3 = sparse_prefill_loop(self.layers, loop2.hidden_states, retained=keep3,
                                     composite_cache=loop2.composite_cache, position_embeddings=rope,
-                                    final_norm=norm, loop=3, reduce=self._reduce)
+                                    final_norm=norm, loop=3, reduce=self._reduce, consume_inputs=True)
         if self.reference_loop4_scores:
             # engine.py:258-275 runs Loop 3 with consume_inputs=True, so prefill.py:236-237,254
             # write the Loop-3 rows into the Loop-2 tensor itself and the score of
@@ -161,20 +175,18 @@ class FlashLoopEngine:
         keep4 = self._retain(4, score4, fraction4, keep3.mask)
         loop4 = sparse_prefill_loop(self.layers, loop3.hidden_states, retained=keep4,
                                     composite_cache=loop3.composite_cache, position_embeddings=rope,
-                                    final_norm=norm, loop=4, reduce=self._reduce)
+                                    final_norm=norm, loop=4, reduce=self._reduce, consume_inputs=True)
 
         physical = CrossLoopKVCache(num_layers=len(self.layers))
         loops = (loop1, loop2, loop3, loop4)
-        for index in range(len(self.layers)):
-            physical.set_layer(index, CrossLoopKVLayer.from_prefill(
-                [lp.composite_cache.keys[index] for lp in loops],
-                [lp.composite_cache.values[index] for lp in loops],
-                mask_loop3=keep3.mask, mask_loop4=keep4.mask, group_size=self.config.group_size,
-                residual_length=self.config.residual_length, bits=self.config.kv_bits,
-                max_new_tokens=self.max_new_tokens))
-            for lp in loops:  # release the dense K/V of this layer
-                lp.composite_cache.keys[index] = None
-                lp.composite_cache.values[index] = None
+        rows3, rows4 = int(keep3.count[0]), int(keep4.count[0])
+        for index, builder in enumerate(builders):
+            physical.set_layer(index, builder.finalize(
+                loop3_positions=keep3.positions[:, :rows3], loop3_keys=loop3.updates[index][0],
+                loop3_values=loop3.updates[index][1], loop4_positions=keep4.positions[:, :rows4],
+                loop4_keys=loop4.updates[index][0], loop4_values=loop4.updates[index][1]))
+            loop4.composite_cache.keys[index] = None  # the composite of this layer (shared by loops 2-4)
+            loop4.composite_cache.values[index] = None
         self._decode_limit = tokens + self.max_new_tokens
         self._state = EngineState(cache=physical, next_position=tokens, mask_loop3=keep3.mask,
                                   mask_loop4=keep4.mask,

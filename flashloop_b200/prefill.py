@@ -51,6 +51,8 @@ class PrefillLoopOutput:
     hidden_states: torch.Tensor
     composite_cache: PrefillCompositeCache
     receipt: PrefillReceipt
+    # a late loop: per layer the (K, V) of its retained rows only, [B, H, rows, D] in position order
+    updates: tuple = ()
 
 
 def _rotate_half(values: torch.Tensor) -> torch.Tensor:
@@ -111,9 +113,12 @@ def dense_prefill_loop(layers: Sequence[nn.Module], hidden_states: torch.Tensor,
 
 def sparse_prefill_loop(layers: Sequence[nn.Module], hidden_states: torch.Tensor, *, retained: RetainedTokens,
                         composite_cache: PrefillCompositeCache, position_embeddings, final_norm: nn.Module,
-                        loop: int, reduce=_identity) -> PrefillLoopOutput:
-    """A late loop over the retained rows only (prefill.py:307-342).  Returns new full
-    composites (retained rows replaced, the others carried over from ``composite_cache``)."""
+                        loop: int, reduce=_identity, consume_inputs: bool = False) -> PrefillLoopOutput:
+    """A late loop over the retained rows only (prefill.py:307-342).  Returns full composites with
+    the retained rows replaced and, per layer, the compact K/V of those rows (``updates``).  With
+    ``consume_inputs`` the rows are written into the tensors of ``composite_cache`` themselves
+    (prefill.py:236-237), so no second full-size composite ever exists; the hidden states are
+    always copied (they are small, and the Loop-4 score needs the previous loop's)."""
 
     if int(loop) not in (3, 4):
         raise ValueError("sparse prefill is defined for Loop 3 or Loop 4")
@@ -133,7 +138,7 @@ def sparse_prefill_loop(layers: Sequence[nn.Module], hidden_states: torch.Tensor
     allowed = torch.arange(tokens, device=hidden.device)[None, None, :] <= pos[:, :, None]
     attn_mask = torch.zeros((batch, 1, rows, tokens), dtype=hidden.dtype, device=hidden.device)
     attn_mask.masked_fill_(~allowed[:, None], float("-inf"))
-    keys, values = [], []
+    keys, values, updates = [], [], []
     for index, layer in enumerate(layers):
         attention = layer.self_attn
         head_dim = int(attention.head_dim)
@@ -141,14 +146,17 @@ def sparse_prefill_loop(layers: Sequence[nn.Module], hidden_states: torch.Tensor
         heads = q.shape[-1] // head_dim
         q, k, v = _heads(q, heads, head_dim), _heads(k, heads, head_dim), _heads(v, heads, head_dim)
         q, k = apply_rope(q, k, cos, sin)
-        full_k = composite_cache.keys[index].clone()
-        full_v = composite_cache.values[index].clone()
-        scatter_rows(full_k.view(batch * heads, tokens, head_dim),
-                     k.contiguous().view(batch * heads, rows, head_dim), positions, count, per_sequence=heads)
-        scatter_rows(full_v.view(batch * heads, tokens, head_dim),
-                     v.contiguous().view(batch * heads, rows, head_dim), positions, count, per_sequence=heads)
+        k, v = k.contiguous(), v.contiguous()
+        full_k, full_v = composite_cache.keys[index], composite_cache.values[index]
+        if not consume_inputs:
+            full_k, full_v = full_k.clone(), full_v.clone()
+        scatter_rows(full_k.view(batch * heads, tokens, head_dim), k.view(batch * heads, rows, head_dim),
+                     positions, count, per_sequence=heads)
+        scatter_rows(full_v.view(batch * heads, tokens, head_dim), v.view(batch * heads, rows, head_dim),
+                     positions, count, per_sequence=heads)
         keys.append(full_k)
         values.append(full_v)
+        updates.append((k, v))
         out = F.scaled_dot_product_attention(q, full_k, full_v, attn_mask=attn_mask, dropout_p=0.0)
         out = reduce(attention.o_proj(out.transpose(1, 2).reshape(batch, rows, -1)))
         active = _layer_tail(layer, active, out, reduce)
@@ -157,4 +165,4 @@ def sparse_prefill_loop(layers: Sequence[nn.Module], hidden_states: torch.Tensor
     n = len(layers)
     receipt = PrefillReceipt(loop, batch * tokens, batch * rows, 3 * batch * rows * n, batch * rows * n,
                              batch * rows * n, 0, n)
-    return PrefillLoopOutput(hidden, PrefillCompositeCache(keys, values), receipt)
+    return PrefillLoopOutput(hidden, PrefillCompositeCache(keys, values), receipt, tuple(updates))

@@ -319,6 +319,22 @@ int fl_encode_prefill(const fl_layer* layer, int32_t sequence_begin, int32_t seq
                       const int32_t* positions4, int64_t positions_stride, void* recon_k, void* recon_v,
                       fl_cuda_stream stream);
 
+/* The same encoder one loop at a time, for a prefill that frees every loop's K/V as soon as it
+ * is packed: CrossLoopKVLayerBuilder.from_loop1 (stage 0, flashloop/cache.py:343-397), add_loop2
+ * (stage 1, :415-439) and the two halves of _install_sparse_streams / finalize (stages 2 and 3,
+ * :469-508, 510-625).  Every stage reads the base it subtracts back from the streams already
+ * packed in the layer (decode(anchor); decode(anchor) + decode(delta-2); + decode(delta-3) at the
+ * position's loop-3 row), as the reference's builder does, so no reconstruction scratch is kept
+ * between the stages and the codes are the same bits as fl_encode_prefill's.  keys / values:
+ * bfloat16 [sequence_count][heads][rows][128] of the stage's loop.  Stages 0 and 1: rows = prompt
+ * tokens.  Stages 2 and 3: positions int32 [sequence_count][positions_stride] (retained positions
+ * ascending, then -1); with compact_input != 0 input row i of a sequence is its i-th retained row
+ * (rows = rows per sequence of that compact tensor), otherwise the row of its logical position.
+ * Stage 3 needs the layer's loop-3 rank map filled. */
+int fl_encode_prefill_stage(const fl_layer* layer, int32_t sequence_begin, int32_t sequence_count, int64_t rows,
+                            int32_t stage, const void* keys, const void* values, const int32_t* positions,
+                            int64_t positions_stride, int32_t compact_input, fl_cuda_stream stream);
+
 /* ---------------------------------------------------------------------------------------
  * Elementwise glue of one decode step around the readers (bfloat16 rows, one token per row).
  * Each restates module arithmetic of the reference's decode loop with the roundings of

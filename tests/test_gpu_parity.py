@@ -139,6 +139,131 @@ def test_prefill_streams_bit_exact_vs_reference_vectors(fl, golden):
         np.testing.assert_array_equal(bits16(ex[f"tail_k{r}"]), golden[f"layer.tail_k{r}"][0])
 
 
+def _compact(t, mask):
+    """Rows of [1, H, T, D] at the True positions of ``mask`` [T], in position order."""
+    return t[:, :, torch.nonzero(mask).flatten()].contiguous()
+
+
+def test_staged_builder_bit_exact_vs_reference_vectors(fl, golden):
+    """CrossLoopKVLayerBuilder (from_loop1 / add_loop2 / finalize on compact Loop-3/4 rows) and
+    from_prefill_updates against the reference's streams, rank maps and tails, and ``gather``
+    against the reference layer's gather."""
+
+    from flashloop_b200.cache import CrossLoopKVLayer, CrossLoopKVLayerBuilder
+
+    keys, values, m3, m4, *_ = golden_inputs(golden)
+    k = [bf16_tensor(x) for x in keys]
+    v = [bf16_tensor(x) for x in values]
+    mask3, mask4 = torch.from_numpy(m3).cuda(), torch.from_numpy(m4).cuda()
+    pos3 = torch.nonzero(mask3).flatten().to(torch.int32)
+    pos4 = torch.nonzero(mask4).flatten().to(torch.int32)
+    builder = CrossLoopKVLayerBuilder.from_loop1(k[0], v[0], max_new_tokens=128)
+    assert not builder.retains_dense_loop1_prefix and builder.packed_tokens == 128
+    with pytest.raises(RuntimeError):
+        builder.finalize(loop3_positions=pos3, loop3_keys=_compact(k[2], mask3), loop3_values=_compact(v[2], mask3),
+                         loop4_positions=pos4, loop4_keys=_compact(k[3], mask4), loop4_values=_compact(v[3], mask4))
+    builder.add_loop2(k[1], v[1])
+    with pytest.raises(RuntimeError):
+        builder.add_loop2(k[1], v[1])
+    staged = builder.finalize(loop3_positions=pos3, loop3_keys=_compact(k[2], mask3),
+                              loop3_values=_compact(v[2], mask3), loop4_positions=pos4,
+                              loop4_keys=_compact(k[3], mask4), loop4_values=_compact(v[3], mask4))
+    at_once = CrossLoopKVLayer.from_prefill_updates(
+        loop1_key=k[0], loop1_value=v[0], loop2_key=k[1], loop2_value=v[1], loop3_positions=pos3,
+        loop3_keys=_compact(k[2], mask3), loop3_values=_compact(v[2], mask3), loop4_positions=pos4,
+        loop4_keys=_compact(k[3], mask4), loop4_values=_compact(v[3], mask4))
+    for layer in (staged, at_once):
+        ex = layer.export_sequence(0)
+        assert ex["quantized_tokens"] == 128 and ex["tail_tokens"] == 72
+        for s in range(4):
+            for kind in ("k", "v"):
+                ref = golden_stream(golden, f"layer.triton_row.{kind}{s}")
+                np.testing.assert_array_equal(ex[f"{kind}{s}.payload"].cpu().numpy(), ref["payload"][0], err_msg=f"{kind}{s}")
+                np.testing.assert_array_equal(bits16(ex[f"{kind}{s}.minimum"]), ref["minimum"][0].view(np.uint16))
+                np.testing.assert_array_equal(bits16(ex[f"{kind}{s}.scale"]), ref["scale"][0].view(np.uint16))
+        np.testing.assert_array_equal(ex["rank3"].cpu().numpy(), golden["layer.triton_row.rank3"])
+        np.testing.assert_array_equal(ex["rank4"].cpu().numpy(), golden["layer.triton_row.rank4"])
+        # The builder sees only the retained Loop-3/4 rows: a tail token that a late loop did not
+        # retain keeps the loop before's row (flashloop/cache.py:584-606), whereas the vectors come
+        # from full Loop-3/4 tensors; the tails of loops 1-2 and the retained rows are the same.
+        for r in range(2):
+            np.testing.assert_array_equal(bits16(ex[f"tail_k{r}"]), golden[f"layer.tail_k{r}"][0])
+            np.testing.assert_array_equal(bits16(ex[f"tail_v{r}"]), golden[f"layer.tail_v{r}"][0])
+        for r, mask in ((2, mask3), (3, mask4)):
+            kept = mask[128:].cpu().numpy()
+            np.testing.assert_array_equal(bits16(ex[f"tail_k{r}"])[:, kept], golden[f"layer.tail_k{r}"][0][:, kept])
+            np.testing.assert_array_equal(bits16(ex[f"tail_k{r}"])[:, ~kept], bits16(ex[f"tail_k{r - 1}"])[:, ~kept])
+            np.testing.assert_array_equal(bits16(ex[f"tail_v{r}"])[:, kept], golden[f"layer.tail_v{r}"][0][:, kept])
+        np.testing.assert_array_equal(ex["tail_active3"].cpu().numpy(), golden["layer.tail_active3"][0])
+        np.testing.assert_array_equal(ex["tail_active4"].cpu().numpy(), golden["layer.tail_active4"][0])
+    every = torch.arange(200)
+    for loop in (1, 3):
+        gk, gv = staged.gather(loop, every)
+        upto = 200 if loop == 1 else 128  # (loop 3: the packed prefix; its tail differs as said above)
+        np.testing.assert_array_equal(bits16(gk)[:, :, :upto], golden[f"gather.loop{loop}.k"][:, :, :upto])
+        np.testing.assert_array_equal(bits16(gv)[:, :, :upto], golden[f"gather.loop{loop}.v"][:, :, :upto])
+    with pytest.raises(IndexError):
+        staged.gather(1, torch.tensor([200]))
+    with pytest.raises(ValueError):  # Loop-4 rows must be Loop-3 rows
+        other = CrossLoopKVLayerBuilder.from_loop1(k[0], v[0])
+        other.add_loop2(k[1], v[1])
+        stray = torch.nonzero(~mask3).flatten()[:3].to(torch.int32)
+        other.finalize(loop3_positions=pos3, loop3_keys=_compact(k[2], mask3), loop3_values=_compact(v[2], mask3),
+                       loop4_positions=stray, loop4_keys=k[3][:, :, stray.long()].contiguous(),
+                       loop4_values=v[3][:, :, stray.long()].contiguous())
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+def test_staged_builder_batch_equals_one_shot_encoder(fl, bits):
+    """A batch of three prompts, retention masks that differ per sequence: the staged builder
+    and the one-shot from_prefill produce identical layers (every stream, rank map and tail)."""
+
+    from flashloop_b200.cache import CrossLoopKVLayer, CrossLoopKVLayerBuilder
+    from flashloop_b200.synthetic import make_loop_kv, make_masks
+
+    heads, tokens, batch = 3, 450, 3
+    per = [make_loop_kv(heads, tokens, seed=900 + b) for b in range(batch)]
+    keys = [torch.cat([per[b][0][r] for b in range(batch)]).cuda() for r in range(4)]
+    values = [torch.cat([per[b][1][r] for b in range(batch)]).cuda() for r in range(4)]
+    masks = [make_masks(tokens, seed=900 + b) for b in range(batch)]
+    m3 = torch.stack([m[0] for m in masks]).cuda()
+    m4 = torch.stack([m[1] for m in masks]).cuda()
+    # composites as a prefill holds them: a late loop's tensor is the loop before with its retained
+    # rows replaced
+    for r, mask in ((2, m3), (3, m4)):
+        keep = mask[:, None, :, None]
+        keys[r] = torch.where(keep, keys[r], keys[r - 1])
+        values[r] = torch.where(keep, values[r], values[r - 1])
+    one_shot = CrossLoopKVLayer.from_prefill(keys, values, mask_loop3=m3, mask_loop4=m4, bits=bits)
+
+    def positions(mask):
+        rows = int(mask.sum(1).max())
+        out = torch.full((batch, rows), -1, dtype=torch.int32, device="cuda")
+        for b in range(batch):
+            p = torch.nonzero(mask[b]).flatten().to(torch.int32)
+            out[b, :p.numel()] = p
+        return out
+
+    def compact(t, pos):
+        idx = pos.clamp(min=0).long()[:, None, :, None].expand(-1, heads, -1, 128)
+        return torch.gather(t, 2, idx).contiguous()
+
+    p3, p4 = positions(m3), positions(m4)
+    builder = CrossLoopKVLayerBuilder.from_loop1(keys[0], values[0], bits=bits)
+    builder.add_loop2(keys[1], values[1])
+    staged = builder.finalize(loop3_positions=p3, loop3_keys=compact(keys[2], p3), loop3_values=compact(values[2], p3),
+                              loop4_positions=p4, loop4_keys=compact(keys[3], p4), loop4_values=compact(values[3], p4))
+    for b in range(batch):
+        a, c = one_shot.export_sequence(b), staged.export_sequence(b)
+        assert a.keys() == c.keys()
+        for name in a:
+            if isinstance(a[name], torch.Tensor):
+                assert torch.equal(a[name], c[name]), (bits, b, name)
+            else:
+                assert a[name] == c[name], (bits, b, name)
+    assert staged.storage_bytes == one_shot.storage_bytes
+
+
 @pytest.mark.parametrize("tokens,all_active", [(100, False), (128, False), (191, False), (200, False),
                                                (333, True), (700, False)])
 def test_prefill_and_readers_vs_oracle(fl, tokens, all_active):
