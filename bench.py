@@ -79,8 +79,13 @@ def parse_args():
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tp", action="store_true",
-                    help="e2e workload: shard heads and FFN columns over the ranks (NCCL all-reduce after o_proj "
-                         "and the MLP) instead of running one replica per rank")
+                    help="e2e workload: make the headline one model sharded by heads and FFN columns over the ranks "
+                         "(strong scaling) instead of one replica per rank; without it an N>1 line still carries that "
+                         "measurement as `tensor_parallel`")
+    ap.add_argument("--tp-allreduce", default="peer", choices=["peer", "nccl"],
+                    help="decode-step sum over the ranks: peer = this library's one-launch all-reduce + norm over "
+                         "peer memory, replayed from a CUDA graph; nccl = NCCL all-reduces, launched eagerly")
+    ap.add_argument("--no-tp-probe", action="store_true", help="N>1 replica runs: skip the tensor-parallel measurement")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-probes", action="store_true",
                     help="skip the configs[1]-shaped reader probes behind roofline_dense / roofline_sparse")
@@ -134,7 +139,8 @@ def bench_config(args) -> dict:
         parallelism = f"batch-sharded x{world}, no data-path collective"
     return {"workload": workload_name(args), "global_batch": args.batch if tp else args.batch * world, "l2": l2,
             "parallelism": parallelism,
-            "launch": "eager" if args.no_graph else "one CUDA graph replay per step"}
+            "launch": ("eager" if args.no_graph or (tp and getattr(args, "tp_allreduce", "peer") == "nccl")
+                       else "one CUDA graph replay per step")}
 
 
 # ----------------------------------------------------------------------------- algorithmic bytes
@@ -866,9 +872,10 @@ def run_e2e(args) -> None:
     tp = args.tp and world > 1
     if tp:
         shard_ouro_model(model, rank, world)  # this rank's heads and FFN columns
+    graph_ok = not args.no_graph and not (tp and args.tp_allreduce == "nccl")
     engine = FlashLoopEngine(model, config=FlashLoopConfig(kv_bits=args.bits), validate_model=False,
-                             max_new_tokens=budget, use_cuda_graph=not (args.no_graph or tp),
-                             tp_group=dist.group.WORLD if tp else None)
+                             max_new_tokens=budget, use_cuda_graph=graph_ok,
+                             tp_group=dist.group.WORLD if tp else None, tp_allreduce=args.tp_allreduce)
     gen = torch.Generator().manual_seed(100 + (0 if tp else rank))
     prompts = torch.randint(0, cfg.vocab_size, (B, T), generator=gen).to(device)
     torch.cuda.synchronize()
@@ -950,6 +957,32 @@ def run_e2e(args) -> None:
     if world > 1:
         dist.barrier()
 
+    # ---- N>1 replica runs: the same model once more, sharded over the ranks (strong scaling)
+    tensor_parallel = None
+    if world > 1 and not tp and not args.no_tp_probe:
+        tp_model = OuroShapedForCausalLM(cfg, seed=0, device=device)
+        shard_ouro_model(tp_model, rank, world)
+        tp_engine = FlashLoopEngine(tp_model, config=FlashLoopConfig(kv_bits=args.bits), validate_model=False,
+                                    max_new_tokens=budget, use_cuda_graph=not args.no_graph,
+                                    tp_group=dist.group.WORLD, tp_allreduce="peer")
+        shared = torch.randint(0, cfg.vocab_size, (B, T), generator=torch.Generator().manual_seed(100)).to(device)
+        tp_state = {"token": tp_engine.prefill(shared).logits.argmax(-1, keepdim=True)}
+
+        def tp_step():
+            tp_state["token"] = tp_engine.decode(tp_state["token"]).logits.argmax(-1, keepdim=True)
+
+        for _ in range(max(3, args.warmup)):
+            tp_step()
+        tp_ms = timed(tp_step, args.steps)
+        peer_status = tp_engine._peer.status()
+        tensor_parallel = {
+            "value": B * args.steps / (tp_ms * 1e-3), "unit": "tok/s", "ms_per_step": tp_ms / args.steps,
+            "scaling": "strong", "global_batch": B, "parallelism": f"tp{world}",
+            "all_reduce": "fl_allreduce_rmsnorm (one launch per sum, peer stores over NVLink, fused with the "
+                          "residual add and the RMSNorms), whole step replayed from a CUDA graph",
+            "peer_status": peer_status}
+        dist.barrier()
+
     if rank == 0:
         peak, peak_kind = load_peak()
         algo = dense_bytes(B * H, 1, quant, tail, args.bits)
@@ -977,6 +1010,11 @@ def run_e2e(args) -> None:
             "reader_status": status,
         }
         line.update(probes)
+        if tensor_parallel is not None:
+            line["tensor_parallel"] = tensor_parallel
+        if tp:
+            line["tensor_parallel_all_reduce"] = args.tp_allreduce
+            line["peer_status"] = engine._peer.status() if engine._peer is not None else None
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_e2e_tokens_per_second(args)
         print(json.dumps(line))

@@ -71,6 +71,13 @@ SIGNATURES = {
     "fl_rmsnorm": (C.c_int, [_vp, _vp, _vp, _f32, _vp, _f32, _i64, _i32, _vp, _vp, _vp]),
     "fl_rope_split": (C.c_int, [_vp, _vp, _vp, _i64, _vp, _vp, _i64, _i32, _vp, _vp, _vp, _vp]),
     "fl_swiglu": (C.c_int, [_vp, _i64, _i32, _vp, _vp]),
+    "fl_comm_handle_bytes": (_sz, []),
+    "fl_comm_create": (C.c_int, [_i32, _i32, _i32, _i32, C.POINTER(_vp), _vp]),
+    "fl_comm_connect": (C.c_int, [_vp, _vp]),
+    "fl_comm_destroy": (C.c_int, [_vp]),
+    "fl_comm_status": (C.c_int, [_vp, C.POINTER(_i32), _i32, _vp]),
+    "fl_allreduce_rmsnorm": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _f32, _vp, _f32, _i64, _vp, _vp, _vp, _i32, _i32,
+                                       _vp]),
 }
 
 # kernels launched by one call of an entry point (entry points that launch nothing are absent)
@@ -80,7 +87,7 @@ LAUNCHES_PER_CALL = {
     "fl_dense_source_attention_static": 1, "fl_sparse_attention_delta": 1, "fl_selected_pv": 1, "fl_selected_qk": 1,
     "fl_append_decode_token": 3, "fl_select_decode_keys": 1, "fl_hidden_delta_score": 1,
     "fl_select_prefill_tokens": 1, "fl_gather_rows": 1, "fl_scatter_rows": 1, "fl_encode_prefill": 3, "fl_encode_prefill_stage": 1,
-    "fl_rmsnorm": 1, "fl_rope_split": 1, "fl_swiglu": 1,
+    "fl_rmsnorm": 1, "fl_rope_split": 1, "fl_swiglu": 1, "fl_allreduce_rmsnorm": 1,
 }
 
 _LIB = None

@@ -26,7 +26,7 @@ from .config import FlashLoopConfig, validate_ouro_model
 from .selection import decode_budget
 from .prefill import PrefillReceipt, apply_rope, dense_prefill_loop, sparse_prefill_loop
 from . import step_ops
-from .tensor_parallel import PartialSum
+from .tensor_parallel import PartialSum, PeerAllReduce
 from .weights import fused_mlp, project_qkv, project_value, repack_projection_weights
 
 
@@ -65,7 +65,8 @@ class FlashLoopEngine:
 
     def __init__(self, model: torch.nn.Module, *, config: FlashLoopConfig | None = None,
                  validate_model: bool = True, max_new_tokens: int = 512, use_cuda_graph: bool = False,
-                 reference_loop4_scores: bool = True, fuse_decode_ops: bool = True, tp_group=None) -> None:
+                 reference_loop4_scores: bool = True, fuse_decode_ops: bool = True, tp_group=None,
+                 tp_allreduce: str = "peer", tp_wait_limit: int = 0) -> None:
         if validate_model:
             validate_ouro_model(model)
         elif int(getattr(model.config, "total_ut_steps", 0)) != 4:
@@ -80,9 +81,18 @@ class FlashLoopEngine:
         self.use_cuda_graph = bool(use_cuda_graph)
         self.reference_loop4_scores = bool(reference_loop4_scores)
         # tensor parallelism: the model holds this rank's heads / FFN columns (see tensor_parallel.py)
-        # and the partial o_proj / down_proj outputs are summed over ``tp_group``
-        if tp_group is not None and use_cuda_graph:
-            raise ValueError("the tensor-parallel decode step is launched eagerly: use_cuda_graph=False")
+        # and the partial o_proj / down_proj outputs are summed over ``tp_group``: with NCCL in
+        # prefill, and in a decode step either with NCCL (tp_allreduce="nccl", eager launches only)
+        # or inside the norm launch over peer memory (tp_allreduce="peer", recordable in a graph)
+        if tp_allreduce not in ("peer", "nccl"):
+            raise ValueError("tp_allreduce is 'peer' or 'nccl'")
+        if tp_group is not None and use_cuda_graph and tp_allreduce != "peer":
+            raise ValueError("with NCCL all-reduces the tensor-parallel decode step is launched eagerly: "
+                             "use_cuda_graph=False or tp_allreduce='peer'")
+        self.tp_group = tp_group
+        self.tp_allreduce = tp_allreduce
+        self.tp_wait_limit = int(tp_wait_limit)
+        self._peer: PeerAllReduce | None = None
         self._reduce = PartialSum(tp_group) if tp_group is not None else (lambda t: t)
         self.fuse_decode_ops = bool(fuse_decode_ops) and self._modules_are_fusable()
         self._reuse = self.config.reuse_selected_probabilities and self.config.enable_sparse_decode
@@ -188,6 +198,11 @@ class FlashLoopEngine:
             loop4.composite_cache.keys[index] = None  # the composite of this layer (shared by loops 2-4)
             loop4.composite_cache.values[index] = None
         self._decode_limit = tokens + self.max_new_tokens
+        if (self.tp_group is not None and self.tp_allreduce == "peer" and input_ids.is_cuda
+                and (self._peer is None or self._peer.rows_max < batch)):
+            # collective over the group: every rank reaches this point of prefill
+            self._peer = PeerAllReduce(self.tp_group, rows_max=batch, width=int(hidden.shape[-1]),
+                                       device=input_ids.device, wait_limit=self.tp_wait_limit)
         self._state = EngineState(cache=physical, next_position=tokens, mask_loop3=keep3.mask,
                                   mask_loop4=keep4.mask,
                                   prefill_receipts=tuple(lp.receipt for lp in loops))
@@ -236,32 +251,57 @@ class FlashLoopEngine:
         return self._decode_step_modules(token_ids, position_ids)
 
     def _attend(self, loop: int, index: int, q, k, v, scaling: float, sources: list, o_proj, batch: int):
-        """The cache-facing part of one layer and loop (engine.py:422-531): returns the projected
-        attention output [B, 1, hidden]."""
+        """The cache-facing part of one layer and loop (engine.py:422-531).  Returns (partial,
+        addend, keep): the projected attention output [B, 1, hidden] is ``[addend +] sum over the
+        tensor-parallel ranks of partial`` (one rank: partial itself), and with ``keep`` the caller
+        stores that output in ``sources[index][0]`` for the late loops."""
 
         physical = self.state.cache.layers[index]
         if loop < 2 or not self.config.enable_sparse_decode:
             want_logits = loop == 1 and self.config.enable_sparse_decode
             out, logits = physical.dense_source_attention(loop, query=q, current_key=k, current_value=v,
                                                           scaling=scaling, return_logits=want_logits)
-            projected = self._reduce(o_proj(out.to(q.dtype).view(batch, 1, -1)))
+            partial = o_proj(out.to(q.dtype).view(batch, 1, -1))
             if want_logits:
                 sel = physical.select_decode_keys(logits, fraction=self.config.effective_decode_key_fraction)
                 aggregate = physical.pv(1, sel.selected_weights, sel.indices, current_value=v,
                                         valid=sel.valid, validate_indices=False)
-                sources[index] = (projected, sel, aggregate)
-            return projected
+                sources[index] = [None, sel, aggregate]
+            return partial, None, want_logits
         projected0, sel, aggregate = sources[index]
         if self.config.reuse_selected_probabilities:
             # engine.py:502-513: the loop-2 probabilities are reused, only V is read
             target = physical.pv(loop, sel.selected_weights, sel.indices, current_value=v, valid=sel.valid,
                                  validate_indices=False)
             delta = sel.global_mass.view(batch, -1, 1, 1) * (target - aggregate)
-            return projected0 + self._reduce(o_proj(delta.to(v.dtype).view(batch, 1, -1)))
+            return o_proj(delta.to(v.dtype).view(batch, 1, -1)), projected0, False
         delta = physical.cached_mass_sparse_attention_delta(
             loop, query=q, current_key=k, current_value=v, indices=sel.indices, valid=sel.valid,
             source_selected_output=aggregate, global_mass=sel.global_mass, scaling=scaling)
-        return projected0 + self._reduce(o_proj(delta.to(v.dtype).view(batch, 1, -1)))
+        return o_proj(delta.to(v.dtype).view(batch, 1, -1)), projected0, False
+
+    def _decode_reduce(self, partial: torch.Tensor) -> torch.Tensor:
+        """Sum of a decode step's partial outputs over the tensor-parallel ranks."""
+
+        if self._peer is not None:
+            return self._peer(partial.contiguous())
+        return self._reduce(partial)
+
+    def _sum_norm(self, partial, addend, norm, norm2, residual, want_sum: bool):
+        """``s = [addend +] sum over ranks of partial``; ``hidden = residual + norm(s)``;
+        ``x = norm2(hidden)``: one launch (with peer tensor parallelism the sum over the ranks
+        happens inside it).  Returns (hidden, x, s or None)."""
+
+        eps = self._norm_eps
+        if self._peer is not None:
+            return self._peer.reduce_norm(partial.contiguous(), norm.weight, eps(norm), residual=residual,
+                                          weight2=norm2.weight, eps2=eps(norm2), addend=addend, want_sum=want_sum)
+        total = self._reduce(partial)
+        if addend is not None:
+            total = addend + total
+        hidden, x = step_ops.rmsnorm(total, norm.weight, eps(norm), residual=residual, weight2=norm2.weight,
+                                     eps2=eps(norm2))
+        return hidden, x, total
 
     def _decode_step_fused(self, token_ids: torch.Tensor, position_ids: torch.Tensor) -> torch.Tensor:
         """One decode step with the elementwise glue as one-launch kernels (``step_ops``): per layer
@@ -293,15 +333,15 @@ class FlashLoopEngine:
                                                                                   dim=-1)
                     q, k, v = step_ops.rope_split(q, k, v, cos, sin, heads=q.shape[-1] // 128)
                 keys[index][loop], values[index][loop] = k, v
-                projected = self._attend(loop, index, q, k, v, float(attention.scaling), sources,
-                                         attention.o_proj, batch)
+                partial, addend, keep = self._attend(loop, index, q, k, v, float(attention.scaling), sources,
+                                                     attention.o_proj, batch)
                 n2, n3, n4 = layer.input_layernorm_2, layer.post_attention_layernorm, layer.post_attention_layernorm_2
-                hidden, x = step_ops.rmsnorm(projected, n2.weight, eps(n2), residual=hidden,
-                                             weight2=n3.weight, eps2=eps(n3))
-                m = self._reduce(mlp.down_proj(step_ops.swiglu(F.linear(x, mlp._flashloop_gate_up_weight))))
+                hidden, x, projected = self._sum_norm(partial, addend, n2, n3, hidden, keep)
+                if keep:
+                    sources[index][0] = projected
+                m = mlp.down_proj(step_ops.swiglu(F.linear(x, mlp._flashloop_gate_up_weight)))
                 following = self.backbone.norm if index == n_layers - 1 else self.layers[index + 1].input_layernorm
-                hidden, x = step_ops.rmsnorm(m, n4.weight, eps(n4), residual=hidden,
-                                             weight2=following.weight, eps2=eps(following))
+                hidden, x, _ = self._sum_norm(m, None, n4, following, hidden, False)
             hidden = x  # the final norm of this loop
         for index in range(n_layers):
             cache.layers[index].append_decode_token(keys[index], values[index])
@@ -335,12 +375,17 @@ class FlashLoopEngine:
                     q, k = apply_rope(q, k, cos, sin)
                     q, k = q.contiguous(), k.contiguous()
                 keys[index][loop], values[index][loop] = k, v
-                projected = self._attend(loop, index, q, k, v, float(attention.scaling), sources,
-                                         attention.o_proj, batch)
+                partial, addend, keep = self._attend(loop, index, q, k, v, float(attention.scaling), sources,
+                                                     attention.o_proj, batch)
+                projected = self._decode_reduce(partial)
+                if addend is not None:
+                    projected = addend + projected
+                if keep:
+                    sources[index][0] = projected
                 residual = hidden
                 hidden = residual + layer.input_layernorm_2(projected)
                 hidden = hidden + layer.post_attention_layernorm_2(
-                    self._reduce(fused_mlp(layer.mlp, layer.post_attention_layernorm(hidden))))
+                    self._decode_reduce(fused_mlp(layer.mlp, layer.post_attention_layernorm(hidden))))
             hidden = self.backbone.norm(hidden)
         for index in range(n_layers):
             cache.layers[index].append_decode_token(keys[index], values[index])

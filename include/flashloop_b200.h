@@ -348,6 +348,59 @@ int fl_encode_prefill_stage(const fl_layer* layer, int32_t sequence_begin, int32
 int fl_rmsnorm(const void* x, const void* residual, const void* weight, float eps, const void* weight2,
                float eps2, int64_t rows, int32_t width, void* out, void* out2, fl_cuda_stream stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Tensor-parallel decode.  No counterpart in the reference, which runs on one GPU
+ * (flashloop/engine.py:112-150): with the heads and FFN columns of a layer split over the
+ * ranks, the o_proj and down_proj outputs of flashloop/engine.py:531-537 are partial sums, and
+ * these entry points sum them over the ranks inside the norm launch that consumes them.
+ *
+ * A communicator is one device allocation per rank (receive slots for two calls in flight,
+ * arrival flags, a sequence counter, a status word), mapped into the other ranks' processes
+ * through CUDA IPC.  One process per GPU; every rank makes the same sequence of calls.
+ * ------------------------------------------------------------------------------------- */
+
+/* Size of the opaque handle fl_comm_create writes (a cudaIpcMemHandle_t).  No counterpart in the
+ * reference. */
+size_t fl_comm_handle_bytes(void);
+
+/* Allocate this rank's part on the current device for rows of `width` bfloat16 values
+ * (a multiple of 8, at most 8192), up to rows_max rows per call, world <= 8 ranks.
+ * *comm_out receives the communicator, handle_out (fl_comm_handle_bytes() bytes) the handle
+ * the other ranks need.  The caller carries the handles between the processes.  No counterpart
+ * in the reference. */
+int fl_comm_create(int32_t rank, int32_t world, int32_t rows_max, int32_t width, void** comm_out,
+                   void* handle_out);
+
+/* handles: world handles in rank order (this rank's own is not opened).  All ranks must have
+ * returned from fl_comm_connect before any of them calls fl_allreduce_rmsnorm.  No counterpart
+ * in the reference. */
+int fl_comm_connect(void* comm, const void* handles);
+
+/* Unmaps the peers' parts and frees this rank's.  No counterpart in the reference. */
+int fl_comm_destroy(void* comm);
+
+/* *status = 0, or 1 after a wait for a peer's rows ran out in some call since the last reset
+ * (that call summed what had arrived).  Synchronises `stream`; with reset != 0 clears it.
+ * No counterpart in the reference. */
+int fl_comm_status(void* comm, int32_t* status, int32_t reset, fl_cuda_stream stream);
+
+/* One launch per rank:  s = [addend +] sum over ranks of x  (float32 in rank order, rounded to
+ * bfloat16); then as fl_rmsnorm on s:  out = [residual +] weight * bf16(s * rsqrt(mean(s^2) +
+ * eps)), and with weight2/out2 the next norm of `out`.  weight == NULL: out = s and nothing
+ * else.  sum_out (or NULL) receives s.  x, addend, residual, sum_out, out, out2:
+ * [rows][width] bfloat16 of this rank, rows <= rows_max, 16-byte aligned.
+ * Each rank stores its rows into every rank's receive slots with plain peer stores, then waits
+ * for the others' rows; a wait gives up after wait_limit polls (0 = the default, a few seconds)
+ * and raises the status word instead of blocking.  skip_store != 0 makes this rank publish
+ * nothing in this call (the way a test lets the other ranks' waits run out).
+ * Allocation-free and recordable in a CUDA graph: the sequence number lives on the device.
+ * The arithmetic after the sum is that of the reference's norm modules
+ * (flashloop/engine.py:533-537), as fl_rmsnorm. */
+int fl_allreduce_rmsnorm(void* comm, const void* x, const void* addend, const void* residual,
+                         const void* weight, float eps, const void* weight2, float eps2, int64_t rows,
+                         void* sum_out, void* out, void* out2, int32_t skip_store, int32_t wait_limit,
+                         fl_cuda_stream stream);
+
 /* The view/transpose of the Q/K/V projections and _apply_rope (flashloop/engine.py:59-75,
  * 410-419) for one token per row: q_out/k_out = x * cos + rotate_half(x) * sin, v_out = v.
  * q_in/k_in/v_in: rows of heads*128 values, in_stride elements apart (three slices of one

@@ -1,5 +1,7 @@
-"""Two GPUs: the tensor-parallel engine (heads and FFN columns sharded, NCCL all-reduce) follows
-the single-GPU engine.  Skipped where fewer than two GPUs are visible."""
+"""Two GPUs: the tensor-parallel engine (heads and FFN columns sharded) follows the single-GPU
+engine, with NCCL all-reduces launched eagerly and with the peer all-reduce fused into the norm
+launches and the whole step replayed from a CUDA graph.  Skipped where fewer than two GPUs are
+visible."""
 
 from __future__ import annotations
 
@@ -15,7 +17,7 @@ pytestmark = pytest.mark.gpu
 STEPS = 10
 
 
-def _worker(rank: int, world: int, port: int, results) -> None:
+def _worker(rank: int, world: int, port: int, results, mode: str) -> None:
     import torch.distributed as dist
 
     from flashloop_b200 import FlashLoopEngine
@@ -36,17 +38,22 @@ def _worker(rank: int, world: int, port: int, results) -> None:
     model = shard_ouro_model(tiny_ouro_model().cuda(), rank, world)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        engine = FlashLoopEngine(model, validate_model=False, max_new_tokens=32, tp_group=dist.group.WORLD)
+        engine = FlashLoopEngine(model, validate_model=False, max_new_tokens=32, tp_group=dist.group.WORLD,
+                                 tp_allreduce=mode, use_cuda_graph=(mode == "peer"))
         pre = engine.prefill(prompts)
         runs["heads"] = engine.state.cache.layers[0].heads
         runs["tp"] = np.stack([pre.logits.cpu().numpy()] + [engine.decode(t).logits.cpu().numpy() for t in tokens])
         torch.cuda.synchronize()
+        runs["peer_status"] = engine._peer.status() if mode == "peer" else 0
+        runs["replayed"] = engine._graph is not None
+        dist.barrier()
         results[rank] = runs
     finally:
         dist.destroy_process_group()
 
 
-def test_two_gpu_tensor_parallel_engine():
+@pytest.mark.parametrize("mode", ["nccl", "peer"])
+def test_two_gpu_tensor_parallel_engine(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -56,7 +63,7 @@ def test_two_gpu_tensor_parallel_engine():
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     results = ctx.Manager().dict()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, results)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, results, mode)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
@@ -67,6 +74,7 @@ def test_two_gpu_tensor_parallel_engine():
     assert not stuck and all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     r0, r1 = results[0], results[1]
     assert r0["heads"] == 1 and r1["heads"] == 1            # one of the two heads per rank
+    assert r0["peer_status"] == 0 and r1["peer_status"] == 0 and r0["replayed"] == (mode == "peer")
     assert np.array_equal(r0["tp"], r1["tp"])               # both ranks hold the same logits
     single = r0["single"]
     err = np.abs(r0["tp"] - single).mean(axis=(1, 2))
@@ -76,9 +84,10 @@ def test_two_gpu_tensor_parallel_engine():
     assert np.corrcoef(r0["tp"].ravel(), single.ravel())[0, 1] > 0.99
 
 
-def test_graph_replay_is_refused_with_tensor_parallelism():
+def test_graph_replay_is_refused_with_nccl_all_reduces():
     from flashloop_b200 import FlashLoopEngine
     from tests.helpers import tiny_ouro_model
 
     with pytest.raises(ValueError, match="eagerly"):
-        FlashLoopEngine(tiny_ouro_model(), validate_model=False, use_cuda_graph=True, tp_group=object())
+        FlashLoopEngine(tiny_ouro_model(), validate_model=False, use_cuda_graph=True, tp_group=object(),
+                        tp_allreduce="nccl")
