@@ -38,6 +38,7 @@ namespace {
 constexpr int kDenseWarps = 8;
 constexpr int kDenseThreads = kDenseWarps * kWarp;
 constexpr int kStages = 2;
+constexpr int kDenseCtasPerSm = 2;
 constexpr int kWaitLimit = 1 << 12;
 constexpr uint32_t kSuspendNs = 100000;
 
@@ -104,13 +105,18 @@ __device__ __forceinline__ Span block_span(const LayerView& L, int s, int b, int
 }
 
 // Work is counted in units: a head has one unit per 64-token block of its packed prefix plus
-// kTailUnits for its BF16 tail and the current token (about what the tail costs a CTA).  The units
+// tail_units_of_loop for its BF16 tail and the current token (about what the tail, the merge of the
+// head and the switch to the next head cost a CTA, counted in blocks of that loop).  The units
 // of all heads form one sequence, head after head, and CTA c owns the contiguous range
 // [c*U/G, (c+1)*U/G) of it, so every CTA gets the same amount of work whatever the context
 // lengths are.  A work item is the part of one head inside that range: some blocks, the tail, or
 // both.  A CTA therefore meets a head once, keeps its online-softmax state in registers across all
 // of the head's blocks it owns, and merges and publishes once per item: one to three times in all.
-constexpr int kTailUnits = 8;
+// Units a head's tail, its merge and the switch to the next head are counted as (loop: 0-based).
+// Their cost is a time, so it is more blocks of a loop that reads fewer streams per block; measured
+// at batch 16 x 2048 tokens, 24 / 16 units for loops 1 / 2 are 5 % faster than 8, at batch 8 x 8192
+// they are level.
+inline int tail_units_of_loop(int loop) { return 8 + 16 / (loop + 1); }
 
 struct ItemDesc {
   int id;  // -1: past the end of this CTA's range
@@ -127,16 +133,16 @@ struct ItemDesc {
 
 constexpr int kEachCached = 256;  // sequences whose unit counts the CTA keeps in shared memory
 
-__device__ __forceinline__ int units_per_head(const LayerView& L, int b) {
-  return L.seq_state[b * FL_STATE_WORDS + FL_STATE_QUANT_TOKENS] / kGroup + kTailUnits;
+__device__ __forceinline__ int units_per_head(const LayerView& L, int tail_units, int b) {
+  return L.seq_state[b * FL_STATE_WORDS + FL_STATE_QUANT_TOKENS] / kGroup + tail_units;
 }
 // `each`: the CTA's shared copy of units_per_head for the first kEachCached sequences
-__device__ __forceinline__ int units_per_head(const LayerView& L, const int* each, int b) {
-  return b < kEachCached ? each[b] : units_per_head(L, b);
+__device__ __forceinline__ int units_per_head(const LayerView& L, int tail_units, const int* each, int b) {
+  return b < kEachCached ? each[b] : units_per_head(L, tail_units, b);
 }
-__device__ __forceinline__ int64_t total_units(const LayerView& L, const int* each) {
+__device__ __forceinline__ int64_t total_units(const LayerView& L, int tail_units, const int* each) {
   int64_t total = 0;
-  for (int b = 0; b < L.batch; ++b) total += static_cast<int64_t>(L.heads) * units_per_head(L, each, b);
+  for (int b = 0; b < L.batch; ++b) total += static_cast<int64_t>(L.heads) * units_per_head(L, tail_units, each, b);
   return total;
 }
 
@@ -149,19 +155,19 @@ struct ItemCursor {
   int blocks_done;     // blocks in those items
 };
 
-__device__ __forceinline__ void cursor_start(const LayerView& L, const int* each, int64_t lo, int64_t hi,
+__device__ __forceinline__ void cursor_start(const LayerView& L, int tail_units, const int* each, int64_t lo, int64_t hi,
                                              ItemCursor* c) {
   c->at = lo;
   c->end = hi;
   c->count = 0;
   c->blocks_done = 0;
   c->b = 0;
-  c->each = units_per_head(L, each, 0);
+  c->each = units_per_head(L, tail_units, each, 0);
   int64_t first = 0;
   while (c->b + 1 < L.batch && lo >= first + static_cast<int64_t>(L.heads) * c->each) {
     first += static_cast<int64_t>(L.heads) * c->each;
     ++c->b;
-    c->each = units_per_head(L, each, c->b);
+    c->each = units_per_head(L, tail_units, each, c->b);
   }
   c->h = static_cast<int>((lo - first) / c->each);
   if (c->h >= L.heads) c->h = L.heads - 1;  // only when the range is empty
@@ -177,7 +183,7 @@ __device__ __forceinline__ void describe_next(const ReaderParams& p, const int* 
   }
   const int64_t head_end = c->head_first + c->each;
   const int64_t seg_end = head_end < c->end ? head_end : c->end;
-  const int blocks = c->each - kTailUnits;
+  const int blocks = c->each - p.tail_units;
   const int u0 = static_cast<int>(c->at - c->head_first), u1 = static_cast<int>(seg_end - c->head_first);
   const int bh = c->b * L.heads + c->h;
   const int32_t* st = L.seq_state + c->b * FL_STATE_WORDS;
@@ -219,7 +225,7 @@ __device__ __forceinline__ void describe_next(const ReaderParams& p, const int* 
       c->h = 0;
       if (c->b + 1 < L.batch) {
         ++c->b;
-        c->each = units_per_head(L, each, c->b);
+        c->each = units_per_head(L, p.tail_units, each, c->b);
       }
     }
   }
@@ -232,8 +238,193 @@ __device__ __forceinline__ int blocks_of_warp(int blk_begin, int blk_end, int wa
   return n > 0 ? (n + kDenseWarps - 1) / kDenseWarps : 0;
 }
 
+// Online-softmax state of a warp on the tensor-pipe path (loops 1 and 2, where every token holds a
+// row in every stream it reads).  Lane (g = lane / 4, j = lane % 4) owns channels 16g .. 16g+15:
+// accumulator i holds two of them (rows g and g + 8 of the mma) in columns of both V scale groups,
+// acc[i][0] / acc[i][1] = first channel with the scale of channel group 0 / 1, acc[i][2] / acc[i][3]
+// the second; the lane's channels live in group g / 4, the other column is dropped at the end.
+template <int BITS>
+struct MmaState {
+  static constexpr int kTypes = BITS == 4 ? 2 : 4;  // positions of a code inside its byte
+  float m, l;
+  float bm;               // sum of p * v_min of channel group g % 2 over this lane's tokens
+  float acc[8][4];        // sum of W * (1024 + t * code), W = p * v_scale / t
+  float off[kTypes][4];   // sum of W * 1024 per position type
+};
+
+template <int BITS>
+__device__ __forceinline__ void mma_state_init(MmaState<BITS>& s) {
+  s.m = -INFINITY;
+  s.l = 0.f;
+  s.bm = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) s.acc[i][k] = 0.f;
+#pragma unroll
+  for (int i = 0; i < MmaState<BITS>::kTypes; ++i)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) s.off[i][k] = 0.f;
+}
+
+template <int BITS>
+__device__ __forceinline__ void mma_state_raise(MmaState<BITS>& s, float mx) {
+  if (mx > s.m) {
+    const float r = exp2f(s.m - mx);
+    s.l *= r;
+    s.bm *= r;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) s.acc[i][k] *= r;
+#pragma unroll
+    for (int i = 0; i < MmaState<BITS>::kTypes; ++i)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) s.off[i][k] *= r;
+    s.m = mx;
+  }
+}
+
+// Accumulator i of a lane: its two channels (within the lane's sixteen) and its position type.
+template <int BITS>
+__host__ __device__ constexpr int mma_channel(int i, int second) {
+  return BITS == 4 ? 8 * (i / 4) + ((i % 4) / 2) * 4 + (i % 2) + 2 * second : 8 * (i / 4) + (i % 4) + 4 * second;
+}
+template <int BITS>
+__host__ __device__ constexpr int mma_type(int i) {
+  return BITS == 4 ? i % 2 : i % 4;
+}
+
+// Park the warp's state in shared memory as acc[128] (natural channel order), m, l.
+template <int BITS>
+__device__ __forceinline__ void mma_state_store(MmaState<BITS>& s, int lane, float* dst) {
+  const int g = lane >> 2, grp = g >> 2;
+  const float l = across_quads_sum(s.l);
+  float bm = s.bm;
+  bm += __shfl_xor_sync(0xffffffffu, bm, 1);
+  bm += __shfl_xor_sync(0xffffffffu, bm, 2);
+  const float bm_mine = __shfl_sync(0xffffffffu, bm, 4 * grp);  // lanes 0-3 hold group 0, lanes 4-7 group 1
+  if ((lane & 3) == 0) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int t = mma_type<BITS>(i);
+      const float o = grp ? s.off[t][1] : s.off[t][0];
+      dst[16 * g + mma_channel<BITS>(i, 0)] = (grp ? s.acc[i][1] : s.acc[i][0]) - o + bm_mine;
+      dst[16 * g + mma_channel<BITS>(i, 1)] = (grp ? s.acc[i][3] : s.acc[i][2]) - o + bm_mine;
+    }
+    if (lane == 0) {
+      dst[128] = s.m;
+      dst[129] = l;
+    }
+  }
+}
+
+// K unit of a full block on the tensor pipe: kc[q] += (rows 16q+g, 16q+g+8) . table, all four
+// lanes of a quad (and all eight columns) ending up with the same sums.
+template <int BITS>
+__device__ __forceinline__ void k_block_mma(const uint8_t* stage, int lane, const uint32_t (&mult)[16],
+                                            float (&kc)[4][4]) {
+  constexpr int kRowBytes = 16 * BITS, kLaneBytes = kRowBytes / 4;
+  constexpr int kWords = BITS, kPairs = 16 / kWords;  // words per lane piece, pairs per word
+  const int g = lane >> 2, j = lane & 3;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint8_t* ra = stage + (16 * q + g) * kRowBytes + j * kLaneBytes;
+    const Codes<BITS> ca = load_codes_shared<BITS>(ra);
+    const Codes<BITS> cb = load_codes_shared<BITS>(ra + 8 * kRowBytes);
+#pragma unroll
+    for (int wd = 0; wd < kWords; ++wd) {
+      uint32_t ha[kPairs], hb[kPairs];
+      unpack_raw_word<BITS>(ca.w[wd], ha);
+      unpack_raw_word<BITS>(cb.w[wd], hb);
+#pragma unroll
+      for (int i = 0; i < kPairs / 2; ++i) {
+        mma16816(kc[q], ha[2 * i], hb[2 * i], ha[2 * i + 1], hb[2 * i + 1], mult[wd * kPairs + 2 * i],
+                 mult[wd * kPairs + 2 * i + 1]);
+      }
+    }
+  }
+}
+
+// V unit of a full block on the tensor pipe.  probs: the warp's 64 probabilities as float16.
+// Lane (g, j) reads channels 16g .. 16g+15 of tokens 2j, 2j+1, 2j+8, 2j+9 of every 16-token set and
+// supplies the probabilities of those tokens times the V scale of channel group g % 2 (even
+// columns of the mma carry group 0, odd columns group 1).
+template <int BITS>
+__device__ __forceinline__ void v_block_mma(const uint8_t* stage, int lane, const __half* probs,
+                                            MmaState<BITS>& st, __half2& hbias) {
+  constexpr int kRowBytes = 16 * BITS, kRecord = kRowBytes + 16;
+  constexpr int kTypes = MmaState<BITS>::kTypes;
+  const int g = lane >> 2, j = lane & 3;
+  const uint32_t sel = (g & 1) ? 0x7632u : 0x5410u;
+  const uint32_t k1024 = 0x64006400u;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint8_t* rec = stage + (16 * q + 2 * j) * kRecord;  // tokens 2j, 2j+1; +8 records: 2j+8, 2j+9
+    uint32_t x[4][BITS / 2];
+    uint2 mt[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint8_t* r = rec + ((k & 1) + (k >> 1) * 8) * kRecord;
+      if constexpr (BITS == 4) {
+        const uint2 v = *reinterpret_cast<const uint2*>(r + 8 * g);
+        x[k][0] = v.x;
+        x[k][1] = v.y;
+      } else {
+        x[k][0] = *reinterpret_cast<const uint32_t*>(r + 4 * g);
+      }
+      mt[k] = *reinterpret_cast<const uint2*>(r + kRowBytes);
+    }
+    const __half2 p01 = *reinterpret_cast<const __half2*>(probs + 16 * q + 2 * j);
+    const __half2 p23 = *reinterpret_cast<const __half2*>(probs + 16 * q + 2 * j + 8);
+    hbias = __hfma2(p01, as_half2(__byte_perm(mt[0].x, mt[1].x, sel)), hbias);
+    hbias = __hfma2(p23, as_half2(__byte_perm(mt[2].x, mt[3].x, sel)), hbias);
+    uint32_t w01[kTypes], w23[kTypes];
+    w01[0] = as_u32(__hmul2(p01, as_half2(__byte_perm(mt[0].y, mt[1].y, sel))));
+    w23[0] = as_u32(__hmul2(p23, as_half2(__byte_perm(mt[2].y, mt[3].y, sel))));
+#pragma unroll
+    for (int t = 1; t < kTypes; ++t) {
+      const float f = BITS == 4 ? 0.0625f : (t == 1 ? 0.25f : (t == 2 ? 0.0625f : 0.015625f));
+      const __half2 f2 = __floats2half2_rn(f, f);
+      w01[t] = as_u32(__hmul2(as_half2(w01[0]), f2));
+      w23[t] = as_u32(__hmul2(as_half2(w23[0]), f2));
+    }
+#pragma unroll
+    for (int t = 0; t < kTypes; ++t) mma16816(st.off[t], k1024, k1024, k1024, k1024, w01[t], w23[t]);
+#pragma unroll
+    for (int wd = 0; wd < BITS / 2; ++wd) {
+      // 16-bit halves of the two tokens of a pair side by side: codes 0-3 (4 bits) or 0-7 (2 bits)
+      // of the word in u, the rest in v
+      const uint32_t u01 = __byte_perm(x[0][wd], x[1][wd], 0x5410), v01 = __byte_perm(x[0][wd], x[1][wd], 0x7632);
+      const uint32_t u23 = __byte_perm(x[2][wd], x[3][wd], 0x5410), v23 = __byte_perm(x[2][wd], x[3][wd], 0x7632);
+      if constexpr (BITS == 4) {
+        uint32_t e[4], f[4];
+        unpack_raw_word<4>(u01, e);
+        unpack_raw_word<4>(u23, f);
+        // pairs of unpack_raw_word<4> on u: (code 0), (code 1, x16), (code 2), (code 3, x16)
+        mma16816(st.acc[4 * wd + 0], e[0], e[2], f[0], f[2], w01[0], w23[0]);
+        mma16816(st.acc[4 * wd + 1], e[1], e[3], f[1], f[3], w01[1], w23[1]);
+        unpack_raw_word<4>(v01, e);
+        unpack_raw_word<4>(v23, f);
+        mma16816(st.acc[4 * wd + 2], e[0], e[2], f[0], f[2], w01[0], w23[0]);
+        mma16816(st.acc[4 * wd + 3], e[1], e[3], f[1], f[3], w01[1], w23[1]);
+      } else {
+        uint32_t e[8], f[8];
+        unpack_raw_word<2>(u01, e);
+        unpack_raw_word<2>(u23, f);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) mma16816(st.acc[t], e[t], e[t + 4], f[t], f[t + 4], w01[t], w23[t]);
+        unpack_raw_word<2>(v01, e);
+        unpack_raw_word<2>(v23, f);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) mma16816(st.acc[4 + t], e[t], e[t + 4], f[t], f[t + 4], w01[t], w23[t]);
+      }
+    }
+  }
+}
+
 template <int BITS, int LOOP>
-__global__ void __launch_bounds__(kDenseThreads, 2)
+__global__ void __launch_bounds__(kDenseThreads, kDenseCtasPerSm)
 dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   using St = Stage<BITS>;
   constexpr int kRowBytes = St::kRowBytes;
@@ -241,7 +432,8 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   extern __shared__ __align__(128) uint8_t s_ring[];  // [warp][stage][St::kBytes]
   __shared__ __align__(16) float s_qf[2][kHeadDim];
   __shared__ __align__(16) __half s_wtab[kDenseWarps][2][kHeadDim];
-  __shared__ __align__(16) float s_merge[2][kDenseWarps][kPartialStride];
+  __shared__ __align__(16) float s_merge[2][(LOOP <= 1 ? 2 : 1) * kDenseWarps][kPartialStride];
+  __shared__ __align__(4) __half s_prob[LOOP <= 1 ? kDenseWarps : 1][kGroup];
   __shared__ __align__(8) uint64_t s_bar[kDenseWarps][kStages];
   __shared__ ItemDesc s_item[4];  // current, next, the one being described, and the one still being merged
   __shared__ ItemCursor s_cursor;
@@ -270,14 +462,14 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   }
   // this CTA's contiguous range of units; the one thread that describes the items walks it with a
   // cursor kept in shared memory (registers are allocated for every thread)
-  for (int bb = tid; bb < L.batch && bb < kEachCached; bb += kDenseThreads) s_each[bb] = units_per_head(L, bb);
+  for (int bb = tid; bb < L.batch && bb < kEachCached; bb += kDenseThreads) s_each[bb] = units_per_head(L, p.tail_units, bb);
   __syncthreads();
   {
     // Every thread finds the CTA's range and the head it starts in (shared-memory reads only), so
     // that the first query is fetched while one thread describes the first two items.
-    const int64_t all_units = total_units(L, s_each);
+    const int64_t all_units = total_units(L, p.tail_units, s_each);
     ItemCursor cursor;
-    cursor_start(L, s_each, all_units * blockIdx.x / gridDim.x, all_units * (blockIdx.x + 1) / gridDim.x, &cursor);
+    cursor_start(L, p.tail_units, s_each, all_units * blockIdx.x / gridDim.x, all_units * (blockIdx.x + 1) / gridDim.x, &cursor);
     if (tid == kHeadDim) {
       s_all_units = all_units;
       s_cursor = cursor;
@@ -298,7 +490,12 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
   bool timed_out = false;
 
   OnlineState S;
-  state_init(S);
+  MmaState<BITS> M;
+  if constexpr (kAllRows) {
+    mma_state_init(M);
+  } else {
+    state_init(S);
+  }
 
   for (int k = 0;; ++k) {
     const ItemDesc* curp = &s_item[k % 4];
@@ -328,6 +525,7 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
       const int my_first = cur.blk_begin + ((warp - cur.rot) & (kDenseWarps - 1));
       const int my_blocks = blocks_of_warp(cur.blk_begin, cur.blk_end, my_first - cur.blk_begin);
       float lg[8];
+      float kc[4][4], kb = 0.f;
       __half2 hacc[16];
       __half2 hbias = __floats2half2_rn(0.f, 0.f);  // sum of p * (v_min + centre * v_scale) of one block
       for (int cb = 0; cb < my_blocks; ++cb) {
@@ -398,7 +596,81 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
         // A block whose 64 tokens are all present in one metadata group (always true for streams
         // 0 and 1) takes the branch-free path: row i of the stage is token i.
         const bool full = kAllRows || (sp.m == kGroup && ng == 1);
-        if (!is_v) {
+        if constexpr (kAllRows) {
+          if (!is_v) {
+            if (s == 0) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) kc[q][c] = 0.f;
+              kb = 0.f;
+            }
+            // table: w_c = q_c * scale_c / t_c as float16; what the uncentred codes add to every
+            // logit, 1024 * sum of the table, goes into the bias with the minima
+            {
+              const uint2 sc = *reinterpret_cast<const uint2*>(stage + St::kCodes + lane * 8);
+              const uint2 mn = *reinterpret_cast<const uint2*>(stage + St::kCodes + 256 + lane * 8);
+              const float2 sc01 = __half22float2(as_half2(sc.x)), sc23 = __half22float2(as_half2(sc.y));
+              const float2 mn01 = __half22float2(as_half2(mn.x)), mn23 = __half22float2(as_half2(mn.y));
+              const float4 q4 = *reinterpret_cast<const float4*>(&qf[4 * lane]);
+              const int cc = (4 * lane) & 31;
+              const __half w0 = __float2half_rn(q4.x * sc01.x * position_factor<BITS>(0));
+              const __half w1 = __float2half_rn(q4.y * sc01.y * position_factor<BITS>(1));
+              const __half w2 = __float2half_rn(q4.z * sc23.x * position_factor<BITS>(2));
+              const __half w3 = __float2half_rn(q4.w * sc23.y * position_factor<BITS>(3));
+              __half* tab = &s_wtab[warp][0][(4 * lane) & ~31];
+              tab[channel_slot<BITS>(cc + 0)] = w0;
+              tab[channel_slot<BITS>(cc + 1)] = w1;
+              tab[channel_slot<BITS>(cc + 2)] = w2;
+              tab[channel_slot<BITS>(cc + 3)] = w3;
+              float bias = fmaf(q4.x, mn01.x, fmaf(q4.y, mn01.y, fmaf(q4.z, mn23.x, q4.w * mn23.y)));
+              bias -= 1024.f * ((__half2float(w0) + __half2float(w1)) + (__half2float(w2) + __half2float(w3)));
+              kb += warp_sum(bias);
+            }
+            __syncwarp();
+            uint32_t mult[16];
+            {
+              const uint4* src = reinterpret_cast<const uint4*>(&s_wtab[warp][0][sub * 32]);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                const uint4 x = src[v];
+                mult[4 * v + 0] = x.x; mult[4 * v + 1] = x.y; mult[4 * v + 2] = x.z; mult[4 * v + 3] = x.w;
+              }
+            }
+            k_block_mma<BITS>(stage, lane, mult, kc);
+            if (s == LOOP) {
+              // all streams summed: this lane holds the logits of tokens 16q + quad and 16q + quad + 8
+              float mx = -INFINITY;
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float raw0 = kc[q][0] + kb, raw1 = kc[q][2] + kb;
+                if (logits_row && sub == 0) {
+                  logits_row[t0 + 16 * q + quad] = raw0 * p.scaling;
+                  logits_row[t0 + 16 * q + quad + 8] = raw1 * p.scaling;
+                }
+                lg[2 * q] = raw0 * p.scaling_log2;
+                lg[2 * q + 1] = raw1 * p.scaling_log2;
+                mx = fmaxf(mx, fmaxf(lg[2 * q], lg[2 * q + 1]));
+              }
+              mma_state_raise(M, across_quads_max(mx));
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float p0 = exp2f(lg[2 * q] - M.m), p1 = exp2f(lg[2 * q + 1] - M.m);
+                M.l += p0 + p1;
+                if (sub == 0) {
+                  s_prob[warp][16 * q + quad] = __float2half_rn(p0);
+                  s_prob[warp][16 * q + quad + 8] = __float2half_rn(p1);
+                }
+              }
+            }
+          } else {
+            v_block_mma<BITS>(stage, lane, s_prob[warp], M, hbias);
+            if (s == LOOP) {
+              M.bm += __low2float(hbias) + __high2float(hbias);
+              hbias = __floats2half2_rn(0.f, 0.f);
+            }
+          }
+        } else if (!is_v) {
           if (s == 0) {
   #pragma unroll
             for (int it = 0; it < 8; ++it) lg[it] = 0.f;
@@ -546,6 +818,11 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
       iss_blk = 0;
       iss_j = 0;
     }
+    if constexpr (kAllRows) {
+      mma_state_store<BITS>(M, lane, s_merge[k & 1][warp]);
+      mma_state_init(M);
+      if (cur.has_tail) state_init(S);
+    }
     if (cur.has_tail) {
       // ---- the BF16 tail and the current token: entries 0..tail_len (the last is the current),
       // one per lane quad; the V row is fetched together with the K row
@@ -578,17 +855,22 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
     // ---- merge the eight warps' states, publish this CTA's partial of the head, finish the head
     // if every CTA that shares it has published
     const int buf = k & 1;
-    state_store<BITS>(S, lane, s_merge[buf][warp]);
-    state_init(S);
+    if constexpr (kAllRows) {
+      if (cur.has_tail) state_store<BITS>(S, lane, s_merge[buf][kDenseWarps + warp]);
+    } else {
+      state_store<BITS>(S, lane, s_merge[buf][warp]);
+      state_init(S);
+    }
     __syncthreads();
     if (warp < 4) {
       const int c = tid;
+      const int entries = (kAllRows && cur.has_tail) ? 2 * kDenseWarps : kDenseWarps;
       float mmax = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < kDenseWarps; ++w) mmax = fmaxf(mmax, s_merge[buf][w][128]);
+#pragma unroll 8
+      for (int w = 0; w < entries; ++w) mmax = fmaxf(mmax, s_merge[buf][w][128]);
       float a = 0.f, l = 0.f;
-#pragma unroll
-      for (int w = 0; w < kDenseWarps; ++w) {
+#pragma unroll 8
+      for (int w = 0; w < entries; ++w) {
         const float mw = s_merge[buf][w][128];
         const float r = (mw == -INFINITY) ? 0.f : exp2f(mw - mmax);
         a += s_merge[buf][w][c] * r;
@@ -644,8 +926,8 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
 // units, so that every CTA's share of the units is non-empty whatever the context lengths are.
 unsigned dense_grid(int64_t batch_heads) {
   const int sm_count = device_sm_count();
-  const int64_t ctas = 2 * static_cast<int64_t>(sm_count < 148 ? sm_count : 148);
-  const int64_t cap = batch_heads * kTailUnits;
+  const int64_t ctas = kDenseCtasPerSm * static_cast<int64_t>(sm_count < 148 ? sm_count : 148);
+  const int64_t cap = batch_heads * 8;  // tail_units_of_loop is at least 8
   return static_cast<unsigned>(cap < ctas ? cap : ctas);
 }
 
@@ -761,6 +1043,7 @@ extern "C" int fl_dense_source_attention(const fl_layer* layer, int32_t loop, co
   p.vcur = static_cast<const __nv_bfloat16*>(current_value);
   p.scaling = scaling;
   p.scaling_log2 = scaling * 1.4426950408889634f;
+  p.tail_units = tail_units_of_loop(loop);
   p.out = output;
   p.logits = logits;
   p.logits_stride = logits_stride;
@@ -870,6 +1153,7 @@ extern "C" int fl_dense_source_attention_static(const fl_layer* layer, int32_t l
   p.vcur = static_cast<const __nv_bfloat16*>(current_value);
   p.scaling = scaling;
   p.scaling_log2 = scaling * 1.4426950408889634f;
+  p.tail_units = tail_units_of_loop(loop);
   p.out = output;
   p.logits = logits;
   p.logits_stride = logits_stride;

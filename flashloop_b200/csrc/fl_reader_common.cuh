@@ -29,6 +29,7 @@ struct ReaderParams {
   int* tickets;
   int* status;
   int max_chunks;
+  int tail_units;  // dense reader: units a head's tail counts as in the static partition
   // selected readers
   const int32_t* indices;
   const uint8_t* valid;
@@ -154,6 +155,56 @@ __device__ __forceinline__ void flush_pairs(__half2 (&hacc)[16], float (&acc)[32
     acc[2 * p] += f.x;
     acc[2 * p + 1] += f.y;
     hacc[p] = __floats2half2_rn(0.f, 0.f);
+  }
+}
+
+// ------------------------------------------------------------------------------ tensor-pipe dot products
+//
+// The dense reader's contractions (q . K rows, p . V rows) have one query per head, so they are
+// GEMVs and HBM-bound; done on the ALU pipes they are issue-bound instead (unpack + centre +
+// multiply-add is about twenty issue slots per eight codes).  Handing the multiply-adds and the
+// sums over the lane quad to mma.sync.m16n8k16 (float16 operands, float32 accumulators) leaves
+// one shift and four logic ops per eight codes on the ALU pipes.  Codes go in uncentred and
+// unscaled, exactly as the magic-number unpack leaves them, 1024 + t * code with t = 1 or 16 (4 bits)
+// or 1, 4, 16, 64 (2 bits) by position: the other operand carries 1/t, and what the 1024s add up to
+// is taken out again as a bias (K: 1024 * sum of the table; V: one more mma with a constant-1024
+// operand), computed from the same rounded operands so that it cancels exactly.
+
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// The 1/t of the code at position `cc` (channel within the lane's run of channels).
+template <int BITS>
+__device__ __forceinline__ float position_factor(int cc) {
+  if constexpr (BITS == 4) return (cc & 1) ? 0.0625f : 1.f;
+  const int t = cc & 3;
+  return t == 0 ? 1.f : (t == 1 ? 0.25f : (t == 2 ? 0.0625f : 0.015625f));
+}
+
+// One 32-bit word of codes -> float16 pairs 1024 + t * code, in the pair order of unpack_centred
+// (4 bits: four pairs; 2 bits: eight pairs).
+template <int BITS>
+__device__ __forceinline__ void unpack_raw_word(uint32_t w, uint32_t* h) {
+  const uint32_t kMagic = 0x64006400u;
+  const uint32_t w8 = w >> 8;
+  if constexpr (BITS == 4) {
+    h[0] = and_or(w, 0x000F000Fu, kMagic);
+    h[1] = and_or(w, 0x00F000F0u, kMagic);
+    h[2] = and_or(w8, 0x000F000Fu, kMagic);
+    h[3] = and_or(w8, 0x00F000F0u, kMagic);
+  } else {
+    h[0] = and_or(w, 0x00030003u, kMagic);
+    h[1] = and_or(w, 0x000C000Cu, kMagic);
+    h[2] = and_or(w, 0x00300030u, kMagic);
+    h[3] = and_or(w, 0x00C000C0u, kMagic);
+    h[4] = and_or(w8, 0x00030003u, kMagic);
+    h[5] = and_or(w8, 0x000C000Cu, kMagic);
+    h[6] = and_or(w8, 0x00300030u, kMagic);
+    h[7] = and_or(w8, 0x00C000C0u, kMagic);
   }
 }
 
