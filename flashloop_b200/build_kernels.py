@@ -17,7 +17,7 @@ from pathlib import Path
 CSRC = Path(__file__).resolve().parent / "csrc"
 LIBRARY = CSRC / "libflashloop_b200.so"
 SOURCES = ("fl_capi.cu", "fl_pack.cu", "fl_reader.cu", "fl_selected.cu", "fl_select.cu", "fl_append.cu", "fl_compact.cu",
-           "fl_step.cu", "fl_encode.cu", "fl_comm.cu")
+           "fl_step.cu", "fl_encode.cu", "fl_comm.cu", "fl_linear.cu")
 FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr")
 

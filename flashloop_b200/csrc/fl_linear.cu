@@ -1,0 +1,277 @@
+// The projections of a decode step: out[m][n] = sum_k x[m][k] * W[n][k] for at most sixteen rows
+// (one token per sequence), bfloat16 in and out, float32 accumulation.
+//
+// With sixteen rows the product is a stream over the weights: every weight byte is read once and
+// used sixteen times, 16 flop per byte, far below what the tensor pipe needs to be busy, so the
+// bound is HBM.  A library GEMM at this shape spends its time in tiles built for hundreds of rows;
+// here a CTA owns eight (or sixteen) weight rows, its eight warps split K, and every lane keeps
+// 16-byte weight loads in flight.  The multiply-adds go to mma.sync.m16n8k16 (the sixteen rows of
+// x are exactly the tile's M): a lane's 16 bytes of a weight row are eight consecutive k, fed to
+// two mmas, and since a dot product does not care about the order of its terms the mma's k index
+// is simply mapped to "lane j holds k0 + 8j .. 8j+7", for x and W alike, so both operands are
+// plain 16-byte loads.  x (32 KB .. 176 KB) stays in L1/L2.
+//
+// Mode 1 computes SwiGLU on the way out: a CTA takes eight rows of the gate half and the same
+// eight of the up half of a fused [2F][K] weight and writes bf16(silu(bf16 gate)) * bf16 up, the
+// roundings of the separate launches it replaces.  Mode 2 is the fused Q/K/V projection of one
+// token per row with rotate-half RoPE on the way out: a CTA takes eight features of the first half of
+// a head and their partners 64 further on, and writes q and k rotated and v as it is, each in
+// [rows][heads * 128] (the layout the readers take).  x may be float32 (the readers' output): it is
+// rounded to bfloat16 as it is loaded, which is what a separate conversion would have stored.
+#include "fl_step_common.cuh"
+
+namespace fl {
+namespace {
+
+constexpr int kLinearWarps = 8;
+constexpr int kLinearThreads = kLinearWarps * 32;
+constexpr int kChunk = 32;  // k per warp-wide 16-byte load of one weight row (4 lanes x 8)
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 load_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+struct LinearParams {
+  const void* x;           // [rows][k], bfloat16 or float32
+  const __nv_bfloat16* w;  // [n][k]
+  __nv_bfloat16* out;      // [rows][out_width]
+  int rows, k, out_width;
+  int up_offset;  // mode 1: the up rows start this many weight rows after the gate rows
+  // mode 2
+  int heads;
+  const __nv_bfloat16* cosv;  // [rows][128]
+  const __nv_bfloat16* sinv;
+  __nv_bfloat16* k_out;
+  __nv_bfloat16* v_out;
+};
+
+// Eight consecutive values of a row of x as four bfloat16 pairs.
+template <bool F32>
+__device__ __forceinline__ uint4 load_x8(const void* x, int64_t element) {
+  if constexpr (F32) {
+    const float* src = static_cast<const float*>(x) + element;
+    const float4 a = __ldg(reinterpret_cast<const float4*>(src));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(src + 4));
+    const __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
+    const __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+    return make_uint4(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1),
+                      *reinterpret_cast<const uint32_t*>(&p2), *reinterpret_cast<const uint32_t*>(&p3));
+  } else {
+    return ldg128(static_cast<const __nv_bfloat16*>(x) + element);
+  }
+}
+
+// TILES weight-row tiles of eight per CTA.  MODE 0: adjacent tiles, TILES * 8 outputs per row.
+// MODE 1 (TILES == 2): tile 0 = gate rows, tile 1 = up rows, eight outputs per row.
+// MODE 2 (TILES == 2): tile 0 = features c0 .. c0+7 of a head of q, k or v, tile 1 = c0+64 .. c0+71.
+template <int TILES, int MODE, bool F32>
+__global__ void __launch_bounds__(kLinearThreads, TILES == 1 ? 3 : 2) linear_rows_kernel(const LinearParams p) {
+  __shared__ float s_red[kLinearWarps][TILES][16][8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, j = lane & 3;
+  // first weight row of tile 0
+  const int n0 = MODE == 2 ? (blockIdx.x >> 3) * 128 + (blockIdx.x & 7) * 8 : blockIdx.x * (MODE == 1 ? 8 : 8 * TILES);
+  const int K = p.k;
+  const __nv_bfloat16* wrow[TILES];
+#pragma unroll
+  for (int t = 0; t < TILES; ++t) {
+    const int n = MODE == 1 ? n0 + t * p.up_offset : (MODE == 2 ? n0 + 64 * t : n0 + 8 * t);
+    wrow[t] = p.w + static_cast<int64_t>(n + g) * K + 8 * j;
+  }
+  const bool row_a = g < p.rows, row_b = g + 8 < p.rows;
+  const int64_t xa = static_cast<int64_t>(g) * K + 8 * j, xb = static_cast<int64_t>(g + 8) * K + 8 * j;
+  float acc[TILES][4];
+#pragma unroll
+  for (int t = 0; t < TILES; ++t)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[t][c] = 0.f;
+
+  // chunk c of a row is k in [32c, 32c + 32); the warps take chunks warp, warp + 8, ...; a batch is
+  // kDepth of a warp's chunks, and the loads of the next batch are in flight while this one is
+  // multiplied (two register sets, the loop unrolled by hand)
+  const int chunks = K / kChunk;
+  constexpr int kDepth = 2, kStride = kLinearWarps * kDepth;
+  const auto load_batch = [&](int c0, uint4 (&wv)[kDepth][TILES], uint4 (&va)[kDepth], uint4 (&vb)[kDepth]) {
+#pragma unroll
+    for (int d = 0; d < kDepth; ++d) {
+      const int c = c0 + d * kLinearWarps;
+      if (c < chunks) {
+#pragma unroll
+        for (int t = 0; t < TILES; ++t) wv[d][t] = load_stream(wrow[t] + c * kChunk);
+      }
+    }
+#pragma unroll
+    for (int d = 0; d < kDepth; ++d) {
+      const int c = c0 + d * kLinearWarps;
+      va[d] = make_uint4(0u, 0u, 0u, 0u);
+      vb[d] = make_uint4(0u, 0u, 0u, 0u);
+      if (c < chunks) {
+        if (row_a) va[d] = load_x8<F32>(p.x, xa + c * kChunk);
+        if (row_b) vb[d] = load_x8<F32>(p.x, xb + c * kChunk);
+      }
+    }
+  };
+  const auto multiply = [&](int c0, const uint4 (&wv)[kDepth][TILES], const uint4 (&va)[kDepth],
+                            const uint4 (&vb)[kDepth]) {
+#pragma unroll
+    for (int d = 0; d < kDepth; ++d) {
+      if (c0 + d * kLinearWarps < chunks) {
+#pragma unroll
+        for (int t = 0; t < TILES; ++t) {
+          mma_bf16_16816(acc[t], va[d].x, vb[d].x, va[d].y, vb[d].y, wv[d][t].x, wv[d][t].y);
+          mma_bf16_16816(acc[t], va[d].z, vb[d].z, va[d].w, vb[d].w, wv[d][t].z, wv[d][t].w);
+        }
+      }
+    }
+  };
+  uint4 w0[kDepth][TILES], a0[kDepth], b0[kDepth], w1[kDepth][TILES], a1[kDepth], b1[kDepth];
+  int c = warp;
+  if (c < chunks) {
+    load_batch(c, w0, a0, b0);
+    while (true) {
+      const int cn = c + kStride;
+      if (cn < chunks) load_batch(cn, w1, a1, b1);
+      multiply(c, w0, a0, b0);
+      if (cn >= chunks) break;
+      c = cn + kStride;
+      if (c < chunks) load_batch(c, w0, a0, b0);
+      multiply(cn, w1, a1, b1);
+      if (c >= chunks) break;
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < TILES; ++t) {
+    s_red[warp][t][g][2 * j] = acc[t][0];
+    s_red[warp][t][g][2 * j + 1] = acc[t][1];
+    s_red[warp][t][g + 8][2 * j] = acc[t][2];
+    s_red[warp][t][g + 8][2 * j + 1] = acc[t][3];
+  }
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    const int m = threadIdx.x >> 3, n = threadIdx.x & 7;
+    float sum[TILES];
+#pragma unroll
+    for (int t = 0; t < TILES; ++t) {
+      sum[t] = 0.f;
+#pragma unroll
+      for (int w = 0; w < kLinearWarps; ++w) sum[t] += s_red[w][t][m][n];
+    }
+    if (m < p.rows) {
+      if constexpr (MODE == 2) {
+        const int width = p.heads * 128;
+        const int section = n0 / width;  // 0: q, 1: k, 2: v
+        const int c = (n0 & 127) + n;    // feature within the head, first half
+        const float a = bf16_round_f(sum[0]), b = bf16_round_f(sum[1]);
+        __nv_bfloat16* dst = (section == 0 ? p.out : (section == 1 ? p.k_out : p.v_out)) +
+                             static_cast<int64_t>(m) * width + (n0 - section * width) + n;
+        if (section < 2) {
+          // x * cos + rotate_half(x) * sin with rotate_half = (-second half, first half)
+          const float c1 = __bfloat162float(p.cosv[m * 128 + c]), s1 = __bfloat162float(p.sinv[m * 128 + c]);
+          const float c2 = __bfloat162float(p.cosv[m * 128 + c + 64]), s2 = __bfloat162float(p.sinv[m * 128 + c + 64]);
+          dst[0] = __float2bfloat16_rn(bf16_round_f(a * c1) + bf16_round_f(-b * s1));
+          dst[64] = __float2bfloat16_rn(bf16_round_f(b * c2) + bf16_round_f(a * s2));
+        } else {
+          dst[0] = __float2bfloat16_rn(a);
+          dst[64] = __float2bfloat16_rn(b);
+        }
+        return;
+      }
+      __nv_bfloat16* dst = p.out + static_cast<int64_t>(m) * p.out_width + n0 + n;
+      if constexpr (MODE == 1) {
+        const float gate = bf16_round_f(sum[0]), up = bf16_round_f(sum[1]);
+        *dst = __float2bfloat16_rn(bf16_round_f(gate / (1.f + expf(-gate))) * up);
+      } else {
+#pragma unroll
+        for (int t = 0; t < TILES; ++t) dst[8 * t] = __float2bfloat16_rn(sum[t]);
+      }
+    }
+  }
+}
+
+}  // namespace
+}  // namespace fl
+
+using namespace fl;
+
+namespace fl {
+namespace {
+template <int TILES, int MODE>
+void launch_linear(bool f32, unsigned grid, cudaStream_t s, const LinearParams& p) {
+  if (f32) {
+    linear_rows_kernel<TILES, MODE, true><<<grid, kLinearThreads, 0, s>>>(p);
+  } else {
+    linear_rows_kernel<TILES, MODE, false><<<grid, kLinearThreads, 0, s>>>(p);
+  }
+}
+}  // namespace
+}  // namespace fl
+
+extern "C" int fl_linear_rows(const void* x, int32_t x_dtype, const void* weight, int64_t rows, int32_t out_features,
+                              int32_t in_features, int32_t swiglu, void* out, fl_cuda_stream stream) {
+  const char* who = "fl_linear_rows";
+  FL_REQUIRE(x && weight && out, "%s: null argument", who);
+  FL_REQUIRE(x_dtype == FL_DTYPE_BF16 || x_dtype == FL_DTYPE_F32, "%s: x is bfloat16 or float32", who);
+  FL_REQUIRE(rows >= 0 && rows <= 16, "%s: at most 16 rows, got %lld", who, static_cast<long long>(rows));
+  FL_REQUIRE(in_features > 0 && in_features % kChunk == 0, "%s: in_features must be a multiple of %d", who, kChunk);
+  FL_REQUIRE(out_features > 0 && out_features % 16 == 0, "%s: out_features must be a multiple of 16", who);
+  FL_REQUIRE(!swiglu || out_features % 32 == 0, "%s: a fused gate/up weight has an even number of 16-row tiles", who);
+  FL_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(out), "%s: pointers must be 16-byte aligned", who);
+  if (rows == 0) return FL_OK;
+  LinearParams p{};
+  p.x = x;
+  p.w = static_cast<const __nv_bfloat16*>(weight);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.rows = static_cast<int>(rows);
+  p.k = in_features;
+  p.out_width = out_features;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool f32 = x_dtype == FL_DTYPE_F32;
+  if (swiglu) {
+    p.out_width = out_features / 2;
+    p.up_offset = out_features / 2;
+    launch_linear<2, 1>(f32, out_features / 16, s, p);
+  } else if (out_features <= 4096) {  // few tiles: eight rows per CTA keep every SM busy
+    launch_linear<1, 0>(f32, out_features / 8, s, p);
+  } else {
+    launch_linear<2, 0>(f32, out_features / 16, s, p);
+  }
+  FL_CHECK_LAUNCH(who);
+  return FL_OK;
+}
+
+extern "C" int fl_qkv_rope_rows(const void* x, const void* weight, int64_t rows, int32_t heads, int32_t in_features,
+                                const void* cosv, const void* sinv, void* q_out, void* k_out, void* v_out,
+                                fl_cuda_stream stream) {
+  const char* who = "fl_qkv_rope_rows";
+  FL_REQUIRE(x && weight && cosv && sinv && q_out && k_out && v_out, "%s: null argument", who);
+  FL_REQUIRE(rows >= 0 && rows <= 16, "%s: at most 16 rows, got %lld", who, static_cast<long long>(rows));
+  FL_REQUIRE(heads > 0 && heads <= 4096, "%s: bad head count", who);
+  FL_REQUIRE(in_features > 0 && in_features % kChunk == 0, "%s: in_features must be a multiple of %d", who, kChunk);
+  FL_REQUIRE(aligned16(x) && aligned16(weight), "%s: pointers must be 16-byte aligned", who);
+  if (rows == 0) return FL_OK;
+  LinearParams p{};
+  p.x = x;
+  p.w = static_cast<const __nv_bfloat16*>(weight);
+  p.out = static_cast<__nv_bfloat16*>(q_out);
+  p.k_out = static_cast<__nv_bfloat16*>(k_out);
+  p.v_out = static_cast<__nv_bfloat16*>(v_out);
+  p.rows = static_cast<int>(rows);
+  p.k = in_features;
+  p.heads = heads;
+  p.cosv = static_cast<const __nv_bfloat16*>(cosv);
+  p.sinv = static_cast<const __nv_bfloat16*>(sinv);
+  launch_linear<2, 2>(false, static_cast<unsigned>(3 * heads * 8), static_cast<cudaStream_t>(stream), p);
+  FL_CHECK_LAUNCH(who);
+  return FL_OK;
+}

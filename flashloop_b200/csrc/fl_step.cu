@@ -14,6 +14,7 @@ namespace {
 
 struct NormParams {
   const __nv_bfloat16* x;         // [rows][width]: the tensor to normalise
+  const __nv_bfloat16* addend;    // [rows][width] or null: bf16(addend + x) is normalised instead
   const __nv_bfloat16* residual;  // [rows][width] or null
   const __nv_bfloat16* weight;    // [width]
   const __nv_bfloat16* weight2;   // [width] or null: a second norm applied to the sum
@@ -35,6 +36,12 @@ __global__ void __launch_bounds__(kStepThreads) norm_kernel(const NormParams p) 
     const int e = (c * kStepThreads + threadIdx.x) * 8;
     if (e < p.width) {
       unpack8(ldg128(x + e), v[c]);
+      if (p.addend) {
+        float a[8];
+        unpack8(ldg128(p.addend + row * p.width + e), a);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[c][k] = bf16_round_f(a[k] + v[c][k]);
+      }
 #pragma unroll
       for (int k = 0; k < 8; ++k) sq = fmaf(v[c][k], v[c][k], sq);
     }
@@ -133,18 +140,19 @@ swiglu_kernel(const __nv_bfloat16* __restrict__ gate_up, int width, __nv_bfloat1
 
 using namespace fl;
 
-extern "C" int fl_rmsnorm(const void* x, const void* residual, const void* weight, float eps,
+extern "C" int fl_rmsnorm(const void* x, const void* addend, const void* residual, const void* weight, float eps,
                           const void* weight2, float eps2, int64_t rows, int32_t width, void* out, void* out2,
                           fl_cuda_stream stream) {
   FL_REQUIRE(x && weight && out, "fl_rmsnorm: null argument");
   FL_REQUIRE(rows >= 0 && width > 0 && width % 8 == 0 && width <= kMaxChunks * kStepThreads * 8,
              "fl_rmsnorm: width must be a multiple of 8 up to %d, got %d", kMaxChunks * kStepThreads * 8, width);
   FL_REQUIRE((weight2 == nullptr) == (out2 == nullptr), "fl_rmsnorm: weight2 and out2 go together");
-  FL_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(out) && aligned16(residual) && aligned16(weight2) &&
-                 aligned16(out2),
+  FL_REQUIRE(aligned16(x) && aligned16(addend) && aligned16(weight) && aligned16(out) && aligned16(residual) &&
+                 aligned16(weight2) && aligned16(out2),
              "fl_rmsnorm: pointers must be 16-byte aligned");
   if (rows == 0) return FL_OK;
-  NormParams p{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
+  NormParams p{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(addend),
+               static_cast<const __nv_bfloat16*>(residual),
                static_cast<const __nv_bfloat16*>(weight), static_cast<const __nv_bfloat16*>(weight2),
                eps, eps2, width, static_cast<__nv_bfloat16*>(out), static_cast<__nv_bfloat16*>(out2)};
   norm_kernel<<<static_cast<unsigned>(rows), kStepThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);

@@ -66,7 +66,7 @@ class FlashLoopEngine:
     def __init__(self, model: torch.nn.Module, *, config: FlashLoopConfig | None = None,
                  validate_model: bool = True, max_new_tokens: int = 512, use_cuda_graph: bool = False,
                  reference_loop4_scores: bool = True, fuse_decode_ops: bool = True, tp_group=None,
-                 tp_allreduce: str = "peer", tp_wait_limit: int = 0) -> None:
+                 tp_allreduce: str = "peer", tp_wait_limit: int = 0, stream_projections: bool = True) -> None:
         if validate_model:
             validate_ouro_model(model)
         elif int(getattr(model.config, "total_ut_steps", 0)) != 4:
@@ -95,6 +95,9 @@ class FlashLoopEngine:
         self._peer: PeerAllReduce | None = None
         self._reduce = PartialSum(tp_group) if tp_group is not None else (lambda t: t)
         self.fuse_decode_ops = bool(fuse_decode_ops) and self._modules_are_fusable()
+        # the projections of a decode step of at most 16 sequences through this library's weight-
+        # streaming kernel (step_ops.linear) instead of the framework's GEMM
+        self.stream_projections = bool(stream_projections)
         self._reuse = self.config.reuse_selected_probabilities and self.config.enable_sparse_decode
         self._state: EngineState | None = None
         self._graph = None
@@ -250,18 +253,23 @@ class FlashLoopEngine:
             return self._decode_step_fused(token_ids, position_ids)
         return self._decode_step_modules(token_ids, position_ids)
 
-    def _attend(self, loop: int, index: int, q, k, v, scaling: float, sources: list, o_proj, batch: int):
+    def _attend(self, loop: int, index: int, q, k, v, scaling: float, sources: list, o_proj, batch: int,
+                convert: bool = True):
         """The cache-facing part of one layer and loop (engine.py:422-531).  Returns (partial,
         addend, keep): the projected attention output [B, 1, hidden] is ``[addend +] sum over the
         tensor-parallel ranks of partial`` (one rank: partial itself), and with ``keep`` the caller
-        stores that output in ``sources[index][0]`` for the late loops."""
+        stores that output in ``sources[index][0]`` for the late loops.  With ``convert`` False the
+        readers' float32 output goes to ``o_proj`` as it is (a projection that rounds on load)."""
+
+        def cast(t, dtype):
+            return t.to(dtype) if convert else t
 
         physical = self.state.cache.layers[index]
         if loop < 2 or not self.config.enable_sparse_decode:
             want_logits = loop == 1 and self.config.enable_sparse_decode
             out, logits = physical.dense_source_attention(loop, query=q, current_key=k, current_value=v,
                                                           scaling=scaling, return_logits=want_logits)
-            partial = o_proj(out.to(q.dtype).view(batch, 1, -1))
+            partial = o_proj(cast(out, q.dtype).view(batch, 1, -1))
             if want_logits:
                 sel = physical.select_decode_keys(logits, fraction=self.config.effective_decode_key_fraction)
                 aggregate = physical.pv(1, sel.selected_weights, sel.indices, current_value=v,
@@ -274,11 +282,20 @@ class FlashLoopEngine:
             target = physical.pv(loop, sel.selected_weights, sel.indices, current_value=v, valid=sel.valid,
                                  validate_indices=False)
             delta = sel.global_mass.view(batch, -1, 1, 1) * (target - aggregate)
-            return o_proj(delta.to(v.dtype).view(batch, 1, -1)), projected0, False
+            return o_proj(cast(delta, v.dtype).view(batch, 1, -1)), projected0, False
         delta = physical.cached_mass_sparse_attention_delta(
             loop, query=q, current_key=k, current_value=v, indices=sel.indices, valid=sel.valid,
             source_selected_output=aggregate, global_mass=sel.global_mass, scaling=scaling)
-        return o_proj(delta.to(v.dtype).view(batch, 1, -1)), projected0, False
+        return o_proj(cast(delta, v.dtype).view(batch, 1, -1)), projected0, False
+
+    def _linear(self, x: torch.Tensor, weight: torch.Tensor, *, swiglu: bool = False) -> torch.Tensor:
+        """A bias-free projection of the fused decode step (and, with ``swiglu``, the gated
+        activation of a fused gate/up weight)."""
+
+        if self.stream_projections and step_ops.linear_fits(x, weight):
+            return step_ops.linear(x, weight, swiglu=swiglu)
+        y = torch.nn.functional.linear(x.to(weight.dtype), weight)
+        return step_ops.swiglu(y) if swiglu else y
 
     def _decode_reduce(self, partial: torch.Tensor) -> torch.Tensor:
         """Sum of a decode step's partial outputs over the tensor-parallel ranks."""
@@ -297,11 +314,9 @@ class FlashLoopEngine:
             return self._peer.reduce_norm(partial.contiguous(), norm.weight, eps(norm), residual=residual,
                                           weight2=norm2.weight, eps2=eps(norm2), addend=addend, want_sum=want_sum)
         total = self._reduce(partial)
-        if addend is not None:
-            total = addend + total
         hidden, x = step_ops.rmsnorm(total, norm.weight, eps(norm), residual=residual, weight2=norm2.weight,
-                                     eps2=eps(norm2))
-        return hidden, x, total
+                                     eps2=eps(norm2), addend=addend)
+        return hidden, x, (total if addend is None else None)
 
     def _decode_step_fused(self, token_ids: torch.Tensor, position_ids: torch.Tensor) -> torch.Tensor:
         """One decode step with the elementwise glue as one-launch kernels (``step_ops``): per layer
@@ -329,23 +344,27 @@ class FlashLoopEngine:
                     v = project_value(attention, x).view(batch, -1, 1, 128)
                     q, k = None, keys[index][1]
                 else:
-                    q, k, v = F.linear(x, attention._flashloop_qkv_weight).split(attention._flashloop_qkv_splits,
-                                                                                  dim=-1)
-                    q, k, v = step_ops.rope_split(q, k, v, cos, sin, heads=q.shape[-1] // 128)
+                    weight, heads = attention._flashloop_qkv_weight, attention._flashloop_qkv_splits[0] // 128
+                    if self.stream_projections and step_ops.linear_fits(x, weight):
+                        q, k, v = step_ops.qkv_rope(x, weight, cos, sin, heads=heads)
+                    else:
+                        q, k, v = F.linear(x, weight).split(attention._flashloop_qkv_splits, dim=-1)
+                        q, k, v = step_ops.rope_split(q, k, v, cos, sin, heads=heads)
                 keys[index][loop], values[index][loop] = k, v
                 partial, addend, keep = self._attend(loop, index, q, k, v, float(attention.scaling), sources,
-                                                     attention.o_proj, batch)
+                                                     lambda t, w=attention.o_proj.weight: self._linear(t, w), batch,
+                                                     convert=False)
                 n2, n3, n4 = layer.input_layernorm_2, layer.post_attention_layernorm, layer.post_attention_layernorm_2
                 hidden, x, projected = self._sum_norm(partial, addend, n2, n3, hidden, keep)
                 if keep:
                     sources[index][0] = projected
-                m = mlp.down_proj(step_ops.swiglu(F.linear(x, mlp._flashloop_gate_up_weight)))
+                m = self._linear(self._linear(x, mlp._flashloop_gate_up_weight, swiglu=True), mlp.down_proj.weight)
                 following = self.backbone.norm if index == n_layers - 1 else self.layers[index + 1].input_layernorm
                 hidden, x, _ = self._sum_norm(m, None, n4, following, hidden, False)
             hidden = x  # the final norm of this loop
         for index in range(n_layers):
             cache.layers[index].append_decode_token(keys[index], values[index])
-        return self.model.lm_head(hidden[:, -1]).float()
+        return self.model.lm_head(hidden[:, -1]).float()  # 200 MB of weights: the library GEMM streams them at 0.88 of peak
 
     def _decode_step_modules(self, token_ids: torch.Tensor, position_ids: torch.Tensor) -> torch.Tensor:
         """One decode step through the model's own modules (any Ouro-style block)."""

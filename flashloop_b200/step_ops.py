@@ -26,18 +26,21 @@ def _bf16(*tensors) -> None:
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, *, residual: torch.Tensor | None = None,
-            weight2: torch.Tensor | None = None, eps2: float = 0.0):
-    """``out = [residual +] RMSNorm(x)``; with ``weight2`` also ``RMSNorm2(out)``.  Returns out or
-    (out, out2)."""
+            weight2: torch.Tensor | None = None, eps2: float = 0.0, addend: torch.Tensor | None = None):
+    """``out = [residual +] RMSNorm([addend +] x)``; with ``weight2`` also ``RMSNorm2(out)``.  Returns
+    out or (out, out2)."""
 
-    _bf16(x, weight, residual, weight2)
+    _bf16(x, weight, residual, weight2, addend)
+    if addend is not None and addend.shape != x.shape:
+        raise ValueError("addend does not match the rows")
     rows, width = _rows(x)
     if weight.numel() != width or (residual is not None and residual.shape != x.shape):
         raise ValueError("weight / residual do not match the rows")
     out = torch.empty_like(x)
     out2 = torch.empty_like(x) if weight2 is not None else None
     _native.check(_native.load().fl_rmsnorm(
-        _native.ptr(x), _native.ptr(residual), _native.ptr(weight), float(eps), _native.ptr(weight2), float(eps2),
+        _native.ptr(x), _native.ptr(addend), _native.ptr(residual), _native.ptr(weight), float(eps),
+        _native.ptr(weight2), float(eps2),
         rows, width, _native.ptr(out), _native.ptr(out2), _native.current_stream(x.device)), "fl_rmsnorm")
     return out if weight2 is None else (out, out2)
 
@@ -75,3 +78,55 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
                                            _native.current_stream(gate_up.device)), "fl_swiglu")
     return out
 
+
+
+MAX_LINEAR_ROWS = 16
+
+
+def linear_fits(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether :func:`linear` takes this product (a decode step's shapes); otherwise the caller uses
+    the framework's GEMM."""
+
+    return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and weight.dtype == torch.bfloat16
+            and weight.is_contiguous() and x.is_contiguous() and x.numel() // x.shape[-1] <= MAX_LINEAR_ROWS
+            and weight.shape[1] % 32 == 0 and weight.shape[0] % 32 == 0 and x.data_ptr() % 16 == 0
+            and weight.data_ptr() % 16 == 0)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, *, swiglu: bool = False) -> torch.Tensor:
+    """``x @ weight.T`` for at most 16 rows, one launch that streams the weight once; bfloat16 out.
+    A float32 ``x`` is rounded to bfloat16 as it is read.  With ``swiglu`` the weight is gate rows then
+    up rows and the result is ``silu(gate) * up`` (as :func:`swiglu` of the product)."""
+
+    if x.dtype not in (torch.bfloat16, torch.float32) or not x.is_contiguous():
+        raise TypeError("x must be contiguous bfloat16 or float32")
+    _bf16(weight)
+    _native.require_cuda(x)
+    rows, width = _rows(x)
+    out_features, in_features = (int(v) for v in weight.shape)
+    if width != in_features:
+        raise ValueError("x and weight do not match")
+    out = torch.empty((*x.shape[:-1], out_features // 2 if swiglu else out_features), dtype=torch.bfloat16,
+                      device=x.device)
+    _native.check(_native.load().fl_linear_rows(
+        _native.ptr(x), _native.DTYPE_CODES[x.dtype], _native.ptr(weight), rows, out_features, in_features,
+        int(bool(swiglu)), _native.ptr(out), _native.current_stream(x.device)), "fl_linear_rows")
+    return out
+
+
+def qkv_rope(x: torch.Tensor, weight: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, *, heads: int):
+    """The fused Q/K/V projection with rotate-half RoPE on the way out: x [B, 1, hidden], weight
+    [3 * heads * 128, hidden] (q, k, v rows), cos/sin [B, 1, 128].  Returns q, k (rotated) and v as
+    [B, heads, 1, 128]: what :func:`linear` followed by :func:`rope_split` returns."""
+
+    cos, sin = cos.contiguous(), sin.contiguous()
+    _bf16(x, weight, cos, sin)
+    batch, width = _rows(x)
+    if tuple(weight.shape) != (3 * heads * 128, width) or cos.numel() != batch * 128 or sin.numel() != batch * 128:
+        raise ValueError("weight must be [3 * heads * 128, hidden] and cos / sin [batch, 1, 128]")
+    outs = [torch.empty((batch, heads, 1, 128), dtype=torch.bfloat16, device=x.device) for _ in range(3)]
+    _native.check(_native.load().fl_qkv_rope_rows(
+        _native.ptr(x), _native.ptr(weight), batch, heads, width, _native.ptr(cos), _native.ptr(sin),
+        _native.ptr(outs[0]), _native.ptr(outs[1]), _native.ptr(outs[2]), _native.current_stream(x.device)),
+        "fl_qkv_rope_rows")
+    return tuple(outs)

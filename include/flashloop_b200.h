@@ -342,11 +342,14 @@ int fl_encode_prefill_stage(const fl_layer* layer, int32_t sequence_begin, int32
  * ------------------------------------------------------------------------------------- */
 
 /* The RMSNorm modules of flashloop/engine.py:396 (input_layernorm) and :533-537 (the sandwich
- * norms around attention and MLP):  out = [residual +] weight * bf16(x * rsqrt(mean(x^2) + eps));
- * with weight2/out2 also out2 = weight2 * bf16(out * rsqrt(mean(out^2) + eps2)), i.e. the next
- * norm of the residual stream in the same launch.  x, residual, out, out2: [rows][width]. */
-int fl_rmsnorm(const void* x, const void* residual, const void* weight, float eps, const void* weight2,
-               float eps2, int64_t rows, int32_t width, void* out, void* out2, fl_cuda_stream stream);
+ * norms around attention and MLP):  out = [residual +] weight * bf16(s * rsqrt(mean(s^2) + eps))
+ * with s = x, or s = bf16(addend + x) when addend is given (the `projected0 + o_proj(delta)` of the
+ * late loops, flashloop/engine.py:529-531, folded in); with weight2/out2 also out2 = weight2 *
+ * bf16(out * rsqrt(mean(out^2) + eps2)), i.e. the next norm of the residual stream in the same
+ * launch.  x, addend, residual, out, out2: [rows][width]. */
+int fl_rmsnorm(const void* x, const void* addend, const void* residual, const void* weight, float eps,
+               const void* weight2, float eps2, int64_t rows, int32_t width, void* out, void* out2,
+               fl_cuda_stream stream);
 
 /* ---------------------------------------------------------------------------------------
  * Tensor-parallel decode.  No counterpart in the reference, which runs on one GPU
@@ -400,6 +403,26 @@ int fl_allreduce_rmsnorm(void* comm, const void* x, const void* addend, const vo
                          const void* weight, float eps, const void* weight2, float eps2, int64_t rows,
                          void* sum_out, void* out, void* out2, int32_t skip_store, int32_t wait_limit,
                          fl_cuda_stream stream);
+
+/* The bias-free nn.Linear modules of a decode step -- q/k/v_proj and o_proj (flashloop/engine.py:410-419,
+ * 531), gate/up/down_proj (flashloop/weights.py:108-117), lm_head (flashloop/engine.py:342) -- for at
+ * most 16 rows (one token per sequence):  out[m][n] = bf16(sum_k x[m][k] * weight[n][k]), float32
+ * accumulation, the weight streamed once.  x [rows][in_features] of x_dtype FL_DTYPE_BF16 or
+ * FL_DTYPE_F32 (rounded to bfloat16 as it is read: the `.to(dtype)` the reference applies to the
+ * readers' float32 output before o_proj); weight [out_features][in_features] bfloat16; 16-byte
+ * aligned; in_features a multiple of 32, out_features of 16.  With swiglu != 0 the weight is the gate
+ * rows followed by the up rows (out_features = 2F, a multiple of 32) and out [rows][F] receives
+ * bf16(silu(bf16 gate)) * bf16 up, i.e. fl_swiglu of the product in the same launch. */
+int fl_linear_rows(const void* x, int32_t x_dtype, const void* weight, int64_t rows, int32_t out_features,
+                   int32_t in_features, int32_t swiglu, void* out, fl_cuda_stream stream);
+
+/* The fused Q/K/V projection of flashloop/weights.py:74-105 (project_qkv) followed by the
+ * view/transpose and _apply_rope of flashloop/engine.py:59-75, 410-419, for at most 16 rows: weight
+ * [3 * heads * 128][in_features] = q rows, k rows, v rows; cos/sin [rows][128]; q_out, k_out (rotated)
+ * and v_out [rows][heads * 128].  The same arithmetic as fl_linear_rows followed by fl_rope_split. */
+int fl_qkv_rope_rows(const void* x, const void* weight, int64_t rows, int32_t heads, int32_t in_features,
+                     const void* cosv, const void* sinv, void* q_out, void* k_out, void* v_out,
+                     fl_cuda_stream stream);
 
 /* The view/transpose of the Q/K/V projections and _apply_rope (flashloop/engine.py:59-75,
  * 410-419) for one token per row: q_out/k_out = x * cos + rotate_half(x) * sin, v_out = v.

@@ -105,3 +105,76 @@ def test_unfusable_model_falls_back_to_modules():
     model.model.layers[0].mlp.act_fn = torch.nn.GELU()
     assert FlashLoopEngine(model, validate_model=False).fuse_decode_ops is False
 
+
+
+@pytest.mark.parametrize("rows,out_features,in_features", [(16, 6144, 2048), (16, 2048, 5632), (2, 768, 256),
+                                                           (5, 256, 384), (1, 49152, 2048), (16, 4128, 1056)])
+def test_linear_rows_matches_float32_product(rows, out_features, in_features):
+    g = torch.Generator(device="cuda").manual_seed(rows + out_features)
+    x = torch.randn(rows, 1, in_features, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(out_features, in_features, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    assert step_ops.linear_fits(x, w)
+    got = step_ops.linear(x, w)
+    want = (x.float() @ w.float().T)
+    # float32 accumulation in another order, then one rounding to bfloat16
+    assert got.shape == (rows, 1, out_features) and got.dtype == torch.bfloat16
+    # float32 accumulation in another order, then one rounding to bfloat16: half an ulp of the
+    # result plus the float32 noise of a sum of in_features terms (visible where the terms cancel)
+    err = (got.float() - want).abs()
+    bound = 2.0 ** -8 * want.abs() + 1e-5 * float((x.float().abs().max() * w.float().abs().max())) * in_features ** 0.5
+    assert bool((err <= bound).all()), (float(err.max()), float(want.abs().max()))
+    assert float((got == want.to(torch.bfloat16)).float().mean()) > 0.97
+
+
+@pytest.mark.parametrize("rows,width,in_features", [(16, 5632, 2048), (3, 192, 256)])
+def test_linear_rows_with_swiglu(rows, width, in_features):
+    g = torch.Generator(device="cuda").manual_seed(rows + width)
+    x = torch.randn(rows, 1, in_features, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(2 * width, in_features, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    got = step_ops.linear(x, w, swiglu=True)
+    want = step_ops.swiglu(step_ops.linear(x, w))           # the two launches it replaces: same roundings
+    assert got.shape == (rows, 1, width) and torch.equal(got, want)
+    ref = torch.nn.functional.silu((x.float() @ w.float().T)[..., :width]) * (x.float() @ w.float().T)[..., width:]
+    assert float((got.float() - ref).abs().max()) <= 2.0 ** -6 * float(ref.abs().max()) + 1e-5
+
+
+def test_linear_rows_rejects():
+    x = torch.zeros(17, 1, 256, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(256, 256, dtype=torch.bfloat16, device="cuda")
+    assert not step_ops.linear_fits(x, w)
+    with pytest.raises(RuntimeError, match="at most 16 rows"):
+        step_ops.linear(x, w)
+    assert not step_ops.linear_fits(x[:4], torch.zeros(256, 250, dtype=torch.bfloat16, device="cuda"))
+
+
+def test_linear_rows_takes_float32_rows():
+    g = torch.Generator(device="cuda").manual_seed(11)
+    x = torch.randn(16, 1, 2048, generator=g, device="cuda")
+    w = (torch.randn(2048, 2048, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    assert torch.equal(step_ops.linear(x, w), step_ops.linear(x.to(torch.bfloat16), w))
+
+
+@pytest.mark.parametrize("batch,heads,hidden", [(16, 16, 2048), (3, 2, 256), (1, 8, 1024)])
+def test_qkv_rope_equals_linear_then_rope_split(batch, heads, hidden):
+    g = torch.Generator(device="cuda").manual_seed(batch + heads)
+    x = torch.randn(batch, 1, hidden, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(3 * heads * 128, hidden, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    pos = torch.randint(0, 5000, (batch, 1), generator=g, device="cuda")
+    inv = 1.0 / (10000.0 ** (torch.arange(0, 128, 2, device="cuda").float() / 128))
+    emb = torch.cat([pos[..., None].float() * inv] * 2, dim=-1)
+    cos, sin = emb.cos().to(torch.bfloat16), emb.sin().to(torch.bfloat16)
+    q, k, v = step_ops.linear(x, w).split(heads * 128, dim=-1)
+    want = step_ops.rope_split(q, k, v, cos, sin, heads=heads)
+    got = step_ops.qkv_rope(x, w, cos, sin, heads=heads)
+    for a, b in zip(got, want):
+        assert a.shape == b.shape and torch.equal(a, b)
+
+
+def test_rmsnorm_addend_equals_separate_add():
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x, a, res = ((torch.randn(16, 1, 2048, generator=g, device="cuda") * 2).to(torch.bfloat16) for _ in range(3))
+    w1 = (1 + 0.1 * torch.randn(2048, generator=g, device="cuda")).to(torch.bfloat16)
+    w2 = (1 + 0.1 * torch.randn(2048, generator=g, device="cuda")).to(torch.bfloat16)
+    got = step_ops.rmsnorm(x, w1, 1e-6, residual=res, weight2=w2, eps2=1e-5, addend=a)
+    want = step_ops.rmsnorm(a + x, w1, 1e-6, residual=res, weight2=w2, eps2=1e-5)
+    assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
