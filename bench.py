@@ -387,6 +387,131 @@ def cpu_oracle_tokens_per_second(args, tasks_per_core: int = 3, pool=None) -> di
     }
 
 
+def run_reference_kernels(args) -> None:
+    """``--impl reference --workload kernels``: the reference's own CUDA readers (its extension
+    ``flashloop_kivi_gemv``, built unmodified from the reference checkout by oracle/build_ref.py into
+    oracle/_ref/) on this GPU, at the shapes of the kernel table: the dense reader of loops 1 and 2
+    and the cached-mass sparse reader of loops 3 and 4, called with the tensors the reference's
+    ``kivi_backend`` hands them.  One JSON line with a row per kernel; the algorithmic bytes are
+    those of this library's table, so the fractions compare like with like."""
+
+    import torch
+
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    module_dir = ROOT / "oracle" / "_ref"
+    if not (module_dir / "flashloop_kivi_gemv.so").exists():
+        print(json.dumps({"impl": "reference", "workload": "kernels",
+                          "unavailable": "oracle/_ref/flashloop_kivi_gemv.so is not built (python oracle/build_ref.py)"}))
+        return
+    sys.path.insert(0, str(module_dir))
+    import flashloop_kivi_gemv as reference_extension
+
+    from flashloop_b200 import kivi_backend as kb
+    from flashloop_b200.synthetic import make_loop_kv
+
+    device = torch.device("cuda", 0)
+    B, H, T = args.batch, HEADS, args.context
+    quant = ((T - 64) // 64) * 64
+    tail = T - quant
+    keys, values = [[] for _ in range(4)], [[] for _ in range(4)]
+    for b in range(B):
+        k, v = make_loop_kv(H, T, seed=7000 + b, device=device)
+        for r in range(4):
+            keys[r].append(k[r])
+            values[r].append(v[r])
+    keys = [torch.cat(k) for k in keys]
+    values = [torch.cat(v) for v in values]
+    # the residual chain of the reference's cache builder (flashloop/cache.py:415-439): every stream
+    # packs what the streams before it leave of that loop's tensor
+    k_streams, v_streams = [], []
+    base_k = base_v = None
+    for r in range(4):
+        dk = keys[r][:, :, :quant] if base_k is None else keys[r][:, :, :quant] - base_k
+        dv = values[r][:, :, :quant] if base_v is None else values[r][:, :, :quant] - base_v
+        k_streams.append(kb.pack_kivi_k_per_channel(dk.contiguous()))
+        v_streams.append(kb.pack_kivi_v_per_token(dv.contiguous()))
+        base_k = k_streams[-1].decode() if base_k is None else base_k + k_streams[-1].decode()
+        base_v = v_streams[-1].decode() if base_v is None else base_v + v_streams[-1].decode()
+    del base_k, base_v
+    tails_k = [k[:, :, quant:].contiguous() for k in keys]
+    tails_v = [v[:, :, quant:].contiguous() for v in values]
+    del keys, values
+    identity = torch.arange(quant, dtype=torch.int32, device=device)
+    gen = torch.Generator(device=device).manual_seed(1)
+    q, ck, cv = (torch.randn(B, H, 1, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16) for _ in range(3))
+
+    class Recorder:
+        """Stands in for the extension: runs it and keeps the arguments of the call."""
+
+        def __init__(self):
+            self.calls = {}
+
+        def __getattr__(self, name):
+            def call(*a):
+                self.calls[name] = a
+                return getattr(reference_extension, name)(*a)
+            return call
+
+    recorder = Recorder()
+    rows = []
+    peak, peak_kind = load_peak()
+
+    def timed(name: str, call_args, reps: int = 5) -> float:
+        fn = getattr(reference_extension, name)
+        fn(*call_args)
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn(*call_args)
+        e1.record()
+        torch.cuda.synchronize(device)
+        return e0.elapsed_time(e1) / reps * 1e3
+
+    logits = None
+    for loop in (0, 1):
+        _, lg = kb.kivi_fused_dense_source_attention(
+            query=q, current_key=ck, current_value=cv, key_streams=k_streams, value_streams=v_streams,
+            rank_maps=(identity, identity), tail_key=tails_k[loop], tail_value=tails_v[loop], scaling=SCALING,
+            loop=loop, extension=recorder, return_logits=True)
+        logits = lg
+        us = timed("dense_source_attention_cuda", recorder.calls["dense_source_attention_cuda"])
+        mb = dense_bytes(B * H, loop, quant, tail, 4) / 1e6
+        rows.append({"kernel": f"reference dense_source_attention_cuda, loop {loop + 1} (3 launches)", "us": us,
+                     "algorithmic_MB": mb, "GBps": mb / us * 1e3, "frac_of_peak": mb / us * 1e3 / peak})
+    # the selection of flashloop/engine.py:438-498 in tensor ops: top 10 % of the loop-2 softmax, ascending
+    weights = torch.softmax(logits.float(), dim=-1)[:, :, 0]
+    total = weights.shape[-1]
+    budget = min(total, max(1, math.ceil(total * KEY_FRACTION)))
+    top = torch.topk(weights, budget, dim=-1)
+    indices = torch.sort(top.indices, dim=-1).values
+    mass = top.values.sum(-1)
+    capacity = (budget // 64 + 1) * 64
+    padded = torch.zeros(B, H, capacity, dtype=torch.int32, device=device)
+    padded[..., :budget] = indices.to(torch.int32)
+    valid = torch.zeros(B, H, capacity, dtype=torch.bool, device=device)
+    valid[..., :budget] = True
+    source = torch.zeros(B, H, 1, HEAD_DIM, device=device)
+    for loop in (2, 3):
+        kb.kivi_fused_sparse_attention_delta(
+            query=q, current_key=ck, current_value=cv, key_streams=k_streams, value_streams=v_streams,
+            rank_maps=(identity, identity), tail_key=tails_k[loop], tail_value=tails_v[loop], indices=padded,
+            valid=valid, source_selected_output=source, global_mass=mass.view(B, H, 1, 1), current_position=quant + tail,
+            scaling=SCALING, loop=loop, extension=recorder)
+        us = timed("sparse_attention_delta_cuda", recorder.calls["sparse_attention_delta_cuda"])
+        mb = sparse_bytes(B * H, loop, budget, quant, 4) / 1e6
+        rows.append({"kernel": f"reference sparse_attention_delta_cuda, loop {loop + 1}, {budget} keys (3 launches)",
+                     "us": us, "algorithmic_MB": mb, "GBps": mb / us * 1e3, "frac_of_peak": mb / us * 1e3 / peak})
+    print(json.dumps({
+        "impl": "reference", "metric": "kernel table: the reference's CUDA readers on this GPU", "unit": "GB/s",
+        "n_gpus": 1, "peak_GBps": peak, "peak_source": peak_kind,
+        "config": {"workload": f"the reference extension's readers alone at batch {B}, {H} heads x {HEAD_DIM}, context {T}, "
+                               "4-bit KIVI words, all-token residuals; CUDA events around five eager calls of each "
+                               "entry point (its output and scratch allocations included, as its callers pay them)"},
+        "kind": "reference-cuda", "rows": rows}))
+
+
 def run_reference(args) -> None:
     """The CPU arm: the port of the reference's path on the host cores.  One step is one bounded
     sample of the workload (one head-step of the KV-attention path per core, plus, for the
@@ -1072,6 +1197,8 @@ def main() -> None:
     args = parse_args()
     if args.update_traffic:
         update_traffic(args)
+    elif args.impl == "reference" and args.workload == "kernels":
+        run_reference_kernels(args)
     elif args.impl == "reference":
         run_reference(args)
     elif args.workload == "e2e":
