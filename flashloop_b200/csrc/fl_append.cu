@@ -55,9 +55,25 @@ __global__ void __launch_bounds__(128) append_tail_kernel(const AppendParams p) 
 }
 
 // ------------------------------------------------------------------------------ rollover
-// grid (batch*heads, 2): y == 0 encodes K (thread = channel), y == 1 encodes V (warp = token).
+// grid (batch*heads, 4), 256 threads: y == 0, 1 encode the two channel halves of K, y == 2, 3 the
+// even and the odd tokens of V.
+//
+// K: a stream's 64 x 128 tile of tail rows is copied to shared memory with 16-byte asynchronous
+// copies, the tile of the next stream while the codes of this one are packed and stored; thread
+// (c, part) owns channel c and sixteen of the tokens (minimum and maximum of a channel are joined
+// over the four parts).
+// V: a warp per token, four channels per lane, the rows of all four streams fetched together.
+constexpr int kRollThreads = 256;
+
+__device__ __forceinline__ void copy16_async(void* dst_shared, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                   static_cast<uint32_t>(__cvta_generic_to_shared(dst_shared))),
+               "l"(src)
+               : "memory");
+}
+
 template <int BITS>
-__global__ void __launch_bounds__(128) rollover_kernel(const AppendParams p) {
+__global__ void __launch_bounds__(kRollThreads) rollover_kernel(const AppendParams p) {
   constexpr float kLevels = float((1 << BITS) - 1);
   constexpr int kRowBytes = 16 * BITS;
   constexpr int kRowWords = kRowBytes / 4;
@@ -91,33 +107,61 @@ __global__ void __launch_bounds__(128) rollover_kernel(const AppendParams p) {
   }
   __syncthreads();
 
-  if (blockIdx.y == 0) {
-    // ---------------- K: per channel over the block's tokens; thread c owns channel c
-    __shared__ __nv_bfloat16 s_recon[kGroup][kHeadDim];
-    __shared__ uint8_t s_tile[kGroup][kHeadDim + 4];
-    const int c = tid;
+  if (blockIdx.y < 2) {
+    // ---------------- K: per channel over the block's tokens; this CTA owns 64 of the 128 channels
+    constexpr int kChan = kHeadDim / 2, kParts = kRollThreads / kChan, kSpan = kGroup / kParts;
+    __shared__ __align__(16) __nv_bfloat16 s_x[kGroup][kChan];
+    __shared__ __nv_bfloat16 s_recon[kGroup][kChan];
+    __shared__ uint8_t s_tile[kGroup][kChan + 4];
+    __shared__ float s_lo[kParts][kChan], s_hi[kParts][kChan];
+    const int c0 = blockIdx.y * kChan;
+    const int c = tid & (kChan - 1), part = tid / kChan;
+    const auto fetch = [&](int s) {
+      const __nv_bfloat16* src = p.tail_k[s] + bh * cap * kHeadDim + c0;
+      for (int idx = tid; idx < kGroup * (kChan / 8); idx += kRollThreads) {
+        const int i = idx / (kChan / 8), v = idx % (kChan / 8);
+        copy16_async(&s_x[i][8 * v], src + ((start + i) % cap) * kHeadDim + 8 * v);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch(0);
 #pragma unroll 1
     for (int s = 0; s < 4; ++s) {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      __syncthreads();  // the tile of stream s is in shared memory
       const int rows = s < 2 ? kGroup : s_count[s - 2];
-      if (rows == 0) continue;  // uniform over the CTA
-      const __nv_bfloat16* src = p.tail_k[s] + bh * cap * kHeadDim + c;
+      if (rows == 0) {  // uniform over the CTA
+        __syncthreads();
+        if (s + 1 < 4) fetch(s + 1);
+        continue;
+      }
       float mn = INFINITY, mx = -INFINITY;
-      for (int i = 0; i < kGroup; ++i) {
+      for (int i = kSpan * part; i < kSpan * part + kSpan; ++i) {
         if (s >= 2 && !s_active[s - 2][i]) continue;
-        float x = __bfloat162float(src[((start + i) % cap) * kHeadDim]);
+        float x = __bfloat162float(s_x[i][c]);
         if (s > 0) x = bf16_round(x - __bfloat162float(s_recon[i][c]));
         mn = fminf(mn, x);
         mx = fmaxf(mx, x);
       }
+      s_lo[part][c] = mn;
+      s_hi[part][c] = mx;
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < kParts; ++k) {
+        mn = fminf(mn, s_lo[k][c]);
+        mx = fmaxf(mx, s_hi[k][c]);
+      }
       const float sc = quant_scale(mn, mx, kLevels);
       const float inv = quant_inverse(sc);
       const __half mn16 = __float2half_rn(mn), sc16 = __float2half_rn(sc);
-      const int64_t group = p.L.group_base[s][bh] + row0[s] / kGroup;
-      p.k_min[s][group * kHeadDim + c] = mn16;
-      p.k_scale[s][group * kHeadDim + c] = sc16;
-      for (int i = 0; i < kGroup; ++i) {
+      if (part == 0) {
+        const int64_t group = p.L.group_base[s][bh] + row0[s] / kGroup;
+        p.k_min[s][group * kHeadDim + c0 + c] = mn16;
+        p.k_scale[s][group * kHeadDim + c0 + c] = sc16;
+      }
+      for (int i = kSpan * part; i < kSpan * part + kSpan; ++i) {
         if (s >= 2 && !s_active[s - 2][i]) continue;
-        float x = __bfloat162float(src[((start + i) % cap) * kHeadDim]);
+        float x = __bfloat162float(s_x[i][c]);
         const float base = s > 0 ? __bfloat162float(s_recon[i][c]) : 0.f;
         if (s > 0) x = bf16_round(x - base);
         const uint32_t code = quant_code(x, mn, sc, inv, kLevels);
@@ -127,32 +171,40 @@ __global__ void __launch_bounds__(128) rollover_kernel(const AppendParams p) {
         s_recon[i][c] = __float2bfloat16_rn(s > 0 ? base + dec : dec);
       }
       __syncthreads();
-      uint32_t* dst = reinterpret_cast<uint32_t*>(p.k_codes[s] + (p.L.row_base[s][bh] + row0[s]) * kRowBytes);
-      for (int idx = tid; idx < rows * kRowWords; idx += 128) {
-        const int row = idx / kRowWords, wr = idx % kRowWords;
+      if (s + 1 < 4) fetch(s + 1);  // the tile is no longer read: the next one lands while this one is packed
+      // this CTA's half of every code row
+      constexpr int kHalfWords = kRowWords / 2;
+      uint32_t* dst = reinterpret_cast<uint32_t*>(p.k_codes[s] + (p.L.row_base[s][bh] + row0[s]) * kRowBytes) +
+                      blockIdx.y * kHalfWords;
+      for (int idx = tid; idx < rows * kHalfWords; idx += kRollThreads) {
+        const int row = idx / kHalfWords, wr = idx % kHalfWords;
         uint32_t word = 0;
 #pragma unroll
         for (int k = 0; k < kPerWord; ++k) word |= uint32_t(s_tile[row][wr * kPerWord + k]) << (BITS * k);
-        dst[idx] = word;
+        dst[row * kRowWords + wr] = word;
       }
-      __syncthreads();
+      __syncthreads();  // s_tile and s_lo / s_hi are free again
     }
   } else {
     // ---------------- V: per token over 64-channel groups; a warp per token, 4 channels per lane
     const int lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 4;
-    for (int i = warp; i < kGroup; i += 4) {
+    // two CTAs share a head's 64 tokens: y == 2 takes the even ones, y == 3 the odd ones
+    for (int i = 2 * warp + (blockIdx.y - 2); i < kGroup; i += 2 * (kRollThreads / 32)) {
       const int slot = (start + i) % cap;
+      uint2 raw[4];
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        raw[s] = ldg64(p.tail_v[s] + (bh * cap + slot) * kHeadDim + 4 * lane);
+      }
       float recon[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
+#pragma unroll
       for (int s = 0; s < 4; ++s) {
         if (s >= 2 && !s_active[s - 2][i]) continue;  // uniform over the warp
-        const __nv_bfloat16* src = p.tail_v[s] + (bh * cap + slot) * kHeadDim + 4 * lane;
-        float x[4];
+        float x[4] = {bf16_lo(raw[s].x), bf16_hi(raw[s].x), bf16_lo(raw[s].y), bf16_hi(raw[s].y)};
+        if (s > 0) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          x[k] = __bfloat162float(src[k]);
-          if (s > 0) x[k] = bf16_round(x[k] - recon[k]);
+          for (int k = 0; k < 4; ++k) x[k] = bf16_round(x[k] - recon[k]);
         }
         float mn = fminf(fminf(x[0], x[1]), fminf(x[2], x[3]));
         float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
@@ -195,7 +247,6 @@ __global__ void advance_state_kernel(const AppendParams p) {
   const int b = blockIdx.x;
   int32_t* st = p.seq_state + b * FL_STATE_WORDS;
   const int cap = p.L.tail_capacity;
-  __shared__ int s_rank[2][kGroup];
   const int tid = threadIdx.x;  // 64 threads
   const int tail_len = st[FL_STATE_TAIL_LEN] + 1;
   const bool roll = tail_len >= 2 * kGroup;
@@ -203,19 +254,24 @@ __global__ void advance_state_kernel(const AppendParams p) {
   const int start = st[FL_STATE_TAIL_START];
   const int rows2 = st[FL_STATE_ROWS2], rows3 = st[FL_STATE_ROWS3];
   if (roll) {
-    if (tid < 2) {
-      int n = 0;
-      for (int i = 0; i < kGroup; ++i) {
-        const bool on = p.tail_active[tid][static_cast<int64_t>(b) * cap + (start + i) % cap] != 0;
-        s_rank[tid][i] = on ? (tid == 0 ? rows2 : rows3) + n : -1;
-        n += on ? 1 : 0;
-      }
+    // thread i owns tail token i: its compact rank in streams 2 / 3 is the number of retained tokens
+    // before it (a ballot per warp, the first warp's count added in the second)
+    __shared__ int s_first[2];
+    const int64_t slot = static_cast<int64_t>(b) * cap + (start + tid) % cap;
+    const bool on0 = p.tail_active[0][slot] != 0, on1 = p.tail_active[1][slot] != 0;
+    const uint32_t m0 = __ballot_sync(0xffffffffu, on0), m1 = __ballot_sync(0xffffffffu, on1);
+    const int lane = tid & 31;
+    if (tid == 0) {
+      s_first[0] = __popc(m0);
+      s_first[1] = __popc(m1);
     }
     __syncthreads();
+    const uint32_t below = (1u << lane) - 1u;
+    const int r0 = __popc(m0 & below) + (tid >= 32 ? s_first[0] : 0);
+    const int r1 = __popc(m1 & below) + (tid >= 32 ? s_first[1] : 0);
     const int64_t base = p.L.rank_base[b] + quant + tid;
-    p.rank[0][base] = s_rank[0][tid];
-    p.rank[1][base] = s_rank[1][tid];
-    const int64_t slot = static_cast<int64_t>(b) * cap + (start + tid) % cap;
+    p.rank[0][base] = on0 ? rows2 + r0 : -1;
+    p.rank[1][base] = on1 ? rows3 + r1 : -1;
     p.tail_active[0][slot] = 0;
     p.tail_active[1][slot] = 0;
   }
@@ -270,9 +326,9 @@ extern "C" int fl_append_decode_token(const fl_layer* layer, const void* const* 
   append_tail_kernel<<<bh, 128, 0, s>>>(p);
   FL_CHECK_LAUNCH("fl_append_decode_token (append)");
   if (layer->bits == 4) {
-    rollover_kernel<4><<<dim3(bh, 2), 128, 0, s>>>(p);
+    rollover_kernel<4><<<dim3(bh, 4), kRollThreads, 0, s>>>(p);
   } else {
-    rollover_kernel<2><<<dim3(bh, 2), 128, 0, s>>>(p);
+    rollover_kernel<2><<<dim3(bh, 4), kRollThreads, 0, s>>>(p);
   }
   FL_CHECK_LAUNCH("fl_append_decode_token (rollover)");
   advance_state_kernel<<<layer->batch, kGroup, 0, s>>>(p);
