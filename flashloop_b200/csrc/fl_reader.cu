@@ -113,10 +113,13 @@ __device__ __forceinline__ Span block_span(const LayerView& L, int s, int b, int
 // both.  A CTA therefore meets a head once, keeps its online-softmax state in registers across all
 // of the head's blocks it owns, and merges and publishes once per item: one to three times in all.
 // Units a head's tail, its merge and the switch to the next head are counted as (loop: 0-based).
-// Their cost is a time, so it is more blocks of a loop that reads fewer streams per block; measured
-// at batch 16 x 2048 tokens, 24 / 16 units for loops 1 / 2 are 5 % faster than 8, at batch 8 x 8192
-// they are level.
-inline int tail_units_of_loop(int loop) { return 8 + 16 / (loop + 1); }
+// Their cost is a time, so it is more blocks of a loop that reads fewer streams per block, and it
+// weighs more where heads are short: measured, 24 / 16 units for loops 1 / 2 are 5 % faster than 8 at
+// batch 16 x 2048 tokens and 2 % slower at batch 8 x 8192, so the longer count is used up to 4096
+// tokens of context (the caller's bound).
+inline int tail_units_of_loop(int loop, int64_t max_context_tokens) {
+  return max_context_tokens <= 4096 ? 8 + 16 / (loop + 1) : 8;
+}
 
 struct ItemDesc {
   int id;  // -1: past the end of this CTA's range
@@ -1043,7 +1046,7 @@ extern "C" int fl_dense_source_attention(const fl_layer* layer, int32_t loop, co
   p.vcur = static_cast<const __nv_bfloat16*>(current_value);
   p.scaling = scaling;
   p.scaling_log2 = scaling * 1.4426950408889634f;
-  p.tail_units = tail_units_of_loop(loop);
+  p.tail_units = tail_units_of_loop(loop, max_context_tokens);
   p.out = output;
   p.logits = logits;
   p.logits_stride = logits_stride;
@@ -1153,7 +1156,7 @@ extern "C" int fl_dense_source_attention_static(const fl_layer* layer, int32_t l
   p.vcur = static_cast<const __nv_bfloat16*>(current_value);
   p.scaling = scaling;
   p.scaling_log2 = scaling * 1.4426950408889634f;
-  p.tail_units = tail_units_of_loop(loop);
+  p.tail_units = tail_units_of_loop(loop, max_context_tokens);
   p.out = output;
   p.logits = logits;
   p.logits_stride = logits_stride;
