@@ -87,6 +87,19 @@ __global__ void __launch_bounds__(kStepThreads) reduce_norm_kernel(const __grid_
   const int half = seq & 1;
   const int64_t my_slot = (static_cast<int64_t>(half) * c.world + c.rank) * c.rows_max + row;
 
+  // ---- what the row needs besides the sum is requested now: it arrives while the peers are waited for
+  uint4 raw_a[kMaxChunks], raw_r[kMaxChunks], raw_w[kMaxChunks], raw_w2[kMaxChunks];
+#pragma unroll
+  for (int ch = 0; ch < kMaxChunks; ++ch) {
+    const int e = (ch * kStepThreads + tid) * 8;
+    if (e < width) {
+      if (p.addend) raw_a[ch] = ldg128(p.addend + static_cast<int64_t>(row) * width + e);
+      if (p.residual) raw_r[ch] = ldg128(p.residual + static_cast<int64_t>(row) * width + e);
+      if (p.weight) raw_w[ch] = ldg128(p.weight + e);
+      if (p.weight2) raw_w2[ch] = ldg128(p.weight2 + e);
+    }
+  }
+
   // ---- this rank's row into every rank's receive buffer (its own included)
   const __nv_bfloat16* x = p.x + static_cast<int64_t>(row) * width;
   if (!p.skip_store) {
@@ -136,7 +149,7 @@ __global__ void __launch_bounds__(kStepThreads) reduce_norm_kernel(const __grid_
       for (int k = 0; k < 8; ++k) sum[k] = bf16_round_f(sum[k]);
       if (p.addend) {
         float a[8];
-        unpack8(ldg128(p.addend + static_cast<int64_t>(row) * width + e), a);
+        unpack8(raw_a[ch], a);
 #pragma unroll
         for (int k = 0; k < 8; ++k) sum[k] = bf16_round_f(a[k] + sum[k]);
       }
@@ -157,8 +170,8 @@ __global__ void __launch_bounds__(kStepThreads) reduce_norm_kernel(const __grid_
       const int e = (ch * kStepThreads + tid) * 8;
       if (e < width) {
         float w[8], r[8];
-        unpack8(ldg128(p.weight + e), w);
-        if (p.residual) unpack8(ldg128(p.residual + static_cast<int64_t>(row) * width + e), r);
+        unpack8(raw_w[ch], w);
+        if (p.residual) unpack8(raw_r[ch], r);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           float y = bf16_round_f(w[k] * bf16_round_f(v[ch][k] * inv));
@@ -176,7 +189,7 @@ __global__ void __launch_bounds__(kStepThreads) reduce_norm_kernel(const __grid_
         const int e = (ch * kStepThreads + tid) * 8;
         if (e < width) {
           float w[8];
-          unpack8(ldg128(p.weight2 + e), w);
+          unpack8(raw_w2[ch], w);
 #pragma unroll
           for (int k = 0; k < 8; ++k) v[ch][k] = w[k] * bf16_round_f(v[ch][k] * inv);
           *reinterpret_cast<uint4*>(p.out2 + static_cast<int64_t>(row) * width + e) = pack8(v[ch]);

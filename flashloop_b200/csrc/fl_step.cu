@@ -24,21 +24,36 @@ struct NormParams {
   __nv_bfloat16* out2;  // [rows][width] or null: norm2(out)
 };
 
-// out = [residual +] w * bf16(x * rsqrt(mean(x^2) + eps));  out2 = w2 * bf16(out * rsqrt(mean(out^2) + eps2))
+// out = [residual +] w * bf16(s * rsqrt(mean(s^2) + eps)), s = x or bf16(addend + x);
+// out2 = w2 * bf16(out * rsqrt(mean(out^2) + eps2)).
+// Everything the row needs (x, addend, residual, both weights) is requested before the first
+// reduction, so the kernel pays one round trip to memory instead of three.
 __global__ void __launch_bounds__(kStepThreads) norm_kernel(const NormParams p) {
   __shared__ float s_part[kStepThreads / 32];
   const int64_t row = blockIdx.x;
   const __nv_bfloat16* x = p.x + row * p.width;
+  uint4 raw_x[kMaxChunks], raw_a[kMaxChunks], raw_r[kMaxChunks], raw_w[kMaxChunks], raw_w2[kMaxChunks];
+#pragma unroll
+  for (int c = 0; c < kMaxChunks; ++c) {
+    const int e = (c * kStepThreads + threadIdx.x) * 8;
+    if (e < p.width) {
+      raw_x[c] = ldg128(x + e);
+      if (p.addend) raw_a[c] = ldg128(p.addend + row * p.width + e);
+      if (p.residual) raw_r[c] = ldg128(p.residual + row * p.width + e);
+      raw_w[c] = ldg128(p.weight + e);
+      if (p.out2) raw_w2[c] = ldg128(p.weight2 + e);
+    }
+  }
   float v[kMaxChunks][8];
   float sq = 0.f;
 #pragma unroll
   for (int c = 0; c < kMaxChunks; ++c) {
     const int e = (c * kStepThreads + threadIdx.x) * 8;
     if (e < p.width) {
-      unpack8(ldg128(x + e), v[c]);
+      unpack8(raw_x[c], v[c]);
       if (p.addend) {
         float a[8];
-        unpack8(ldg128(p.addend + row * p.width + e), a);
+        unpack8(raw_a[c], a);
 #pragma unroll
         for (int k = 0; k < 8; ++k) v[c][k] = bf16_round_f(a[k] + v[c][k]);
       }
@@ -53,8 +68,8 @@ __global__ void __launch_bounds__(kStepThreads) norm_kernel(const NormParams p) 
     const int e = (c * kStepThreads + threadIdx.x) * 8;
     if (e < p.width) {
       float w[8], r[8];
-      unpack8(ldg128(p.weight + e), w);
-      if (p.residual) unpack8(ldg128(p.residual + row * p.width + e), r);
+      unpack8(raw_w[c], w);
+      if (p.residual) unpack8(raw_r[c], r);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         float y = bf16_round_f(w[k] * bf16_round_f(v[c][k] * inv));
@@ -72,7 +87,7 @@ __global__ void __launch_bounds__(kStepThreads) norm_kernel(const NormParams p) 
     const int e = (c * kStepThreads + threadIdx.x) * 8;
     if (e < p.width) {
       float w[8];
-      unpack8(ldg128(p.weight2 + e), w);
+      unpack8(raw_w2[c], w);
 #pragma unroll
       for (int k = 0; k < 8; ++k) v[c][k] = w[k] * bf16_round_f(v[c][k] * inv);
       *reinterpret_cast<uint4*>(p.out2 + row * p.width + e) = pack8(v[c]);
