@@ -99,7 +99,7 @@ enum { kModeDelta = 0, kModePV = 1, kModeQK = 2 };
 constexpr int kGatherWarps = 8;
 constexpr int kGatherThreads = kGatherWarps * kWarp;
 constexpr int kSlotBatch = kGatherThreads;  // slots staged per round: one per thread
-constexpr int kDepth = 4;                   // passes in flight per warp
+constexpr int kDepth = 4;                   // passes in flight per warp (8 measured the same, 16 costs a CTA per SM)
 constexpr int kPassBytes = 1024;            // K: 8 rows (<= 512 B) + one metadata group (512 B); V: 8 records (<= 640 B)
 constexpr int kTailClass = 4;               // list of the slots that are tail tokens or the current token
 constexpr int kGatherCtasPerSm = 2;
