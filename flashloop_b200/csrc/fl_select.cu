@@ -11,8 +11,8 @@
 namespace fl {
 namespace {
 
-constexpr int kSelThreads = 1024;
-constexpr int kSelWarps = kSelThreads / 32;
+constexpr int kSelThreadsMax = 1024;  // 1024 threads per head for long rows, 512 up to 4096 keys (the time of a
+                                      // short row is barriers, and those are cheaper among fewer warps)
 constexpr int kSelMaxSharedKeys = 50 * 1024;  // keys held in shared memory (200 KiB)
 
 __device__ __forceinline__ uint32_t sortable(float v) {
@@ -23,13 +23,14 @@ __device__ __forceinline__ float unsortable(uint32_t k) {
   return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
 }
 
+template <int WARPS>
 __device__ __forceinline__ float block_reduce(float v, float* s_red, bool is_max) {
   v = is_max ? warp_max(v) : warp_sum(v);
   __syncthreads();
   if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = v;
   __syncthreads();
   float r = is_max ? -INFINITY : 0.f;
-  for (int w = 0; w < kSelWarps; ++w) r = is_max ? fmaxf(r, s_red[w]) : r + s_red[w];
+  for (int w = 0; w < WARPS; ++w) r = is_max ? fmaxf(r, s_red[w]) : r + s_red[w];
   return r;
 }
 
@@ -51,8 +52,9 @@ struct SelectParams {
 
 // SHARED: the keys of this (b,h) are staged once in shared memory (n <= kSelMaxSharedKeys);
 // otherwise every pass re-reads the values from global memory (L2).
-template <bool SHARED>
-__global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams p) {
+template <bool SHARED, int THREADS>
+__global__ void __launch_bounds__(THREADS) select_kernel(const SelectParams p) {
+  constexpr int kSelThreads = THREADS, kSelWarps = THREADS / 32;
   extern __shared__ uint32_t s_keys[];
   __shared__ int s_hist[256];
   __shared__ float s_red[kSelWarps];
@@ -90,10 +92,10 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
       m = fmaxf(m, x);
     }
     if (p.is_logits) {
-      vmax = block_reduce(m, s_red, true);
+      vmax = block_reduce<kSelWarps>(m, s_red, true);
       float z = 0.f;
       for (int i = tid; i < n; i += kSelThreads) z += expf(unsortable(key_at(i)) - vmax);
-      inv_z = 1.f / block_reduce(z, s_red, false);
+      inv_z = 1.f / block_reduce<kSelWarps>(z, s_red, false);
     }
   }
   if (tid == 0) {
@@ -189,7 +191,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
   }
   __syncthreads();
   if (warp == 0) {
-    int wg = s_wgt[lane], we = s_weq[lane];
+    int wg = lane < kSelWarps ? s_wgt[lane] : 0, we = lane < kSelWarps ? s_weq[lane] : 0;
     const int tg = wg, te = we;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -200,8 +202,10 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         we += ue;
       }
     }
-    s_wgt[lane] = wg - tg;  // exclusive
-    s_weq[lane] = we - te;
+    if (lane < kSelWarps) {
+      s_wgt[lane] = wg - tg;  // exclusive
+      s_weq[lane] = we - te;
+    }
   }
   __syncthreads();
   int gt_before = s_wgt[warp] + inc_gt - my_gt;
@@ -222,7 +226,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     gt_before += gt;
     eq_before += eq;
   }
-  const float mass = block_reduce(mass_part, s_red, false);
+  const float mass = block_reduce<kSelWarps>(mass_part, s_red, false);
   if (tid == 0) {
     p.mass[bh] = mass;
     if (p.counts) p.counts[bh] = budget;
@@ -282,14 +286,18 @@ extern "C" int fl_select_decode_keys(const float* values, int64_t values_stride,
   // keys per head are bounded by the stride of the values (or by n_keys when it is given)
   const int64_t bound = seq_state ? values_stride : n_keys;
   const unsigned grid = static_cast<unsigned>(batch) * heads;
-  if (bound <= kSelMaxSharedKeys) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bound <= 4096) {
+    select_kernel<true, 512><<<grid, 512, static_cast<size_t>(bound) * sizeof(uint32_t), s>>>(p);
+  } else if (bound <= kSelMaxSharedKeys) {
     const size_t smem = static_cast<size_t>(bound) * sizeof(uint32_t);
-    static const cudaError_t attr = cudaFuncSetAttribute(
-        select_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSelMaxSharedKeys * sizeof(uint32_t));
+    static const cudaError_t attr =
+        cudaFuncSetAttribute(select_kernel<true, kSelThreadsMax>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSelMaxSharedKeys * sizeof(uint32_t));
     (void)attr;
-    select_kernel<true><<<grid, kSelThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
+    select_kernel<true, kSelThreadsMax><<<grid, kSelThreadsMax, smem, s>>>(p);
   } else {
-    select_kernel<false><<<grid, kSelThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    select_kernel<false, kSelThreadsMax><<<grid, kSelThreadsMax, 0, s>>>(p);
   }
   FL_CHECK_LAUNCH(who);
   return FL_OK;
