@@ -9,7 +9,7 @@
 // system-scope fence, waits (bounded) for the sequence numbers of the others to appear in its own
 // flags and reduces the slots locally in rank order (float32), then goes straight on to
 // `[addend +] sum`, `residual + RMSNorm(.)` and the next RMSNorm exactly as fl_rmsnorm does.
-// No collective library on the path, no multicast objects, no TMA: plain loads and stores on
+// No collective library on the path, no NVLS objects, no TMA: plain loads and stores on
 // cudaIpc-mapped memory, which a CUDA graph can replay.
 //
 // One CTA per row.  Slots alternate between two halves by the parity of the sequence number: a

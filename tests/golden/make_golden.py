@@ -2,7 +2,7 @@
 
 Run here (needs the reference checkout; it is never needed at test time):
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path of the reference checkout>
 
 It imports the reference's ``flashloop`` and ``flashloop_torch`` packages, runs
 their CPU/Torch code on small seeded inputs and writes ``reference_vectors.npz``

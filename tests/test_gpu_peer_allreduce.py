@@ -3,7 +3,7 @@ against ``step_ops.rmsnorm`` of the summed rows, eagerly and replayed from a CUD
 bounded wait: a rank that publishes nothing makes the call give up with status 1, the GPUs keep
 answering and the next call is right again.  Skipped where fewer than two GPUs are visible.
 
-The ranks talk through a ``gloo`` group on the host (handle exchange only): no NCCL, no multicast
+The ranks talk through a ``gloo`` group on the host (handle exchange only): no NCCL, no NVLS
 object, plain peer stores."""
 
 from __future__ import annotations
