@@ -311,6 +311,49 @@ def probe_configs1_readers(device, bits: int, layers_n: int = 4) -> dict:
     }
 
 
+def probe_projection(model, rows: int, device) -> dict:
+    """The largest launch group of the end-to-end step by time: the fused gate/up projection with
+    SwiGLU (``fl_linear_rows``), timed with CUDA events around a graph that walks the layers' own
+    weights (24 x 46 MB, so no launch finds its weights in L2).  Algorithmic bytes = the weight, once.
+    Returns {"roofline_projection": ...} or {} when the step does not use the kernel at this batch."""
+
+    import torch
+
+    from flashloop_b200 import step_ops
+
+    weights = [layer.mlp._flashloop_gate_up_weight for layer in model.model.layers
+               if hasattr(layer.mlp, "_flashloop_gate_up_weight")]
+    if not weights:
+        return {}
+    x = torch.randn(rows, 1, weights[0].shape[1], device=device).to(torch.bfloat16)
+    if not step_ops.linear_fits(x, weights[0]):
+        return {}
+    for w in weights:
+        step_ops.linear(x, w, swiglu=True)
+    torch.cuda.synchronize(device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for w in weights:
+            step_ops.linear(x, w, swiglu=True)
+    graph.replay()
+    torch.cuda.synchronize(device)
+    ms = []
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize(device)
+        ms.append(e0.elapsed_time(e1) / len(weights))
+    peak, peak_kind = load_peak()
+    out_f, in_f = (int(v) for v in weights[0].shape)
+    obj = roofline_object(
+        f"linear_rows_kernel<2,1> (gate/up projection + SwiGLU, {rows} rows x [{out_f} x {in_f}] bfloat16 weight), the "
+        "largest launch group of the step by time", "projection", float(weights[0].numel() * 2), ms, peak, peak_kind,
+        f"CUDA events around a graph of {len(weights)} launches over the layers' own weights, 5 replays")
+    return {"roofline_projection": obj}
+
+
 # ----------------------------------------------------------------------------- the CPU oracle leg
 
 
@@ -1081,6 +1124,7 @@ def run_e2e(args) -> None:
     probes = {}
     if rank == 0 and not args.no_probes:
         probes = probe_configs1_readers(device, args.bits)
+        probes.update(probe_projection(model, B, device))
     if world > 1:
         dist.barrier()
 
