@@ -102,10 +102,7 @@ constexpr int kSlotBatch = kGatherThreads;  // slots staged per round: one per t
 constexpr int kDepth = 4;                   // passes in flight per warp (8 measured the same, 16 costs a CTA per SM)
 constexpr int kPassBytes = 1024;            // K: 8 rows (<= 512 B) + one metadata group (512 B); V: 8 records (<= 640 B)
 constexpr int kTailClass = 4;               // list of the slots that are tail tokens or the current token
-#ifndef FL_GATHER_CTAS
-#define FL_GATHER_CTAS 2
-#endif
-constexpr int kGatherCtasPerSm = FL_GATHER_CTAS;
+constexpr int kGatherCtasPerSm = 2;  // 3 and 4 (fewer slots per CTA) measured 18-22 % slower
 static_assert(kGatherWarps * kDepth * kPassBytes >= kGatherWarps * kPartialStride * 4,
               "the merge buffer reuses the rings");
 
