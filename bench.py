@@ -348,7 +348,7 @@ def probe_projection(model, rows: int, device) -> dict:
     peak, peak_kind = load_peak()
     out_f, in_f = (int(v) for v in weights[0].shape)
     obj = roofline_object(
-        f"linear_rows_kernel<2,1> (gate/up projection + SwiGLU, {rows} rows x [{out_f} x {in_f}] bfloat16 weight), the "
+        f"linear_ring_kernel<2,1> (gate/up projection + SwiGLU, {rows} rows x [{out_f} x {in_f}] bfloat16 weight), the "
         "largest launch group of the step by time", "projection", float(weights[0].numel() * 2), ms, peak, peak_kind,
         f"CUDA events around a graph of {len(weights)} launches over the layers' own weights, 5 replays")
     return {"roofline_projection": obj}
