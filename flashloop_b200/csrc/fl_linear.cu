@@ -11,14 +11,17 @@
 // index is simply mapped to "lane j holds k0 + 8j .. 8j+7", for x and W alike, so both operands
 // are plain 16-byte loads.  x (32 KB .. 176 KB) stays in L1/L2.
 //
-//   linear_rows_kernel  one tile of eight weight rows per CTA, the weights through registers (two
-//                       sets, the next batch in flight while this one is multiplied).  Used where
-//                       few output rows leave few tiles (o_proj, down_proj): it uses almost no
-//                       shared memory, so L1 keeps the whole of x (128 KB of float32 rows, 176 KB).
+//   linear_rows_kernel  one tile of eight weight rows (or a pair of tiles) per CTA, the weights
+//                       through registers (two sets, the next batch in flight while this one is
+//                       multiplied).  Used where few output rows leave few tiles (o_proj,
+//                       down_proj): it uses almost no shared memory, so L1 keeps the whole of x
+//                       (128 KB of float32 rows, 176 KB).
 //   linear_ring_kernel  pairs of tiles, persistent CTAs (three per SM), the weights through a
 //                       per-lane ring of 16-byte asynchronous copies in shared memory that runs on
 //                       across the pairs of a CTA.  Used for the wide projections (Q/K/V, gate/up,
-//                       more than 4096 output rows): 7.5 / 12.0 / 37 us against 8.6 / 12.8 / 43 for
+//                       more than 4096 output rows) when they have at least two pairs per SM
+//                       (a tensor-parallel rank's slice falls back to the register version with a
+//                       CTA per pair): 7.5 / 12.0 / 37 us against 8.6 / 12.8 / 43 for
 //                       the register version at 25 / 46 / 201 MB of weights.  Measured on the way: a
 //                       deeper ring is slower (8 stages 14.3 us, 16 stages 17.1 us for gate/up; the
 //                       shared memory comes out of L1, where x lives), and a read of the same bytes
@@ -352,10 +355,18 @@ void launch_linear(bool f32, unsigned grid, cudaStream_t s, const LinearParams& 
     linear_rows_kernel<TILES, MODE, false><<<grid, kLinearThreads, 0, s>>>(p);
   }
 }
+// Pairs of tiles: the ring kernel where there are at least two pairs per SM, else (a tensor-parallel
+// rank's slice of a projection) a CTA per pair with the weights through registers.
+constexpr int kRingMinGroups = 2 * 148;
+
 template <int MODE>
 void launch_ring(bool f32, int groups, cudaStream_t s, LinearParams& p) {
   constexpr int kSmem = kLinearWarps * kRing * 2 * 512;
   static_assert(kSmem <= 48 * 1024, "the ring fits the default dynamic shared memory");
+  if (groups < kRingMinGroups) {
+    launch_linear<2, MODE>(f32, static_cast<unsigned>(groups), s, p);
+    return;
+  }
   p.groups = groups;
   const unsigned grid = static_cast<unsigned>(groups < 148 * kRingCtasPerSm ? groups : 148 * kRingCtasPerSm);
   if (f32) {

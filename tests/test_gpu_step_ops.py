@@ -108,7 +108,8 @@ def test_unfusable_model_falls_back_to_modules():
 
 
 @pytest.mark.parametrize("rows,out_features,in_features", [(16, 6144, 2048), (16, 2048, 5632), (2, 768, 256),
-                                                           (5, 256, 384), (1, 49152, 2048), (16, 4128, 1056)])
+                                                           (5, 256, 384), (1, 49152, 2048), (16, 4128, 1056),
+                                                           (5, 8192, 1056)])
 def test_linear_rows_matches_float32_product(rows, out_features, in_features):
     g = torch.Generator(device="cuda").manual_seed(rows + out_features)
     x = torch.randn(rows, 1, in_features, generator=g, device="cuda").to(torch.bfloat16)
