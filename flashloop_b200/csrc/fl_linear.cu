@@ -21,7 +21,8 @@
 //                       across the pairs of a CTA.  Used for the wide projections (Q/K/V, gate/up,
 //                       more than 4096 output rows) when they have at least two pairs per SM
 //                       (a tensor-parallel rank's slice falls back to the register version with a
-//                       CTA per pair): 7.5 / 12.0 / 37 us against 8.6 / 12.8 / 43 for
+//                       CTA per pair; from four pairs per SM on, one CTA of sixteen warps per SM
+//                       that keeps its x fragments in registers): 7.5 / 11.0 / 36 us against 8.6 / 12.8 / 43 for
 //                       the register version at 25 / 46 / 201 MB of weights.  Measured on the way: a
 //                       deeper ring is slower (8 stages 14.3 us, 16 stages 17.1 us for gate/up; the
 //                       shared memory comes out of L1, where x lives), and a read of the same bytes
@@ -44,6 +45,9 @@ constexpr int kLinearThreads = kLinearWarps * 32;
 constexpr int kChunk = 32;  // k per warp-wide 16-byte load of one weight row (4 lanes x 8)
 constexpr int kRing = 4;    // stages of a warp's weight ring: three chunks in flight
 constexpr int kRingCtasPerSm = 3;
+// the ring kernel with the rows of x in registers: one CTA of sixteen warps per SM
+constexpr int kWideWarps = 16, kWideRing = 8;
+constexpr int kWideChunks = 4;  // chunks of K per warp whose x fragments a lane keeps (K <= 2048)
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
@@ -229,8 +233,14 @@ __device__ __forceinline__ int group_first_row(int group) {
   return group * (MODE == 1 ? 8 : 8 * TILES);
 }
 
-template <int TILES, int MODE, bool F32>
-__global__ void __launch_bounds__(kLinearThreads, kRingCtasPerSm) linear_ring_kernel(const LinearParams p) {
+// WIDE: sixteen warps, one CTA per SM, a ring of eight stages, and the x fragments of the warp's
+// chunks loaded once into registers (K <= 2048) instead of through L1 at every pair: the rows of x
+// then cross from L2 once per SM and not once per pair.
+template <int TILES, int MODE, bool F32, bool WIDE>
+__global__ void __launch_bounds__(WIDE ? kWideWarps * 32 : kLinearThreads, WIDE ? 1 : kRingCtasPerSm)
+linear_ring_kernel(const LinearParams p) {
+  constexpr int kLinearWarps = WIDE ? kWideWarps : fl::kLinearWarps;
+  constexpr int kRing = WIDE ? kWideRing : fl::kRing;
   extern __shared__ __align__(16) uint8_t s_ring[];  // [warp][kRing][TILES][32] x 16 bytes
   __shared__ float s_red[2][kLinearWarps][TILES][16][8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -288,6 +298,11 @@ __global__ void __launch_bounds__(kLinearThreads, kRingCtasPerSm) linear_ring_ke
   };
 #pragma unroll
   for (int i = 0; i < kRing - 1; ++i) issue();
+  uint4 xra[WIDE ? kWideChunks : 1], xrb[WIDE ? kWideChunks : 1];
+  if constexpr (WIDE) {
+#pragma unroll
+    for (int i = 0; i < kWideChunks; ++i) load_x(i, xra[i], xrb[i]);
+  }
 
   int stage = 0, round = 0;
   for (int group = blockIdx.x; group < p.groups; group += gridDim.x, round ^= 1) {
@@ -296,22 +311,39 @@ __global__ void __launch_bounds__(kLinearThreads, kRingCtasPerSm) linear_ring_ke
     for (int t = 0; t < TILES; ++t)
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[t][c] = 0.f;
-    uint4 va[2], vb[2];
-    load_x(0, va[0], vb[0]);
-    for (int i = 0; i < n_mine; i += 2) {
+    if constexpr (WIDE) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        if (i + h < n_mine) {
+      for (int i = 0; i < kWideChunks; ++i) {
+        if (i < n_mine) {
           issue();  // into the stage this lane read one step ago
-          load_x(i + h + 1, va[h ^ 1], vb[h ^ 1]);
           asm volatile("cp.async.wait_group %0;" ::"n"(kRing - 1) : "memory");
 #pragma unroll
           for (int t = 0; t < TILES; ++t) {
             const uint4 wv = *reinterpret_cast<const uint4*>(mine + (stage * TILES + t) * 512);
-            mma_bf16_16816(acc[t], va[h].x, vb[h].x, va[h].y, vb[h].y, wv.x, wv.y);
-            mma_bf16_16816(acc[t], va[h].z, vb[h].z, va[h].w, vb[h].w, wv.z, wv.w);
+            mma_bf16_16816(acc[t], xra[i].x, xrb[i].x, xra[i].y, xrb[i].y, wv.x, wv.y);
+            mma_bf16_16816(acc[t], xra[i].z, xrb[i].z, xra[i].w, xrb[i].w, wv.z, wv.w);
           }
           stage = (stage + 1) & (kRing - 1);
+        }
+      }
+    } else {
+      uint4 va[2], vb[2];
+      load_x(0, va[0], vb[0]);
+      for (int i = 0; i < n_mine; i += 2) {
+  #pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (i + h < n_mine) {
+            issue();  // into the stage this lane read one step ago
+            load_x(i + h + 1, va[h ^ 1], vb[h ^ 1]);
+            asm volatile("cp.async.wait_group %0;" ::"n"(kRing - 1) : "memory");
+  #pragma unroll
+            for (int t = 0; t < TILES; ++t) {
+              const uint4 wv = *reinterpret_cast<const uint4*>(mine + (stage * TILES + t) * 512);
+              mma_bf16_16816(acc[t], va[h].x, vb[h].x, va[h].y, vb[h].y, wv.x, wv.y);
+              mma_bf16_16816(acc[t], va[h].z, vb[h].z, va[h].w, vb[h].w, wv.z, wv.w);
+            }
+            stage = (stage + 1) & (kRing - 1);
+          }
         }
       }
     }
@@ -359,20 +391,32 @@ void launch_linear(bool f32, unsigned grid, cudaStream_t s, const LinearParams& 
 // rank's slice of a projection) a CTA per pair with the weights through registers.
 constexpr int kRingMinGroups = 2 * 148;
 
+template <int MODE, bool F32, bool WIDE>
+void launch_ring_as(int groups, cudaStream_t s, const LinearParams& p) {
+  constexpr int kWarps = WIDE ? kWideWarps : kLinearWarps;
+  constexpr int kSmem = kWarps * (WIDE ? kWideRing : kRing) * 2 * 512;
+  static const cudaError_t attr = cudaFuncSetAttribute(linear_ring_kernel<2, MODE, F32, WIDE>,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  (void)attr;
+  const int slots = 148 * (WIDE ? 1 : kRingCtasPerSm);
+  linear_ring_kernel<2, MODE, F32, WIDE><<<static_cast<unsigned>(groups < slots ? groups : slots), kWarps * 32, kSmem, s>>>(p);
+}
+
 template <int MODE>
 void launch_ring(bool f32, int groups, cudaStream_t s, LinearParams& p) {
-  constexpr int kSmem = kLinearWarps * kRing * 2 * 512;
-  static_assert(kSmem <= 48 * 1024, "the ring fits the default dynamic shared memory");
   if (groups < kRingMinGroups) {
     launch_linear<2, MODE>(f32, static_cast<unsigned>(groups), s, p);
     return;
   }
   p.groups = groups;
-  const unsigned grid = static_cast<unsigned>(groups < 148 * kRingCtasPerSm ? groups : 148 * kRingCtasPerSm);
+  // four pairs per SM or more: one wide CTA per SM (11.0 against 12.1 us for gate/up, 35.9 against
+  // 38.1 us for a 49152-row head); Q/K/V with its 2.6 pairs per SM is better off with one pair
+  // per CTA of the three-per-SM version (7.6 against 8.0 us)
+  const bool wide = groups >= 4 * 148 && p.k / kChunk <= kWideChunks * kWideWarps;
   if (f32) {
-    linear_ring_kernel<2, MODE, true><<<grid, kLinearThreads, kSmem, s>>>(p);
+    if (wide) launch_ring_as<MODE, true, true>(groups, s, p); else launch_ring_as<MODE, true, false>(groups, s, p);
   } else {
-    linear_ring_kernel<2, MODE, false><<<grid, kLinearThreads, kSmem, s>>>(p);
+    if (wide) launch_ring_as<MODE, false, true>(groups, s, p); else launch_ring_as<MODE, false, false>(groups, s, p);
   }
 }
 }  // namespace
