@@ -73,6 +73,8 @@ SIGNATURES = {
     "fl_swiglu": (C.c_int, [_vp, _i64, _i32, _vp, _vp]),
     "fl_linear_rows": (C.c_int, [_vp, _i32, _vp, _i64, _i32, _i32, _i32, _vp, _vp]),
     "fl_qkv_rope_rows": (C.c_int, [_vp, _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "fl_linear_rows_partial": (C.c_int, [_vp, _i32, _vp, _i64, _i32, _i32, _i32, _vp, _vp]),
+    "fl_rmsnorm_partial": (C.c_int, [_vp, _i32, _vp, _vp, _vp, _f32, _vp, _f32, _i64, _i32, _vp, _vp, _vp, _vp]),
     "fl_comm_handle_bytes": (_sz, []),
     "fl_comm_create": (C.c_int, [_i32, _i32, _i32, _i32, C.POINTER(_vp), _vp]),
     "fl_comm_connect": (C.c_int, [_vp, _vp]),
@@ -89,7 +91,7 @@ LAUNCHES_PER_CALL = {
     "fl_dense_source_attention_static": 1, "fl_sparse_attention_delta": 1, "fl_selected_pv": 1, "fl_selected_qk": 1,
     "fl_append_decode_token": 3, "fl_select_decode_keys": 1, "fl_hidden_delta_score": 1,
     "fl_select_prefill_tokens": 1, "fl_gather_rows": 1, "fl_scatter_rows": 1, "fl_encode_prefill": 3, "fl_encode_prefill_stage": 1,
-    "fl_rmsnorm": 1, "fl_rope_split": 1, "fl_swiglu": 1, "fl_allreduce_rmsnorm": 1, "fl_linear_rows": 1, "fl_qkv_rope_rows": 1,
+    "fl_rmsnorm": 1, "fl_rope_split": 1, "fl_swiglu": 1, "fl_allreduce_rmsnorm": 1, "fl_linear_rows": 1, "fl_qkv_rope_rows": 1, "fl_linear_rows_partial": 1, "fl_rmsnorm_partial": 1,
 }
 
 _LIB = None

@@ -12,8 +12,14 @@
 namespace fl {
 namespace {
 
+constexpr int kMaxSplits = 4;  // slices of K a projection may leave to the norm that follows it
+
 struct NormParams {
-  const __nv_bfloat16* x;         // [rows][width]: the tensor to normalise
+  const __nv_bfloat16* x;         // [rows][width]: the tensor to normalise, or null with `partial`
+  const float* partial;           // [splits][rows][width] or null: x = bf16(sum over the slices, in order)
+  int splits;
+  int64_t split_stride;           // rows * width
+  __nv_bfloat16* sum_out;         // [rows][width] or null: x as rebuilt from `partial`
   const __nv_bfloat16* addend;    // [rows][width] or null: bf16(addend + x) is normalised instead
   const __nv_bfloat16* residual;  // [rows][width] or null
   const __nv_bfloat16* weight;    // [width]
@@ -37,7 +43,31 @@ __global__ void __launch_bounds__(kStepThreads) norm_kernel(const NormParams p) 
   for (int c = 0; c < kMaxChunks; ++c) {
     const int e = (c * kStepThreads + threadIdx.x) * 8;
     if (e < p.width) {
-      raw_x[c] = ldg128(x + e);
+      if (p.partial) {
+        // the projection's float32 slices, added in order and rounded once: what a projection
+        // that sums all of K itself would have stored
+        float4 lo[kMaxSplits], hi[kMaxSplits];
+#pragma unroll
+        for (int s = 0; s < kMaxSplits; ++s) {
+          if (s < p.splits) {
+            const float* src = p.partial + s * p.split_stride + row * p.width + e;
+            lo[s] = __ldg(reinterpret_cast<const float4*>(src));
+            hi[s] = __ldg(reinterpret_cast<const float4*>(src + 4));
+          }
+        }
+        float sum[8] = {lo[0].x, lo[0].y, lo[0].z, lo[0].w, hi[0].x, hi[0].y, hi[0].z, hi[0].w};
+#pragma unroll
+        for (int s = 1; s < kMaxSplits; ++s) {
+          if (s < p.splits) {
+            sum[0] += lo[s].x; sum[1] += lo[s].y; sum[2] += lo[s].z; sum[3] += lo[s].w;
+            sum[4] += hi[s].x; sum[5] += hi[s].y; sum[6] += hi[s].z; sum[7] += hi[s].w;
+          }
+        }
+        raw_x[c] = pack8(sum);
+        if (p.sum_out) *reinterpret_cast<uint4*>(p.sum_out + row * p.width + e) = raw_x[c];
+      } else {
+        raw_x[c] = ldg128(x + e);
+      }
       if (p.addend) raw_a[c] = ldg128(p.addend + row * p.width + e);
       if (p.residual) raw_r[c] = ldg128(p.residual + row * p.width + e);
       raw_w[c] = ldg128(p.weight + e);
@@ -166,12 +196,51 @@ extern "C" int fl_rmsnorm(const void* x, const void* addend, const void* residua
                  aligned16(weight2) && aligned16(out2),
              "fl_rmsnorm: pointers must be 16-byte aligned");
   if (rows == 0) return FL_OK;
-  NormParams p{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(addend),
-               static_cast<const __nv_bfloat16*>(residual),
-               static_cast<const __nv_bfloat16*>(weight), static_cast<const __nv_bfloat16*>(weight2),
-               eps, eps2, width, static_cast<__nv_bfloat16*>(out), static_cast<__nv_bfloat16*>(out2)};
+  NormParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.addend = static_cast<const __nv_bfloat16*>(addend);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.weight = static_cast<const __nv_bfloat16*>(weight);
+  p.weight2 = static_cast<const __nv_bfloat16*>(weight2);
+  p.eps = eps;
+  p.eps2 = eps2;
+  p.width = width;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.out2 = static_cast<__nv_bfloat16*>(out2);
   norm_kernel<<<static_cast<unsigned>(rows), kStepThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   FL_CHECK_LAUNCH("fl_rmsnorm");
+  return FL_OK;
+}
+
+extern "C" int fl_rmsnorm_partial(const float* partial, int32_t splits, const void* addend, const void* residual,
+                                  const void* weight, float eps, const void* weight2, float eps2, int64_t rows,
+                                  int32_t width, void* sum_out, void* out, void* out2, fl_cuda_stream stream) {
+  const char* who = "fl_rmsnorm_partial";
+  FL_REQUIRE(partial && weight && out, "%s: null argument", who);
+  FL_REQUIRE(splits >= 1 && splits <= kMaxSplits, "%s: 1 to %d slices", who, kMaxSplits);
+  FL_REQUIRE(rows >= 0 && width > 0 && width % 8 == 0 && width <= kMaxChunks * kStepThreads * 8,
+             "%s: width must be a multiple of 8 up to %d, got %d", who, kMaxChunks * kStepThreads * 8, width);
+  FL_REQUIRE((weight2 == nullptr) == (out2 == nullptr), "%s: weight2 and out2 go together", who);
+  FL_REQUIRE(aligned16(partial) && aligned16(addend) && aligned16(weight) && aligned16(out) && aligned16(residual) &&
+                 aligned16(weight2) && aligned16(out2) && aligned16(sum_out),
+             "%s: pointers must be 16-byte aligned", who);
+  if (rows == 0) return FL_OK;
+  NormParams p{};
+  p.partial = partial;
+  p.splits = splits;
+  p.split_stride = rows * width;
+  p.sum_out = static_cast<__nv_bfloat16*>(sum_out);
+  p.addend = static_cast<const __nv_bfloat16*>(addend);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.weight = static_cast<const __nv_bfloat16*>(weight);
+  p.weight2 = static_cast<const __nv_bfloat16*>(weight2);
+  p.eps = eps;
+  p.eps2 = eps2;
+  p.width = width;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.out2 = static_cast<__nv_bfloat16*>(out2);
+  norm_kernel<<<static_cast<unsigned>(rows), kStepThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  FL_CHECK_LAUNCH(who);
   return FL_OK;
 }
 

@@ -288,10 +288,16 @@ class FlashLoopEngine:
             source_selected_output=aggregate, global_mass=sel.global_mass, scaling=scaling)
         return o_proj(cast(delta, v.dtype).view(batch, 1, -1)), projected0, False
 
-    def _linear(self, x: torch.Tensor, weight: torch.Tensor, *, swiglu: bool = False) -> torch.Tensor:
+    def _linear(self, x: torch.Tensor, weight: torch.Tensor, *, swiglu: bool = False,
+                to_norm: bool = False) -> torch.Tensor:
         """A bias-free projection of the fused decode step (and, with ``swiglu``, the gated
-        activation of a fused gate/up weight)."""
+        activation of a fused gate/up weight).  With ``to_norm`` the result goes straight to
+        :meth:`_sum_norm`, which on one GPU also takes the float32 partial sums
+        [splits, rows, 1, out] of ``step_ops.linear_partial``."""
 
+        if (to_norm and self.stream_projections and self._peer is None and self.tp_group is None
+                and step_ops.linear_partial_fits(x, weight)):
+            return step_ops.linear_partial(x, weight)
         if self.stream_projections and step_ops.linear_fits(x, weight):
             return step_ops.linear(x, weight, swiglu=swiglu)
         y = torch.nn.functional.linear(x.to(weight.dtype), weight)
@@ -310,6 +316,11 @@ class FlashLoopEngine:
         happens inside it).  Returns (hidden, x, s or None)."""
 
         eps = self._norm_eps
+        if partial.dtype == torch.float32 and partial.ndim == 4:  # step_ops.linear_partial's slices
+            hidden, x, total = step_ops.rmsnorm_partial(
+                partial, norm.weight, eps(norm), residual=residual, weight2=norm2.weight, eps2=eps(norm2),
+                addend=addend, want_sum=want_sum and addend is None)
+            return hidden, x, total
         if self._peer is not None:
             return self._peer.reduce_norm(partial.contiguous(), norm.weight, eps(norm), residual=residual,
                                           weight2=norm2.weight, eps2=eps(norm2), addend=addend, want_sum=want_sum)
@@ -352,13 +363,14 @@ class FlashLoopEngine:
                         q, k, v = step_ops.rope_split(q, k, v, cos, sin, heads=heads)
                 keys[index][loop], values[index][loop] = k, v
                 partial, addend, keep = self._attend(loop, index, q, k, v, float(attention.scaling), sources,
-                                                     lambda t, w=attention.o_proj.weight: self._linear(t, w), batch,
-                                                     convert=False)
+                                                     lambda t, w=attention.o_proj.weight: self._linear(t, w, to_norm=True),
+                                                     batch, convert=False)
                 n2, n3, n4 = layer.input_layernorm_2, layer.post_attention_layernorm, layer.post_attention_layernorm_2
                 hidden, x, projected = self._sum_norm(partial, addend, n2, n3, hidden, keep)
                 if keep:
                     sources[index][0] = projected
-                m = self._linear(self._linear(x, mlp._flashloop_gate_up_weight, swiglu=True), mlp.down_proj.weight)
+                m = self._linear(self._linear(x, mlp._flashloop_gate_up_weight, swiglu=True), mlp.down_proj.weight,
+                                 to_norm=True)
                 following = self.backbone.norm if index == n_layers - 1 else self.layers[index + 1].input_layernorm
                 hidden, x, _ = self._sum_norm(m, None, n4, following, hidden, False)
             hidden = x  # the final norm of this loop

@@ -45,6 +45,34 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, *, residual: torc
     return out if weight2 is None else (out, out2)
 
 
+def rmsnorm_partial(partial: torch.Tensor, weight: torch.Tensor, eps: float, *,
+                    residual: torch.Tensor | None = None, weight2: torch.Tensor | None = None, eps2: float = 0.0,
+                    addend: torch.Tensor | None = None, want_sum: bool = False):
+    """:func:`rmsnorm` of ``x = bfloat16(sum of the float32 slices partial[s])`` ([splits, rows, 1, width],
+    as :func:`linear_partial` leaves them), the sum and its one rounding done in the same launch.
+    Returns (out, out2 or None, x or None): x only with ``want_sum``."""
+
+    if partial.dtype != torch.float32 or partial.ndim != 4 or not partial.is_contiguous():
+        raise ValueError("partial sums must be contiguous float32 [splits, rows, 1, width]")
+    _native.require_cuda(partial)
+    splits, rows, _, width = (int(v) for v in partial.shape)
+    _bf16(weight, residual, weight2, addend)
+    shape = (rows, 1, width)
+    for t in (residual, addend):
+        if t is not None and tuple(t.shape) != shape:
+            raise ValueError("addend / residual do not match the rows")
+    if weight.numel() != width:
+        raise ValueError("weight does not match the rows")
+    out = torch.empty(shape, dtype=torch.bfloat16, device=partial.device)
+    out2 = torch.empty_like(out) if weight2 is not None else None
+    total = torch.empty_like(out) if want_sum else None
+    _native.check(_native.load().fl_rmsnorm_partial(
+        _native.ptr(partial), splits, _native.ptr(addend), _native.ptr(residual), _native.ptr(weight), float(eps),
+        _native.ptr(weight2), float(eps2), rows, width, _native.ptr(total), _native.ptr(out), _native.ptr(out2),
+        _native.current_stream(partial.device)), "fl_rmsnorm_partial")
+    return out, out2, total
+
+
 def rope_split(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, *,
                heads: int):
     """q, k, v: [B, 1, heads*128] (views of one fused projection are fine: rows may be strided);
@@ -112,6 +140,39 @@ def linear(x: torch.Tensor, weight: torch.Tensor, *, swiglu: bool = False) -> to
         _native.ptr(x), _native.DTYPE_CODES[x.dtype], _native.ptr(weight), rows, out_features, in_features,
         int(bool(swiglu)), _native.ptr(out), _native.current_stream(x.device)), "fl_linear_rows")
     return out
+
+
+LINEAR_SPLITS = 4              # slices of in_features of a split projection
+MAX_SPLIT_OUT_FEATURES = 4096  # above that the weight has tiles enough for linear()'s kernels
+
+
+def linear_partial_fits(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether :func:`linear_partial` takes this product: what :func:`linear` takes, few output
+    rows, and in_features that fall into LINEAR_SPLITS slices of at most 1536 values."""
+
+    if not linear_fits(x, weight):
+        return False
+    out_features, in_features = (int(v) for v in weight.shape)
+    return (out_features <= MAX_SPLIT_OUT_FEATURES and out_features % 8 == 0
+            and in_features % (32 * LINEAR_SPLITS) == 0 and in_features // LINEAR_SPLITS <= 1536)
+
+
+def linear_partial(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``x @ weight.T`` left as LINEAR_SPLITS float32 partial sums [splits, rows, 1, out_features] over
+    slices of in_features (``fl_linear_rows_partial``): every CTA keeps one slice of x in registers
+    instead of reading all of it, which for the projections with few output rows (``o_proj``,
+    ``down_proj``) is more bytes than the weight.  :func:`rmsnorm_partial` adds the slices."""
+
+    if not linear_partial_fits(x, weight):
+        raise ValueError("this product does not fit linear_partial")
+    rows = x.numel() // x.shape[-1]
+    out_features, in_features = (int(v) for v in weight.shape)
+    partial = torch.empty((LINEAR_SPLITS, rows, 1, out_features), dtype=torch.float32, device=x.device)
+    _native.check(_native.load().fl_linear_rows_partial(
+        _native.ptr(x), _native.DTYPE_CODES[x.dtype],
+        _native.ptr(weight), rows, out_features, in_features, LINEAR_SPLITS, _native.ptr(partial),
+        _native.current_stream(x.device)), "fl_linear_rows_partial")
+    return partial
 
 
 def qkv_rope(x: torch.Tensor, weight: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, *, heads: int):

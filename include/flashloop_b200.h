@@ -424,6 +424,23 @@ int fl_qkv_rope_rows(const void* x, const void* weight, int64_t rows, int32_t he
                      const void* cosv, const void* sinv, void* q_out, void* k_out, void* v_out,
                      fl_cuda_stream stream);
 
+/* fl_linear_rows for a weight with few output rows (o_proj, down_proj:
+ * flashloop/engine.py:531, flashloop/weights.py:108-117 fused_mlp's down projection) on one GPU,
+ * split over `splits` (1..4) slices of in_features: partial [splits][rows][out_features] float32
+ * receives every slice's sums; their sum in slice order, rounded once to bfloat16, is what
+ * fl_linear_rows would have written.  fl_rmsnorm_partial takes them as they are.  in_features a
+ * multiple of 32 * splits with at most 1536 values per slice, out_features a multiple of 8. */
+int fl_linear_rows_partial(const void* x, int32_t x_dtype, const void* weight, int64_t rows,
+                           int32_t out_features, int32_t in_features, int32_t splits, float* partial,
+                           fl_cuda_stream stream);
+
+/* fl_rmsnorm whose input is bf16(sum of `splits` float32 slices [splits][rows][width]) as left by
+ * fl_linear_rows_partial (no counterpart in the reference: the sum belongs to the projection);
+ * sum_out (nullable) receives that bfloat16 input. */
+int fl_rmsnorm_partial(const float* partial, int32_t splits, const void* addend, const void* residual,
+                       const void* weight, float eps, const void* weight2, float eps2, int64_t rows,
+                       int32_t width, void* sum_out, void* out, void* out2, fl_cuda_stream stream);
+
 /* The view/transpose of the Q/K/V projections and _apply_rope (flashloop/engine.py:59-75,
  * 410-419) for one token per row: q_out/k_out = x * cos + rotate_half(x) * sin, v_out = v.
  * q_in/k_in/v_in: rows of heads*128 values, in_stride elements apart (three slices of one

@@ -127,6 +127,48 @@ def test_linear_rows_matches_float32_product(rows, out_features, in_features):
     assert float((got == want.to(torch.bfloat16)).float().mean()) > 0.97
 
 
+@pytest.mark.parametrize("rows,out_features,in_features,dtype", [(16, 2048, 2048, torch.float32),
+                                                                  (16, 2048, 5632, torch.bfloat16),
+                                                                  (3, 256, 384, torch.bfloat16),
+                                                                  (1, 4096, 1024, torch.float32)])
+def test_split_projection_and_its_norm(rows, out_features, in_features, dtype):
+    """``linear_partial`` leaves float32 sums over four slices of in_features; their sum is the
+    float32 product, and ``rmsnorm_partial`` equals ``rmsnorm`` of that sum rounded to bfloat16, bit
+    for bit, with and without addend, residual and second norm."""
+
+    g = torch.Generator(device="cuda").manual_seed(rows + out_features + in_features)
+    x = torch.randn(rows, 1, in_features, generator=g, device="cuda").to(dtype)
+    w = (torch.randn(out_features, in_features, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    assert step_ops.linear_partial_fits(x, w)
+    partial = step_ops.linear_partial(x, w)
+    assert partial.shape == (step_ops.LINEAR_SPLITS, rows, 1, out_features) and partial.dtype == torch.float32
+    want = x.to(torch.bfloat16).float() @ w.float().T
+    total = partial.sum(0)
+    bound = 1e-5 * float(x.float().abs().max() * w.float().abs().max()) * in_features ** 0.5
+    assert float((total - want).abs().max()) <= bound
+    summed = total.to(torch.bfloat16)
+    n1 = (1 + 0.1 * torch.randn(out_features, generator=g, device="cuda")).to(torch.bfloat16)
+    n2 = (1 + 0.1 * torch.randn(out_features, generator=g, device="cuda")).to(torch.bfloat16)
+    addend = torch.randn(rows, 1, out_features, generator=g, device="cuda").to(torch.bfloat16)
+    residual = torch.randn(rows, 1, out_features, generator=g, device="cuda").to(torch.bfloat16)
+    out, out2, kept = step_ops.rmsnorm_partial(partial, n1, 1e-6, want_sum=True)
+    assert out2 is None and torch.equal(kept, summed) and torch.equal(out, step_ops.rmsnorm(summed, n1, 1e-6))
+    out, out2, kept = step_ops.rmsnorm_partial(partial, n1, 1e-6, residual=residual, weight2=n2, eps2=1e-5,
+                                               addend=addend)
+    want_out, want_out2 = step_ops.rmsnorm(summed, n1, 1e-6, residual=residual, weight2=n2, eps2=1e-5, addend=addend)
+    assert kept is None and torch.equal(out, want_out) and torch.equal(out2, want_out2)
+
+
+def test_split_projection_rejects_what_it_cannot_slice():
+    x = torch.randn(2, 1, 96, device="cuda").to(torch.bfloat16)
+    w = torch.randn(64, 96, device="cuda").to(torch.bfloat16)   # 96 is not four slices of chunks of 32
+    assert not step_ops.linear_partial_fits(x, w)
+    with pytest.raises(ValueError):
+        step_ops.linear_partial(x, w)
+    wide = torch.randn(8192, 128, device="cuda").to(torch.bfloat16)  # enough tiles for the other kernels
+    assert not step_ops.linear_partial_fits(torch.randn(2, 1, 128, device="cuda").to(torch.bfloat16), wide)
+
+
 @pytest.mark.parametrize("rows,width,in_features", [(16, 5632, 2048), (3, 192, 256)])
 def test_linear_rows_with_swiglu(rows, width, in_features):
     g = torch.Generator(device="cuda").manual_seed(rows + width)
