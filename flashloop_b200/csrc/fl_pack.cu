@@ -92,57 +92,64 @@ pack_k_kernel(const T* __restrict__ values, int64_t tokens, void* __restrict__ o
 }
 
 // ------------------------------------------------------------------------------- V: per token
-// A warp per token, four tokens per warp with their loads issued together; lane l owns channels
-// 4l .. 4l+3; the two 64-channel groups are the two 16-lane halves of the warp.
-constexpr int kVTokensPerWarp = 4;
+// Half a warp per token: lane l of the half owns channels 8l .. 8l+7 (one 16-byte load of
+// bfloat16), so a 64-channel group is eight lanes (three shuffle steps for its minimum and maximum,
+// one division for its scale) and a lane's eight codes are one 32-bit word of the row.  A warp takes
+// eight tokens, two at a time, their loads issued together.  The KIVI word layout is token-minor
+// ([bh][16 words][tokens]): there the CTA's 32 consecutive tokens meet in shared memory and leave
+// as 128-byte runs of one word row, instead of one 4-byte store per word.
+constexpr int kVWarps = 4;
+constexpr int kVPairs = 4;                       // pairs of tokens per warp
+constexpr int kVPerCta = kVWarps * kVPairs * 2;  // 32 tokens
 
 template <typename T>
-__device__ __forceinline__ void load_four(const T* src, float (&x)[4]) {
-  if constexpr (sizeof(T) == 2) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(src);  // 8-byte aligned: 4 channels of 2 bytes
+__device__ __forceinline__ void load_eight(const T* src, bool vector_ok, float (&x)[8]) {
+  if (!vector_ok) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) x[k] = load_as_float(src + k);
+  } else if constexpr (sizeof(T) == 2) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(src);
     const T* h = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) x[k] = load_as_float(h + k);
+    for (int k = 0; k < 8; ++k) x[k] = load_as_float(h + k);
   } else {
-    const float4 raw = *reinterpret_cast<const float4*>(src);
-    x[0] = raw.x; x[1] = raw.y; x[2] = raw.z; x[3] = raw.w;
+    const float4 lo = *reinterpret_cast<const float4*>(src);
+    const float4 hi = *reinterpret_cast<const float4*>(src + 4);
+    x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
+    x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
   }
 }
 
 template <typename T, int BITS, bool KIVI>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kVWarps * 32)
 pack_v_kernel(const T* __restrict__ values, int64_t tokens, int64_t total_tokens,
               void* __restrict__ out_codes, __half* __restrict__ minimum,
               __half* __restrict__ scale, int64_t meta_stride) {
   constexpr float kLevels = float((1 << BITS) - 1);
   constexpr int kRowBytes = 16 * BITS;
-  const int lane = threadIdx.x & 31;
-  const int64_t first = (static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5)) * kVTokensPerWarp;
-  if (first >= total_tokens) return;
+  __shared__ uint32_t s_words[KIVI ? 16 : 1][KIVI ? kVPerCta + 1 : 1];
+  __shared__ __half s_meta[KIVI ? 4 : 1][KIVI ? kVPerCta : 1];  // min of group 0, 1, scale of group 0, 1
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int half = lane >> 4, sub = lane & 15, g = sub >> 3;
+  const int64_t cta_first = static_cast<int64_t>(blockIdx.x) * kVPerCta;
   const bool vector_ok = (reinterpret_cast<uintptr_t>(values) & 15u) == 0;
-  float xs[kVTokensPerWarp][4];
+  float xs[kVPairs][8];
 #pragma unroll
-  for (int j = 0; j < kVTokensPerWarp; ++j) {
-    const int64_t wg = first + j < total_tokens ? first + j : total_tokens - 1;
-    const T* src = values + wg * kHeadDim + 4 * lane;
-    if (vector_ok) {
-      load_four(src, xs[j]);
-    } else {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) xs[j][k] = load_as_float(src + k);
-    }
+  for (int j = 0; j < kVPairs; ++j) {
+    const int64_t want = cta_first + (warp * kVPairs + j) * 2 + half;
+    const int64_t wg = want < total_tokens ? want : total_tokens - 1;
+    load_eight(values + wg * kHeadDim + 8 * sub, vector_ok, xs[j]);
   }
 #pragma unroll
-  for (int j = 0; j < kVTokensPerWarp; ++j) {
-    const int64_t wg = first + j;
-    if (wg >= total_tokens) break;
-    const int64_t bh = wg / tokens;
-    const int64_t t = wg % tokens;
-    const float (&x)[4] = xs[j];
-    float mn = fminf(fminf(x[0], x[1]), fminf(x[2], x[3]));
-    float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+  for (int j = 0; j < kVPairs; ++j) {
+    const int slot = (warp * kVPairs + j) * 2 + half;
+    const int64_t wg = cta_first + slot;
+    const bool on = wg < total_tokens;  // the shuffles below are for the whole warp
+    const float (&x)[8] = xs[j];
+    float mn = fminf(fminf(fminf(x[0], x[1]), fminf(x[2], x[3])), fminf(fminf(x[4], x[5]), fminf(x[6], x[7])));
+    float mx = fmaxf(fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3])), fmaxf(fmaxf(x[4], x[5]), fmaxf(x[6], x[7])));
 #pragma unroll
-    for (int o = 8; o > 0; o >>= 1) {
+    for (int o = 4; o > 0; o >>= 1) {
       mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     }
@@ -150,29 +157,45 @@ pack_v_kernel(const T* __restrict__ values, int64_t tokens, int64_t total_tokens
     const float inv = quant_inverse(sc);
     uint32_t packed = 0;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) packed |= quant_code(x[k], mn, sc, inv, kLevels) << (BITS * k);
-    const int g = lane >> 4;
+    for (int k = 0; k < 8; ++k) packed |= quant_code(x[k], mn, sc, inv, kLevels) << (BITS * k);
+    if (!on) continue;
     if constexpr (KIVI) {
       static_assert(BITS == 4, "the KIVI word layout is 4-bit");
-      const uint32_t other = __shfl_down_sync(0xffffffffu, packed, 1);
-      if ((lane & 1) == 0) {
-        static_cast<int32_t*>(out_codes)[(bh * 16 + (lane >> 1)) * tokens + t] =
-            static_cast<int32_t>(packed | (other << 16));
-      }
-      if ((lane & 15) == 0) {
-        minimum[(bh * 2 + g) * tokens + t] = __float2half_rn(mn);
-        scale[(bh * 2 + g) * tokens + t] = __float2half_rn(sc);
+      s_words[sub][slot] = packed;
+      if ((sub & 7) == 0) {
+        s_meta[g][slot] = __float2half_rn(mn);
+        s_meta[2 + g][slot] = __float2half_rn(sc);
       }
     } else {
       uint8_t* row = static_cast<uint8_t*>(out_codes) + wg * kRowBytes;
       if constexpr (BITS == 4) {
-        reinterpret_cast<uint16_t*>(row)[lane] = static_cast<uint16_t>(packed);
+        reinterpret_cast<uint32_t*>(row)[sub] = packed;
       } else {
-        row[lane] = static_cast<uint8_t>(packed);
+        reinterpret_cast<uint16_t*>(row)[sub] = static_cast<uint16_t>(packed);
       }
-      if ((lane & 15) == 0) {
+      if ((sub & 7) == 0) {
         minimum[wg * meta_stride + g] = __float2half_rn(mn);
         scale[wg * meta_stride + g] = __float2half_rn(sc);
+      }
+    }
+  }
+  if constexpr (KIVI) {
+    __syncthreads();
+    // word row r of the CTA's tokens: consecutive tokens of one (b,h) are consecutive words
+    for (int idx = threadIdx.x; idx < 16 * kVPerCta; idx += kVWarps * 32) {
+      const int r = idx / kVPerCta, slot = idx % kVPerCta;
+      const int64_t wg = cta_first + slot;
+      if (wg < total_tokens) {
+        const int64_t bh = wg / tokens, t = wg % tokens;
+        static_cast<int32_t*>(out_codes)[(bh * 16 + r) * tokens + t] = static_cast<int32_t>(s_words[r][slot]);
+      }
+    }
+    for (int idx = threadIdx.x; idx < 4 * kVPerCta; idx += kVWarps * 32) {
+      const int which = idx / kVPerCta, slot = idx % kVPerCta;
+      const int64_t wg = cta_first + slot;
+      if (wg < total_tokens) {
+        const int64_t bh = wg / tokens, t = wg % tokens;
+        (which < 2 ? minimum : scale)[(bh * 2 + (which & 1)) * tokens + t] = s_meta[which][slot];
       }
     }
   }
@@ -276,7 +299,7 @@ template <int BITS, bool KIVI>
 int launch_pack_v(const void* values, int32_t dtype, int64_t bh, int64_t tokens, void* codes,
                   void* minimum, void* scale, int64_t meta_stride, cudaStream_t stream) {
   const int64_t total = bh * tokens;
-  const int64_t per_cta = 4 * kVTokensPerWarp;
+  const int64_t per_cta = kVPerCta;
   const unsigned grid = static_cast<unsigned>((total + per_cta - 1) / per_cta);
   __half* mn = static_cast<__half*>(minimum);
   __half* sc = static_cast<__half*>(scale);
