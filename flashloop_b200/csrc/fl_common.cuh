@@ -204,6 +204,29 @@ __device__ __forceinline__ uint32_t quant_code(float x, float minimum, float sca
   r = fminf(fmaxf(r, 0.f), levels);
   return static_cast<uint32_t>(r);
 }
+// Eight codes at once, code k in bits [BITS*k, BITS*k + BITS): the fast path of quant_code for all
+// eight and one test whether any of them sits at a rounding boundary, in which case (about once in
+// a thousand groups) all eight go through the division.  Same codes as eight quant_code calls.
+template <int BITS>
+__device__ __forceinline__ uint32_t quant_codes8(const float (&x)[8], float minimum, float scale, float inverse,
+                                                 float levels) {
+  float r[8];
+  bool exact = inverse == 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float q = __fmul_rn(__fsub_rn(x[k], minimum), inverse);
+    r[k] = rintf(q);
+    exact |= !(fabsf(fabsf(q - r[k]) - 0.5f) > 1e-4f);
+  }
+  if (exact) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) r[k] = rintf(__fdiv_rn(__fsub_rn(x[k], minimum), scale));
+  }
+  uint32_t packed = 0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) packed |= static_cast<uint32_t>(fminf(fmaxf(r[k], 0.f), levels)) << (BITS * k);
+  return packed;
+}
 // code * scale + minimum in float32 (two roundings, as torch computes it), then bf16 RNE.
 __device__ __forceinline__ float dequant_f32(uint32_t code, __half scale, __half minimum) {
   return __fadd_rn(__fmul_rn(static_cast<float>(code), __half2float(scale)),

@@ -59,12 +59,19 @@ pack_k_kernel(const T* __restrict__ values, int64_t tokens, void* __restrict__ o
     const int64_t word_rows = (tokens + 7) / 8;
     for (int w = 0; w * 8 < cnt; ++w) {
       uint32_t word = 0;
+      if (w * 8 + 8 <= cnt) {
+        float x[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int i = w * 8 + j;
-        if (i < cnt) {
-          const float x = load_as_float(src + static_cast<int64_t>(i) * kHeadDim);
-          word |= quant_code(x, mn, sc, inv, kLevels) << (4 * j);
+        for (int j = 0; j < 8; ++j) x[j] = load_as_float(src + static_cast<int64_t>(w * 8 + j) * kHeadDim);
+        word = quant_codes8<4>(x, mn, sc, inv, kLevels);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int i = w * 8 + j;
+          if (i < cnt) {
+            const float x = load_as_float(src + static_cast<int64_t>(i) * kHeadDim);
+            word |= quant_code(x, mn, sc, inv, kLevels) << (4 * j);
+          }
         }
       }
       payload[(bh * word_rows + t0 / 8 + w) * kHeadDim + c] = static_cast<int32_t>(word);
@@ -75,8 +82,7 @@ pack_k_kernel(const T* __restrict__ values, int64_t tokens, void* __restrict__ o
       const float x = load_as_float(src + static_cast<int64_t>(i) * kHeadDim);
       tile[i][c] = static_cast<uint8_t>(quant_code(x, mn, sc, inv, kLevels));
     }
-    __syncthreads();
-    constexpr int kRowWords = kRowBytes / 4;
+    __syncthreads();    constexpr int kRowWords = kRowBytes / 4;
     constexpr int kPerWord = 32 / BITS;
     uint32_t* dst =
         reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(out_codes) + (bh * tokens + t0) * kRowBytes);
@@ -155,9 +161,7 @@ pack_v_kernel(const T* __restrict__ values, int64_t tokens, int64_t total_tokens
     }
     const float sc = quant_scale(mn, mx, kLevels);
     const float inv = quant_inverse(sc);
-    uint32_t packed = 0;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) packed |= quant_code(x[k], mn, sc, inv, kLevels) << (BITS * k);
+    const uint32_t packed = quant_codes8<BITS>(x, mn, sc, inv, kLevels);
     if (!on) continue;
     if constexpr (KIVI) {
       static_assert(BITS == 4, "the KIVI word layout is 4-bit");
