@@ -935,9 +935,10 @@ unsigned dense_grid(int64_t batch_heads) {
   // contexts are equal.  With one CTA per head nothing is merged across CTAs (256 heads x 2048
   // tokens: 28.6 / 44.0 us against 32.9 / 48.7 for loops 1 / 2 with 296 CTAs); a whole number of
   // CTAs per head saves the second merge of a CTA that straddles two heads, which pays as long as
-  // it costs few CTAs (16 heads x 8192 as 18 CTAs per head: 16.1 / 19.8 against 17.1 / 24.6 us; 128
+  // it costs few CTAs (48 heads x 8192 as 6 CTAs per head: 23.5 / 35.6 against 27.9 / 37.9 us; 128
   // heads as two per head, 256 CTAs, is slower: 81 against 75 us for loop 2).  More heads than
-  // CTAs keep the full grid: with ragged contexts fewer CTAs only cost bandwidth.
+  // CTAs keep the full grid: with ragged contexts fewer CTAs only cost bandwidth.  Fewer than 37
+  // heads get eight CTAs each, the most that short contexts can keep busy.
   const int64_t cap = batch_heads * 8;  // tail_units_of_loop is at least 8
   if (cap < ctas) return static_cast<unsigned>(cap);
   if (batch_heads <= ctas) {
