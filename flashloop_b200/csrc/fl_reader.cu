@@ -199,7 +199,7 @@ __device__ __forceinline__ void describe_next(const ReaderParams& p, const int* 
   d->blk_end = u1 < blocks ? u1 : blocks;
   d->has_tail = u0 <= blocks && blocks < u1;
   // CTA that owns unit u: the largest c with c*U/G <= u
-  const int64_t grid = gridDim.x;
+  const int64_t grid = all_units < static_cast<int64_t>(gridDim.x) ? all_units : static_cast<int64_t>(gridDim.x);
   const int64_t first_owner = ((c->head_first + 1) * grid - 1) / all_units;
   const int64_t last_owner = (head_end * grid - 1) / all_units;
   d->part = static_cast<int>(static_cast<int64_t>(blockIdx.x) - first_owner);
@@ -472,7 +472,11 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
     // that the first query is fetched while one thread describes the first two items.
     const int64_t all_units = total_units(L, p.tail_units, s_each);
     ItemCursor cursor;
-    cursor_start(L, p.tail_units, s_each, all_units * blockIdx.x / gridDim.x, all_units * (blockIdx.x + 1) / gridDim.x, &cursor);
+    // the partition is over min(grid, units) CTAs, so that every CTA that takes part owns at least
+    // one unit (a head counts the CTAs that share it as a contiguous range); the others leave at once
+    const int64_t ctas = all_units < static_cast<int64_t>(gridDim.x) ? all_units : static_cast<int64_t>(gridDim.x);
+    const int64_t me = static_cast<int64_t>(blockIdx.x) < ctas ? static_cast<int64_t>(blockIdx.x) : ctas;
+    cursor_start(L, p.tail_units, s_each, all_units * me / ctas, me < ctas ? all_units * (me + 1) / ctas : all_units, &cursor);
     if (tid == kHeadDim) {
       s_all_units = all_units;
       s_cursor = cursor;
@@ -928,7 +932,7 @@ dense_reader_kernel(const __grid_constant__ ReaderParams p) {
 // Grid of the persistent dense reader: two CTAs per SM at most, lined up with the heads where that
 // helps, and never more CTAs than there are tail units, so that every CTA's share of the units is
 // non-empty whatever the context lengths are.
-unsigned dense_grid(int64_t batch_heads) {
+unsigned dense_grid(int64_t batch_heads, int64_t max_context_tokens, int tail_units) {
   const int sm_count = device_sm_count();
   const int64_t ctas = kDenseCtasPerSm * static_cast<int64_t>(sm_count < 148 ? sm_count : 148);
   // A grid that is a whole multiple of the heads lines the CTAs' shares up with the heads when the
@@ -937,10 +941,18 @@ unsigned dense_grid(int64_t batch_heads) {
   // CTAs per head saves the second merge of a CTA that straddles two heads, which pays as long as
   // it costs few CTAs (48 heads x 8192 as 6 CTAs per head: 23.5 / 35.6 against 27.9 / 37.9 us; 128
   // heads as two per head, 256 CTAs, is slower: 81 against 75 us for loop 2).  More heads than
-  // CTAs keep the full grid: with ragged contexts fewer CTAs only cost bandwidth.  Fewer than 37
-  // heads get eight CTAs each, the most that short contexts can keep busy.
-  const int64_t cap = batch_heads * 8;  // tail_units_of_loop is at least 8
-  if (cap < ctas) return static_cast<unsigned>(cap);
+  // CTAs keep the full grid: with ragged contexts fewer CTAs only cost bandwidth.
+  //
+  // Few heads: a head gets at most one CTA per eight units of the longest context it may hold, at
+  // least eight, and never more than 32 (two partial slots per CTA, kMaxSplits per head): 16 heads x
+  // 8192 tokens 16.3 / 19.3 us against 17.0 / 24.3 with eight CTAs per head, 32 heads 19.4 / 26.9
+  // against 20.8 / 30.7; one CTA per four units was slower at 2048 tokens (13.8 against 12.5 us).
+  // Should the contexts be so short that there are fewer units than CTAs, the kernel partitions
+  // over as many CTAs as there are units and the rest leave at once.
+  const int64_t units_at_most = max_context_tokens / kGroup + tail_units;
+  int64_t per_head = units_at_most / 8;
+  per_head = per_head < 8 ? 8 : (per_head > kMaxSplits / 2 ? kMaxSplits / 2 : per_head);
+  if (batch_heads * per_head < ctas) return static_cast<unsigned>(batch_heads * per_head);
   if (batch_heads <= ctas) {
     const int64_t aligned = batch_heads * (ctas / batch_heads);
     // one CTA per head if that fills three quarters of the CTAs (160 heads x 8192 tokens on 160 CTAs
@@ -1066,7 +1078,7 @@ extern "C" int fl_dense_source_attention(const fl_layer* layer, int32_t loop, co
   p.out = output;
   p.logits = logits;
   p.logits_stride = logits_stride;
-  const unsigned grid = dense_grid(bh);
+  const unsigned grid = dense_grid(bh, max_context_tokens, p.tail_units);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (cudaError_t err = launch_dense(layer->bits, loop, grid, s, p); err != cudaSuccess) {
     set_error("fl_dense_source_attention: %s", cudaGetErrorString(err));
@@ -1176,7 +1188,7 @@ extern "C" int fl_dense_source_attention_static(const fl_layer* layer, int32_t l
   p.out = output;
   p.logits = logits;
   p.logits_stride = logits_stride;
-  const unsigned grid = dense_grid(bh);
+  const unsigned grid = dense_grid(bh, max_context_tokens, p.tail_units);
   if (cudaError_t err = launch_dense(layer->bits, loop, grid, s, p); err != cudaSuccess) {
     set_error("%s: %s", who, cudaGetErrorString(err));
     return FL_ERR_CUDA;
